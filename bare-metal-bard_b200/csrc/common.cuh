@@ -1,0 +1,106 @@
+// Shared host/device helpers for libbmb: status plumbing, the per-thread
+// stream, per-device scratch, and small device utilities.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdarg>
+#include <cstdint>
+#include "../../include/bmb.h"
+
+namespace bmb {
+
+// ---- status -------------------------------------------------------------
+int fail(int code, const char *fmt, ...);
+
+#define BMB_CUDA(x)                                                           \
+    do {                                                                      \
+        cudaError_t e__ = (x);                                                \
+        if (e__ != cudaSuccess)                                               \
+            return ::bmb::fail(BMB_E_CUDA, "%s -> %s (%s:%d)", #x,            \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);  \
+    } while (0)
+
+// After a kernel launch: report a launch-configuration error, never sync.
+#define BMB_LAUNCH_CHECK()                                                    \
+    do {                                                                      \
+        cudaError_t e__ = cudaGetLastError();                                 \
+        if (e__ != cudaSuccess)                                               \
+            return ::bmb::fail(BMB_E_CUDA, "launch -> %s (%s:%d)",            \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);  \
+    } while (0)
+
+#define BMB_TRY(x)                                                            \
+    do {                                                                      \
+        int s__ = (x);                                                        \
+        if (s__ != BMB_OK) return s__;                                        \
+    } while (0)
+
+// ---- per-thread stream ----------------------------------------------------
+cudaStream_t cur_stream();
+
+// ---- per-device scratch ---------------------------------------------------
+// The reference keeps process-wide static device scratch (src/nn.cu:347, 362)
+// that every rank thread shares regardless of device.  Here each device owns
+// its own block, grown on demand and kept until process exit.
+// Returns nullptr (and records an error) on failure.
+enum ScratchSlot { SCR_REDUCE = 0, SCR_GEMM_A = 1, SCR_GEMM_B = 2, SCR_MISC = 3, SCR_SLOTS = 4 };
+void *device_scratch(ScratchSlot slot, size_t bytes);
+int current_device();
+int sm_count();
+
+// Launch counter (all kernels launched by this library in this process).
+void count_launch(int n = 1);
+long long launches_total();
+
+inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Internal GEMM dispatch shared by attention and the trainer: math is a
+// BMB_MATH_* value, flags the BMB_GEMM_* bits, strides in elements.
+int gemm_any(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
+             const float *A, long long sA, const float *B, long long sB, float beta, float *C,
+             long long sC, cudaStream_t st);
+
+}  // namespace bmb
+
+// ---- device helpers ---------------------------------------------------------
+#ifdef __CUDACC__
+namespace bmb {
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Block-wide sum / max with the result in every thread.  `red` is a shared
+// array of at least 32 floats; two barriers per call, safe to call repeatedly
+// with the same array.
+template <bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v, float *red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nw = (blockDim.x + 31) >> 5;
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    v = (lane < nw) ? red[lane] : (IS_MAX ? -3.402823466e38f : 0.0f);
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    return v;
+}
+// Round to nearest TF32 (ties away), result as an fp32 bit pattern whose low
+// 13 mantissa bits are zero.
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+}  // namespace bmb
+#endif

@@ -1,0 +1,178 @@
+// The reference's C++ entry points (src/kernels.h, src/gemm.h, src/flash.h,
+// src/attention.h, src/nn.h, src/ddp.h), defined as thin shims over the C ABI
+// so that gpt.cu / train_gpt.cu-shaped host code links against libbmb.so
+// without a source change.  Conventions kept from the reference: functions
+// return void (or the reference's bool / float), and a failure is fatal --
+// message on stderr, exit(1) -- like its CUDA_CHECK (src/gpt.cu:18-26).
+#include <cstdio>
+#include <cstdlib>
+#include "../../include/bmb.h"
+#include "../../include/kernels.h"
+#include "../../include/gemm.h"
+#include "../../include/flash.h"
+#include "../../include/attention.h"
+#include "../../include/nn.h"
+#include "../../include/ddp.h"
+
+#define BMB_EXPORT __attribute__((visibility("default")))
+
+static void must(int status, const char *what) {
+    if (status == BMB_OK) return;
+    fprintf(stderr, "bmb: %s failed (%d): %s\n", what, status, bmb_last_error());
+    exit(1);
+}
+
+// ---- registry ---------------------------------------------------------------
+void sgemm_simt_fp32(int M, int N, int K, float a, const float *A, const float *B, float b, float *C) { must(bmb_sgemm_simt(M, N, K, a, A, B, b, C), "sgemm_simt_fp32"); }
+void sgemm_tcgen05_tf32(int M, int N, int K, float a, const float *A, const float *B, float b, float *C) { must(bmb_sgemm_tf32(M, N, K, a, A, B, b, C), "sgemm_tcgen05_tf32"); }
+void sgemm_tcgen05_bf16(int M, int N, int K, float a, const float *A, const float *B, float b, float *C) { must(bmb_sgemm_bf16(M, N, K, a, A, B, b, C), "sgemm_tcgen05_bf16"); }
+#define BMB_ALIAS(name, target) \
+    void name(int M, int N, int K, float a, const float *A, const float *B, float b, float *C) { target(M, N, K, a, A, B, b, C); }
+BMB_ALIAS(sgemm_naive, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_coalesced, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_smem, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_tile1d, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_tile2d, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_vectorized, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_warptile, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_doublebuffer, sgemm_simt_fp32)
+BMB_ALIAS(sgemm_tensorcore, sgemm_tcgen05_tf32)
+
+extern const KernelEntry KERNELS[] = {
+    {1, "simt_fp32", sgemm_simt_fp32, "sm_100a FFMA, 128x128x16 tile, 8x8 per thread, register-prefetch double buffer", 1e-6},
+    {2, "tcgen05_tf32", sgemm_tcgen05_tf32, "tcgen05.mma kind::tf32, TMA-fed swizzled ring, TMEM accumulators, rna-rounded operands", 5e-4},
+    {3, "tcgen05_bf16", sgemm_tcgen05_bf16, "tcgen05.mma kind::f16 on bf16-rounded operands, fp32 accumulate in TMEM", 8e-3},
+};
+extern const int NUM_KERNELS = sizeof(KERNELS) / sizeof(KERNELS[0]);
+const KernelEntry *find_kernel(int id) {
+    for (int i = 0; i < NUM_KERNELS; ++i)
+        if (KERNELS[i].id == id) return &KERNELS[i];
+    return nullptr;
+}
+
+// ---- gemm -------------------------------------------------------------------
+void gemm(bool ta, bool tb, int M, int N, int K, float alpha, const float *A, const float *B, float beta, float *C, cudaStream_t s) {
+    must(bmb_gemm(ta, tb, M, N, K, alpha, A, B, beta, C, (void *)s), "gemm");
+}
+void batched_gemm(bool ta, bool tb, int batch, int M, int N, int K, float alpha, const float *A, long long sA,
+                  const float *B, long long sB, float beta, float *C, long long sC, cudaStream_t s) {
+    must(bmb_batched_gemm(ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, (void *)s), "batched_gemm");
+}
+
+// ---- flash ------------------------------------------------------------------
+void flash_attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH) {
+    must(bmb_flash_attention_forward(out, lse, qkv, B, T, C, NH), "flash_attention_forward");
+}
+void flash_attention_backward(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
+                              const float *lse, int B, int T, int C, int NH) {
+    must(bmb_flash_attention_backward(dqkv, dsum, dout, qkv, out, lse, B, T, C, NH), "flash_attention_backward");
+}
+int flash_num_configs() { return bmb_flash_num_configs(); }
+const char *flash_config_name(int cfg) { return bmb_flash_config_name(cfg); }
+int flash_default_config() { return bmb_flash_default_config(); }
+bool flash_attention_forward_cfg(int cfg, float *out, float *lse, const float *qkv, int B, int T, int C, int NH) {
+    const int s = bmb_flash_attention_forward_cfg(cfg, out, lse, qkv, B, T, C, NH);
+    if (s == BMB_E_UNSUPPORTED) return false;
+    must(s, "flash_attention_forward_cfg");
+    return true;
+}
+int flash_num_bwd_configs() { return bmb_flash_num_bwd_configs(); }
+const char *flash_bwd_config_name(int cfg) { return bmb_flash_bwd_config_name(cfg); }
+int flash_default_bwd_config() { return bmb_flash_default_bwd_config(); }
+bool flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum, const float *dout, const float *qkv,
+                                  const float *out, const float *lse, int B, int T, int C, int NH) {
+    const int s = bmb_flash_attention_backward_cfg(cfg, dqkv, dsum, dout, qkv, out, lse, B, T, C, NH);
+    if (s == BMB_E_UNSUPPORTED) return false;
+    must(s, "flash_attention_backward_cfg");
+    return true;
+}
+
+// ---- unfused attention ------------------------------------------------------
+void attention_forward(float *out, float *qkvr, float *att, const float *qkv, int B, int T, int C, int NH) {
+    must(bmb_attention_forward(out, qkvr, att, qkv, B, T, C, NH), "attention_forward");
+}
+void attention_backward(float *dqkv, float *dqkvr, float *datt, float *dpreatt, const float *dout,
+                        const float *qkvr, const float *att, int B, int T, int C, int NH) {
+    must(bmb_attention_backward(dqkv, dqkvr, datt, dpreatt, dout, qkvr, att, B, T, C, NH), "attention_backward");
+}
+
+// ---- nn ---------------------------------------------------------------------
+void encoder_forward(float *out, const int *tokens, const float *wte, const float *wpe, int B, int T, int C) {
+    must(bmb_encoder_forward(out, tokens, wte, wpe, B, T, C), "encoder_forward");
+}
+void encoder_backward(float *dwte, float *dwpe, const float *dout, const int *tokens, int B, int T, int C) {
+    must(bmb_encoder_backward(dwte, dwpe, dout, tokens, B, T, C), "encoder_backward");
+}
+void layernorm_forward(float *out, float *mean, float *rstd, const float *inp, const float *w, const float *b, int N, int C) {
+    must(bmb_layernorm_forward(out, mean, rstd, inp, w, b, N, C), "layernorm_forward");
+}
+void layernorm_backward(float *dinp, float *dw, float *db, const float *dout, const float *inp, const float *w,
+                        const float *mean, const float *rstd, int N, int C) {
+    must(bmb_layernorm_backward(dinp, dw, db, dout, inp, w, mean, rstd, N, C), "layernorm_backward");
+}
+void gelu_forward(float *out, const float *inp, int n) { must(bmb_gelu_forward(out, inp, n), "gelu_forward"); }
+void gelu_backward(float *dinp, const float *inp, const float *dout, int n) { must(bmb_gelu_backward(dinp, inp, dout, n), "gelu_backward"); }
+void residual_forward(float *out, const float *a, const float *b, int n) { must(bmb_residual_forward(out, a, b, n), "residual_forward"); }
+void add_inplace(float *dst, const float *src, int n) { must(bmb_add_inplace(dst, src, n), "add_inplace"); }
+void bias_forward(float *out, const float *bias, int N, int C) { must(bmb_bias_forward(out, bias, N, C), "bias_forward"); }
+void bias_backward(float *dbias, const float *dout, int N, int C) { must(bmb_bias_backward(dbias, dout, N, C), "bias_backward"); }
+void softmax_crossentropy_forward(float *probs, float *losses, const float *logits, const int *targets, int N, int V, int Vp) {
+    must(bmb_softmax_crossentropy_forward(probs, losses, logits, targets, N, V, Vp), "softmax_crossentropy_forward");
+}
+void crossentropy_softmax_backward(float *dlogits, const float *probs, const int *targets, int N, int V, int Vp, float s) {
+    must(bmb_crossentropy_softmax_backward(dlogits, probs, targets, N, V, Vp, s), "crossentropy_softmax_backward");
+}
+void adamw_update(float *p, float *g, float *m, float *v, int n, float lr, float b1, float b2, float eps, float wd, int step, float gs) {
+    must(bmb_adamw_update(p, g, m, v, n, lr, b1, b2, eps, wd, step, gs), "adamw_update");
+}
+float grad_global_norm(const float *grads, int n) {
+    float r = 0.0f;
+    must(bmb_grad_global_norm(grads, n, &r), "grad_global_norm");
+    return r;
+}
+void zero_buffer(float *p, size_t n) { must(bmb_zero_buffer(p, n), "zero_buffer"); }
+float reduce_mean(const float *v, int n) {
+    float r = 0.0f;
+    must(bmb_reduce_mean(v, n, &r), "reduce_mean");
+    return r;
+}
+
+// ---- ddp --------------------------------------------------------------------
+static bmb_ddp *handle_of(const DDP &d) { return reinterpret_cast<bmb_ddp *>(d.host_stage); }
+
+void ddp_init(DDP &d, int n, const int *devices) {
+    bmb_ddp *h = nullptr;
+    must(bmb_ddp_create(&h, n, devices), "ddp_init");
+    d.n = n;
+    for (int r = 0; r < 8; ++r) {
+        d.dev[r] = r < n ? devices[r] : 0;
+        d.recv[r] = nullptr; d.stream[r] = nullptr; d.start[r] = nullptr; d.stop[r] = nullptr;
+        for (int j = 0; j < 8; ++j) d.peer[r][j] = false;
+    }
+    unsigned char pm[64];
+    must(bmb_ddp_peer_matrix(h, nullptr, nullptr, pm), "ddp_init");
+    d.any_peer = false;
+    for (int i = 0; i < n; ++i)
+        for (int j = 0; j < n; ++j) {
+            d.peer[i][j] = pm[i * n + j] != 0;
+            if (i != j) d.any_peer = d.any_peer || d.peer[i][j];
+        }
+    d.recv_cap = 0; d.stage_cap = 0;
+    d.host_stage = reinterpret_cast<float *>(h);
+    d.last = {0.0, 0.0, 0.0, 0};
+}
+void ddp_free(DDP &d) {
+    must(bmb_ddp_destroy(handle_of(d)), "ddp_free");
+    d.host_stage = nullptr;
+}
+void ddp_allreduce(DDP &d, float **bufs, size_t count) {
+    must(bmb_ddp_allreduce(handle_of(d), bufs, count), "ddp_allreduce");
+    bmb_ddp_timing t;
+    must(bmb_ddp_timing_get(handle_of(d), &t), "ddp_allreduce");
+    d.last.reduce_scatter_ms = t.reduce_scatter_ms;
+    d.last.all_gather_ms = t.all_gather_ms;
+    d.last.total_ms = t.total_ms;
+    d.last.bytes_per_device = t.bytes_per_device;
+}
+const DDPTiming &ddp_timing(const DDP &d) { return d.last; }
+void ddp_report_topology(const DDP &d) { must(bmb_ddp_report_topology(handle_of(d)), "ddp_report_topology"); }

@@ -1,0 +1,441 @@
+// GPT training step on one GPU, the caller of every kernel in this library:
+// the host-side loop of src/gpt.cu:222-385 (forward, backward) and
+// src/train_gpt.cu:397-464 (all-reduce, global-norm clip, AdamW), restated
+// so that one optimiser step issues no blocking call: tokens arrive by async
+// copy, the loss mean and the gradient norm stay on the device, and the
+// all-reduce is enqueued on the same stream as the backward pass.
+//
+// Parameter and gradient storage is one flat buffer in the reference's tensor
+// order (src/gpt.cu:32-51), so raw parameter dumps are interchangeable.
+#include "common.cuh"
+#include <cmath>
+#include <random>
+#include <vector>
+
+namespace bmb {
+int layernorm_bwd_blocks(int N);
+}
+using namespace bmb;
+
+namespace {
+constexpr int NPT = 16;  // parameter tensors
+}
+
+struct bmb_trainer {
+    bmb_train_config c;
+    int dev = 0;
+    cudaStream_t st = nullptr;
+    size_t psize[NPT], poff[NPT], num_params = 0;
+    float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
+    float *shadow = nullptr;  // TF32-rounded parameters (tensor-core modes only)
+    float *acts = nullptr, *bacts = nullptr;
+    size_t num_acts = 0, num_bacts = 0;
+    int *d_tokens = nullptr, *d_targets = nullptr;
+    float *d_loss = nullptr;
+    double *d_sumsq = nullptr;
+    bmb_comm *comm = nullptr;
+    int nranks = 1;
+    // activation pointers
+    float *encoded, *ln1, *ln1_mean, *ln1_rstd, *qkv, *qkvr, *att, *lse, *atty, *attproj, *residual2,
+        *ln2, *ln2_mean, *ln2_rstd, *fch, *fch_gelu, *fcproj, *residual3, *lnf, *lnf_mean, *lnf_rstd,
+        *logits, *probs, *losses;
+    float *dres, *dln1, *dln2, *datty, *dqkv, *dqkvr, *datt, *dsum, *dfch, *dfch_gelu, *dlogits, *dlnf;
+    // profiling
+    bool prof = false;
+    std::vector<cudaEvent_t> ev;
+    size_t ev_used = 0;
+    double prof_flop = 0.0, prof_ms = 0.0;
+    long long prof_calls = 0, launches0 = 0;
+};
+
+namespace {
+
+void param_sizes(size_t *s, const bmb_train_config &c) {
+    const size_t L = c.n_layer, C = c.n_embd, Vp = c.padded_vocab, maxT = c.max_seq_len;
+    const size_t sz[NPT] = {Vp * C, maxT * C, L * C, L * C, L * 3 * C * C, L * 3 * C, L * C * C, L * C,
+                            L * C,  L * C,    L * 4 * C * C, L * 4 * C, L * C * 4 * C, L * C, C, C};
+    for (int i = 0; i < NPT; ++i) s[i] = sz[i];
+}
+enum { P_WTE, P_WPE, P_LN1W, P_LN1B, P_QKVW, P_QKVB, P_APW, P_APB, P_LN2W, P_LN2B, P_FCW, P_FCB, P_FPW, P_FPB, P_LNFW, P_LNFB };
+
+struct Scope {
+    int prev_dev = 0;
+    void *prev_stream;
+    explicit Scope(bmb_trainer *t) {
+        cudaGetDevice(&prev_dev);
+        cudaSetDevice(t->dev);
+        prev_stream = bmb_get_stream();
+        bmb_set_stream(t->st);
+    }
+    ~Scope() { bmb_set_stream(prev_stream); cudaSetDevice(prev_dev); }
+};
+
+int collect_profile(bmb_trainer *t) {
+    for (size_t i = 0; i + 1 < t->ev_used; i += 2) {
+        float ms = 0.f;
+        BMB_CUDA(cudaEventElapsedTime(&ms, t->ev[i], t->ev[i + 1]));
+        t->prof_ms += ms;
+    }
+    t->ev_used = 0;
+    return BMB_OK;
+}
+
+// One matmul of the model, optionally bracketed by events.
+int mm(bmb_trainer *t, int flags, int ta, int tb, int M, int N, int K, const float *A, const float *B,
+       float beta, float *C) {
+    if (t->prof) {
+        if (t->ev_used + 2 > t->ev.size()) {
+            for (int i = 0; i < 64; ++i) {
+                cudaEvent_t e;
+                BMB_CUDA(cudaEventCreate(&e));
+                t->ev.push_back(e);
+            }
+        }
+        BMB_CUDA(cudaEventRecord(t->ev[t->ev_used], t->st));
+    }
+    BMB_TRY(gemm_any(t->c.math, flags, ta, tb, 1, M, N, K, 1.0f, A, 0, B, 0, beta, C, 0, t->st));
+    if (t->prof) {
+        BMB_CUDA(cudaEventRecord(t->ev[t->ev_used + 1], t->st));
+        t->ev_used += 2;
+        t->prof_flop += 2.0 * M * N * K;
+        t->prof_calls += 1;
+    }
+    return BMB_OK;
+}
+
+int forward(bmb_trainer *t) {
+    const bmb_train_config &c = t->c;
+    const int B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head;
+    const int Vp = c.padded_vocab, V = c.vocab_size, N = B * T;
+    const size_t BTC = (size_t)N * C, BT = N, BT3C = 3 * BTC, BT4C = 4 * BTC;
+    const size_t qkvr_sz = 4 * BTC, att_sz = (size_t)B * NH * T * T, lse_sz = (size_t)B * NH * T;
+    // Weights: the tensor-core modes read the pre-rounded shadow copy.
+    const float *W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
+    const int wflag = (W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0;
+    const float *P = t->params;
+
+    BMB_TRY(bmb_encoder_forward(t->encoded, t->d_tokens, P + t->poff[P_WTE], P + t->poff[P_WPE], B, T, C));
+    float *residual = t->encoded;
+    for (int l = 0; l < L; ++l) {
+        float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * BT3C, *atty = t->atty + l * BTC;
+        float *attproj = t->attproj + l * BTC, *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
+        float *fch = t->fch + l * BT4C, *fchg = t->fch_gelu + l * BT4C, *fcproj = t->fcproj + l * BTC;
+        float *res3 = t->residual3 + l * BTC;
+        BMB_TRY(bmb_layernorm_forward(ln1, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, residual,
+                                      P + t->poff[P_LN1W] + (size_t)l * C, P + t->poff[P_LN1B] + (size_t)l * C, N, C));
+        BMB_TRY(mm(t, wflag, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv));
+        BMB_TRY(bmb_bias_forward(qkv, P + t->poff[P_QKVB] + (size_t)l * 3 * C, N, 3 * C));
+        if (c.use_flash)
+            BMB_TRY(bmb_flash_attention_forward(atty, t->lse + l * lse_sz, qkv, B, T, C, NH));
+        else
+            BMB_TRY(bmb_attention_forward(atty, t->qkvr + l * qkvr_sz, t->att + l * att_sz, qkv, B, T, C, NH));
+        BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
+        BMB_TRY(bmb_bias_forward(attproj, P + t->poff[P_APB] + (size_t)l * C, N, C));
+        BMB_TRY(bmb_residual_forward(res2, residual, attproj, (int)BTC));
+        BMB_TRY(bmb_layernorm_forward(ln2, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, res2,
+                                      P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
+        BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch));
+        BMB_TRY(bmb_bias_forward(fch, P + t->poff[P_FCB] + (size_t)l * 4 * C, N, 4 * C));
+        BMB_TRY(bmb_gelu_forward(fchg, fch, (int)BT4C));
+        BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj));
+        BMB_TRY(bmb_bias_forward(fcproj, P + t->poff[P_FPB] + (size_t)l * C, N, C));
+        BMB_TRY(bmb_residual_forward(res3, res2, fcproj, (int)BTC));
+        residual = res3;
+    }
+    BMB_TRY(bmb_layernorm_forward(t->lnf, t->lnf_mean, t->lnf_rstd, residual, P + t->poff[P_LNFW],
+                                  P + t->poff[P_LNFB], N, C));
+    BMB_TRY(mm(t, wflag, 0, 1, N, Vp, C, t->lnf, W + t->poff[P_WTE], 0.0f, t->logits));
+    BMB_TRY(bmb_softmax_crossentropy_forward(t->probs, t->losses, t->logits, t->d_targets, N, V, Vp));
+    BMB_TRY(bmb_reduce_mean_device(t->losses, N, t->d_loss));
+    return BMB_OK;
+}
+
+int backward(bmb_trainer *t) {
+    const bmb_train_config &c = t->c;
+    const int B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head;
+    const int Vp = c.padded_vocab, V = c.vocab_size, N = B * T;
+    const size_t BTC = (size_t)N * C, BT = N, BT3C = 3 * BTC, BT4C = 4 * BTC;
+    const size_t qkvr_sz = 4 * BTC, att_sz = (size_t)B * NH * T * T, lse_sz = (size_t)B * NH * T;
+    const float *W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
+    const int wflag = (W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0;
+    const float *P = t->params;
+    float *G = t->grads;
+
+    BMB_CUDA(cudaMemsetAsync(G, 0, t->num_params * sizeof(float), t->st));
+    BMB_TRY(bmb_crossentropy_softmax_backward(t->dlogits, t->probs, t->d_targets, N, V, Vp, 1.0f / N));
+    BMB_TRY(mm(t, wflag, 0, 0, N, C, Vp, t->dlogits, W + t->poff[P_WTE], 0.0f, t->dlnf));
+    BMB_TRY(mm(t, 0, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
+    float *last_res = t->residual3 + (size_t)(L - 1) * BTC;
+    BMB_CUDA(cudaMemsetAsync(t->dres, 0, BTC * sizeof(float), t->st));
+    BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LNFW], G + t->poff[P_LNFB], t->dlnf, last_res,
+                                   P + t->poff[P_LNFW], t->lnf_mean, t->lnf_rstd, N, C));
+    for (int l = L - 1; l >= 0; --l) {
+        float *residual = (l == 0) ? t->encoded : t->residual3 + (size_t)(l - 1) * BTC;
+        float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * BT3C, *atty = t->atty + l * BTC;
+        float *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
+        float *fch = t->fch + l * BT4C, *fchg = t->fch_gelu + l * BT4C;
+        const size_t lC = (size_t)l * C;
+
+        BMB_TRY(mm(t, wflag, 0, 0, N, 4 * C, C, t->dres, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, t->dfch_gelu));
+        BMB_TRY(mm(t, 0, 1, 0, C, 4 * C, N, t->dres, fchg, 1.0f, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
+        BMB_TRY(bmb_bias_backward(G + t->poff[P_FPB] + lC, t->dres, N, C));
+        BMB_TRY(bmb_gelu_backward(t->dfch, fch, t->dfch_gelu, (int)BT4C));
+        BMB_TRY(mm(t, wflag, 0, 0, N, C, 4 * C, t->dfch, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, t->dln2));
+        BMB_TRY(mm(t, 0, 1, 0, 4 * C, C, N, t->dfch, ln2, 1.0f, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
+        BMB_TRY(bmb_bias_backward(G + t->poff[P_FCB] + 4 * lC, t->dfch, N, 4 * C));
+        BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC, t->dln2, res2,
+                                       P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
+        BMB_TRY(mm(t, wflag, 0, 0, N, C, C, t->dres, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, t->datty));
+        BMB_TRY(mm(t, 0, 1, 0, C, C, N, t->dres, atty, 1.0f, G + t->poff[P_APW] + (size_t)l * C * C));
+        BMB_TRY(bmb_bias_backward(G + t->poff[P_APB] + lC, t->dres, N, C));
+        if (c.use_flash)
+            BMB_TRY(bmb_flash_attention_backward(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH));
+        else
+            BMB_TRY(bmb_attention_backward(t->dqkv, t->dqkvr, t->datt, t->datt, t->datty, t->qkvr + l * qkvr_sz,
+                                           t->att + l * att_sz, B, T, C, NH));
+        BMB_TRY(mm(t, wflag, 0, 0, N, C, 3 * C, t->dqkv, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, t->dln1));
+        BMB_TRY(mm(t, 0, 1, 0, 3 * C, C, N, t->dqkv, ln1, 1.0f, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
+        BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
+        BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC, t->dln1, residual,
+                                       P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C));
+    }
+    BMB_TRY(bmb_encoder_backward(G + t->poff[P_WTE], G + t->poff[P_WPE], t->dres, t->d_tokens, B, T, C));
+    return BMB_OK;
+}
+
+int refresh_shadow(bmb_trainer *t) {
+    if (!t->shadow) return BMB_OK;
+    return bmb_round_tf32(t->shadow, t->params, t->num_params, t->st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned seed) {
+    if (!out || !cfg) return fail(BMB_E_ARG, "trainer_create: null argument");
+    const bmb_train_config &c = *cfg;
+    if (c.n_layer < 1 || c.n_head < 1 || c.n_embd < 4 || c.n_embd % c.n_head || c.n_embd % 4 ||
+        c.B < 1 || c.T < 1 || c.T > c.max_seq_len || c.vocab_size < 1 || c.padded_vocab < c.vocab_size ||
+        c.padded_vocab % 4)
+        return fail(BMB_E_ARG, "trainer_create: inconsistent configuration");
+    if (c.math < BMB_MATH_FP32 || c.math > BMB_MATH_BF16) return fail(BMB_E_ARG, "trainer_create: math %d", c.math);
+    const int hs = c.n_embd / c.n_head;
+    if (c.use_flash && hs != 32 && hs != 64 && hs != 128)
+        return fail(BMB_E_UNSUPPORTED, "trainer_create: fused attention needs head size 32, 64 or 128 (got %d)", hs);
+
+    bmb_trainer *t = new bmb_trainer();
+    t->c = c;
+    BMB_CUDA(cudaGetDevice(&t->dev));
+    BMB_CUDA(cudaStreamCreateWithFlags(&t->st, cudaStreamNonBlocking));
+    param_sizes(t->psize, c);
+    t->num_params = 0;
+    for (int i = 0; i < NPT; ++i) { t->poff[i] = t->num_params; t->num_params += t->psize[i]; }
+    const size_t pb = t->num_params * sizeof(float);
+    BMB_CUDA(cudaMalloc(&t->params, pb));
+    BMB_CUDA(cudaMalloc(&t->grads, pb));
+    BMB_CUDA(cudaMalloc(&t->m, pb));
+    BMB_CUDA(cudaMalloc(&t->v, pb));
+    BMB_CUDA(cudaMemset(t->m, 0, pb));
+    BMB_CUDA(cudaMemset(t->v, 0, pb));
+    BMB_CUDA(cudaMemset(t->grads, 0, pb));
+    if (c.math != BMB_MATH_FP32) BMB_CUDA(cudaMalloc(&t->shadow, pb));
+
+    const size_t B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head, Vp = c.padded_vocab;
+    const size_t BT = B * T, BTC = BT * C, BT3C = 3 * BTC, BT4C = 4 * BTC;
+    const size_t qkvr = 4 * BTC, att = B * NH * T * T, lse = B * NH * T;
+    // Every tensor starts on a 256-byte boundary: the first call sizes the
+    // arena (base = nullptr), the second hands out the pointers.
+    auto layout_fwd = [&](float *base) -> size_t {
+        size_t off = 0;
+        auto take = [&](size_t n) { float *r = base + off; off += (n + 63) & ~(size_t)63; return r; };
+        t->encoded = take(BTC);
+        t->ln1 = take(BTC * L); t->ln1_mean = take(BT * L); t->ln1_rstd = take(BT * L);
+        t->qkv = take(BT3C * L);
+        t->qkvr = c.use_flash ? nullptr : take(qkvr * L);
+        t->att = c.use_flash ? nullptr : take(att * L);
+        t->lse = c.use_flash ? take(lse * L) : nullptr;
+        t->atty = take(BTC * L); t->attproj = take(BTC * L); t->residual2 = take(BTC * L);
+        t->ln2 = take(BTC * L); t->ln2_mean = take(BT * L); t->ln2_rstd = take(BT * L);
+        t->fch = take(BT4C * L); t->fch_gelu = take(BT4C * L); t->fcproj = take(BTC * L);
+        t->residual3 = take(BTC * L);
+        t->lnf = take(BTC); t->lnf_mean = take(BT); t->lnf_rstd = take(BT);
+        t->logits = take(BT * Vp); t->probs = take(BT * Vp); t->losses = take(BT);
+        return off;
+    };
+    auto layout_bwd = [&](float *base) -> size_t {
+        size_t off = 0;
+        auto take = [&](size_t n) { float *r = base + off; off += (n + 63) & ~(size_t)63; return r; };
+        t->dres = take(BTC); t->dln1 = take(BTC); t->dln2 = take(BTC); t->datty = take(BTC);
+        t->dqkv = take(BT3C);
+        t->dqkvr = c.use_flash ? nullptr : take(qkvr);
+        t->datt = c.use_flash ? nullptr : take(att);
+        t->dsum = c.use_flash ? take(lse) : nullptr;
+        t->dfch = take(BT4C); t->dfch_gelu = take(BT4C);
+        t->dlogits = take(BT * Vp); t->dlnf = take(BTC);
+        return off;
+    };
+    t->num_acts = layout_fwd(nullptr);
+    BMB_CUDA(cudaMalloc(&t->acts, t->num_acts * sizeof(float)));
+    layout_fwd(t->acts);
+    t->num_bacts = layout_bwd(nullptr);
+    BMB_CUDA(cudaMalloc(&t->bacts, t->num_bacts * sizeof(float)));
+    layout_bwd(t->bacts);
+
+    BMB_CUDA(cudaMalloc(&t->d_tokens, BT * sizeof(int)));
+    BMB_CUDA(cudaMalloc(&t->d_targets, BT * sizeof(int)));
+    BMB_CUDA(cudaMemset(t->d_tokens, 0, BT * sizeof(int)));
+    BMB_CUDA(cudaMemset(t->d_targets, 0, BT * sizeof(int)));
+    BMB_CUDA(cudaMalloc(&t->d_loss, sizeof(float)));
+    BMB_CUDA(cudaMalloc(&t->d_sumsq, sizeof(double)));
+    BMB_CUDA(cudaMemset(t->d_loss, 0, sizeof(float)));
+
+    // GPT-2 initialisation with the reference's draw order (src/gpt.cu:189-218):
+    // one mt19937 stream; a fresh normal_distribution per tensor; N(0, 0.02)
+    // except the two residual projections at 0.02/sqrt(2L); gains 1, biases 0.
+    {
+        std::vector<float> h(t->num_params, 0.0f);
+        std::mt19937 rng(seed);
+        const float resid = 0.02f / sqrtf(2.0f * c.n_layer);
+        auto fill = [&](int i, float sd) {
+            std::normal_distribution<float> d(0.0f, sd);
+            float *dst = h.data() + t->poff[i];
+            for (size_t k = 0; k < t->psize[i]; ++k) dst[k] = d(rng);
+        };
+        auto ones = [&](int i) {
+            float *dst = h.data() + t->poff[i];
+            for (size_t k = 0; k < t->psize[i]; ++k) dst[k] = 1.0f;
+        };
+        fill(P_WTE, 0.02f); fill(P_WPE, 0.02f); ones(P_LN1W);
+        fill(P_QKVW, 0.02f); fill(P_APW, resid); ones(P_LN2W);
+        fill(P_FCW, 0.02f); fill(P_FPW, resid); ones(P_LNFW);
+        BMB_CUDA(cudaMemcpy(t->params, h.data(), pb, cudaMemcpyHostToDevice));
+    }
+    {
+        Scope sc(t);
+        BMB_TRY(refresh_shadow(t));
+        BMB_CUDA(cudaStreamSynchronize(t->st));
+    }
+    *out = t;
+    return BMB_OK;
+}
+
+int bmb_trainer_destroy(bmb_trainer *t) {
+    if (!t) return BMB_OK;
+    cudaSetDevice(t->dev);
+    cudaStreamSynchronize(t->st);
+    for (cudaEvent_t e : t->ev) cudaEventDestroy(e);
+    cudaFree(t->params); cudaFree(t->grads); cudaFree(t->m); cudaFree(t->v);
+    if (t->shadow) cudaFree(t->shadow);
+    cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
+    cudaFree(t->d_loss); cudaFree(t->d_sumsq);
+    cudaStreamDestroy(t->st);
+    delete t;
+    return BMB_OK;
+}
+
+int bmb_trainer_attach_comm(bmb_trainer *t, bmb_comm *c, int nranks) {
+    if (!t || nranks < 1) return fail(BMB_E_ARG, "trainer_attach_comm: bad argument");
+    t->comm = c;
+    t->nranks = nranks;
+    return BMB_OK;
+}
+
+size_t bmb_trainer_num_params(const bmb_trainer *t) { return t ? t->num_params : 0; }
+
+int bmb_trainer_get_params(bmb_trainer *t, float *host_out) {
+    if (!t || !host_out) return fail(BMB_E_ARG, "trainer_get_params: null argument");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    BMB_CUDA(cudaMemcpy(host_out, t->params, t->num_params * sizeof(float), cudaMemcpyDeviceToHost));
+    return BMB_OK;
+}
+int bmb_trainer_set_params(bmb_trainer *t, const float *host_in) {
+    if (!t || !host_in) return fail(BMB_E_ARG, "trainer_set_params: null argument");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    BMB_CUDA(cudaMemcpy(t->params, host_in, t->num_params * sizeof(float), cudaMemcpyHostToDevice));
+    BMB_TRY(refresh_shadow(t));
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    return BMB_OK;
+}
+int bmb_trainer_get_grads(bmb_trainer *t, float *host_out) {
+    if (!t || !host_out) return fail(BMB_E_ARG, "trainer_get_grads: null argument");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    BMB_CUDA(cudaMemcpy(host_out, t->grads, t->num_params * sizeof(float), cudaMemcpyDeviceToHost));
+    return BMB_OK;
+}
+
+int bmb_trainer_upload(bmb_trainer *t, const int *host_tokens, const int *host_targets) {
+    if (!t || !host_tokens || !host_targets) return fail(BMB_E_ARG, "trainer_upload: null argument");
+    Scope sc(t);
+    const size_t n = (size_t)t->c.B * t->c.T * sizeof(int);
+    BMB_CUDA(cudaMemcpyAsync(t->d_tokens, host_tokens, n, cudaMemcpyHostToDevice, t->st));
+    BMB_CUDA(cudaMemcpyAsync(t->d_targets, host_targets, n, cudaMemcpyHostToDevice, t->st));
+    return BMB_OK;
+}
+
+int bmb_trainer_forward_backward(bmb_trainer *t) {
+    if (!t) return fail(BMB_E_ARG, "trainer: null handle");
+    Scope sc(t);
+    BMB_TRY(forward(t));
+    BMB_TRY(backward(t));
+    return BMB_OK;
+}
+
+int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
+    if (!t || step < 1) return fail(BMB_E_ARG, "trainer_step: bad argument");
+    Scope sc(t);
+    BMB_TRY(forward(t));
+    BMB_TRY(backward(t));
+    if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
+    BMB_TRY(bmb_grad_sumsq_device(t->grads, t->num_params, t->d_sumsq));
+    BMB_TRY(bmb_adamw_update_clipped(t->params, t->grads, t->m, t->v, t->num_params, lr, t->c.beta1, t->c.beta2,
+                                     t->c.eps, t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip,
+                                     (float)t->nranks, t->shadow));
+    return BMB_OK;
+}
+
+int bmb_trainer_loss(bmb_trainer *t, float *host_loss) {
+    if (!t || !host_loss) return fail(BMB_E_ARG, "trainer_loss: null argument");
+    Scope sc(t);
+    BMB_CUDA(cudaMemcpyAsync(host_loss, t->d_loss, sizeof(float), cudaMemcpyDeviceToHost, t->st));
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    return BMB_OK;
+}
+
+void *bmb_trainer_stream(bmb_trainer *t) { return t ? (void *)t->st : nullptr; }
+
+int bmb_trainer_sync(bmb_trainer *t) {
+    if (!t) return fail(BMB_E_ARG, "trainer: null handle");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    return BMB_OK;
+}
+
+int bmb_trainer_profile(bmb_trainer *t, int on) {
+    if (!t) return fail(BMB_E_ARG, "trainer: null handle");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    BMB_TRY(collect_profile(t));
+    t->prof = on != 0;
+    t->prof_flop = 0.0; t->prof_ms = 0.0; t->prof_calls = 0;
+    t->launches0 = launches_total();
+    return BMB_OK;
+}
+
+int bmb_trainer_profile_read(bmb_trainer *t, double *gemm_flop, double *gemm_ms, long long *gemm_calls,
+                             long long *kernel_launches) {
+    if (!t) return fail(BMB_E_ARG, "trainer: null handle");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    BMB_TRY(collect_profile(t));
+    if (gemm_flop) *gemm_flop = t->prof_flop;
+    if (gemm_ms) *gemm_ms = t->prof_ms;
+    if (gemm_calls) *gemm_calls = t->prof_calls;
+    if (kernel_launches) *kernel_launches = launches_total() - t->launches0;
+    return BMB_OK;
+}
+
+}  // extern "C"

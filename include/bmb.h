@@ -1,0 +1,256 @@
+/* bmb.h -- the C ABI of libbmb.so: a B200 (sm_100a) implementation of the
+ * GEMM / attention / nn / data-parallel hot path of bare-metal-bard.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status
+ * (0 = ok, otherwise one of BMB_E_*; bmb_last_error() gives the text for the
+ * calling thread) and never takes ownership of a caller's buffer.  Pointers
+ * are device pointers on the current CUDA device unless a parameter is named
+ * host_*.  Calls are asynchronous on the calling thread's "current stream"
+ * (bmb_set_stream; the legacy default stream unless set) except where a
+ * parameter named `stream` is given or the comment says the call blocks.
+ *
+ * The C++ headers beside this file (kernels.h, gemm.h, flash.h, attention.h,
+ * nn.h, ddp.h, gpt.h) are inline shims with the reference's own names and
+ * signatures over these functions, so gpt.cu / train_gpt.cu-shaped host code
+ * compiles against them unchanged.  Each declaration cites the reference
+ * interface it replaces as path:line inside the reference project.
+ */
+#ifndef BMB_H
+#define BMB_H
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BMB_OK 0
+#define BMB_E_ARG 1      /* bad argument (shape, alignment, null pointer)     */
+#define BMB_E_CUDA 2     /* a CUDA runtime / driver call failed               */
+#define BMB_E_UNSUPPORTED 3 /* valid request this build cannot serve          */
+#define BMB_E_TIMEOUT 4  /* a bounded device-side wait expired                */
+#define BMB_E_NCCL 5     /* NCCL missing or an NCCL call failed               */
+#define BMB_E_LIMIT 6    /* size beyond a stated maximum                      */
+
+const char *bmb_last_error(void);
+const char *bmb_version(void);
+
+/* ---- per-thread launch context ---------------------------------------- */
+/* Stream used by every entry point without a `stream` parameter.  Thread
+ * local: rank threads of one process do not disturb one another. */
+int bmb_set_stream(void *cuda_stream);
+void *bmb_get_stream(void);
+
+/* Arithmetic used by bmb_gemm / bmb_batched_gemm / flash attention when the
+ * caller does not say.  fp32 = SIMT FFMA, bit-comparable with the reference's
+ * fp32 kernels up to summation order; tf32 = tcgen05 kind::tf32 with operands
+ * rounded to nearest TF32 first and fp32 accumulation in tensor memory;
+ * bf16 = tcgen05 kind::f16 on bf16-rounded operands. */
+#define BMB_MATH_FP32 0
+#define BMB_MATH_TF32 1
+#define BMB_MATH_BF16 2
+int bmb_set_math_mode(int mode);   /* process wide */
+int bmb_get_math_mode(void);
+
+/* ---- registry (src/kernels.h:10-31, src/registry.cu:4-23) -------------- */
+typedef void (*bmb_sgemm_fn)(int M, int N, int K, float alpha, const float *A,
+                             const float *B, float beta, float *C);
+typedef struct bmb_kernel_entry {
+    int id;
+    const char *name;
+    bmb_sgemm_fn fn;
+    const char *note;
+    double tol; /* normwise tolerance against an fp32 reference product */
+} bmb_kernel_entry;
+int bmb_num_kernels(void);
+const bmb_kernel_entry *bmb_kernel_table(void);
+const bmb_kernel_entry *bmb_find_kernel(int id);
+/* Row-major C = alpha*A@B + beta*C, the three registry kernels
+ * (replaces sgemm_naive..sgemm_tensorcore, src/kernels.h:34-42). */
+int bmb_sgemm_simt(int M, int N, int K, float alpha, const float *A,
+                   const float *B, float beta, float *C);
+int bmb_sgemm_tf32(int M, int N, int K, float alpha, const float *A,
+                   const float *B, float beta, float *C);
+int bmb_sgemm_bf16(int M, int N, int K, float alpha, const float *A,
+                   const float *B, float beta, float *C);
+
+/* ---- GEMM (src/gemm.h:17-19, 26-29) ----------------------------------- */
+/* C[M,N] = alpha*op(A)@op(B) + beta*C, row-major, dense leading dimensions
+ * exactly as src/gemm.h:6-11 defines them. */
+int bmb_gemm(int transA, int transB, int M, int N, int K, float alpha,
+             const float *A, const float *B, float beta, float *C,
+             void *stream);
+/* Same, with the arithmetic stated per call (BMB_MATH_*) and flags. */
+#define BMB_GEMM_A_ROUNDED 1 /* A already holds TF32-representable values */
+#define BMB_GEMM_B_ROUNDED 2 /* B already holds TF32-representable values */
+int bmb_gemm_ex(int math, int flags, int transA, int transB, int M, int N,
+                int K, float alpha, const float *A, const float *B, float beta,
+                float *C, void *stream);
+int bmb_batched_gemm(int transA, int transB, int batch, int M, int N, int K,
+                     float alpha, const float *A, long long strideA,
+                     const float *B, long long strideB, float beta, float *C,
+                     long long strideC, void *stream);
+/* Round n floats to the nearest TF32 value (ties away from zero, the
+ * cvt.rna.tf32.f32 rule the reference applies at k09_tensorcore.cu:119-128). */
+int bmb_round_tf32(float *dst, const float *src, size_t n, void *stream);
+
+/* ---- fused causal attention (src/flash.h:36-62) ------------------------ */
+int bmb_flash_attention_forward(float *out, float *lse, const float *qkv,
+                                int B, int T, int C, int NH);
+int bmb_flash_attention_backward(float *dqkv, float *dsum, const float *dout,
+                                 const float *qkv, const float *out,
+                                 const float *lse, int B, int T, int C, int NH);
+int bmb_flash_num_configs(void);
+const char *bmb_flash_config_name(int cfg);
+int bmb_flash_default_config(void);
+/* status BMB_E_UNSUPPORTED <=> the reference's `false` (config cannot run for
+ * this head size). */
+int bmb_flash_attention_forward_cfg(int cfg, float *out, float *lse,
+                                    const float *qkv, int B, int T, int C,
+                                    int NH);
+int bmb_flash_num_bwd_configs(void);
+const char *bmb_flash_bwd_config_name(int cfg);
+int bmb_flash_default_bwd_config(void);
+int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum,
+                                     const float *dout, const float *qkv,
+                                     const float *out, const float *lse, int B,
+                                     int T, int C, int NH);
+
+/* ---- unfused attention (src/attention.h:18-24) ------------------------- */
+int bmb_attention_forward(float *out, float *qkvr, float *att,
+                          const float *qkv, int B, int T, int C, int NH);
+int bmb_attention_backward(float *dqkv, float *dqkvr, float *datt,
+                           float *dpreatt, const float *dout,
+                           const float *qkvr, const float *att, int B, int T,
+                           int C, int NH);
+
+/* ---- nn kernels (src/nn.h:10-60) -------------------------------------- */
+int bmb_encoder_forward(float *out, const int *tokens, const float *wte,
+                        const float *wpe, int B, int T, int C);
+int bmb_encoder_backward(float *dwte, float *dwpe, const float *dout,
+                         const int *tokens, int B, int T, int C);
+int bmb_layernorm_forward(float *out, float *mean, float *rstd,
+                          const float *inp, const float *weight,
+                          const float *bias, int N, int C);
+/* dinp, dweight and dbias are accumulated into (+=), as src/nn.cu:108-111. */
+int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias,
+                           const float *dout, const float *inp,
+                           const float *weight, const float *mean,
+                           const float *rstd, int N, int C);
+int bmb_gelu_forward(float *out, const float *inp, int n);
+int bmb_gelu_backward(float *dinp, const float *inp, const float *dout, int n);
+int bmb_residual_forward(float *out, const float *a, const float *b, int n);
+int bmb_add_inplace(float *dst, const float *src, int n);
+int bmb_bias_forward(float *out, const float *bias, int N, int C);
+/* dbias += column sums of dout (src/nn.cu:184-191). */
+int bmb_bias_backward(float *dbias, const float *dout, int N, int C);
+int bmb_softmax_crossentropy_forward(float *probs, float *losses,
+                                     const float *logits, const int *targets,
+                                     int N, int V, int Vp);
+int bmb_crossentropy_softmax_backward(float *dlogits, const float *probs,
+                                      const int *targets, int N, int V, int Vp,
+                                      float dloss_scale);
+int bmb_adamw_update(float *params, float *grads, float *m, float *v, int n,
+                     float lr, float beta1, float beta2, float eps,
+                     float weight_decay, int step, float grad_scale);
+/* Blocks; *host_norm = sqrt(sum g^2) (src/nn.cu:336-355). */
+int bmb_grad_global_norm(const float *grads, int n, float *host_norm);
+int bmb_zero_buffer(float *p, size_t n);
+/* Blocks; *host_mean = mean of n device values (src/nn.cu:359-368). */
+int bmb_reduce_mean(const float *d_values, int n, float *host_mean);
+
+/* Device-resident variants used by the training step so that a step has no
+ * host round trip: the squared norm and the loss stay on the device, and the
+ * optimiser derives its clip factor from the device value.
+ * sumsq_out[0] = sum g^2 (double).  */
+int bmb_grad_sumsq_device(const float *grads, size_t n, double *sumsq_out);
+int bmb_reduce_mean_device(const float *d_values, int n, float *d_mean);
+/* grad_scale = (norm/div > clip ? clip/(norm/div) : 1)/div with
+ * norm = sqrt(*d_sumsq), the rule of src/train_gpt.cu:442-448 (div = ranks).
+ * shadow (may be null) receives the TF32-rounded copy of the new params. */
+int bmb_adamw_update_clipped(float *params, const float *grads, float *m,
+                             float *v, size_t n, float lr, float beta1,
+                             float beta2, float eps, float weight_decay,
+                             int step, const double *d_sumsq, float clip,
+                             float div, float *shadow);
+
+/* ---- data-parallel all-reduce (src/ddp.h:32-69) ------------------------ */
+typedef struct bmb_ddp_timing {
+    double reduce_scatter_ms;
+    double all_gather_ms;
+    double total_ms;
+    size_t bytes_per_device;
+} bmb_ddp_timing;
+
+/* Single-process form, one rank per entry of `devices` (a device may repeat,
+ * src/ddp.h:53-57).  The handle is opaque; the C++ shim keeps it inside the
+ * reference-shaped DDP struct. */
+typedef struct bmb_ddp bmb_ddp;
+int bmb_ddp_create(bmb_ddp **out, int n, const int *devices);
+int bmb_ddp_destroy(bmb_ddp *d);
+/* In-place sum over ranks of bufs[r][0..count); blocks until complete. */
+int bmb_ddp_allreduce(bmb_ddp *d, float **bufs, size_t count);
+int bmb_ddp_timing_get(const bmb_ddp *d, bmb_ddp_timing *out);
+/* The part of a count-element buffer that rank r reduces and then serves to
+ * the others: ceil(count/n) elements from r*ceil(count/n), clipped to the end
+ * (the chunking of src/ddp.cu:34-40).  Host-only arithmetic. */
+int bmb_ddp_slice(size_t count, int n, int r, size_t *off_out, size_t *len_out);
+/* peer[i*n+j] = 1 when rank i reaches rank j's memory directly. */
+int bmb_ddp_peer_matrix(const bmb_ddp *d, int *n_out, int *dev_out,
+                        unsigned char *peer_out);
+int bmb_ddp_report_topology(const bmb_ddp *d);
+
+/* One-process-per-GPU form (NCCL over NVLink/NVSwitch; libnccl.so.2 is
+ * opened on first use).  id is the 128-byte NCCL unique id made by rank 0 and
+ * handed to every rank by the launcher. */
+typedef struct bmb_comm bmb_comm;
+int bmb_comm_unique_id(unsigned char id_out[128]);
+int bmb_comm_create(bmb_comm **out, const unsigned char id[128], int nranks,
+                    int rank);
+int bmb_comm_destroy(bmb_comm *c);
+/* In-place sum of count floats over all ranks, asynchronous on `stream`. */
+int bmb_comm_allreduce(bmb_comm *c, float *buf, size_t count, void *stream);
+
+/* ---- GPT training step (caller of all of the above; src/gpt.h:10-79,
+ *      src/train_gpt.cu:397-464) ---------------------------------------- */
+typedef struct bmb_trainer bmb_trainer;
+typedef struct bmb_train_config {
+    int max_seq_len, vocab_size, padded_vocab, n_layer, n_head, n_embd;
+    int B, T;          /* per-rank batch and sequence length               */
+    int use_flash;     /* 1 fused attention, 0 the unfused path             */
+    int math;          /* BMB_MATH_* for the GEMMs and attention            */
+    int fused;         /* 1 = fused epilogues, 0 = the reference's op list  */
+    float beta1, beta2, eps, weight_decay, grad_clip;
+} bmb_train_config;
+int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg,
+                       unsigned seed);
+int bmb_trainer_destroy(bmb_trainer *t);
+int bmb_trainer_attach_comm(bmb_trainer *t, bmb_comm *c, int nranks);
+size_t bmb_trainer_num_params(const bmb_trainer *t);
+int bmb_trainer_get_params(bmb_trainer *t, float *host_out);
+int bmb_trainer_set_params(bmb_trainer *t, const float *host_in);
+int bmb_trainer_get_grads(bmb_trainer *t, float *host_out);
+/* Upload host tokens/targets (B*T ints each, pinned or pageable). Async. */
+int bmb_trainer_upload(bmb_trainer *t, const int *host_tokens,
+                       const int *host_targets);
+/* One optimiser step on the resident batch: forward, backward, gradient
+ * all-reduce (if a comm is attached), global-norm clip, AdamW.  Asynchronous;
+ * the mean loss of the step lands in a device scalar. `step` counts from 1. */
+int bmb_trainer_step(bmb_trainer *t, float lr, int step);
+/* Forward+backward only (gradients left in place), for gradient parity. */
+int bmb_trainer_forward_backward(bmb_trainer *t);
+/* Blocks: waits for the stream and returns the last step's mean loss. */
+int bmb_trainer_loss(bmb_trainer *t, float *host_loss);
+int bmb_trainer_sync(bmb_trainer *t);
+/* The CUDA stream every step of this trainer is enqueued on (for events). */
+void *bmb_trainer_stream(bmb_trainer *t);
+/* Per-call event timing of the GEMMs inside steps (on = 1 / off = 0); the
+ * totals since the last reset: flop count, device milliseconds, launches. */
+int bmb_trainer_profile(bmb_trainer *t, int on);
+int bmb_trainer_profile_read(bmb_trainer *t, double *gemm_flop,
+                             double *gemm_ms, long long *gemm_calls,
+                             long long *kernel_launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BMB_H */

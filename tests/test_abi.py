@@ -1,0 +1,89 @@
+"""The C ABI surface, checked without a GPU: the library loads, exports every
+function include/bmb.h declares (and the reference's C++ names), and the
+host-only entry points behave."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "bmb.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bmb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound(bmb):
+    names = declared_functions()
+    assert len(names) > 60
+    lib = C.CDLL(bmb.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), "libbmb.so does not export %s" % n
+        assert n in bmb.SIGNATURES, "python binding table misses %s" % n
+    assert set(bmb.SIGNATURES) <= set(names)
+
+
+def test_reference_cxx_names_are_exported(bmb):
+    out = subprocess.run(["nm", "-DC", bmb.LIB_PATH], capture_output=True, text=True).stdout
+    for sym in ["gemm(bool, bool, int, int, int, float, float const*, float const*, float, float*, CUstream_st*)",
+                "batched_gemm(bool, bool, int, int, int, int, float, float const*, long long, float const*, long long, float, float*, long long, CUstream_st*)",
+                "flash_attention_forward(float*, float*, float const*, int, int, int, int)",
+                "flash_attention_backward(float*, float*, float const*, float const*, float const*, float const*, int, int, int, int)",
+                "flash_attention_forward_cfg(int, float*, float*, float const*, int, int, int, int)",
+                "attention_forward(float*, float*, float*, float const*, int, int, int, int)",
+                "layernorm_backward(float*, float*, float*, float const*, float const*, float const*, float const*, float const*, int, int)",
+                "adamw_update(float*, float*, float*, float*, int, float, float, float, float, float, int, float)",
+                "grad_global_norm(float const*, int)", "reduce_mean(float const*, int)",
+                "ddp_init(DDP&, int, int const*)", "ddp_allreduce(DDP&, float**, unsigned long)",
+                "ddp_timing(DDP const&)", "find_kernel(int)", "KERNELS", "NUM_KERNELS"]:
+        assert sym in out, sym
+
+
+def test_registry_entries(bmb):
+    lib = bmb.lib()
+    assert lib.bmb_num_kernels() == 3
+    want = {1: (b"simt_fp32", 1e-6), 2: (b"tcgen05_tf32", 5e-4), 3: (b"tcgen05_bf16", 8e-3)}
+    for kid, (name, tol) in want.items():
+        e = lib.bmb_find_kernel(kid).contents
+        assert e.name == name and e.tol == tol and e.fn
+    assert not lib.bmb_find_kernel(99)
+
+
+def test_host_only_calls(bmb):
+    lib = bmb.lib()
+    assert b"sm_100a" in lib.bmb_version()
+    assert lib.bmb_flash_num_configs() >= 1 and lib.bmb_flash_num_bwd_configs() >= 1
+    assert lib.bmb_flash_config_name(lib.bmb_flash_default_config()) != b"?"
+    assert lib.bmb_flash_config_name(999) == b"?"
+    assert lib.bmb_set_math_mode(7) != 0 and b"math mode" in lib.bmb_last_error()
+    prev = lib.bmb_get_math_mode()
+    assert lib.bmb_set_math_mode(bmb.MATH_TF32) == 0 and lib.bmb_get_math_mode() == bmb.MATH_TF32
+    lib.bmb_set_math_mode(prev)
+    lib.bmb_set_stream(None)
+    assert lib.bmb_get_stream() is None
+
+
+@pytest.mark.parametrize("count,n", [(1, 8), (3, 2), (17, 4), (1000, 3), (65537, 8), (124475904, 8), (5, 8)])
+def test_ddp_slices_partition_the_buffer(bmb, count, n):
+    lib = bmb.lib()
+    off, ln = C.c_size_t(), C.c_size_t()
+    covered = 0
+    per = (count + n - 1) // n
+    for r in range(n):
+        assert lib.bmb_ddp_slice(count, n, r, C.byref(off), C.byref(ln)) == 0
+        if ln.value:
+            assert off.value == covered and ln.value <= per
+        covered += ln.value
+    assert covered == count
+    assert lib.bmb_ddp_slice(10, 2, 2, C.byref(off), C.byref(ln)) != 0
+
+
+def test_missing_library_fails_loudly(bmb, tmp_path, monkeypatch):
+    monkeypatch.setattr(bmb, "_lib", None)
+    monkeypatch.setattr(bmb, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(bmb.BmbError, match="no CPU or PyTorch fallback"):
+        bmb.lib()
