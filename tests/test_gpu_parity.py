@@ -102,7 +102,7 @@ def test_gemm_full_size_linearity_and_sampled_rows(bmb, orc, cuda):
     bmb.call("bmb_sgemm_simt", n, n, n, 1.0, dA, dB1, 0.0, c1)
     bmb.call("bmb_sgemm_simt", n, n, n, 1.0, dA, dB2, 0.0, c2)
     bmb.call("bmb_sgemm_simt", n, n, n, 1.0, dA, dB1 + dB2, 0.0, c3)
-    assert normwise(host(cuda, c1 + c2), host(cuda, c3)) < 2e-6
+    assert normwise(host(cuda, c1 + c2), host(cuda, c3)) < 1e-5   # three roundings, not one
     rows = [0, 1, 127, 128, 2047, 3000, 4094, 4095]
     Asub = np.ascontiguousarray(A.reshape(n, n)[rows])
     want = np.zeros((len(rows), n), np.float32)
