@@ -1,0 +1,131 @@
+"""GPU parity of the tcgen05 tensor-core GEMM (TF32 and BF16 kinds), through the
+C ABI, against the CPU oracle.
+
+Two bars per case:
+  * against the fp32 product of the unrounded inputs: normwise 5e-4 for TF32
+    (the registry tolerance), 8e-3 for BF16;
+  * against the float64 product of the *rounded* inputs: 2e-5.  Only the
+    accumulation order differs there, so a wrong descriptor, swizzle or tile
+    coordinate cannot hide inside the TF32 tolerance.
+"""
+import numpy as np
+import pytest
+
+from helpers import _np, normwise, uniform
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(torch, t):
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+def rounded(orc, x, kind):
+    out = np.empty_like(x)
+    if kind == "tf32":
+        orc.orc_round_tf32_n(_np(out), _np(x), x.size)
+    else:
+        u = x.view(np.uint32).astype(np.uint64)
+        u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+        out = u.astype(np.uint32).view(np.float32)
+    return out
+
+
+SHAPES = [(128, 256, 32), (128, 256, 128), (256, 512, 96), (384, 768, 200), (1024, 1024, 1024), (300, 515, 77),
+          (129, 257, 33), (2304, 768, 512), (768, 2304, 64)]
+
+
+@pytest.mark.parametrize("kind", ["tf32", "bf16"])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_tensorcore_gemm_vs_oracle(bmb, orc, cuda, kind, ta, tb, M, N, K):
+    math = bmb.MATH_TF32 if kind == "tf32" else bmb.MATH_BF16
+    A, B, C0 = uniform(M * K, 1), uniform(K * N, 2), uniform(M * N, 3)
+    want32 = C0.copy()
+    orc.orc_gemm_fast(ta, tb, M, N, K, 0.75, _np(A), _np(B), 1.25, _np(want32))
+    want_r = C0.copy()
+    Ar, Br = rounded(orc, A, kind), rounded(orc, B, kind)
+    orc.orc_gemm_f64(ta, tb, M, N, K, 0.75, _np(Ar), _np(Br), 1.25, _np(want_r))
+    dA, dB, dC = dev(cuda, A), dev(cuda, B), dev(cuda, C0)
+    bmb.call("bmb_gemm_ex", math, 0, ta, tb, M, N, K, 0.75, dA, dB, 1.25, dC, None)
+    got = host(cuda, dC)
+    assert normwise(got, want_r) < 2e-5, "layout/descriptor error, not rounding"
+    assert normwise(got, want32) < (5e-4 if kind == "tf32" else 8e-3)
+
+
+def test_registry_tf32_entry_at_2048(bmb, orc, cuda):
+    """Registry entry 2 at the harness's verification setting alpha 0.5, beta 3
+    (src/bench.cu:261), inputs uniform [-1,1): normwise below the entry's tol."""
+    n = 2048
+    A, B, C0 = uniform(n * n, 0), uniform(n * n, 1), uniform(n * n, 2)
+    want = C0.copy()
+    orc.orc_gemm_fast(0, 0, n, n, n, 0.5, _np(A), _np(B), 3.0, _np(want))
+    dA, dB, dC = dev(cuda, A), dev(cuda, B), dev(cuda, C0)
+    bmb.call("bmb_sgemm_tf32", n, n, n, 0.5, dA, dB, 3.0, dC)
+    e = bmb.lib().bmb_find_kernel(2).contents
+    err = normwise(host(cuda, dC), want)
+    assert err < e.tol, err
+    dC = dev(cuda, C0)
+    bmb.call("bmb_sgemm_bf16", n, n, n, 0.5, dA, dB, 3.0, dC)
+    assert normwise(host(cuda, dC), want) < bmb.lib().bmb_find_kernel(3).contents.tol
+
+
+def test_prerounded_operands_are_read_in_place(bmb, orc, cuda):
+    """With both operands K-contiguous and flagged as already rounded the kernel
+    reads them where they lie; the result equals the prepass route bit for bit."""
+    M, N, K = 512, 768, 256
+    A, B = rounded(orc, uniform(M * K, 4), "tf32"), rounded(orc, uniform(N * K, 5), "tf32")
+    dA, dB = dev(cuda, A), dev(cuda, B)
+    c1, c2 = cuda.zeros(M * N, device="cuda"), cuda.zeros(M * N, device="cuda")
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, 0, 0, 1, M, N, K, 1.0, dA, dB, 0.0, c1, None)
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED, 0, 1, M, N, K, 1.0, dA, dB, 0.0, c2, None)
+    assert np.array_equal(host(cuda, c1), host(cuda, c2))
+
+
+def test_unrounded_operands_show_why_rounding_is_needed(bmb, orc, cuda, capsys):
+    """Raw fp32 handed to kind::tf32 (flagged as rounded although it is not):
+    records how far truncation lands from the fp32 product.  Informational: the
+    only assertion is that rounding first is at least as accurate."""
+    M = N = K = 1024
+    A, B = uniform(M * K, 6), uniform(N * K, 7)
+    want = np.zeros(M * N, np.float32)
+    orc.orc_gemm_fast(0, 1, M, N, K, 1.0, _np(A), _np(B), 0.0, _np(want))
+    dA, dB = dev(cuda, A), dev(cuda, B)
+    c1, c2 = cuda.zeros(M * N, device="cuda"), cuda.zeros(M * N, device="cuda")
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, 0, 0, 1, M, N, K, 1.0, dA, dB, 0.0, c1, None)
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED, 0, 1, M, N, K, 1.0, dA, dB, 0.0, c2, None)
+    e_round, e_raw = normwise(host(cuda, c1), want), normwise(host(cuda, c2), want)
+    with capsys.disabled():
+        print("\n[tf32] normwise vs fp32 product: rounded operands %.3e, raw operands %.3e" % (e_round, e_raw))
+    assert e_round < 5e-4 and e_round <= e_raw * 1.05
+
+
+TINY = dict(max_seq_len=64, vocab_size=300, padded_vocab=384, n_layer=2, n_head=2, n_embd=256, B=4, T=64)
+
+
+def test_train_step_tf32_loss_vs_oracle(bmb, orc, cuda):
+    """TF32 GEMMs inside the train step: loss per step within 2e-2 of the fp32
+    CPU oracle over 20 steps (shapes large enough to take the tensor-core path)."""
+    tr = bmb.Trainer(seed=1337, use_flash=1, math=bmb.MATH_TF32, **TINY)
+    n = tr.num_params
+    params0 = np.empty(n, np.float32)
+    tr.get_params(params0)
+    rng = np.random.default_rng(4242)
+    toks = rng.integers(0, TINY["vocab_size"], (20, TINY["B"], TINY["T"]), dtype=np.int32)
+    tgts = rng.integers(0, TINY["vocab_size"], (20, TINY["B"], TINY["T"]), dtype=np.int32)
+    g = orc.orc_gpt_create(TINY["max_seq_len"], TINY["vocab_size"], TINY["padded_vocab"], TINY["n_layer"],
+                           TINY["n_head"], TINY["n_embd"], TINY["B"], TINY["T"])
+    np.ctypeslib.as_array(orc.orc_gpt_params(g), shape=(n,))[:] = params0
+    for s in range(20):
+        orc.orc_gpt_set_batch(g, _np(toks[s].copy()), _np(tgts[s].copy()))
+        want = orc.orc_gpt_step(g, 3e-4, 0.9, 0.95, 1e-8, 0.1, 1.0, s + 1)
+        tr.upload(toks[s], tgts[s])
+        tr.step(3e-4, s + 1)
+        assert abs(tr.loss() - want) < 2e-2, s
+    orc.orc_gpt_destroy(g)
+    tr.close()
