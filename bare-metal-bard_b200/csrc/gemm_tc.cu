@@ -5,133 +5,55 @@
 //
 // kind::tf32 multiplies fp32 operands of which the tensor core reads only the
 // upper 19 bits; feeding it raw fp32 therefore truncates, which biases every
-// product low by about 2^-10.  The reference rounds to nearest instead
-// (src/kernels/k09_tensorcore.cu:119-128), so operands are first rounded with
-// cvt.rna.tf32.f32 -- by the prepass below into per-device scratch, or by the
-// caller (BMB_GEMM_A_ROUNDED / BMB_GEMM_B_ROUNDED), in which case a K-contiguous
-// operand is read in place.  kind::f16 takes the same route with a bf16 copy.
+// product low (measured on B200: normwise 6.4e-4 against 2.6e-4 with rounding).
+// The reference rounds to nearest (src/kernels/k09_tensorcore.cu:119-128), so
+// operands are first rounded with cvt.rna.tf32.f32 -- by the prepass below
+// into per-device scratch, or by the caller (BMB_GEMM_A_ROUNDED /
+// BMB_GEMM_B_ROUNDED), in which case the operand is read where it lies.
+// kind::f16 takes the prepass route with a bf16 copy.
+//
+// All four transpose cases run without a transposed copy: an operand stored
+// with K contiguous becomes a K-major tile (rows of 128 bytes of K), one
+// stored with M (or N) contiguous becomes an MN-major tile (one 128-byte row
+// of M/N per K index, 32-wide chunks side by side; for 32-bit elements the
+// tensor core takes this only in the 128-byte swizzle with 32-byte atoms),
+// and the instruction descriptor says which.
 //
 // Kernel shape.  One persistent CTA per SM, 192 threads in three roles:
-//   warp 0      producer: one lane issues the TMA loads of a K-slice
-//               (A 128 x 128 B, B 256 x 128 B) into a 4-deep ring, each slice
-//               armed on an mbarrier with its byte count;
+//   warp 0      producer: one lane issues the TMA loads of a K-slice (32 fp32
+//               or 64 bf16 of K: A 16 KB, B 32 KB) into a 4-deep ring, each
+//               slice armed on an mbarrier with its byte count;
 //   warp 1      issuer: one lane waits for a slice, issues 4 tcgen05.mma
-//               (128 x 256 x 32 B of K each) and commits them to the slice's
-//               "empty" barrier; after the last slice of a tile it commits to
-//               the accumulator's "full" barrier.  This warp also owns the
-//               TMEM allocation (512 columns: two 128 x 256 fp32 accumulators,
-//               so the epilogue of tile i overlaps the main loop of tile i+1);
+//               (128 x 256 x 32 bytes of K each) and commits them to the
+//               slice's "empty" barrier; after the last slice of a tile it
+//               commits to the accumulator's "full" barrier.  This warp owns
+//               the TMEM allocation (512 columns: two 128 x 256 fp32
+//               accumulators, so the epilogue of tile i overlaps the main loop
+//               of tile i+1);
 //   warps 2..5  epilogue: each warp reads its 32 TMEM lanes 32 columns at a
 //               time (tcgen05.ld 32x32b.x32), applies alpha/beta and stores.
-// Both operand tiles are K-major in shared memory (rows of 128 bytes of K,
-// SWIZZLE_128B), so a K step of 32 bytes is a +2 on the descriptor's address
-// field.  Tiles are visited in groups of 8 M-tiles so that concurrently
-// resident CTAs share A and B slices in L2.
+// Tiles are visited in groups of 8 M-tiles so that concurrently resident CTAs
+// share A and B slices in L2.
 //
-// Every wait on an mbarrier is bounded: when a wait runs out, the CTA raises a
+// Every wait on an mbarrier is bounded: when one runs out, the CTA raises a
 // flag all roles poll, the producer waits (bounded again) for the copies it
-// has in flight, the TMEM allocation is released, and the kernel writes a
+// has in flight, the TMEM allocation is released, and the kernel stores a
 // nonzero word into a host-visible status that the next call reports as
 // BMB_E_TIMEOUT.  No TMA load uses cluster multicast.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
 #include <cuda_bf16.h>
 #include <mutex>
 
 namespace bmb {
 namespace {
 
+using namespace tc;
+
 constexpr int BM = 128, BN = 256, STAGES = 4, KBYTES = 128;
 constexpr int A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NTHREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr long long WAIT_CYCLES = 4000000000LL;  // about two seconds at 2 GHz
-
-// ---- PTX wrappers ---------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the limit ran out or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *giveup) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*giveup) return false;
-        if (clock64() - t0 > WAIT_CYCLES) { *giveup = 1; return false; }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-template <int KIND>  // 0 = tf32, 1 = f16 (bf16 inputs)
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    if (KIND == 0)
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-    else
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// K-major, SWIZZLE_128B shared-memory matrix descriptor: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
-           (2ull << 61);
-}
+constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 128 bytes of M/N
 
 struct TileSched {
     int tiles_m, tiles_n, num_tiles;
@@ -146,11 +68,13 @@ struct TileSched {
     }
 };
 
+// KIND 0 = tf32 (fp32 operands), 1 = f16 (bf16 operands, always K-major).
+// a_mn / b_mn: the operand's tile is MN-major (TF32 only).
 template <int KIND>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, int M, int N,
-          int kblocks, int kelems_per_block, float alpha, float beta, float *__restrict__ C, int vec_ok,
-          int *__restrict__ status) {
+          int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
+          int vec_ok, int *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -173,12 +97,12 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); armed[s] = -1; }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
         *giveup = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
-    tc_fence_before();
+    fence_before();
     __syncthreads();
-    tc_fence_after();
+    fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -196,46 +120,57 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     mbar_arrive_expect_tx(fb, STAGE_BYTES);
                     armed[s] = (int)ph;
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
-                    tma_load_2d(sa, &mapA, kb * kelems_per_block, tm * BM, fb);
-                    tma_load_2d(sb, &mapB, kb * kelems_per_block, tn * BN, fb);
+                    const int k0 = kb * kelems_per_block;
+                    if (a_mn) {
+#pragma unroll 1
+                        for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * CHUNK_BYTES, &mapA, tm * BM + c * 32, k0, fb);
+                    } else {
+                        tma_load_2d(sa, &mapA, k0, tm * BM, fb);
+                    }
+                    if (b_mn) {
+#pragma unroll 1
+                        for (int c = 0; c < BN / 32; ++c) tma_load_2d(sb + c * CHUNK_BYTES, &mapB, tn * BN + c * 32, k0, fb);
+                    } else {
+                        tma_load_2d(sb, &mapB, k0, tn * BN, fb);
+                    }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
             if (!ok) {
                 // Leave no copy in flight behind us: every armed slice must land.
-                for (int i = 0; i < STAGES; ++i) {
-                    if (armed[i] < 0) continue;
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(full0 + 8 * i, (uint32_t)armed[i]) && clock64() - t0 < WAIT_CYCLES) {}
-                }
+                for (int i = 0; i < STAGES; ++i)
+                    if (armed[i] >= 0) mbar_drain(full0 + 8 * i, (uint32_t)armed[i]);
             }
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- issuer
         if (lane == 0) {
-            // instruction descriptor: fp32 accumulate, A/B format, both K-major, N = 256, M = 128
-            const uint32_t fmt = (KIND == 0) ? 2u : 1u;
-            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint32_t idesc = make_idesc(KIND == 0 ? 2u : 1u, a_mn ? 1u : 0u, b_mn ? 1u : 0u, BN, BM);
+            // per 32-byte K step: K-major tiles move 32 bytes along the row, MN-major tiles move 8 K rows
+            const uint32_t a_step = a_mn ? 1024u : 32u, b_step = b_mn ? 1024u : 32u;
             int s = 0, acc = 0;
             uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < sch.num_tiles; tile += gridDim.x) {
                 if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
-                tc_fence_after();
+                fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
-                    tc_fence_after();
+                    fence_after();
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
-                    const uint64_t da = smem_desc_kmajor(sa), db = smem_desc_kmajor(sb);
 #pragma unroll
-                    for (int k = 0; k < KBYTES / 32; ++k)
-                        tc_mma<KIND>(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-                    tc_commit(empty0 + 8 * s);          // slice reusable once these MMAs retire
+                    for (int k = 0; k < KBYTES / 32; ++k) {
+                        const uint64_t da = a_mn ? smem_desc_mnmajor32(sa + k * a_step, CHUNK_BYTES) : smem_desc_kmajor(sa + k * a_step);
+                        const uint64_t db = b_mn ? smem_desc_mnmajor32(sb + k * b_step, CHUNK_BYTES) : smem_desc_kmajor(sb + k * b_step);
+                        if (KIND == 0) mma_tf32(d, da, db, idesc, (kb | k) ? 1u : 0u);
+                        else mma_f16(d, da, db, idesc, (kb | k) ? 1u : 0u);
+                    }
+                    commit(empty0 + 8 * s);             // slice reusable once these MMAs retire
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
-                tc_commit(tfull0 + 8 * acc);            // accumulator complete
+                commit(tfull0 + 8 * acc);               // accumulator complete
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
         }
@@ -249,7 +184,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int tm, tn;
             sch.coords(tile, tm, tn);
             if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
-            tc_fence_after();
+            fence_after();
             const int m = tm * BM + q * 32 + lane;
             const uint32_t trow = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
             float *crow = C + (size_t)m * N;
@@ -282,18 +217,18 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     }
                 }
             }
-            tc_fence_before();
+            fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
     }
 
-    tc_fence_before();
+    fence_before();
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
-        tc_fence_after();
+        fence_after();
         tmem_dealloc(tmem_base, 512);
     }
     if (threadIdx.x == 0 && *giveup) {
@@ -303,13 +238,12 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
 }
 
 // ---- operand prepass --------------------------------------------------------
-// dst[r][k] (row pitch Kp elements) = round(src(r, k)), zero for k in [K, Kp).
-// KCONTIG: src(r,k) = src[r*K + k]; otherwise src(r,k) = src[k*R + r].
 template <typename OUT>
 __device__ __forceinline__ OUT cvt_out(float x);
 template <> __device__ __forceinline__ float cvt_out<float>(float x) { return round_tf32(x); }
 template <> __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// dst[r][k] (row pitch Kp) = convert(src[r*K + k]), zero for k in [K, Kp).
 template <typename OUT>
 __global__ void prep_rows_k(OUT *__restrict__ dst, const float *__restrict__ src, long long R, int K, int Kp) {
     const long long total = R * (long long)Kp;
@@ -320,13 +254,15 @@ __global__ void prep_rows_k(OUT *__restrict__ dst, const float *__restrict__ src
         dst[i] = cvt_out<OUT>(k < K ? src[r * K + k] : 0.0f);
     }
 }
-__global__ void prep_rows_vec4_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
+// Same-layout rounding copy of n4 float4.
+__global__ void prep_round_vec4_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
          i += (long long)gridDim.x * blockDim.x) {
         const float4 v = reinterpret_cast<const float4 *>(src)[i];
         reinterpret_cast<float4 *>(dst)[i] = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
     }
 }
+// dst[r][k] (row pitch Kp) = convert(src[k*R + r]): transposing copy through shared memory.
 template <typename OUT>
 __global__ void prep_transpose_k(OUT *__restrict__ dst, const float *__restrict__ src, int R, int K, int Kp) {
     __shared__ float t[32][33];
@@ -342,88 +278,73 @@ __global__ void prep_transpose_k(OUT *__restrict__ dst, const float *__restrict_
     }
 }
 
-// ---- host side ----------------------------------------------------------------
-typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                             const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeFn g_encode = nullptr;
-std::once_flag g_encode_once;
+struct Operand {
+    const void *ptr;      // what the tensor map points at
+    bool mn_major;        // tile layout
+    long long rows, cols, pitch_bytes;   // tensor-map geometry (cols contiguous)
+    int box_rows;
+};
 
-EncodeFn encode_fn() {
-    std::call_once(g_encode_once, [] {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            g_encode = (EncodeFn)fn;
-    });
-    return g_encode;
+inline int blocks_for(long long items) {
+    long long b = (items + 255) / 256, cap = 8LL * sm_count();
+    return (int)(b > cap ? cap : (b < 1 ? 1 : b));
 }
 
-// rows x Kelems matrix, K contiguous, row pitch `pitch_bytes`; box = 128 bytes of K x box_rows rows.
-int make_map(CUtensorMap *map, const void *ptr, int esize, long long rows, long long kelems, long long pitch_bytes,
-             int box_rows) {
-    EncodeFn enc = encode_fn();
-    if (!enc) return fail(BMB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t dims[2] = {(cuuint64_t)kelems, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)(KBYTES / esize), (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                           const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(BMB_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    return BMB_OK;
-}
-
-struct DevState { int *status_dev = nullptr; int *status_host = nullptr; bool attr_set[2] = {false, false}; };
-DevState g_dev[64];
-std::mutex g_dev_mu;
-
-int dev_state(DevState **out) {
-    const int d = current_device();
-    if (d < 0 || d >= 64) return fail(BMB_E_ARG, "device index %d out of range", d);
-    std::lock_guard<std::mutex> lk(g_dev_mu);
-    DevState &s = g_dev[d];
-    if (!s.status_host) {
-        BMB_CUDA(cudaHostAlloc((void **)&s.status_host, sizeof(int), cudaHostAllocMapped));
-        *s.status_host = 0;
-        BMB_CUDA(cudaHostGetDevicePointer((void **)&s.status_dev, s.status_host, 0));
-    }
-    *out = &s;
-    return BMB_OK;
-}
-
-template <typename OUT>
-int prepare_operand(OUT *dst, const float *src, bool kcontig, long long R, int K, int Kp, cudaStream_t st) {
-    if (kcontig) {
-        if (sizeof(OUT) == 4 && Kp == K && ((uintptr_t)src % 16 == 0) && ((R * (long long)K) % 4 == 0)) {
-            const long long n4 = R * (long long)K / 4;
-            long long blocks = (n4 + 255) / 256;
-            if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
-            prep_rows_vec4_k<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<float *>(dst), src, n4);
-        } else {
-            long long blocks = (R * (long long)Kp + 255) / 256;
-            if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
-            prep_rows_k<OUT><<<(int)blocks, 256, 0, st>>>(dst, src, R, K, Kp);
+// Decide how an operand reaches the tensor core.  X = its M or N extent, kcontig =
+// element (x,k) at src[x*K + k], otherwise at src[k*X + x].
+int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int K, bool bf16, bool rounded,
+                  ScratchSlot slot, int tile_rows, cudaStream_t st) {
+    const bool aligned = ((uintptr_t)src % 16) == 0;
+    if (!bf16) {
+        const bool geom_ok = aligned && (kcontig ? (K % 4 == 0) : (X % 4 == 0));
+        if (geom_ok) {
+            const float *use = src;
+            if (!rounded) {
+                float *scr = (float *)device_scratch(slot, (size_t)X * K * sizeof(float));
+                if (!scr) return BMB_E_CUDA;
+                const long long n4 = X * (long long)K / 4;
+                prep_round_vec4_k<<<blocks_for(n4), 256, 0, st>>>(scr, src, n4);
+                count_launch();
+                BMB_LAUNCH_CHECK();
+                use = scr;
+            }
+            op->ptr = use;
+            op->mn_major = !kcontig;
+            if (kcontig) { op->rows = X; op->cols = K; op->pitch_bytes = (long long)K * 4; op->box_rows = tile_rows; }
+            else { op->rows = K; op->cols = X; op->pitch_bytes = X * 4; op->box_rows = 32; }
+            return BMB_OK;
         }
+    }
+    // General route: a K-major, padded, converted copy.
+    const int esize = bf16 ? 2 : 4, kalign = 16 / esize;
+    const int Kp = (K + kalign - 1) / kalign * kalign;
+    void *scr = device_scratch(slot, (size_t)X * Kp * esize);
+    if (!scr) return BMB_E_CUDA;
+    if (kcontig) {
+        if (bf16) prep_rows_k<__nv_bfloat16><<<blocks_for(X * (long long)Kp), 256, 0, st>>>((__nv_bfloat16 *)scr, src, X, K, Kp);
+        else prep_rows_k<float><<<blocks_for(X * (long long)Kp), 256, 0, st>>>((float *)scr, src, X, K, Kp);
     } else {
-        dim3 grid((unsigned)((R + 31) / 32), (unsigned)((Kp + 31) / 32));
-        prep_transpose_k<OUT><<<grid, dim3(32, 8), 0, st>>>(dst, src, (int)R, K, Kp);
+        dim3 grid((unsigned)((X + 31) / 32), (unsigned)((Kp + 31) / 32));
+        if (bf16) prep_transpose_k<__nv_bfloat16><<<grid, dim3(32, 8), 0, st>>>((__nv_bfloat16 *)scr, src, (int)X, K, Kp);
+        else prep_transpose_k<float><<<grid, dim3(32, 8), 0, st>>>((float *)scr, src, (int)X, K, Kp);
     }
     count_launch();
     BMB_LAUNCH_CHECK();
+    op->ptr = scr; op->mn_major = false;
+    op->rows = X; op->cols = Kp; op->pitch_bytes = (long long)Kp * esize; op->box_rows = tile_rows;
     return BMB_OK;
 }
+
+bool g_attr_set[64][2];
+std::mutex g_attr_mu;
 
 }  // namespace
 
 bool gemm_tc_accepts(int math, int, int, int batch, int M, int N, int K, const float *, long long, const float *,
                      long long, const float *C, long long) {
     if (math != BMB_MATH_TF32 && math != BMB_MATH_BF16) return false;
-    if (batch != 1) return false;                // batched problems stay on the SIMT kernel for now
-    // Smaller problems than one tile stay on the SIMT kernel (still fp32-exact).
+    if (batch != 1) return false;                // batched problems stay on the SIMT kernel
+    // Problems smaller than one tile stay on the SIMT kernel (fp32-exact, so within any tensor-core tolerance).
     if (M < BM || N < BN || K < 32 || !C) return false;
     if ((long long)M * K >= (1LL << 40) || (long long)N * K >= (1LL << 40)) return false;
     return true;
@@ -433,53 +354,39 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
             const float *A, long long, const float *B, long long, float beta, float *C, long long,
             cudaStream_t st) {
     (void)batch;
-    DevState *ds = nullptr;
-    BMB_TRY(dev_state(&ds));
-    if (*ds->status_host != 0)
-        return fail(BMB_E_TIMEOUT, "an earlier tensor-core GEMM on this device gave up waiting on a barrier");
+    int *status_dev = nullptr;
+    volatile int *status_host = nullptr;
+    BMB_TRY(tc::status_word(&status_dev, &status_host));
+    if (*status_host != 0)
+        return fail(BMB_E_TIMEOUT, "an earlier tensor-core kernel on this device gave up waiting on a barrier");
     const bool bf16 = (math == BMB_MATH_BF16);
+    Operand a, b;
+    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st));
+    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, BN, st));
     const int esize = bf16 ? 2 : 4;
-    const int kalign = 16 / esize;                       // elements per 16 bytes
-    const bool a_kc = !transA, b_kc = transB != 0;
-    // In-place use of a caller's operand: TF32 only, K-contiguous, already rounded, TMA-aligned.
-    const bool a_direct = !bf16 && a_kc && (flags & BMB_GEMM_A_ROUNDED) && K % 4 == 0 && (uintptr_t)A % 16 == 0;
-    const bool b_direct = !bf16 && b_kc && (flags & BMB_GEMM_B_ROUNDED) && K % 4 == 0 && (uintptr_t)B % 16 == 0;
-    const int Kp = (K + kalign - 1) / kalign * kalign;
-    const void *pa = A, *pb = B;
-    long long pitch_a = (long long)K * 4, pitch_b = (long long)K * 4;
-    long long kel_a = K, kel_b = K;
-    if (!a_direct) {
-        void *sa = device_scratch(SCR_GEMM_A, (size_t)M * Kp * esize);
-        if (!sa) return BMB_E_CUDA;
-        if (bf16) BMB_TRY(prepare_operand<__nv_bfloat16>((__nv_bfloat16 *)sa, A, a_kc, M, K, Kp, st));
-        else BMB_TRY(prepare_operand<float>((float *)sa, A, a_kc, M, K, Kp, st));
-        pa = sa; pitch_a = (long long)Kp * esize; kel_a = Kp;
-    }
-    if (!b_direct) {
-        void *sb = device_scratch(SCR_GEMM_B, (size_t)N * Kp * esize);
-        if (!sb) return BMB_E_CUDA;
-        if (bf16) BMB_TRY(prepare_operand<__nv_bfloat16>((__nv_bfloat16 *)sb, B, b_kc, N, K, Kp, st));
-        else BMB_TRY(prepare_operand<float>((float *)sb, B, b_kc, N, K, Kp, st));
-        pb = sb; pitch_b = (long long)Kp * esize; kel_b = Kp;
-    }
     CUtensorMap mapA, mapB;
-    BMB_TRY(make_map(&mapA, pa, esize, M, kel_a, pitch_a, BM));
-    BMB_TRY(make_map(&mapB, pb, esize, N, kel_b, pitch_b, BN));
+    BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
+    BMB_TRY(make_map_2d(&mapB, b.ptr, esize, b.rows, b.cols, b.pitch_bytes, b.box_rows, b.mn_major));
     const int kper = KBYTES / esize;
     const int kblocks = (K + kper - 1) / kper;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
     const int kind = bf16 ? 1 : 0;
-    if (!ds->attr_set[kind]) {
-        if (bf16) BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        else BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        ds->attr_set[kind] = true;
+    {
+        std::lock_guard<std::mutex> lk(g_attr_mu);
+        const int d = current_device();
+        if (d >= 0 && d < 64 && !g_attr_set[d][kind]) {
+            if (bf16) BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            else BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            g_attr_set[d][kind] = true;
+        }
     }
     if (bf16)
-        gemm_tc_k<1><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, alpha, beta, C, vec_ok, ds->status_dev);
+        gemm_tc_k<1><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, 0, 0, alpha, beta, C, vec_ok, status_dev);
     else
-        gemm_tc_k<0><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, alpha, beta, C, vec_ok, ds->status_dev);
+        gemm_tc_k<0><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, a.mn_major ? 1 : 0,
+                                                        b.mn_major ? 1 : 0, alpha, beta, C, vec_ok, status_dev);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
