@@ -20,6 +20,9 @@
 #include <cmath>
 
 namespace bmb {
+bool flash_tc_supported(int T, int C, int NH, const float *qkv, const float *out);
+int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, bool qkv_rounded,
+                     cudaStream_t st);
 namespace {
 
 #define LD4(p) (*reinterpret_cast<const float4 *>(p))
@@ -347,9 +350,11 @@ flash_bwd_kv_simt_k(float *__restrict__ dqkv, const float *__restrict__ qkv,
 
 struct FwdCfg { int kc; const char *name; };
 struct BwdCfg { int kc; const char *name; };
-const FwdCfg FWD[] = {{16, "simt-fp32 rowgroup keys16"}, {8, "simt-fp32 rowgroup keys8"}};
+// Forward config 2 is the tensor-core kernel (flash_tc.cu), head size 64 only.
+const FwdCfg FWD[] = {{16, "simt-fp32 rowgroup keys16"}, {8, "simt-fp32 rowgroup keys8"},
+                      {0, "tcgen05-tf32 q2x128 k64"}};
 const BwdCfg BWD[] = {{4, "simt-fp32 rowgroup keys4"}, {8, "simt-fp32 rowgroup keys8"}};
-constexpr int NFWD = 2, NBWD = 2;
+constexpr int NFWD = 3, NBWD = 2, FWD_TC = 2;
 
 bool shape_ok(const float *a, const float *b, int C, int NH) {
     return NH > 0 && C % NH == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
@@ -395,7 +400,8 @@ extern "C" {
 
 int bmb_flash_num_configs(void) { return NFWD; }
 const char *bmb_flash_config_name(int cfg) { return (cfg >= 0 && cfg < NFWD) ? FWD[cfg].name : "?"; }
-int bmb_flash_default_config(void) { return 0; }
+// fp32 arithmetic: the SIMT kernel; TF32/BF16 math modes: the tensor-core kernel.
+int bmb_flash_default_config(void) { return bmb_get_math_mode() == BMB_MATH_FP32 ? 0 : FWD_TC; }
 
 int bmb_flash_attention_forward_cfg(int cfg, float *out, float *lse, const float *qkv, int B, int T,
                                     int C, int NH) {
@@ -405,6 +411,11 @@ int bmb_flash_attention_forward_cfg(int cfg, float *out, float *lse, const float
     const int hs = C / NH;
     const float scale = 1.0f / sqrtf((float)hs);
     cudaStream_t st = cur_stream();
+    if (cfg == FWD_TC) {
+        if (!flash_tc_supported(T, C, NH, qkv, out))
+            return fail(BMB_E_UNSUPPORTED, "flash: the tensor-core config needs head size 64 (got %d)", hs);
+        return flash_forward_tc(out, lse, qkv, B, T, C, NH, false, st);
+    }
     switch (hs) {
     case 32:  return run_fwd<32>(cfg, out, lse, qkv, B, T, NH, scale, st);
     case 64:  return run_fwd<64>(cfg, out, lse, qkv, B, T, NH, scale, st);
@@ -415,7 +426,10 @@ int bmb_flash_attention_forward_cfg(int cfg, float *out, float *lse, const float
 
 int bmb_flash_attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C,
                                 int NH) {
-    return bmb_flash_attention_forward_cfg(bmb_flash_default_config(), out, lse, qkv, B, T, C, NH);
+    int cfg = bmb_flash_default_config();
+    // The preferred config may not serve this head size: fall back through the table (src/flash.cu:419-432).
+    if (cfg == FWD_TC && !(NH > 0 && C % NH == 0 && flash_tc_supported(T, C, NH, qkv, out))) cfg = 0;
+    return bmb_flash_attention_forward_cfg(cfg, out, lse, qkv, B, T, C, NH);
 }
 
 int bmb_flash_num_bwd_configs(void) { return NBWD; }

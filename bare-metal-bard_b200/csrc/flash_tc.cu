@@ -1,0 +1,367 @@
+// Fused causal attention forward on the tensor cores (head size 64):
+// S = Q K^T and O += P V as tcgen05.mma kind::tf32 with S and P V in tensor
+// memory, Q / K / V tiles brought in by TMA straight out of the fused
+// (B,T,3C) projection, softmax in registers with one query row per thread.
+// The (T x T) score matrix never leaves the SM (src/flash.h:1-34).
+//
+// One CTA owns 256 consecutive queries of one (batch, head) as two tiles of
+// 128 and walks the keys in blocks of 64 up to the diagonal.  320 threads:
+//   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: a thread reads its row
+//                    of S from TMEM (tcgen05.ld), scales, masks the diagonal
+//                    block, updates the running max and sum, writes
+//                    P = exp2(s - max) rounded to TF32 into shared memory
+//                    (K-major, 128-byte swizzle) and folds the previous block's
+//                    P V into its output registers: o = o * exp2(m_old - m_new) + PV;
+//   warp 8           producer: TMA loads of the two Q tiles, then K and V
+//                    blocks into a 2-deep ring;
+//   warp 9           issuer: S_t = Q_t K_j^T as soon as the group has taken
+//                    S_t(j-1) out of TMEM, PV_t = P_t V_j as soon as P_t is
+//                    written.  The two tiles interleave, so one group's
+//                    exponentials overlap the other's matrix products.
+// V is the B operand of P V with the head dimension contiguous, i.e. MN-major:
+// its TMA map uses the 128-byte swizzle with 32-byte atoms.  K and Q are
+// K-major.  Keys beyond the end of a sequence are never seen unmasked: a key
+// index >= T exceeds every valid query index, so the causal mask covers it.
+//
+// All mbarrier waits are bounded (tc_common.cuh); on expiry the CTA drains its
+// copies in flight, frees its TMEM columns and raises the device status word.
+#include "tc_common.cuh"
+#include <cmath>
+#include <mutex>
+
+namespace bmb {
+namespace {
+
+using namespace tc;
+
+constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KV_STAGES = 2;
+constexpr int Q_TILE_BYTES = QT * HS * 4;          // 32 KB: two halves of 128 rows x 128 B
+constexpr int KV_TILE_BYTES = KB * HS * 4;         // 16 KB: two halves / chunks of 64 rows x 128 B
+constexpr int P_TILE_BYTES = QT * KB * 4;          // 32 KB: two halves of 128 rows x 128 B
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + NQ * Q_TILE_BYTES;
+constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
+constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE_BYTES;
+constexpr int OFF_BAR = OFF_P + NQ * P_TILE_BYTES;
+constexpr int FWD_SMEM = OFF_BAR + 256 + 1024;
+constexpr int FWD_THREADS = 320;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant__ CUtensorMap mapV,
+               float *__restrict__ out, float *__restrict__ lse, int T, int NH, float scale_log2e,
+               int *__restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
+    // barrier indices
+    enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, PV_FULL = 11, NBARS = 13 };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
+    volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bh = blockIdx.y, b = bh / NH, h = bh % NH;
+    const int C = NH * HS;
+    const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;      // longest rows first
+    const int q0 = qblk * (NQ * QT);
+
+    int nblk[NQ];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+        const int first = q0 + t * QT;
+        nblk[t] = (first < T) ? (min(T - 1, first + QT - 1) / KB + 1) : 0;
+    }
+    const int maxblk = max(nblk[0], nblk[1]);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(bar(KV_FULL + s), 1); mbar_init(bar(KV_EMPTY + s), 1); }
+        for (int t = 0; t < NQ; ++t) {
+            mbar_init(bar(S_FULL + t), 1); mbar_init(bar(S_EMPTY + t), 4);
+            mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_FULL + t), 1);
+        }
+        *giveup = 0;
+        mbar_init_fence();
+    }
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 256);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            const int row0 = b * T;
+            int ntiles = 0;
+            for (int t = 0; t < NQ; ++t) ntiles += (nblk[t] > 0);
+            mbar_arrive_expect_tx(bar(Q_FULL), (uint32_t)(ntiles * Q_TILE_BYTES));
+            for (int t = 0; t < NQ; ++t) {
+                if (nblk[t] == 0) continue;
+                for (int half = 0; half < 2; ++half)
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_Q + t * Q_TILE_BYTES + half * (QT * 128) + rr * (64 * 128), &mapQK,
+                                    h * HS + half * 32, row0 + q0 + t * QT + rr * 64, bar(Q_FULL));
+            }
+            bool ok = true;
+            int armed_parity[KV_STAGES] = {-1, -1};
+            for (int j = 0; j < maxblk; ++j) {
+                const int st = j % KV_STAGES;
+                const uint32_t ph = (uint32_t)((j / KV_STAGES) & 1);
+                if (!mbar_wait(bar(KV_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(KV_FULL + st), 2 * KV_TILE_BYTES);
+                armed_parity[st] = (int)ph;
+                for (int half = 0; half < 2; ++half) {
+                    tma_load_2d(base + OFF_K + st * KV_TILE_BYTES + half * (KB * 128), &mapQK,
+                                C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
+                    tma_load_2d(base + OFF_V + st * KV_TILE_BYTES + half * (KB * 128), &mapV,
+                                2 * C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
+                }
+            }
+            if (!ok) {
+                mbar_drain(bar(Q_FULL), 0);
+                for (int s = 0; s < KV_STAGES; ++s)
+                    if (armed_parity[s] >= 0) mbar_drain(bar(KV_FULL + s), (uint32_t)armed_parity[s]);
+            }
+        }
+    } else if (warp == 9) {
+        // -------------------------------------------------------------- issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = make_idesc(2, 0, 0, KB, QT);    // Q (K-major) x K (K-major)
+            const uint32_t idesc_pv = make_idesc(2, 0, 1, HS, QT);   // P (K-major) x V (MN-major)
+            auto issue_s = [&](int t, int st) {
+                const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES, ka = base + OFF_K + st * KV_TILE_BYTES;
+                const uint32_t d = tmem_base + (uint32_t)(t * 128);
+#pragma unroll
+                for (int ks = 0; ks < HS / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(d, smem_desc_kmajor(qa + half * (QT * 128) + off),
+                             smem_desc_kmajor(ka + half * (KB * 128) + off), idesc_s, ks ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int st) {
+                const uint32_t pa = base + OFF_P + t * P_TILE_BYTES, va = base + OFF_V + st * KV_TILE_BYTES;
+                const uint32_t d = tmem_base + (uint32_t)(t * 128 + 64);
+#pragma unroll
+                for (int ks = 0; ks < KB / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(d, smem_desc_kmajor(pa + half * (QT * 128) + off),
+                             smem_desc_mnmajor32(va + ks * 1024, KB * 128), idesc_pv, ks ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
+            if (ok) ok = mbar_wait(bar(KV_FULL + 0), 0, giveup);
+            if (ok) {
+                fence_after();
+                for (int t = 0; t < NQ; ++t)
+                    if (nblk[t] > 0) { issue_s(t, 0); commit(bar(S_FULL + t)); }
+            }
+            for (int j = 0; ok && j < maxblk; ++j) {
+                const int st = j % KV_STAGES;
+                if (j + 1 < maxblk) {
+                    if (!mbar_wait(bar(KV_FULL + (j + 1) % KV_STAGES), (uint32_t)(((j + 1) / KV_STAGES) & 1), giveup)) { ok = false; break; }
+                }
+                for (int t = 0; ok && t < NQ; ++t) {
+                    if (j + 1 < nblk[t]) {
+                        if (!mbar_wait(bar(S_EMPTY + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                        fence_after();
+                        issue_s(t, (j + 1) % KV_STAGES);
+                        commit(bar(S_FULL + t));
+                    }
+                }
+                for (int t = 0; ok && t < NQ; ++t) {
+                    if (j < nblk[t]) {
+                        if (!mbar_wait(bar(P_FULL + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                        fence_after();
+                        issue_pv(t, st);
+                        commit(bar(PV_FULL + t));
+                    }
+                }
+                if (!ok) break;
+                commit(bar(KV_EMPTY + st));     // every MMA that read this K/V block has been issued
+            }
+        }
+    } else {
+        // ------------------------------------------------------ softmax groups
+        const int t = warp >> 2, quad = warp & 3;
+        const int r = quad * 32 + lane;                 // row inside the tile = TMEM lane
+        const int tile_q0 = q0 + t * QT;
+        const int qi = tile_q0 + r;
+        const int nb = nblk[t];
+        if (nb > 0) {
+            const uint32_t s_addr = tmem_base + (uint32_t)(t * 128) + ((uint32_t)(quad * 32) << 16);
+            const uint32_t pv_addr = s_addr + 64;
+            uint8_t *prow = gen + OFF_P + t * P_TILE_BYTES + r * 128;
+            float o[HS];
+#pragma unroll
+            for (int d = 0; d < HS; ++d) o[d] = 0.0f;
+            float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
+            bool ok = true;
+            for (int j = 0; j < nb; ++j) {
+                if (!mbar_wait(bar(S_FULL + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                fence_after();
+                float s[KB];
+                {
+                    float v[32];
+                    tmem_ld32(s_addr, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[i] = v[i];
+                    tmem_ld32(s_addr + 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[32 + i] = v[i];
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(S_EMPTY + t));       // S_t may be overwritten
+
+                const int k0 = j * KB;
+                const bool diag = (k0 + KB - 1 > tile_q0);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < KB; ++i) {
+                    float x = s[i] * scale_log2e;
+                    if (diag && (k0 + i > qi)) x = -INFINITY;
+                    s[i] = x;
+                    mx = fmaxf(mx, x);
+                }
+                const float m_new = fmaxf(m, mx);           // finite: key 0 is visible to every row
+                const float alpha = fast_exp2(m - m_new);
+                float sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < KB; ++i) {
+                    const float p = fast_exp2(s[i] - m_new);
+                    sum += p;
+                    s[i] = round_tf32(p);
+                }
+                l = l * alpha + sum;
+                m = m_new;
+
+                if (j > 0) {
+                    // P V of the previous block is complete: the P buffer is free and PV readable.
+                    if (!mbar_wait(bar(PV_FULL + t), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    float v[32];
+                    tmem_ld32(pv_addr, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha_prev, v[i]);
+                    tmem_ld32(pv_addr + 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], alpha_prev, v[i]);
+                }
+                alpha_prev = alpha;
+                // P row -> shared memory, K-major with the 128-byte swizzle (16-byte unit c of row r at c ^ (r & 7)).
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 val = make_float4(s[half * 32 + c * 4], s[half * 32 + c * 4 + 1],
+                                                       s[half * 32 + c * 4 + 2], s[half * 32 + c * 4 + 3]);
+                        *reinterpret_cast<float4 *>(prow + half * (QT * 128) + ((c ^ (r & 7)) << 4)) = val;
+                    }
+                }
+                fence_proxy_async();
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(P_FULL + t));
+            }
+            if (ok && mbar_wait(bar(PV_FULL + t), (uint32_t)((nb - 1) & 1), giveup)) {
+                fence_after();
+                float v[32];
+                tmem_ld32(pv_addr, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha_prev, v[i]);
+                tmem_ld32(pv_addr + 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], alpha_prev, v[i]);
+                if (qi < T) {
+                    const float inv = 1.0f / l;
+                    float *dst = out + ((size_t)b * T + qi) * C + h * HS;
+#pragma unroll
+                    for (int d = 0; d < HS; d += 4)
+                        *reinterpret_cast<float4 *>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+                    lse[(size_t)bh * T + qi] = (m + log2f(l)) * 0.6931471805599453f;
+                }
+            }
+        }
+    }
+
+    fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+    if (threadIdx.x == 0 && *giveup) {
+        *reinterpret_cast<volatile int *>(status) = 2;
+        __threadfence_system();
+    }
+}
+
+__global__ void round_copy_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float4 v = reinterpret_cast<const float4 *>(src)[i];
+        reinterpret_cast<float4 *>(dst)[i] = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+    }
+}
+
+bool g_fwd_attr[64];
+std::mutex g_mu;
+
+}  // namespace
+
+bool flash_tc_supported(int T, int C, int NH, const float *qkv, const float *out) {
+    if (NH <= 0 || C % NH || C / NH != HS) return false;
+    if (T < 1 || (((uintptr_t)qkv | (uintptr_t)out) & 15)) return false;
+    return true;
+}
+
+// qkv_rounded: the caller guarantees that qkv already holds TF32-representable
+// values; otherwise a rounded copy is made in per-device scratch first.
+int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, bool qkv_rounded,
+                     cudaStream_t st) {
+    int *status_dev = nullptr;
+    volatile int *status_host = nullptr;
+    BMB_TRY(tc::status_word(&status_dev, &status_host));
+    if (*status_host != 0)
+        return fail(BMB_E_TIMEOUT, "an earlier tensor-core kernel on this device gave up waiting on a barrier");
+    const float *src = qkv;
+    if (!qkv_rounded) {
+        const long long n = (long long)B * T * 3 * C;
+        float *scr = (float *)device_scratch(SCR_GEMM_A, (size_t)n * sizeof(float));
+        if (!scr) return BMB_E_CUDA;
+        long long blocks = (n / 4 + 255) / 256, cap = 8LL * sm_count();
+        round_copy_k<<<(int)(blocks > cap ? cap : blocks), 256, 0, st>>>(scr, qkv, n / 4);
+        count_launch();
+        BMB_LAUNCH_CHECK();
+        src = scr;
+    }
+    CUtensorMap mapQK, mapV;
+    BMB_TRY(make_map_2d(&mapQK, src, 4, (long long)B * T, 3LL * C, 3LL * C * 4, 64, false));
+    BMB_TRY(make_map_2d(&mapV, src, 4, (long long)B * T, 3LL * C, 3LL * C * 4, 64, true));
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        const int d = current_device();
+        if (d >= 0 && d < 64 && !g_fwd_attr[d]) {
+            BMB_CUDA(cudaFuncSetAttribute(flash_fwd_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
+            g_fwd_attr[d] = true;
+        }
+    }
+    const float scale_log2e = (1.0f / sqrtf((float)HS)) * 1.4426950408889634f;
+    dim3 grid((T + NQ * QT - 1) / (NQ * QT), B * NH);
+    flash_fwd_tc_k<<<grid, FWD_THREADS, FWD_SMEM, st>>>(mapQK, mapV, out, lse, T, NH, scale_log2e, status_dev);
+    count_launch();
+    BMB_LAUNCH_CHECK();
+    return BMB_OK;
+}
+
+}  // namespace bmb

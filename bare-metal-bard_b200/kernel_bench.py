@@ -1,0 +1,165 @@
+"""Per-kernel timings of libbmb.so on one GPU, one JSON line per case.
+
+    python bare-metal-bard_b200/kernel_bench.py [gemm] [bgemm] [flash] [nn] [--small]
+
+Timing follows the reference harness (src/bench.cu:75-105): 5 warm-up calls,
+then 20 calls bracketed by CUDA events one at a time; best and median are
+reported.  Work counts are the algorithmic ones:
+  GEMM          2*M*N*K FLOP
+  flash fwd     4*B*NH*hs*T*(T+1)/2 FLOP ("useful causal", tools/test_flash.cu:186-187)
+  flash bwd     2.5x (five products) and the reference's 3.5x count of that
+  nn kernels    bytes that must cross HBM once
+`--small` shrinks every case so that a profiler capture of one launch ends in
+seconds; the shapes stay larger than the 126 MB L2 where DRAM figures matter.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+from __graft_entry__ import load_package  # noqa: E402
+
+
+def timed(fn, warmup=5, iters=20):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[0], ts[len(ts) // 2]
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def bench_gemm(bmb, small):
+    lib = bmb.lib()
+    sizes = (1024, 2048) if small else (1024, 1536, 2048, 4096, 6144, 8192)
+    for n in sizes:
+        A = torch.rand(n * n, device="cuda") * 2 - 1
+        B = torch.rand(n * n, device="cuda") * 2 - 1
+        Cm = torch.zeros(n * n, device="cuda")
+        for name, fn in (("simt_fp32", lib.bmb_sgemm_simt), ("tcgen05_tf32", lib.bmb_sgemm_tf32),
+                         ("tcgen05_bf16", lib.bmb_sgemm_bf16)):
+            best, med = timed(lambda: bmb.check(fn(n, n, n, 1.0, A.data_ptr(), B.data_ptr(), 0.0, Cm.data_ptr())),
+                              iters=8 if (name == "simt_fp32" and n > 4096) else 20)
+            emit(kernel=name, M=n, N=n, K=n, best_ms=round(best, 4), median_ms=round(med, 4),
+                 tflops_best=round(2.0 * n ** 3 / best / 1e9, 2), tflops_median=round(2.0 * n ** 3 / med / 1e9, 2))
+    # the GEMM shapes of the 124M-parameter training step (8192 rows)
+    if not small:
+        shapes = [("fwd qkv NT", 0, 1, 8192, 2304, 768), ("fwd fc NT", 0, 1, 8192, 3072, 768),
+                  ("fwd fcproj NT", 0, 1, 8192, 768, 3072), ("fwd head NT", 0, 1, 8192, 50304, 768),
+                  ("dX fc NN", 0, 0, 8192, 768, 3072), ("dW fc TN", 1, 0, 3072, 768, 8192),
+                  ("dW head TN", 1, 0, 50304, 768, 8192)]
+        for tag, ta, tb, M, N, K in shapes:
+            A = torch.rand(M * K, device="cuda") * 2 - 1
+            B = torch.rand(K * N, device="cuda") * 2 - 1
+            Cm = torch.zeros(M * N, device="cuda")
+            for math, mname in ((bmb.MATH_FP32, "simt_fp32"), (bmb.MATH_TF32, "tcgen05_tf32")):
+                best, med = timed(lambda: bmb.call("bmb_gemm_ex", math, 0, ta, tb, M, N, K, 1.0, A, B, 0.0, Cm, None),
+                                  iters=10)
+                emit(kernel=mname, shape=tag, M=M, N=N, K=K, best_ms=round(best, 4), median_ms=round(med, 4),
+                     tflops_best=round(2.0 * M * N * K / best / 1e9, 2))
+            del A, B, Cm
+
+
+def bench_bgemm(bmb, small):
+    # attention-shaped batched GEMM: batch 96, Q.K^T (M=N=1024, K=64) and P.V (K=1024, N=64)
+    batch, T, hs = (24 if small else 96), 1024, 64
+    q = torch.randn(batch * T * hs, device="cuda")
+    k = torch.randn(batch * T * hs, device="cuda")
+    att = torch.zeros(batch * T * T, device="cuda")
+    o = torch.zeros(batch * T * hs, device="cuda")
+    for tag, fn, flop, nbytes in (
+            ("QK^T NT", lambda: bmb.call("bmb_batched_gemm", 0, 1, batch, T, T, hs, 0.125, q, T * hs, k, T * hs, 0.0, att, T * T, None),
+             2.0 * batch * T * T * hs, 4.0 * batch * (2 * T * hs + T * T)),
+            ("PV NN", lambda: bmb.call("bmb_batched_gemm", 0, 0, batch, T, hs, T, 1.0, att, T * T, k, T * hs, 0.0, o, T * hs, None),
+             2.0 * batch * T * T * hs, 4.0 * batch * (2 * T * hs + T * T))):
+        best, med = timed(fn)
+        emit(kernel="bgemm_simt_fp32", shape=tag, batch=batch, best_ms=round(best, 4), median_ms=round(med, 4),
+             tflops_best=round(flop / best / 1e9, 2), gbs_best=round(nbytes / best / 1e6, 1))
+
+
+def bench_flash(bmb, small):
+    lib = bmb.lib()
+    B, NH, T, hs = (2 if small else 8), 12, 1024, 64
+    C = NH * hs
+    qkv = torch.randn(B * T * 3 * C, device="cuda")
+    dout = torch.randn(B * T * C, device="cuda")
+    out, lse = torch.zeros(B * T * C, device="cuda"), torch.zeros(B * NH * T, device="cuda")
+    dqkv, dsum = torch.zeros(B * T * 3 * C, device="cuda"), torch.zeros(B * NH * T, device="cuda")
+    useful = 4.0 * B * NH * hs * T * (T + 1) / 2
+    fbytes = 4.0 * (B * T * 3 * C + B * T * C + B * NH * T)
+    for cfg in range(lib.bmb_flash_num_configs()):
+        name = lib.bmb_flash_config_name(cfg).decode()
+        best, med = timed(lambda: bmb.call("bmb_flash_attention_forward_cfg", cfg, out, lse, qkv, B, T, C, NH))
+        emit(kernel="flash_fwd", config=name, B=B, NH=NH, T=T, hs=hs, best_ms=round(best, 4), median_ms=round(med, 4),
+             useful_tflops_best=round(useful / best / 1e9, 2), gbs_best=round(fbytes / best / 1e6, 1))
+    bmb.call("bmb_flash_attention_forward_cfg", 0, out, lse, qkv, B, T, C, NH)
+    bbytes = 4.0 * (2 * B * T * 3 * C + 2 * B * T * C + 2 * B * NH * T)
+    for cfg in range(lib.bmb_flash_num_bwd_configs()):
+        name = lib.bmb_flash_bwd_config_name(cfg).decode()
+        best, med = timed(lambda: bmb.call("bmb_flash_attention_backward_cfg", cfg, dqkv, dsum, dout, qkv, out, lse, B, T, C, NH))
+        emit(kernel="flash_bwd", config=name, B=B, NH=NH, T=T, hs=hs, best_ms=round(best, 4), median_ms=round(med, 4),
+             tflops_2p5x_best=round(2.5 * useful / best / 1e9, 2), tflops_3p5x_best=round(3.5 * useful / best / 1e9, 2),
+             gbs_best=round(bbytes / best / 1e6, 1))
+
+
+def bench_nn(bmb, small):
+    N, C, V = (2048 if small else 8192), 768, 50304
+    x = torch.randn(N * C, device="cuda")
+    w, b = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda")
+    y, mean, rstd = torch.zeros(N * C, device="cuda"), torch.zeros(N, device="cuda"), torch.zeros(N, device="cuda")
+    dx, dw, db = torch.zeros(N * C, device="cuda"), torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    cases = [("layernorm_fwd", lambda: bmb.call("bmb_layernorm_forward", y, mean, rstd, x, w, b, N, C), 2.0 * N * C * 4),
+             ("layernorm_bwd", lambda: bmb.call("bmb_layernorm_backward", dx, dw, db, y, x, w, mean, rstd, N, C), 4.0 * N * C * 4)]
+    h = torch.randn(N * 4 * C, device="cuda")
+    g = torch.zeros(N * 4 * C, device="cuda")
+    g2 = torch.zeros(N * 4 * C, device="cuda")
+    b4 = torch.zeros(4 * C, device="cuda")
+    cases += [("gelu_fwd", lambda: bmb.call("bmb_gelu_forward", g, h, N * 4 * C), 2.0 * N * 4 * C * 4),
+              ("gelu_bwd", lambda: bmb.call("bmb_gelu_backward", g2, h, g, N * 4 * C), 3.0 * N * 4 * C * 4),
+              ("bias_fwd", lambda: bmb.call("bmb_bias_forward", g, b4, N, 4 * C), 2.0 * N * 4 * C * 4),
+              ("bias_bwd", lambda: bmb.call("bmb_bias_backward", b4, g, N, 4 * C), 1.0 * N * 4 * C * 4),
+              ("residual", lambda: bmb.call("bmb_residual_forward", dx, x, y, N * C), 3.0 * N * C * 4)]
+    logits = torch.randn(N * V, device="cuda")
+    probs, dlog = torch.zeros(N * V, device="cuda"), torch.zeros(N * V, device="cuda")
+    losses = torch.zeros(N, device="cuda")
+    tg = torch.randint(0, V, (N,), device="cuda", dtype=torch.int32)
+    cases += [("softmax_xent_fwd", lambda: bmb.call("bmb_softmax_crossentropy_forward", probs, losses, logits, tg, N, V, V), 2.0 * N * V * 4),
+              ("xent_bwd", lambda: bmb.call("bmb_crossentropy_softmax_backward", dlog, probs, tg, N, V, V, 1.0 / N), 2.0 * N * V * 4)]
+    n = 31118976 if small else 124475904
+    p, gr, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
+    cases += [("adamw", lambda: bmb.call("bmb_adamw_update", p, gr, m, v, n, 3e-4, 0.9, 0.95, 1e-8, 0.1, 1, 1.0), 7.0 * n * 4)]
+    sq = torch.zeros(1, device="cuda", dtype=torch.float64)
+    cases += [("grad_sumsq", lambda: bmb.call("bmb_grad_sumsq_device", gr, n, sq), 1.0 * n * 4)]
+    for name, fn, nbytes in cases:
+        best, med = timed(fn)
+        emit(kernel=name, best_ms=round(best, 4), median_ms=round(med, 4), algorithmic_MB=round(nbytes / 1e6, 1),
+             gbs_best=round(nbytes / best / 1e6, 1), gbs_median=round(nbytes / med / 1e6, 1))
+
+
+def main():
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    small = "--small" in sys.argv
+    which = args or ["gemm", "bgemm", "flash", "nn"]
+    bmb = load_package()
+    torch.cuda.set_device(0)
+    for w in which:
+        {"gemm": bench_gemm, "bgemm": bench_bgemm, "flash": bench_flash, "nn": bench_nn}[w](bmb, small)
+
+
+if __name__ == "__main__":
+    main()

@@ -128,9 +128,16 @@ def test_flash_forward_backward_vs_oracle(bmb, orc, cuda, B, T, C, NH):
         # outputs poisoned first, as tools/test_flash.cu:103-106
         out = cuda.full((B * T * C,), float("nan"), device="cuda")
         lse = cuda.full((B * NH * T,), float("nan"), device="cuda")
-        bmb.call("bmb_flash_attention_forward_cfg", cfg, out, lse, dq, B, T, C, NH)
-        assert normwise(host(cuda, out), wout) < 1e-5
-        assert normwise(host(cuda, lse), wlse) < 1e-5
+        tensor_core = lib.bmb_flash_config_name(cfg).startswith(b"tcgen05")
+        st = lib.bmb_flash_attention_forward_cfg(cfg, out.data_ptr(), lse.data_ptr(), dq.data_ptr(), B, T, C, NH)
+        if st == bmb.E_UNSUPPORTED and tensor_core and C // NH != 64:
+            continue                      # that config serves head size 64 only
+        bmb.check(st, "bmb_flash_attention_forward_cfg")
+        tol = 2e-3 if tensor_core else 1e-5     # TF32 products vs fp32 arithmetic
+        assert normwise(host(cuda, out), wout) < tol
+        assert normwise(host(cuda, lse), wlse) < tol
+    # the backward below starts from the fp32 forward's out / lse
+    bmb.call("bmb_flash_attention_forward_cfg", 0, out, lse, dq, B, T, C, NH)
     for cfg in range(lib.bmb_flash_num_bwd_configs()):
         dqkv = cuda.full((B * T * 3 * C,), float("nan"), device="cuda")
         dsum = cuda.full((B * NH * T,), float("nan"), device="cuda")

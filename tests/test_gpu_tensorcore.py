@@ -105,6 +105,33 @@ def test_unrounded_operands_show_why_rounding_is_needed(bmb, orc, cuda, capsys):
     assert e_round < 5e-4 and e_round <= e_raw * 1.05
 
 
+ATT_SHAPES = [(2, 64, 128, 2), (1, 256, 128, 2), (2, 300, 192, 3), (3, 100, 384, 6), (2, 33, 384, 6), (1, 1, 384, 6),
+              (2, 129, 128, 2), (1, 1024, 128, 2), (2, 513, 64, 1)]
+
+
+@pytest.mark.parametrize("B,T,C,NH", ATT_SHAPES)
+def test_tensorcore_flash_forward_vs_oracle(bmb, orc, cuda, B, T, C, NH):
+    """Forward config 2 (tcgen05, TF32 products, fp32 softmax) against the fp32
+    oracle.  TF32 rounding of q, k, p and v bounds the error: out within 2e-3
+    normwise (measured about 4e-4), lse within 1e-3 of max|lse|."""
+    from helpers import normal
+    qkv = normal(B * T * 3 * C, 1234)
+    wout, wlse = np.empty(B * T * C, np.float32), np.empty(B * NH * T, np.float32)
+    orc.orc_attention_forward(_np(wout), _np(wlse), None, _np(qkv), B, T, C, NH)
+    dq = dev(cuda, qkv)
+    out = cuda.full((B * T * C,), float("nan"), device="cuda")
+    lse = cuda.full((B * NH * T,), float("nan"), device="cuda")
+    bmb.call("bmb_flash_attention_forward_cfg", 2, out, lse, dq, B, T, C, NH)
+    e_out, e_lse = normwise(host(cuda, out), wout), normwise(host(cuda, lse), wlse)
+    assert e_out < 2e-3 and e_lse < 1e-3, (e_out, e_lse)
+
+
+def test_tensorcore_flash_rejects_other_head_sizes(bmb, cuda):
+    x = cuda.zeros(4096, device="cuda")
+    st = bmb.lib().bmb_flash_attention_forward_cfg(2, x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 4, 128, 4)
+    assert st == bmb.E_UNSUPPORTED
+
+
 TINY = dict(max_seq_len=64, vocab_size=300, padded_vocab=384, n_layer=2, n_head=2, n_embd=256, B=4, T=64)
 
 
