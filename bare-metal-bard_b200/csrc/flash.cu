@@ -23,6 +23,8 @@ namespace bmb {
 bool flash_tc_supported(int T, int C, int NH, const float *qkv, const float *out);
 int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, bool qkv_rounded,
                      cudaStream_t st);
+int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
+                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st);
 namespace {
 
 #define LD4(p) (*reinterpret_cast<const float4 *>(p))
@@ -353,8 +355,10 @@ struct BwdCfg { int kc; const char *name; };
 // Forward config 2 is the tensor-core kernel (flash_tc.cu), head size 64 only.
 const FwdCfg FWD[] = {{16, "simt-fp32 rowgroup keys16"}, {8, "simt-fp32 rowgroup keys8"},
                       {0, "tcgen05-tf32 q2x128 k64"}};
-const BwdCfg BWD[] = {{4, "simt-fp32 rowgroup keys4"}, {8, "simt-fp32 rowgroup keys8"}};
-constexpr int NFWD = 3, NBWD = 2, FWD_TC = 2;
+// Backward config 2 is the tensor-core kernel pair (flash_tc_bwd.cu), head size 64 only.
+const BwdCfg BWD[] = {{4, "simt-fp32 rowgroup keys4"}, {8, "simt-fp32 rowgroup keys8"},
+                      {0, "tcgen05-tf32 dq128x64 dkv128x32"}};
+constexpr int NFWD = 3, NBWD = 3, FWD_TC = 2, BWD_TC = 2;
 
 bool shape_ok(const float *a, const float *b, int C, int NH) {
     return NH > 0 && C % NH == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
@@ -392,6 +396,14 @@ int run_bwd(int cfg, float *dqkv, float *dsum, const float *dout, const float *q
 }
 
 }  // namespace
+
+int launch_flash_dsum(float *dsum, const float *dout, const float *out, int B, int T, int NH, int HS, cudaStream_t st) {
+    const long long rows = (long long)B * NH * T;
+    flash_dsum_k<<<ceil_div(rows * 32, 256), 256, 0, st>>>(dsum, dout, out, T, NH, HS, rows);
+    count_launch();
+    BMB_LAUNCH_CHECK();
+    return BMB_OK;
+}
 }  // namespace bmb
 
 using namespace bmb;
@@ -434,7 +446,7 @@ int bmb_flash_attention_forward(float *out, float *lse, const float *qkv, int B,
 
 int bmb_flash_num_bwd_configs(void) { return NBWD; }
 const char *bmb_flash_bwd_config_name(int cfg) { return (cfg >= 0 && cfg < NBWD) ? BWD[cfg].name : "?"; }
-int bmb_flash_default_bwd_config(void) { return 0; }
+int bmb_flash_default_bwd_config(void) { return bmb_get_math_mode() == BMB_MATH_FP32 ? 0 : BWD_TC; }
 
 int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum, const float *dout,
                                      const float *qkv, const float *out, const float *lse, int B,
@@ -446,6 +458,11 @@ int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum, const fl
     const int hs = C / NH;
     const float scale = 1.0f / sqrtf((float)hs);
     cudaStream_t st = cur_stream();
+    if (cfg == BWD_TC) {
+        if (!flash_tc_supported(T, C, NH, qkv, dqkv))
+            return fail(BMB_E_UNSUPPORTED, "flash: the tensor-core config needs head size 64 (got %d)", hs);
+        return flash_backward_tc(dqkv, dsum, dout, qkv, out, lse, B, T, C, NH, false, st);
+    }
     switch (hs) {
     case 32:  return run_bwd<32>(cfg, dqkv, dsum, dout, qkv, out, lse, B, T, NH, scale, st);
     case 64:  return run_bwd<64>(cfg, dqkv, dsum, dout, qkv, out, lse, B, T, NH, scale, st);
@@ -456,8 +473,9 @@ int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum, const fl
 
 int bmb_flash_attention_backward(float *dqkv, float *dsum, const float *dout, const float *qkv,
                                  const float *out, const float *lse, int B, int T, int C, int NH) {
-    return bmb_flash_attention_backward_cfg(bmb_flash_default_bwd_config(), dqkv, dsum, dout, qkv, out,
-                                            lse, B, T, C, NH);
+    int cfg = bmb_flash_default_bwd_config();
+    if (cfg == BWD_TC && !(NH > 0 && C % NH == 0 && flash_tc_supported(T, C, NH, qkv, dqkv))) cfg = 0;
+    return bmb_flash_attention_backward_cfg(cfg, dqkv, dsum, dout, qkv, out, lse, B, T, C, NH);
 }
 
 }  // extern "C"

@@ -1,0 +1,504 @@
+// Fused causal attention backward on the tensor cores (head size 64), two
+// kernels as in the reference (src/flash.cu:434-470): dQ reduces over keys,
+// dK and dV reduce over queries, so each keeps its accumulators on chip -- here
+// in tensor memory -- and writes its part of dqkv with plain stores.
+// P is rebuilt from the saved lse, P = exp(S - lse), and
+// dS = P * (dP - D) with D = rowsum(dO * O)   (src/flash.cu:447-453).
+//
+// dQ kernel: a CTA owns 128 queries and walks key blocks of 64 up to the
+//   diagonal.  Per block the issuer forms S = Q K^T and dP = dO V^T in TMEM
+//   (double buffered, so block j+1 is being multiplied while block j is in the
+//   registers); 256 threads -- a row of 128 per 32-column half -- turn them
+//   into dS, rounded to TF32 and written K-major into shared memory; then
+//   dQ += dS K accumulates in TMEM over the whole walk.
+// dK/dV kernel: a CTA owns 128 keys and walks query blocks of 32 from the
+//   diagonal to the end, with everything transposed so that the owned keys are
+//   again the rows: S^T = K Q^T, dP^T = V dO^T, then dV += P^T dO and
+//   dK += dS^T Q accumulate in TMEM.  lse and D now vary along the columns.
+// K (dQ kernel) and Q, dO (dK/dV kernel) serve twice, once as a K-major operand
+// and once with the head dimension as N, i.e. MN-major; the two uses need
+// different swizzles (128-byte, and 128-byte with 32-byte atoms), so TMA brings
+// each of those tiles in twice.
+// Products are TF32 with fp32 accumulation; the exponentials, the subtraction
+// of D and the scaling are fp32.  Waits are bounded as in the other kernels.
+#include "tc_common.cuh"
+#include <cmath>
+#include <mutex>
+
+namespace bmb {
+int launch_flash_dsum(float *dsum, const float *dout, const float *out, int B, int T, int NH, int HS, cudaStream_t st);
+
+namespace {
+
+using namespace tc;
+
+constexpr int HS = 64;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ============================================================== dQ kernel
+namespace dq {
+constexpr int QT = 128, KB = 64, STAGES = 2;
+constexpr int OFF_Q = 0, OFF_DO = 32768, OFF_ST = 65536, STAGE_BYTES = 49152;   // Kk | Kn | Vk, 16 KB each
+constexpr int OFF_DS = OFF_ST + STAGES * STAGE_BYTES;                            // 32 KB
+constexpr int OFF_BAR = OFF_DS + 32768;
+constexpr int SMEM = OFF_BAR + 256 + 1024;
+constexpr int THREADS = 320;
+enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, SP_FULL = 5, SP_EMPTY = 7, DS_FULL = 9, DQ_DONE = 10, NBARS = 11 };
+}  // namespace dq
+
+__global__ void __launch_bounds__(dq::THREADS, 1)
+flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_constant__ CUtensorMap mapQKV_n,
+                  const __grid_constant__ CUtensorMap mapDO_k, float *__restrict__ dqkv,
+                  const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
+                  int *__restrict__ status) {
+    using namespace dq;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
+    volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bh = blockIdx.y, b = bh / NH, h = bh % NH;
+    const int C = NH * HS;
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * QT;
+    const int nb = min(T - 1, q0 + QT - 1) / KB + 1;       // key blocks up to the diagonal
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(bar(KV_FULL + s), 1); mbar_init(bar(KV_EMPTY + s), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(SP_EMPTY + s), 8); }
+        mbar_init(bar(DS_FULL), 8);
+        mbar_init(bar(DQ_DONE), 1);
+        *giveup = 0;
+        mbar_init_fence();
+    }
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // TMEM columns: S[2] at 0 / 64, dP[2] at 128 / 192, dQ at 256
+
+    if (warp == 8) {
+        if (lane == 0) {
+            const int row0 = b * T;
+            mbar_arrive_expect_tx(bar(Q_FULL), 65536);
+            for (int half = 0; half < 2; ++half)
+                for (int rr = 0; rr < 2; ++rr) {
+                    tma_load_2d(base + OFF_Q + half * 16384 + rr * 8192, &mapQKV_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(Q_FULL));
+                    tma_load_2d(base + OFF_DO + half * 16384 + rr * 8192, &mapDO_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(Q_FULL));
+                }
+            bool ok = true;
+            int armed[STAGES] = {-1, -1};
+            for (int j = 0; j < nb; ++j) {
+                const int st = j % STAGES;
+                const uint32_t ph = (uint32_t)((j / STAGES) & 1);
+                if (!mbar_wait(bar(KV_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(KV_FULL + st), STAGE_BYTES);
+                armed[st] = (int)ph;
+                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+                for (int half = 0; half < 2; ++half) {
+                    tma_load_2d(sb + half * 8192, &mapQKV_k, C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
+                    tma_load_2d(sb + 16384 + half * 8192, &mapQKV_n, C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
+                    tma_load_2d(sb + 32768 + half * 8192, &mapQKV_k, 2 * C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
+                }
+            }
+            if (!ok) {
+                mbar_drain(bar(Q_FULL), 0);
+                for (int s = 0; s < STAGES; ++s)
+                    if (armed[s] >= 0) mbar_drain(bar(KV_FULL + s), (uint32_t)armed[s]);
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            const uint32_t idesc_kk = make_idesc(2, 0, 0, KB, QT);     // [128 x 64] = A(K-major) x B(K-major)
+            const uint32_t idesc_kn = make_idesc(2, 0, 1, HS, QT);     // dQ: dS (K-major) x K (MN-major)
+            auto issue_sp = [&](int st, int buf) {
+                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HS / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(tmem_base + (uint32_t)(buf * 64), smem_desc_kmajor(base + OFF_Q + half * 16384 + off),
+                             smem_desc_kmajor(sb + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < HS / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(tmem_base + (uint32_t)(128 + buf * 64), smem_desc_kmajor(base + OFF_DO + half * 16384 + off),
+                             smem_desc_kmajor(sb + 32768 + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
+            if (ok) ok = mbar_wait(bar(KV_FULL + 0), 0, giveup);
+            if (ok) { fence_after(); issue_sp(0, 0); commit(bar(SP_FULL + 0)); }
+            for (int j = 0; ok && j < nb; ++j) {
+                const int st = j % STAGES;
+                if (j + 1 < nb) {
+                    const int nbuf = (j + 1) & 1;
+                    if (!mbar_wait(bar(KV_FULL + (j + 1) % STAGES), (uint32_t)(((j + 1) / STAGES) & 1), giveup)) { ok = false; break; }
+                    if (j >= 1 && !mbar_wait(bar(SP_EMPTY + nbuf), (uint32_t)(((j - 1) / 2) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    issue_sp((j + 1) % STAGES, nbuf);
+                    commit(bar(SP_FULL + nbuf));
+                }
+                if (!mbar_wait(bar(DS_FULL), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                fence_after();
+                const uint32_t kn = base + OFF_ST + st * STAGE_BYTES + 16384;
+#pragma unroll
+                for (int ks = 0; ks < KB / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(tmem_base + 256, smem_desc_kmajor(base + OFF_DS + half * 16384 + off),
+                             smem_desc_mnmajor32(kn + ks * 1024, 8192), idesc_kn, (j | ks) ? 1u : 0u);
+                }
+                commit(bar(DQ_DONE));
+                commit(bar(KV_EMPTY + st));
+            }
+        }
+    } else {
+        const int quad = warp & 3, colhalf = warp >> 2;
+        const int r = quad * 32 + lane;
+        const int qi = q0 + r;
+        const float lse_r = (qi < T) ? lse[(size_t)bh * T + qi] * LOG2E : 0.0f;
+        const float d_r = (qi < T) ? dsum[(size_t)bh * T + qi] : 0.0f;
+        const float scale_log2e = scale * LOG2E;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        uint8_t *dsrow = gen + OFF_DS + colhalf * 16384 + r * 128;
+        bool ok = true;
+        for (int j = 0; j < nb; ++j) {
+            const int buf = j & 1;
+            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((j / 2) & 1), giveup)) { ok = false; break; }
+            fence_after();
+            float s[32], dp[32];
+            tmem_ld32(lane_addr + (uint32_t)(buf * 64 + colhalf * 32), s);
+            tmem_ld32(lane_addr + (uint32_t)(128 + buf * 64 + colhalf * 32), dp);
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(SP_EMPTY + buf));
+            const int k0 = j * KB + colhalf * 32;
+            const bool diag = (k0 + 31 > q0);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float p = fast_exp2(fmaf(s[i], scale_log2e, -lse_r));
+                if (diag && (k0 + i > qi)) p = 0.0f;
+                s[i] = round_tf32(p * (dp[i] - d_r));
+            }
+            if (j > 0 && !mbar_wait(bar(DQ_DONE), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4 *>(dsrow + ((c ^ (r & 7)) << 4)) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(DS_FULL));
+        }
+        if (ok && mbar_wait(bar(DQ_DONE), (uint32_t)((nb - 1) & 1), giveup)) {
+            fence_after();
+            float v[32];
+            tmem_ld32(lane_addr + (uint32_t)(256 + colhalf * 32), v);
+            if (qi < T) {
+                float *dst = dqkv + ((size_t)b * T + qi) * 3 * C + h * HS + colhalf * 32;
+#pragma unroll
+                for (int d = 0; d < 32; d += 4)
+                    *reinterpret_cast<float4 *>(dst + d) = make_float4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale);
+            }
+        }
+    }
+
+    fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *giveup) {
+        *reinterpret_cast<volatile int *>(status) = 3;
+        __threadfence_system();
+    }
+}
+
+// ============================================================ dK/dV kernel
+namespace dkv {
+constexpr int KT = 128, QB = 32, STAGES = 3;
+constexpr int OFF_K = 0, OFF_V = 32768, OFF_ST = 65536, STAGE_BYTES = 32768;    // Qk | Qn | dOk | dOn, 8 KB each
+constexpr int OFF_PT = OFF_ST + STAGES * STAGE_BYTES;                            // 16 KB
+constexpr int OFF_DST = OFF_PT + 16384;                                          // 16 KB
+constexpr int OFF_BAR = OFF_DST + 16384;
+constexpr int SMEM = OFF_BAR + 256 + 1024;
+constexpr int THREADS = 320;
+enum { KV_FULL = 0, ST_FULL = 1, ST_EMPTY = 4, SP_FULL = 7, SP_EMPTY = 9, PD_FULL = 11, PD_DONE = 12, NBARS = 13 };
+}  // namespace dkv
+
+__global__ void __launch_bounds__(dkv::THREADS, 1)
+flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_k32,
+                   const __grid_constant__ CUtensorMap mapQKV_n32, const __grid_constant__ CUtensorMap mapDO_k32,
+                   const __grid_constant__ CUtensorMap mapDO_n32, float *__restrict__ dqkv,
+                   const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
+                   int *__restrict__ status) {
+    using namespace dkv;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
+    volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bh = blockIdx.y, b = bh / NH, h = bh % NH;
+    const int C = NH * HS;
+    const int j0 = (int)blockIdx.x * KT;                   // first key of this CTA (earliest keys walk longest)
+    const int ib0 = j0 / QB;                               // first query block that can see these keys
+    const int nb = (T + QB - 1) / QB - ib0;                // query blocks to walk
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(KV_FULL), 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(bar(ST_FULL + s), 1); mbar_init(bar(ST_EMPTY + s), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(SP_EMPTY + s), 8); }
+        mbar_init(bar(PD_FULL), 8);
+        mbar_init(bar(PD_DONE), 1);
+        *giveup = 0;
+        mbar_init_fence();
+    }
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 256);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // TMEM columns: S^T[2] at 0 / 32, dP^T[2] at 64 / 96, dV at 128, dK at 192
+
+    if (warp == 8) {
+        if (lane == 0) {
+            const int row0 = b * T;
+            mbar_arrive_expect_tx(bar(KV_FULL), 65536);
+            for (int half = 0; half < 2; ++half)
+                for (int rr = 0; rr < 2; ++rr) {
+                    tma_load_2d(base + OFF_K + half * 16384 + rr * 8192, &mapQKV_k64, C + h * HS + half * 32, row0 + j0 + rr * 64, bar(KV_FULL));
+                    tma_load_2d(base + OFF_V + half * 16384 + rr * 8192, &mapQKV_k64, 2 * C + h * HS + half * 32, row0 + j0 + rr * 64, bar(KV_FULL));
+                }
+            bool ok = true;
+            int armed[STAGES] = {-1, -1, -1};
+            for (int i = 0; i < nb; ++i) {
+                const int st = i % STAGES;
+                const uint32_t ph = (uint32_t)((i / STAGES) & 1);
+                if (!mbar_wait(bar(ST_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(ST_FULL + st), STAGE_BYTES);
+                armed[st] = (int)ph;
+                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+                const int qrow = row0 + (ib0 + i) * QB;
+                for (int half = 0; half < 2; ++half) {
+                    tma_load_2d(sb + half * 4096, &mapQKV_k32, h * HS + half * 32, qrow, bar(ST_FULL + st));
+                    tma_load_2d(sb + 8192 + half * 4096, &mapQKV_n32, h * HS + half * 32, qrow, bar(ST_FULL + st));
+                    tma_load_2d(sb + 16384 + half * 4096, &mapDO_k32, h * HS + half * 32, qrow, bar(ST_FULL + st));
+                    tma_load_2d(sb + 24576 + half * 4096, &mapDO_n32, h * HS + half * 32, qrow, bar(ST_FULL + st));
+                }
+            }
+            if (!ok) {
+                mbar_drain(bar(KV_FULL), 0);
+                for (int s = 0; s < STAGES; ++s)
+                    if (armed[s] >= 0) mbar_drain(bar(ST_FULL + s), (uint32_t)armed[s]);
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            const uint32_t idesc_st = make_idesc(2, 0, 0, QB, KT);     // [128 keys x 32 queries]
+            const uint32_t idesc_acc = make_idesc(2, 0, 1, HS, KT);    // [128 keys x 64] = A (K-major) x B (MN-major)
+            auto issue_sp = [&](int st, int buf) {
+                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HS / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(tmem_base + (uint32_t)(buf * 32), smem_desc_kmajor(base + OFF_K + half * 16384 + off),
+                             smem_desc_kmajor(sb + half * 4096 + off), idesc_st, ks ? 1u : 0u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < HS / 8; ++ks) {
+                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                    mma_tf32(tmem_base + (uint32_t)(64 + buf * 32), smem_desc_kmajor(base + OFF_V + half * 16384 + off),
+                             smem_desc_kmajor(sb + 16384 + half * 4096 + off), idesc_st, ks ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(bar(KV_FULL), 0, giveup);
+            if (ok) ok = mbar_wait(bar(ST_FULL + 0), 0, giveup);
+            if (ok) { fence_after(); issue_sp(0, 0); commit(bar(SP_FULL + 0)); }
+            for (int i = 0; ok && i < nb; ++i) {
+                const int st = i % STAGES;
+                if (i + 1 < nb) {
+                    const int nbuf = (i + 1) & 1;
+                    if (!mbar_wait(bar(ST_FULL + (i + 1) % STAGES), (uint32_t)(((i + 1) / STAGES) & 1), giveup)) { ok = false; break; }
+                    if (i >= 1 && !mbar_wait(bar(SP_EMPTY + nbuf), (uint32_t)(((i - 1) / 2) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    issue_sp((i + 1) % STAGES, nbuf);
+                    commit(bar(SP_FULL + nbuf));
+                }
+                if (!mbar_wait(bar(PD_FULL), (uint32_t)(i & 1), giveup)) { ok = false; break; }
+                fence_after();
+                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < QB / 8; ++ks) {     // dV += P^T dO
+                    mma_tf32(tmem_base + 128, smem_desc_kmajor(base + OFF_PT + ks * 32),
+                             smem_desc_mnmajor32(sb + 24576 + ks * 1024, 4096), idesc_acc, (i | ks) ? 1u : 0u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < QB / 8; ++ks) {     // dK += dS^T Q
+                    mma_tf32(tmem_base + 192, smem_desc_kmajor(base + OFF_DST + ks * 32),
+                             smem_desc_mnmajor32(sb + 8192 + ks * 1024, 4096), idesc_acc, (i | ks) ? 1u : 0u);
+                }
+                commit(bar(PD_DONE));
+                commit(bar(ST_EMPTY + st));
+            }
+        }
+    } else {
+        const int quad = warp & 3, colhalf = warp >> 2;
+        const int r = quad * 32 + lane;
+        const int kj = j0 + r;                             // this thread's key
+        const float scale_log2e = scale * LOG2E;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        uint8_t *ptrow = gen + OFF_PT + r * 128, *dstrow = gen + OFF_DST + r * 128;
+        bool ok = true;
+        for (int i = 0; i < nb; ++i) {
+            const int buf = i & 1;
+            const int qc0 = (ib0 + i) * QB + colhalf * 16;     // first query column of this thread
+            // per-column lse (in log2 units) and D; every thread of the CTA reads the same 32 values
+            float lc[16], dc[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const int q = qc0 + c;
+                lc[c] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
+                dc[c] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+            }
+            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((i / 2) & 1), giveup)) { ok = false; break; }
+            fence_after();
+            float s[16], dp[16];
+            tmem_ld16(lane_addr + (uint32_t)(buf * 32 + colhalf * 16), s);
+            tmem_ld16(lane_addr + (uint32_t)(64 + buf * 32 + colhalf * 16), dp);
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(SP_EMPTY + buf));
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const int q = qc0 + c;
+                float p = fast_exp2(fmaf(s[c], scale_log2e, -lc[c]));
+                if (q < kj || q >= T) p = 0.0f;            // causal mask and the ragged end
+                s[c] = round_tf32(p);
+                dp[c] = round_tf32(p * (dp[c] - dc[c]));
+            }
+            if (i > 0 && !mbar_wait(bar(PD_DONE), (uint32_t)((i - 1) & 1), giveup)) { ok = false; break; }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int unit = ((colhalf * 4 + c) ^ (r & 7)) << 4;
+                *reinterpret_cast<float4 *>(ptrow + unit) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+                *reinterpret_cast<float4 *>(dstrow + unit) = make_float4(dp[c * 4], dp[c * 4 + 1], dp[c * 4 + 2], dp[c * 4 + 3]);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(PD_FULL));
+        }
+        if (ok && nb > 0 && mbar_wait(bar(PD_DONE), (uint32_t)((nb - 1) & 1), giveup)) {
+            fence_after();
+            float v[32];
+            tmem_ld32(lane_addr + (uint32_t)(128 + colhalf * 32), v);
+            if (kj < T) {
+                float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + 2 * C + h * HS + colhalf * 32;
+#pragma unroll
+                for (int d = 0; d < 32; d += 4)
+                    *reinterpret_cast<float4 *>(dst + d) = make_float4(v[d], v[d + 1], v[d + 2], v[d + 3]);
+            }
+            tmem_ld32(lane_addr + (uint32_t)(192 + colhalf * 32), v);
+            if (kj < T) {
+                float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + C + h * HS + colhalf * 32;
+#pragma unroll
+                for (int d = 0; d < 32; d += 4)
+                    *reinterpret_cast<float4 *>(dst + d) = make_float4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale);
+            }
+        }
+    }
+
+    fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+    if (threadIdx.x == 0 && *giveup) {
+        *reinterpret_cast<volatile int *>(status) = 4;
+        __threadfence_system();
+    }
+}
+
+__global__ void round_copy2_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float4 v = reinterpret_cast<const float4 *>(src)[i];
+        reinterpret_cast<float4 *>(dst)[i] = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+    }
+}
+
+bool g_attr[64];
+std::mutex g_mu;
+
+}  // namespace
+
+// dqkv is overwritten.  `rounded`: qkv and dout already hold TF32-representable
+// values; otherwise rounded copies are made in per-device scratch first.
+int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
+                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st) {
+    int *status_dev = nullptr;
+    volatile int *status_host = nullptr;
+    BMB_TRY(tc::status_word(&status_dev, &status_host));
+    if (*status_host != 0)
+        return fail(BMB_E_TIMEOUT, "an earlier tensor-core kernel on this device gave up waiting on a barrier");
+    BMB_TRY(launch_flash_dsum(dsum, dout, out, B, T, NH, HS, st));
+    const float *q = qkv, *g = dout;
+    if (!rounded) {
+        const long long nq = (long long)B * T * 3 * C, ng = (long long)B * T * C;
+        float *sq = (float *)device_scratch(SCR_GEMM_A, (size_t)nq * sizeof(float));
+        float *sg = (float *)device_scratch(SCR_GEMM_B, (size_t)ng * sizeof(float));
+        if (!sq || !sg) return BMB_E_CUDA;
+        const long long cap = 8LL * sm_count();
+        long long b1 = (nq / 4 + 255) / 256, b2 = (ng / 4 + 255) / 256;
+        round_copy2_k<<<(int)(b1 > cap ? cap : b1), 256, 0, st>>>(sq, qkv, nq / 4);
+        round_copy2_k<<<(int)(b2 > cap ? cap : b2), 256, 0, st>>>(sg, dout, ng / 4);
+        count_launch(2);
+        BMB_LAUNCH_CHECK();
+        q = sq; g = sg;
+    }
+    const long long rows = (long long)B * T;
+    CUtensorMap qk64, qn64, qk32, qn32, gk64, gk32, gn32;
+    BMB_TRY(make_map_2d(&qk64, q, 4, rows, 3LL * C, 3LL * C * 4, 64, false));
+    BMB_TRY(make_map_2d(&qn64, q, 4, rows, 3LL * C, 3LL * C * 4, 64, true));
+    BMB_TRY(make_map_2d(&qk32, q, 4, rows, 3LL * C, 3LL * C * 4, 32, false));
+    BMB_TRY(make_map_2d(&qn32, q, 4, rows, 3LL * C, 3LL * C * 4, 32, true));
+    BMB_TRY(make_map_2d(&gk64, g, 4, rows, C, (long long)C * 4, 64, false));
+    BMB_TRY(make_map_2d(&gk32, g, 4, rows, C, (long long)C * 4, 32, false));
+    BMB_TRY(make_map_2d(&gn32, g, 4, rows, C, (long long)C * 4, 32, true));
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        const int d = current_device();
+        if (d >= 0 && d < 64 && !g_attr[d]) {
+            BMB_CUDA(cudaFuncSetAttribute(flash_bwd_dq_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::SMEM));
+            BMB_CUDA(cudaFuncSetAttribute(flash_bwd_dkv_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM));
+            g_attr[d] = true;
+        }
+    }
+    const float scale = 1.0f / sqrtf((float)HS);
+    dim3 gkv((T + dkv::KT - 1) / dkv::KT, B * NH), gq((T + dq::QT - 1) / dq::QT, B * NH);
+    flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qk32, qn32, gk32, gn32, dqkv, lse, dsum, T, NH, scale, status_dev);
+    flash_bwd_dq_tc_k<<<gq, dq::THREADS, dq::SMEM, st>>>(qk64, qn64, gk64, dqkv, lse, dsum, T, NH, scale, status_dev);
+    count_launch(2);
+    BMB_LAUNCH_CHECK();
+    return BMB_OK;
+}
+
+}  // namespace bmb

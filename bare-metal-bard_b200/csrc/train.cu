@@ -70,6 +70,13 @@ struct Scope {
     ~Scope() { bmb_set_stream(prev_stream); cudaSetDevice(prev_dev); }
 };
 
+// Attention kernel configuration for this trainer's arithmetic: the SIMT fp32
+// kernels, or the tensor-core pair (config 2 of both tables) when the GEMMs
+// run on tensor cores and the head size is the one those kernels serve.
+int attn_cfg(const bmb_train_config &c) {
+    return (c.math != BMB_MATH_FP32 && c.n_embd / c.n_head == 64) ? 2 : 0;
+}
+
 int collect_profile(bmb_trainer *t) {
     for (size_t i = 0; i + 1 < t->ev_used; i += 2) {
         float ms = 0.f;
@@ -126,7 +133,7 @@ int forward(bmb_trainer *t) {
         BMB_TRY(mm(t, wflag, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv));
         BMB_TRY(bmb_bias_forward(qkv, P + t->poff[P_QKVB] + (size_t)l * 3 * C, N, 3 * C));
         if (c.use_flash)
-            BMB_TRY(bmb_flash_attention_forward(atty, t->lse + l * lse_sz, qkv, B, T, C, NH));
+            BMB_TRY(bmb_flash_attention_forward_cfg(attn_cfg(c), atty, t->lse + l * lse_sz, qkv, B, T, C, NH));
         else
             BMB_TRY(bmb_attention_forward(atty, t->qkvr + l * qkvr_sz, t->att + l * att_sz, qkv, B, T, C, NH));
         BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
@@ -189,7 +196,7 @@ int backward(bmb_trainer *t) {
         BMB_TRY(mm(t, 0, 1, 0, C, C, N, t->dres, atty, 1.0f, G + t->poff[P_APW] + (size_t)l * C * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_APB] + lC, t->dres, N, C));
         if (c.use_flash)
-            BMB_TRY(bmb_flash_attention_backward(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH));
+            BMB_TRY(bmb_flash_attention_backward_cfg(attn_cfg(c), t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH));
         else
             BMB_TRY(bmb_attention_backward(t->dqkv, t->dqkvr, t->datt, t->datt, t->datty, t->qkvr + l * qkvr_sz,
                                            t->att + l * att_sz, B, T, C, NH));

@@ -141,10 +141,20 @@ def test_flash_forward_backward_vs_oracle(bmb, orc, cuda, B, T, C, NH):
     for cfg in range(lib.bmb_flash_num_bwd_configs()):
         dqkv = cuda.full((B * T * 3 * C,), float("nan"), device="cuda")
         dsum = cuda.full((B * NH * T,), float("nan"), device="cuda")
-        bmb.call("bmb_flash_attention_backward_cfg", cfg, dqkv, dsum, dd, dq, out, lse, B, T, C, NH)
+        tensor_core = lib.bmb_flash_bwd_config_name(cfg).startswith(b"tcgen05")
+        st = lib.bmb_flash_attention_backward_cfg(cfg, dqkv.data_ptr(), dsum.data_ptr(), dd.data_ptr(), dq.data_ptr(),
+                                                  out.data_ptr(), lse.data_ptr(), B, T, C, NH)
+        if st == bmb.E_UNSUPPORTED and tensor_core and C // NH != 64:
+            continue
+        bmb.check(st, "bmb_flash_attention_backward_cfg")
         g, w = host(cuda, dqkv).reshape(B * T, 3, C), wd.reshape(B * T, 3, C)
         for i in range(3):
-            assert normwise(g[:, i], w[:, i]) < 1e-5, (cfg, i)
+            # dq, dk, dv separately (tools/test_flash.cu:312-314); the denominator is floored at 5 % of the
+            # whole gradient's magnitude (25 % for TF32, whose residue in dP - D scales with dO and v) because at T = 1
+            # dq and dk are exactly zero.  fp32: 1e-5, TF32: 5e-3.
+            den = max(float(np.max(np.abs(w[:, i]))), (0.25 if tensor_core else 0.05) * float(np.max(np.abs(w))))
+            err = float(np.max(np.abs(g[:, i].astype(np.float64) - w[:, i]))) / den
+            assert np.all(np.isfinite(g)) and err < (5e-3 if tensor_core else 1e-5), (cfg, i, err)
 
 
 def test_flash_vs_reference_fused_and_unfused(bmb, ref, orc, cuda):
