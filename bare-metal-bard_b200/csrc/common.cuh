@@ -38,6 +38,13 @@ int fail(int code, const char *fmt, ...);
 // ---- per-thread stream ----------------------------------------------------
 cudaStream_t cur_stream();
 
+// Per-thread switch read by the kernels that produce GEMM / attention operands
+// (layernorm, GELU, bias add, cross-entropy backward, attention): when on, they
+// store TF32-rounded values so that the tensor-core kernels can read them in
+// place.  The training step turns it on in TF32 mode; the C ABI leaves it off.
+bool emit_rounded();
+void set_emit_rounded(bool on);
+
 // ---- per-device scratch ---------------------------------------------------
 // The reference keeps process-wide static device scratch (src/nn.cu:347, 362)
 // that every rank thread shares regardless of device.  Here each device owns
@@ -59,6 +66,10 @@ inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 int gemm_any(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
              const float *A, long long sA, const float *B, long long sB, float beta, float *C,
              long long sC, cudaStream_t st);
+// Same with a bias row added to every output row (null = none).
+int gemm_any_bias(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
+                  const float *A, long long sA, const float *B, long long sB, float beta, float *C,
+                  long long sC, const float *bias, cudaStream_t st);
 
 }  // namespace bmb
 

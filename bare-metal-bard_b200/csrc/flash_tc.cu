@@ -55,7 +55,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant__ CUtensorMap mapV,
                float *__restrict__ out, float *__restrict__ lse, int T, int NH, float scale_log2e,
-               int *__restrict__ status) {
+               int round_out, int *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -286,7 +286,11 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     float *dst = out + ((size_t)b * T + qi) * C + h * HS;
 #pragma unroll
                     for (int d = 0; d < HS; d += 4)
-                        *reinterpret_cast<float4 *>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+                    {
+                        float4 w = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+                        if (round_out) w = make_float4(round_tf32(w.x), round_tf32(w.y), round_tf32(w.z), round_tf32(w.w));
+                        *reinterpret_cast<float4 *>(dst + d) = w;
+                    }
                     lse[(size_t)bh * T + qi] = (m + log2f(l)) * 0.6931471805599453f;
                 }
             }
@@ -358,7 +362,8 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
     }
     const float scale_log2e = (1.0f / sqrtf((float)HS)) * 1.4426950408889634f;
     dim3 grid((T + NQ * QT - 1) / (NQ * QT), B * NH);
-    flash_fwd_tc_k<<<grid, FWD_THREADS, FWD_SMEM, st>>>(mapQK, mapV, out, lse, T, NH, scale_log2e, status_dev);
+    flash_fwd_tc_k<<<grid, FWD_THREADS, FWD_SMEM, st>>>(mapQK, mapV, out, lse, T, NH, scale_log2e,
+                                                        emit_rounded() ? 1 : 0, status_dev);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;

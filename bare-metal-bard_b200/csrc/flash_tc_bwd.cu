@@ -35,6 +35,10 @@ using namespace tc;
 constexpr int HS = 64;
 constexpr float LOG2E = 1.4426950408889634f;
 
+__device__ __forceinline__ float4 out4(float a, float b, float c, float d, int rnd) {
+    return rnd ? make_float4(round_tf32(a), round_tf32(b), round_tf32(c), round_tf32(d)) : make_float4(a, b, c, d);
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -56,7 +60,7 @@ __global__ void __launch_bounds__(dq::THREADS, 1)
 flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_constant__ CUtensorMap mapQKV_n,
                   const __grid_constant__ CUtensorMap mapDO_k, float *__restrict__ dqkv,
                   const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
-                  int *__restrict__ status) {
+                  int round_out, int *__restrict__ status) {
     using namespace dq;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -208,7 +212,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                 float *dst = dqkv + ((size_t)b * T + qi) * 3 * C + h * HS + colhalf * 32;
 #pragma unroll
                 for (int d = 0; d < 32; d += 4)
-                    *reinterpret_cast<float4 *>(dst + d) = make_float4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale);
+                    *reinterpret_cast<float4 *>(dst + d) = out4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale, round_out);
             }
         }
     }
@@ -243,7 +247,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                    const __grid_constant__ CUtensorMap mapQKV_n32, const __grid_constant__ CUtensorMap mapDO_k32,
                    const __grid_constant__ CUtensorMap mapDO_n32, float *__restrict__ dqkv,
                    const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
-                   int *__restrict__ status) {
+                   int round_out, int *__restrict__ status) {
     using namespace dkv;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -412,14 +416,14 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                 float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + 2 * C + h * HS + colhalf * 32;
 #pragma unroll
                 for (int d = 0; d < 32; d += 4)
-                    *reinterpret_cast<float4 *>(dst + d) = make_float4(v[d], v[d + 1], v[d + 2], v[d + 3]);
+                    *reinterpret_cast<float4 *>(dst + d) = out4(v[d], v[d + 1], v[d + 2], v[d + 3], round_out);
             }
             tmem_ld32(lane_addr + (uint32_t)(192 + colhalf * 32), v);
             if (kj < T) {
                 float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + C + h * HS + colhalf * 32;
 #pragma unroll
                 for (int d = 0; d < 32; d += 4)
-                    *reinterpret_cast<float4 *>(dst + d) = make_float4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale);
+                    *reinterpret_cast<float4 *>(dst + d) = out4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale, round_out);
             }
         }
     }
@@ -494,8 +498,8 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
     }
     const float scale = 1.0f / sqrtf((float)HS);
     dim3 gkv((T + dkv::KT - 1) / dkv::KT, B * NH), gq((T + dq::QT - 1) / dq::QT, B * NH);
-    flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qk32, qn32, gk32, gn32, dqkv, lse, dsum, T, NH, scale, status_dev);
-    flash_bwd_dq_tc_k<<<gq, dq::THREADS, dq::SMEM, st>>>(qk64, qn64, gk64, dqkv, lse, dsum, T, NH, scale, status_dev);
+    flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qk32, qn32, gk32, gn32, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
+    flash_bwd_dq_tc_k<<<gq, dq::THREADS, dq::SMEM, st>>>(qk64, qn64, gk64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     count_launch(2);
     BMB_LAUNCH_CHECK();
     return BMB_OK;

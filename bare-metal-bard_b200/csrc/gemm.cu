@@ -11,18 +11,34 @@ int gemm_simt(int transA, int transB, int batch, int M, int N, int K, float alph
 // not take; the caller then falls back to the SIMT kernel (still on the GPU).
 int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N, int K,
             float alpha, const float *A, long long sA, const float *B, long long sB, float beta,
-            float *C, long long sC, cudaStream_t st);
+            float *C, long long sC, const float *bias, cudaStream_t st);
 bool gemm_tc_accepts(int math, int transA, int transB, int batch, int M, int N, int K,
                      const float *A, long long sA, const float *B, long long sB, const float *C,
                      long long sC);
 
-int gemm_any(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
-                    const float *A, long long sA, const float *B, long long sB, float beta,
-                    float *C, long long sC, cudaStream_t st) {
+// C = alpha*op(A)op(B) + bias (broadcast over rows, may be null) + beta*C.
+int gemm_any_bias(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
+                  const float *A, long long sA, const float *B, long long sB, float beta, float *C,
+                  long long sC, const float *bias, cudaStream_t st) {
     if (math != BMB_MATH_FP32 && M > 0 && N > 0 && K > 0 && batch > 0 &&
         gemm_tc_accepts(math, ta, tb, batch, M, N, K, A, sA, B, sB, C, sC))
-        return gemm_tc(math, flags, ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st);
-    return gemm_simt(ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st);
+        return gemm_tc(math, flags, ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, bias, st);
+    BMB_TRY(gemm_simt(ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st));
+    // SIMT route: the bias and the optional rounding are separate passes on the same stream.
+    void *prev = bmb_get_stream();
+    bmb_set_stream((void *)st);
+    int rc = BMB_OK;
+    if (bias && batch == 1) rc = bmb_bias_forward(C, bias, M, N);
+    if (rc == BMB_OK && (flags & BMB_GEMM_C_ROUNDED) && batch == 1)
+        rc = bmb_round_tf32(C, C, (size_t)M * N, (void *)st);
+    bmb_set_stream(prev);
+    return rc;
+}
+
+int gemm_any(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
+             const float *A, long long sA, const float *B, long long sB, float beta, float *C,
+             long long sC, cudaStream_t st) {
+    return gemm_any_bias(math, flags, ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, nullptr, st);
 }
 }  // namespace bmb
 

@@ -74,7 +74,7 @@ template <int KIND>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, int M, int N,
           int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
-          int vec_ok, int *__restrict__ status) {
+          int vec_ok, int nsplit, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -92,6 +92,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     sch.tiles_m = (M + BM - 1) / BM;
     sch.tiles_n = (N + BN - 1) / BN;
     sch.num_tiles = sch.tiles_m * sch.tiles_n;
+    // Split-K: a work unit is (tile, split); split s covers K slices [s*kbs, min(kblocks, (s+1)*kbs)).
+    const int num_units = sch.num_tiles * nsplit;
+    const int kbs = (kblocks + nsplit - 1) / nsplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); armed[s] = -1; }
@@ -111,10 +114,11 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < sch.num_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
                 int tm, tn;
-                sch.coords(tile, tm, tn);
-                for (int kb = 0; kb < kblocks; ++kb) {
+                sch.coords(unit / nsplit, tm, tn);
+                const int kb0 = (unit % nsplit) * kbs, kb1 = min(kblocks, kb0 + kbs);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * s;
                     mbar_arrive_expect_tx(fb, STAGE_BYTES);
@@ -151,11 +155,12 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0, acc = 0;
             uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < sch.num_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
                 if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
                 fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int kb0 = (unit % nsplit) * kbs, kb1 = min(kblocks, kb0 + kbs);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
                     fence_after();
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
@@ -163,8 +168,8 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     for (int k = 0; k < KBYTES / 32; ++k) {
                         const uint64_t da = a_mn ? smem_desc_mnmajor32(sa + k * a_step, CHUNK_BYTES) : smem_desc_kmajor(sa + k * a_step);
                         const uint64_t db = b_mn ? smem_desc_mnmajor32(sb + k * b_step, CHUNK_BYTES) : smem_desc_kmajor(sb + k * b_step);
-                        if (KIND == 0) mma_tf32(d, da, db, idesc, (kb | k) ? 1u : 0u);
-                        else mma_f16(d, da, db, idesc, (kb | k) ? 1u : 0u);
+                        if (KIND == 0) mma_tf32(d, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
+                        else mma_f16(d, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
                     }
                     commit(empty0 + 8 * s);             // slice reusable once these MMAs retire
                     if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -180,9 +185,10 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < sch.num_tiles; tile += gridDim.x) {
+        for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
             int tm, tn;
-            sch.coords(tile, tm, tn);
+            sch.coords(unit / nsplit, tm, tn);
+            const bool first_split = (unit % nsplit) == 0;
             if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
             fence_after();
             const int m = tm * BM + q * 32 + lane;
@@ -193,16 +199,39 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 float v[32];
                 tmem_ld32(trow + (uint32_t)(c * 32), v);
                 const int n0 = tn * BN + c * 32;
-                if (m < M && n0 < N) {
+                if (m < M && n0 < N && nsplit > 1) {
+                    // Split-K: partial products are added into C (the host has already applied beta);
+                    // the split that owns K slice 0 also adds the bias.
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        if (vec_ok && n0 + j + 4 <= N) {
+                            float4 o = make_float4(alpha * v[j], alpha * v[j + 1], alpha * v[j + 2], alpha * v[j + 3]);
+                            if (bias && first_split) {
+                                const float4 bb = *reinterpret_cast<const float4 *>(bias + n0 + j);
+                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                            }
+                            atomicAdd(reinterpret_cast<float4 *>(crow + n0 + j), o);
+                        } else {
+                            for (int e = 0; e < 4; ++e)
+                                if (n0 + j + e < N)
+                                    atomicAdd(crow + n0 + j + e, alpha * v[j + e] + ((bias && first_split) ? bias[n0 + j + e] : 0.0f));
+                        }
+                    }
+                } else if (m < M && n0 < N) {
                     if (vec_ok && n0 + 32 <= N) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
                             float4 o = make_float4(alpha * v[j], alpha * v[j + 1], alpha * v[j + 2], alpha * v[j + 3]);
+                            if (bias) {
+                                const float4 bb = *reinterpret_cast<const float4 *>(bias + n0 + j);
+                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                            }
                             if (beta != 0.0f) {
                                 const float4 cc = *reinterpret_cast<const float4 *>(crow + n0 + j);
                                 o.x = fmaf(beta, cc.x, o.x); o.y = fmaf(beta, cc.y, o.y);
                                 o.z = fmaf(beta, cc.z, o.z); o.w = fmaf(beta, cc.w, o.w);
                             }
+                            if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
                             *reinterpret_cast<float4 *>(crow + n0 + j) = o;
                         }
                     } else {
@@ -210,8 +239,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                         for (int j = 0; j < 32; ++j) {
                             if (n0 + j < N) {
                                 float o = alpha * v[j];
+                                if (bias) o += bias[n0 + j];
                                 if (beta != 0.0f) o = fmaf(beta, crow[n0 + j], o);
-                                crow[n0 + j] = o;
+                                crow[n0 + j] = round_c ? round_tf32(o) : o;
                             }
                         }
                     }
@@ -350,9 +380,34 @@ bool gemm_tc_accepts(int math, int, int, int batch, int M, int N, int K, const f
     return true;
 }
 
+namespace {
+__global__ void scale_c_k(float *C, long long n, float beta) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        C[i] *= beta;
+}
+
+// Number of K splits for a problem with `tiles` output tiles and `kblocks` K slices on `sms` SMs: the
+// split count that minimises (waves of work units) x (slices per unit + a fixed per-unit cost).
+int choose_split(int tiles, int kblocks, int sms) {
+    if (tiles * 4 >= sms * 3 || kblocks < 16) return 1;
+    int best = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= 16 && s * 8 <= kblocks; ++s) {
+        const int kbs = (kblocks + s - 1) / s;
+        if ((s - 1) * kbs >= kblocks) continue;            // an empty split
+        const long long waves = (tiles * s + sms - 1) / sms;
+        const long long cost = waves * (kbs + 6);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+}  // namespace
+
 int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N, int K, float alpha,
             const float *A, long long, const float *B, long long, float beta, float *C, long long,
-            cudaStream_t st) {
+            const float *bias, cudaStream_t st) {
     (void)batch;
     int *status_dev = nullptr;
     volatile int *status_host = nullptr;
@@ -370,8 +425,21 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     const int kper = KBYTES / esize;
     const int kblocks = (K + kper - 1) / kper;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = tiles < sm_count() ? tiles : sm_count();
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
+    // Split-K when the tiles cannot fill the GPU (the dW products of a training step: few tiles, long K).
+    // The partial products are added atomically, so the summation order -- not the result beyond fp32
+    // rounding -- varies from run to run; BMB_GEMM_NO_SPLIT keeps one CTA per tile.
+    int nsplit = (flags & BMB_GEMM_NO_SPLIT) ? 1 : choose_split(tiles, kblocks, sm_count());
+    if (nsplit > 1) {
+        if (beta == 0.0f) BMB_CUDA(cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), st));
+        else if (beta != 1.0f) {
+            scale_c_k<<<blocks_for((long long)M * N), 256, 0, st>>>(C, (long long)M * N, beta);
+            count_launch();
+        }
+    }
+    const int units = tiles * nsplit;
+    const int grid = units < sm_count() ? units : sm_count();
+    const int round_c = (flags & BMB_GEMM_C_ROUNDED) && nsplit == 1 ? 1 : 0;
     const int kind = bf16 ? 1 : 0;
     {
         std::lock_guard<std::mutex> lk(g_attr_mu);
@@ -383,10 +451,16 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
         }
     }
     if (bf16)
-        gemm_tc_k<1><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, 0, 0, alpha, beta, C, vec_ok, status_dev);
+        gemm_tc_k<1><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, 0, 0, alpha, beta, C, vec_ok, nsplit, bias,
+                                                        round_c, status_dev);
     else
         gemm_tc_k<0><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, a.mn_major ? 1 : 0,
-                                                        b.mn_major ? 1 : 0, alpha, beta, C, vec_ok, status_dev);
+                                                        b.mn_major ? 1 : 0, alpha, beta, C, vec_ok, nsplit, bias, round_c, status_dev);
+    if (nsplit > 1 && (flags & BMB_GEMM_C_ROUNDED)) {
+        count_launch();
+        BMB_LAUNCH_CHECK();
+        return bmb_round_tf32(C, C, (size_t)M * N, (void *)st);
+    }
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;

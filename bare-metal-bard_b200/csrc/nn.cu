@@ -14,6 +14,13 @@ namespace {
 #define LD4(p) (*reinterpret_cast<const float4 *>(p))
 #define ST4(p) (*reinterpret_cast<float4 *>(p))
 
+// Values headed for a tensor-core GEMM or attention kernel are stored already
+// rounded to TF32 when the caller (the training step in TF32 mode) asks for it.
+__device__ __forceinline__ float rnd1(float v, int rnd) { return rnd ? round_tf32(v) : v; }
+__device__ __forceinline__ float4 rnd4(float4 v, int rnd) {
+    return rnd ? make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w)) : v;
+}
+
 inline int grid_for(long long work_items, int threads, int per_sm) {
     long long b = (work_items + threads - 1) / threads;
     long long cap = (long long)sm_count() * per_sm;
@@ -78,7 +85,7 @@ template <int V4>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_warp_k(float *__restrict__ out, float *__restrict__ mean, float *__restrict__ rstd,
                      const float *__restrict__ inp, const float *__restrict__ weight,
-                     const float *__restrict__ bias, int N, int C) {
+                     const float *__restrict__ bias, int N, int C, int rnd) {
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int C4 = C >> 2;
@@ -116,7 +123,7 @@ layernorm_fwd_warp_k(float *__restrict__ out, float *__restrict__ mean, float *_
                 o.y = ((v[i].y - mu) * rs) * w.y + b.y;
                 o.z = ((v[i].z - mu) * rs) * w.z + b.z;
                 o.w = ((v[i].w - mu) * rs) * w.w + b.w;
-                ST4(y + c4 * 4) = o;
+                ST4(y + c4 * 4) = rnd4(o, rnd);
             }
         }
     }
@@ -126,7 +133,7 @@ layernorm_fwd_warp_k(float *__restrict__ out, float *__restrict__ mean, float *_
 __global__ void layernorm_fwd_block_k(float *__restrict__ out, float *__restrict__ mean,
                                       float *__restrict__ rstd, const float *__restrict__ inp,
                                       const float *__restrict__ weight,
-                                      const float *__restrict__ bias, int C) {
+                                      const float *__restrict__ bias, int C, int rnd) {
     __shared__ float red[32];
     const int row = blockIdx.x;
     const float *x = inp + (size_t)row * C;
@@ -139,7 +146,7 @@ __global__ void layernorm_fwd_block_k(float *__restrict__ out, float *__restrict
     const float rs = rsqrtf(var + 1e-5f);
     if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
     float *y = out + (size_t)row * C;
-    for (int i = threadIdx.x; i < C; i += blockDim.x) y[i] = ((x[i] - mu) * rs) * weight[i] + bias[i];
+    for (int i = threadIdx.x; i < C; i += blockDim.x) y[i] = rnd1(((x[i] - mu) * rs) * weight[i] + bias[i], rnd);
 }
 
 // Backward (src/nn.cu:85-113):
@@ -155,7 +162,7 @@ __global__ void __launch_bounds__(256)
 layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
                      const float *__restrict__ dout, const float *__restrict__ inp,
                      const float *__restrict__ weight, const float *__restrict__ mean,
-                     const float *__restrict__ rstd, int N, int C) {
+                     const float *__restrict__ rstd, int N, int C, int rnd) {
     extern __shared__ float fold[];  // 2*C floats
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
@@ -201,7 +208,7 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
                 d.y += rs * (g[i].y * w[i].y - m1 - xh[i].y * m2);
                 d.z += rs * (g[i].z * w[i].z - m1 - xh[i].z * m2);
                 d.w += rs * (g[i].w * w[i].w - m1 - xh[i].w * m2);
-                ST4(dx + c4 * 4) = d;
+                ST4(dx + c4 * 4) = rnd4(d, rnd);
             }
         }
     }
@@ -234,7 +241,7 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
 __global__ void layernorm_bwd_block_k(float *__restrict__ dinp, float *__restrict__ partial, int parts,
                                       const float *__restrict__ dout, const float *__restrict__ inp,
                                       const float *__restrict__ weight, const float *__restrict__ mean,
-                                      const float *__restrict__ rstd, int C) {
+                                      const float *__restrict__ rstd, int C, int rnd) {
     __shared__ float red[32];
     const int row = blockIdx.x;
     const float *x = inp + (size_t)row * C, *dy = dout + (size_t)row * C;
@@ -250,22 +257,34 @@ __global__ void layernorm_bwd_block_k(float *__restrict__ dinp, float *__restric
     float *p = partial + (size_t)(row % parts) * 2 * C;
     for (int i = threadIdx.x; i < C; i += blockDim.x) {
         const float xh = (x[i] - mu) * rs, d = dy[i] * weight[i];
-        dx[i] += rs * (d - m1 - xh * m2);
+        dx[i] = rnd1(dx[i] + rs * (d - m1 - xh * m2), rnd);
         atomicAdd(&p[i], dy[i] * xh);
         atomicAdd(&p[C + i], dy[i]);
     }
 }
 
-// dst[c] += sum_{g < G} partial[g][c]   for c < ncols, fixed summation order.
-// If dst2 != nullptr the columns [ncols_first, ncols) go to dst2.
-__global__ void column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
-                             const float *__restrict__ partial, int G, int ncols) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= ncols) return;
+// dst[c] += sum_{g < G} partial[g][c]   for c < ncols, in a fixed order: a block
+// covers 32 columns, its 8 warps each sum every 8th row of `partial`, and the 8
+// sub-sums are added in warp order.  If dst2 != nullptr the columns
+// [ncols_first, ncols) go to dst2.
+__global__ void __launch_bounds__(256)
+column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
+             const float *__restrict__ partial, int G, int ncols) {
+    __shared__ float red[8][33];
+    const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
     float s = 0.0f;
-    for (int g = 0; g < G; ++g) s += partial[(size_t)g * ncols + c];
-    if (dst2 && c >= ncols_first) dst2[c - ncols_first] += s;
-    else dst[c] += s;
+    if (c < ncols)
+        for (int g = gy; g < G; g += 8) s += partial[(size_t)g * ncols + c];
+    red[gy][cx] = s;
+    __syncthreads();
+    if (gy == 0 && c < ncols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i][cx];
+        if (dst2 && c >= ncols_first) dst2[c - ncols_first] += t;
+        else dst[c] += t;
+    }
 }
 
 // --------------------------------------------------------------------- gelu
@@ -283,22 +302,22 @@ __device__ __forceinline__ float dgelu1(float x, float g) {
     return g * (0.5f * (1.0f + t) + 0.5f * x * sech2 * dinner);
 }
 
-__global__ void gelu_fwd_k(float *__restrict__ out, const float *__restrict__ inp, long long n4) {
+__global__ void gelu_fwd_k(float *__restrict__ out, const float *__restrict__ inp, long long n4, int rnd) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
          i += (long long)gridDim.x * blockDim.x) {
         float4 v = LD4(inp + i * 4);
         v.x = gelu1(v.x); v.y = gelu1(v.y); v.z = gelu1(v.z); v.w = gelu1(v.w);
-        ST4(out + i * 4) = v;
+        ST4(out + i * 4) = rnd4(v, rnd);
     }
 }
 __global__ void gelu_bwd_k(float *__restrict__ dinp, const float *__restrict__ inp,
-                           const float *__restrict__ dout, long long n4) {
+                           const float *__restrict__ dout, long long n4, int rnd) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
          i += (long long)gridDim.x * blockDim.x) {
         const float4 x = LD4(inp + i * 4), g = LD4(dout + i * 4);
         float4 d;
         d.x = dgelu1(x.x, g.x); d.y = dgelu1(x.y, g.y); d.z = dgelu1(x.z, g.z); d.w = dgelu1(x.w, g.w);
-        ST4(dinp + i * 4) = d;
+        ST4(dinp + i * 4) = rnd4(d, rnd);
     }
 }
 
@@ -312,7 +331,7 @@ __global__ void add3_k(float *__restrict__ out, const float *__restrict__ a,
     }
 }
 __global__ void bias_fwd_k(float *__restrict__ out, const float *__restrict__ bias, int C,
-                           long long n4) {
+                           long long n4, int rnd) {
     const int C4 = C >> 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
          i += (long long)gridDim.x * blockDim.x) {
@@ -320,7 +339,7 @@ __global__ void bias_fwd_k(float *__restrict__ out, const float *__restrict__ bi
         float4 v = LD4(out + i * 4);
         const float4 b = LD4(bias + c);
         v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-        ST4(out + i * 4) = v;
+        ST4(out + i * 4) = rnd4(v, rnd);
     }
 }
 // Column sums of dout (N x C): blockIdx.x picks a strip of 256 float4 columns,
@@ -418,7 +437,7 @@ softmax_xent_fwd_k(float *__restrict__ probs, float *__restrict__ losses,
 // dlogits = (p - onehot) * scale on real columns, 0 on padding (src/nn.cu:226-237).
 __global__ void xent_bwd_k(float *__restrict__ dlogits, const float *__restrict__ probs,
                            const int *__restrict__ targets, int V, int Vp, float scale,
-                           long long n4) {
+                           long long n4, int rnd) {
     const int Vp4 = Vp >> 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
          i += (long long)gridDim.x * blockDim.x) {
@@ -431,17 +450,17 @@ __global__ void xent_bwd_k(float *__restrict__ dlogits, const float *__restrict_
         d.y = (c + 1 < V) ? (p.y - (c + 1 == t ? 1.0f : 0.0f)) * scale : 0.0f;
         d.z = (c + 2 < V) ? (p.z - (c + 2 == t ? 1.0f : 0.0f)) * scale : 0.0f;
         d.w = (c + 3 < V) ? (p.w - (c + 3 == t ? 1.0f : 0.0f)) * scale : 0.0f;
-        ST4(dlogits + i * 4) = d;
+        ST4(dlogits + i * 4) = rnd4(d, rnd);
     }
 }
 __global__ void xent_bwd_scalar_k(float *__restrict__ dlogits, const float *__restrict__ probs,
-                                  const int *__restrict__ targets, int V, int Vp, float scale) {
+                                  const int *__restrict__ targets, int V, int Vp, float scale, int rnd) {
     const int row = blockIdx.x;
     const float *p = probs + (size_t)row * Vp;
     float *d = dlogits + (size_t)row * Vp;
     const int t = targets[row];
     for (int i = threadIdx.x; i < Vp; i += blockDim.x)
-        d[i] = (i < V) ? (p[i] - (i == t ? 1.0f : 0.0f)) * scale : 0.0f;
+        d[i] = rnd1((i < V) ? (p[i] - (i == t ? 1.0f : 0.0f)) * scale : 0.0f, rnd);
 }
 
 // ---------------------------------------------------------------- optimizer
@@ -551,7 +570,7 @@ bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 // Shared with other translation units of the library.
 int launch_column_add(float *dst, float *dst2, int ncols_first, const float *partial, int G,
                       int ncols, cudaStream_t st) {
-    column_add_k<<<ceil_div(ncols, 256), 256, 0, st>>>(dst, dst2, ncols_first, partial, G, ncols);
+    column_add_k<<<ceil_div(ncols, 32), 256, 0, st>>>(dst, dst2, ncols_first, partial, G, ncols);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -568,8 +587,13 @@ int layernorm_backward_with_scratch(float *dinp, float *dweight, float *dbias, c
                                     const float *inp, const float *weight, const float *mean,
                                     const float *rstd, int N, int C, float *partial, int G,
                                     cudaStream_t st) {
-    layernorm_bwd_warp_k<8><<<G, 256, 2 * C * sizeof(float), st>>>(dinp, partial, dout, inp, weight,
-                                                                   mean, rstd, N, C);
+    const int rnd = emit_rounded() ? 1 : 0;
+    const size_t sm = 2 * C * sizeof(float);
+    // registers follow the row length: V4 float4 per lane cover C <= 128 * V4
+    if (C <= 256) layernorm_bwd_warp_k<2><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    else if (C <= 512) layernorm_bwd_warp_k<4><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    else if (C <= 768) layernorm_bwd_warp_k<6><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    else layernorm_bwd_warp_k<8><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
     count_launch();
     BMB_LAUNCH_CHECK();
     return launch_column_add(dweight, dbias, C, partial, G, 2 * C, st);
@@ -615,9 +639,13 @@ int bmb_layernorm_forward(float *out, float *mean, float *rstd, const float *inp
         int g = ceil_div(N, 8);
         const int cap = sm_count() * 8;
         if (g > cap) g = cap;
-        layernorm_fwd_warp_k<8><<<g, 256, 0, st>>>(out, mean, rstd, inp, weight, bias, N, C);
+        const int rnd = emit_rounded() ? 1 : 0;
+        if (C <= 256) layernorm_fwd_warp_k<2><<<g, 256, 0, st>>>(out, mean, rstd, inp, weight, bias, N, C, rnd);
+        else if (C <= 512) layernorm_fwd_warp_k<4><<<g, 256, 0, st>>>(out, mean, rstd, inp, weight, bias, N, C, rnd);
+        else if (C <= 768) layernorm_fwd_warp_k<6><<<g, 256, 0, st>>>(out, mean, rstd, inp, weight, bias, N, C, rnd);
+        else layernorm_fwd_warp_k<8><<<g, 256, 0, st>>>(out, mean, rstd, inp, weight, bias, N, C, rnd);
     } else {
-        layernorm_fwd_block_k<<<N, 128, 0, st>>>(out, mean, rstd, inp, weight, bias, C);
+        layernorm_fwd_block_k<<<N, 128, 0, st>>>(out, mean, rstd, inp, weight, bias, C, emit_rounded() ? 1 : 0);
     }
     count_launch();
     BMB_LAUNCH_CHECK();
@@ -642,7 +670,7 @@ int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias, const floa
     float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)parts * 2 * C * sizeof(float));
     if (!partial) return BMB_E_CUDA;
     BMB_CUDA(cudaMemsetAsync(partial, 0, (size_t)parts * 2 * C * sizeof(float), st));
-    layernorm_bwd_block_k<<<N, 128, 0, st>>>(dinp, partial, parts, dout, inp, weight, mean, rstd, C);
+    layernorm_bwd_block_k<<<N, 128, 0, st>>>(dinp, partial, parts, dout, inp, weight, mean, rstd, C, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return launch_column_add(dweight, dbias, C, partial, parts, 2 * C, st);
@@ -651,7 +679,7 @@ int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias, const floa
 int bmb_gelu_forward(float *out, const float *inp, int n) {
     if (n % 4) return fail(BMB_E_ARG, "gelu_forward: n=%d must be a multiple of 4", n);
     if (n == 0) return BMB_OK;
-    gelu_fwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(out, inp, n / 4);
+    gelu_fwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(out, inp, n / 4, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -659,7 +687,7 @@ int bmb_gelu_forward(float *out, const float *inp, int n) {
 int bmb_gelu_backward(float *dinp, const float *inp, const float *dout, int n) {
     if (n % 4) return fail(BMB_E_ARG, "gelu_backward: n=%d must be a multiple of 4", n);
     if (n == 0) return BMB_OK;
-    gelu_bwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(dinp, inp, dout, n / 4);
+    gelu_bwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(dinp, inp, dout, n / 4, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -679,7 +707,7 @@ int bmb_bias_forward(float *out, const float *bias, int N, int C) {
     if (C % 4) return fail(BMB_E_ARG, "bias_forward: C=%d must be a multiple of 4", C);
     const long long n4 = (long long)N * C / 4;
     if (n4 == 0) return BMB_OK;
-    bias_fwd_k<<<grid_for(n4, 256, 8), 256, 0, cur_stream()>>>(out, bias, C, n4);
+    bias_fwd_k<<<grid_for(n4, 256, 8), 256, 0, cur_stream()>>>(out, bias, C, n4, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -720,9 +748,9 @@ int bmb_crossentropy_softmax_backward(float *dlogits, const float *probs, const 
     cudaStream_t st = cur_stream();
     if (Vp % 4 == 0 && aligned16(dlogits) && aligned16(probs)) {
         const long long n4 = (long long)N * Vp / 4;
-        xent_bwd_k<<<grid_for(n4, 256, 8), 256, 0, st>>>(dlogits, probs, targets, V, Vp, dloss_scale, n4);
+        xent_bwd_k<<<grid_for(n4, 256, 8), 256, 0, st>>>(dlogits, probs, targets, V, Vp, dloss_scale, n4, emit_rounded() ? 1 : 0);
     } else {
-        xent_bwd_scalar_k<<<N, 128, 0, st>>>(dlogits, probs, targets, V, Vp, dloss_scale);
+        xent_bwd_scalar_k<<<N, 128, 0, st>>>(dlogits, probs, targets, V, Vp, dloss_scale, emit_rounded() ? 1 : 0);
     }
     count_launch();
     BMB_LAUNCH_CHECK();

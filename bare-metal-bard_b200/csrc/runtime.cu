@@ -24,6 +24,10 @@ int fail(int code, const char *fmt, ...) {
 
 cudaStream_t cur_stream() { return g_stream; }
 
+static thread_local bool g_emit_rounded = false;
+bool emit_rounded() { return g_emit_rounded; }
+void set_emit_rounded(bool on) { g_emit_rounded = on; }
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long launches_total() { return g_launches.load(std::memory_order_relaxed); }
 

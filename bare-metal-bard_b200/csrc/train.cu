@@ -14,6 +14,11 @@
 
 namespace bmb {
 int layernorm_bwd_blocks(int N);
+bool flash_tc_supported(int T, int C, int NH, const float *qkv, const float *out);
+int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, bool qkv_rounded,
+                     cudaStream_t st);
+int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
+                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st);
 }
 using namespace bmb;
 
@@ -67,8 +72,13 @@ struct Scope {
         prev_stream = bmb_get_stream();
         bmb_set_stream(t->st);
     }
-    ~Scope() { bmb_set_stream(prev_stream); cudaSetDevice(prev_dev); }
+    ~Scope() { set_emit_rounded(false); bmb_set_stream(prev_stream); cudaSetDevice(prev_dev); }
 };
+
+// "Fused" TF32 mode: every kernel that produces a GEMM or attention operand
+// stores it already rounded to TF32 (so the tensor-core kernels read activations
+// and gradients where they lie), and the bias add rides in the GEMM epilogue.
+bool fused_tf32(const bmb_train_config &c) { return c.fused && c.math == BMB_MATH_TF32; }
 
 // Attention kernel configuration for this trainer's arithmetic: the SIMT fp32
 // kernels, or the tensor-core pair (config 2 of both tables) when the GEMMs
@@ -89,7 +99,7 @@ int collect_profile(bmb_trainer *t) {
 
 // One matmul of the model, optionally bracketed by events.
 int mm(bmb_trainer *t, int flags, int ta, int tb, int M, int N, int K, const float *A, const float *B,
-       float beta, float *C) {
+       float beta, float *C, const float *bias = nullptr) {
     if (t->prof) {
         if (t->ev_used + 2 > t->ev.size()) {
             for (int i = 0; i < 64; ++i) {
@@ -100,7 +110,7 @@ int mm(bmb_trainer *t, int flags, int ta, int tb, int M, int N, int K, const flo
         }
         BMB_CUDA(cudaEventRecord(t->ev[t->ev_used], t->st));
     }
-    BMB_TRY(gemm_any(t->c.math, flags, ta, tb, 1, M, N, K, 1.0f, A, 0, B, 0, beta, C, 0, t->st));
+    BMB_TRY(gemm_any_bias(t->c.math, flags, ta, tb, 1, M, N, K, 1.0f, A, 0, B, 0, beta, C, 0, bias, t->st));
     if (t->prof) {
         BMB_CUDA(cudaEventRecord(t->ev[t->ev_used + 1], t->st));
         t->ev_used += 2;
@@ -118,8 +128,11 @@ int forward(bmb_trainer *t) {
     const size_t qkvr_sz = 4 * BTC, att_sz = (size_t)B * NH * T * T, lse_sz = (size_t)B * NH * T;
     // Weights: the tensor-core modes read the pre-rounded shadow copy.
     const float *W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
-    const int wflag = (W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0;
+    const bool fz = fused_tf32(c);
+    // forward GEMMs: A = an activation (rounded by its producer when fused), B = a weight (rounded shadow)
+    const int wflag = ((W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0) | (fz ? BMB_GEMM_A_ROUNDED : 0);
     const float *P = t->params;
+    set_emit_rounded(fz);
 
     BMB_TRY(bmb_encoder_forward(t->encoded, t->d_tokens, P + t->poff[P_WTE], P + t->poff[P_WPE], B, T, C));
     float *residual = t->encoded;
@@ -130,22 +143,44 @@ int forward(bmb_trainer *t) {
         float *res3 = t->residual3 + l * BTC;
         BMB_TRY(bmb_layernorm_forward(ln1, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, residual,
                                       P + t->poff[P_LN1W] + (size_t)l * C, P + t->poff[P_LN1B] + (size_t)l * C, N, C));
-        BMB_TRY(mm(t, wflag, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv));
-        BMB_TRY(bmb_bias_forward(qkv, P + t->poff[P_QKVB] + (size_t)l * 3 * C, N, 3 * C));
-        if (c.use_flash)
+        if (fz) {
+            BMB_TRY(mm(t, wflag | BMB_GEMM_C_ROUNDED, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv,
+                       P + t->poff[P_QKVB] + (size_t)l * 3 * C));
+        } else {
+            BMB_TRY(mm(t, wflag, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv));
+            BMB_TRY(bmb_bias_forward(qkv, P + t->poff[P_QKVB] + (size_t)l * 3 * C, N, 3 * C));
+        }
+        if (c.use_flash && fz && attn_cfg(c) == 2)
+            BMB_TRY(flash_forward_tc(atty, t->lse + l * lse_sz, qkv, B, T, C, NH, true, t->st));
+        else if (c.use_flash)
             BMB_TRY(bmb_flash_attention_forward_cfg(attn_cfg(c), atty, t->lse + l * lse_sz, qkv, B, T, C, NH));
         else
             BMB_TRY(bmb_attention_forward(atty, t->qkvr + l * qkvr_sz, t->att + l * att_sz, qkv, B, T, C, NH));
-        BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
-        BMB_TRY(bmb_bias_forward(attproj, P + t->poff[P_APB] + (size_t)l * C, N, C));
+        if (fz) {
+            BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj,
+                       P + t->poff[P_APB] + (size_t)l * C));
+        } else {
+            BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
+            BMB_TRY(bmb_bias_forward(attproj, P + t->poff[P_APB] + (size_t)l * C, N, C));
+        }
         BMB_TRY(bmb_residual_forward(res2, residual, attproj, (int)BTC));
         BMB_TRY(bmb_layernorm_forward(ln2, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, res2,
                                       P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
-        BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch));
-        BMB_TRY(bmb_bias_forward(fch, P + t->poff[P_FCB] + (size_t)l * 4 * C, N, 4 * C));
+        if (fz) {
+            BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch,
+                       P + t->poff[P_FCB] + (size_t)l * 4 * C));
+        } else {
+            BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch));
+            BMB_TRY(bmb_bias_forward(fch, P + t->poff[P_FCB] + (size_t)l * 4 * C, N, 4 * C));
+        }
         BMB_TRY(bmb_gelu_forward(fchg, fch, (int)BT4C));
-        BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj));
-        BMB_TRY(bmb_bias_forward(fcproj, P + t->poff[P_FPB] + (size_t)l * C, N, C));
+        if (fz) {
+            BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj,
+                       P + t->poff[P_FPB] + (size_t)l * C));
+        } else {
+            BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj));
+            BMB_TRY(bmb_bias_forward(fcproj, P + t->poff[P_FPB] + (size_t)l * C, N, C));
+        }
         BMB_TRY(bmb_residual_forward(res3, res2, fcproj, (int)BTC));
         residual = res3;
     }
@@ -164,14 +199,19 @@ int backward(bmb_trainer *t) {
     const size_t BTC = (size_t)N * C, BT = N, BT3C = 3 * BTC, BT4C = 4 * BTC;
     const size_t qkvr_sz = 4 * BTC, att_sz = (size_t)B * NH * T * T, lse_sz = (size_t)B * NH * T;
     const float *W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
-    const int wflag = (W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0;
+    const bool fz = fused_tf32(c);
+    // dX GEMMs: A = a gradient (rounded by its producer when fused), B = a weight (rounded shadow);
+    // dW GEMMs: both operands are activations / gradients.
+    const int wflag = ((W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0) | (fz ? BMB_GEMM_A_ROUNDED : 0);
+    const int gflag = fz ? (BMB_GEMM_A_ROUNDED | BMB_GEMM_B_ROUNDED) : 0;
     const float *P = t->params;
     float *G = t->grads;
+    set_emit_rounded(fz);
 
     BMB_CUDA(cudaMemsetAsync(G, 0, t->num_params * sizeof(float), t->st));
     BMB_TRY(bmb_crossentropy_softmax_backward(t->dlogits, t->probs, t->d_targets, N, V, Vp, 1.0f / N));
     BMB_TRY(mm(t, wflag, 0, 0, N, C, Vp, t->dlogits, W + t->poff[P_WTE], 0.0f, t->dlnf));
-    BMB_TRY(mm(t, 0, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
+    BMB_TRY(mm(t, gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
     float *last_res = t->residual3 + (size_t)(L - 1) * BTC;
     BMB_CUDA(cudaMemsetAsync(t->dres, 0, BTC * sizeof(float), t->st));
     BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LNFW], G + t->poff[P_LNFB], t->dlnf, last_res,
@@ -184,24 +224,26 @@ int backward(bmb_trainer *t) {
         const size_t lC = (size_t)l * C;
 
         BMB_TRY(mm(t, wflag, 0, 0, N, 4 * C, C, t->dres, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, t->dfch_gelu));
-        BMB_TRY(mm(t, 0, 1, 0, C, 4 * C, N, t->dres, fchg, 1.0f, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
+        BMB_TRY(mm(t, gflag, 1, 0, C, 4 * C, N, t->dres, fchg, 1.0f, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_FPB] + lC, t->dres, N, C));
         BMB_TRY(bmb_gelu_backward(t->dfch, fch, t->dfch_gelu, (int)BT4C));
         BMB_TRY(mm(t, wflag, 0, 0, N, C, 4 * C, t->dfch, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, t->dln2));
-        BMB_TRY(mm(t, 0, 1, 0, 4 * C, C, N, t->dfch, ln2, 1.0f, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
+        BMB_TRY(mm(t, gflag, 1, 0, 4 * C, C, N, t->dfch, ln2, 1.0f, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_FCB] + 4 * lC, t->dfch, N, 4 * C));
         BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC, t->dln2, res2,
                                        P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
-        BMB_TRY(mm(t, wflag, 0, 0, N, C, C, t->dres, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, t->datty));
-        BMB_TRY(mm(t, 0, 1, 0, C, C, N, t->dres, atty, 1.0f, G + t->poff[P_APW] + (size_t)l * C * C));
+        BMB_TRY(mm(t, wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), 0, 0, N, C, C, t->dres, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, t->datty));
+        BMB_TRY(mm(t, gflag, 1, 0, C, C, N, t->dres, atty, 1.0f, G + t->poff[P_APW] + (size_t)l * C * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_APB] + lC, t->dres, N, C));
-        if (c.use_flash)
+        if (c.use_flash && fz && attn_cfg(c) == 2)
+            BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH, true, t->st));
+        else if (c.use_flash)
             BMB_TRY(bmb_flash_attention_backward_cfg(attn_cfg(c), t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH));
         else
             BMB_TRY(bmb_attention_backward(t->dqkv, t->dqkvr, t->datt, t->datt, t->datty, t->qkvr + l * qkvr_sz,
                                            t->att + l * att_sz, B, T, C, NH));
         BMB_TRY(mm(t, wflag, 0, 0, N, C, 3 * C, t->dqkv, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, t->dln1));
-        BMB_TRY(mm(t, 0, 1, 0, 3 * C, C, N, t->dqkv, ln1, 1.0f, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
+        BMB_TRY(mm(t, gflag, 1, 0, 3 * C, C, N, t->dqkv, ln1, 1.0f, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
         BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC, t->dln1, residual,
                                        P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C));

@@ -188,7 +188,7 @@ def run_bmb(args):
     math = {"fp32": bmb.MATH_FP32, "tf32": bmb.MATH_TF32, "bf16": bmb.MATH_BF16}[args.math]
     peaks = measured_peaks()
 
-    tr = bmb.Trainer(seed=1337, B=B_PER_GPU, T=T, use_flash=1, math=math, fused=0,
+    tr = bmb.Trainer(seed=1337, B=B_PER_GPU, T=T, use_flash=1, math=math, fused=0 if args.unfused else 1,
                      beta1=HP["beta1"], beta2=HP["beta2"], eps=HP["eps"], weight_decay=HP["weight_decay"],
                      grad_clip=HP["grad_clip"], **GPT124M)
     comm = None
@@ -385,6 +385,8 @@ def main():
     ap.add_argument("--impl", default="bmb", choices=["bmb", "reference"])
     ap.add_argument("--math", default=os.environ.get("BMB_BENCH_MATH", "tf32"), choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the square GEMM sweep")
+    ap.add_argument("--unfused", action="store_true", help="the reference's op list: separate bias kernels, "
+                    "operands rounded by a prepass instead of by their producers")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.warmup < 3:

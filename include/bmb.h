@@ -82,6 +82,8 @@ int bmb_gemm(int transA, int transB, int M, int N, int K, float alpha,
 /* Same, with the arithmetic stated per call (BMB_MATH_*) and flags. */
 #define BMB_GEMM_A_ROUNDED 1 /* A already holds TF32-representable values */
 #define BMB_GEMM_B_ROUNDED 2 /* B already holds TF32-representable values */
+#define BMB_GEMM_C_ROUNDED 4 /* store C rounded to TF32 (it feeds another tensor-core kernel) */
+#define BMB_GEMM_NO_SPLIT 8  /* never split K across CTAs (keeps the summation order fixed) */
 int bmb_gemm_ex(int math, int flags, int transA, int transB, int M, int N,
                 int K, float alpha, const float *A, const float *B, float beta,
                 float *C, void *stream);

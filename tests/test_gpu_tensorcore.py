@@ -156,13 +156,16 @@ def test_tensorcore_flash_rejects_other_head_sizes(bmb, cuda):
     assert st == bmb.E_UNSUPPORTED
 
 
-TINY = dict(max_seq_len=64, vocab_size=300, padded_vocab=384, n_layer=2, n_head=2, n_embd=256, B=4, T=64)
+TINY = dict(max_seq_len=64, vocab_size=300, padded_vocab=384, n_layer=2, n_head=4, n_embd=256, B=4, T=64)
 
 
-def test_train_step_tf32_loss_vs_oracle(bmb, orc, cuda):
-    """TF32 GEMMs inside the train step: loss per step within 2e-2 of the fp32
-    CPU oracle over 20 steps (shapes large enough to take the tensor-core path)."""
-    tr = bmb.Trainer(seed=1337, use_flash=1, math=bmb.MATH_TF32, **TINY)
+@pytest.mark.parametrize("fused", [0, 1])
+def test_train_step_tf32_loss_vs_oracle(bmb, orc, cuda, fused):
+    """TF32 GEMMs and attention inside the train step: loss per step within 2e-2
+    of the fp32 CPU oracle over 20 steps (shapes large enough to take the
+    tensor-core path).  fused = 1 additionally keeps every GEMM / attention
+    operand TF32-rounded at its producer and adds the biases in the GEMM epilogue."""
+    tr = bmb.Trainer(seed=1337, use_flash=1, math=bmb.MATH_TF32, fused=fused, **TINY)
     n = tr.num_params
     params0 = np.empty(n, np.float32)
     tr.get_params(params0)
