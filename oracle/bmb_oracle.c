@@ -381,7 +381,17 @@ void orc_softmax_crossentropy_forward(float *probs, float *losses, const float *
         float m = -3.402823466e38f;
         for (int i = 0; i < V; ++i) if (x[i] > m) m = x[i];
         float s = 0.0f;
-        for (int i = 0; i < V; ++i) { p[i] = expf(x[i] - m); s += p[i]; }
+        /* The reference sums with 128 threads striding the row and a shuffle tree
+         * (src/nn.cu:207-214, src/reduce.cuh:46-60): 128 strided partial sums, then
+         * pairwise folding.  A single running fp32 sum over 50k terms would itself be
+         * off by ~5e-5, so the same order is kept here. */
+        float part[128];
+        for (int t = 0; t < 128; ++t) part[t] = 0.0f;
+        for (int i = 0; i < V; ++i) { p[i] = expf(x[i] - m); part[i & 127] += p[i]; }
+        for (int w = 0; w < 4; ++w)
+            for (int off = 16; off > 0; off >>= 1)
+                for (int t = 0; t < off; ++t) part[w * 32 + t] += part[w * 32 + t + off];
+        s = (part[0] + part[64]) + (part[32] + part[96]);   /* xor-2 then xor-1 over the four warp sums */
         const float inv = 1.0f / s;
         for (int i = 0; i < V; ++i) p[i] *= inv;
         for (int i = V; i < Vp; ++i) p[i] = 0.0f;

@@ -265,7 +265,7 @@ def test_elementwise_bias_encoder_vs_oracle(bmb, orc, cuda):
     assert np.array_equal(host(cuda, r), ((x + dy) + x).ravel())
     t2 = dev(cuda, x)
     bmb.call("bmb_bias_forward", t2, tbias, N, Cc)
-    assert np.array_equal(host(cuda, t2), (x + bias).ravel())
+    assert np.array_equal(host(cuda, t2).ravel(), (x + bias).ravel())
     for (n2, c2) in [(N, Cc), (1000, 768), (5, 50)]:
         d = normal((n2, c2), 5)
         db0 = normal(c2, 6)
