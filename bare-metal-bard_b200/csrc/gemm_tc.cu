@@ -52,7 +52,9 @@ using namespace tc;
 constexpr int BM = 128, BN = 256, STAGES = 4, KBYTES = 128;
 constexpr int A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NTHREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int EPI_PITCH = 36;                       // floats per parked row: 32 + 4 keeps 128-bit accesses conflict-free
+constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;   // one 32 x 32 staging block per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES;
 constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 128 bytes of M/N
 
 struct TileSched {
@@ -191,61 +193,62 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             const bool first_split = (unit % nsplit) == 0;
             if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
             fence_after();
-            const int m = tm * BM + q * 32 + lane;
+            // The accumulator leaves TMEM one row per thread; the rows are parked in shared memory and
+            // written out four rows per instruction, each row segment a contiguous 128 bytes, so that
+            // the global stores (loads of C, atomics) are fully coalesced.
+            const int row_base = tm * BM + q * 32;
             const uint32_t trow = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
-            float *crow = C + (size_t)m * N;
+            float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256) + (warp - 2) * (32 * EPI_PITCH);
+            const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
+            const bool add_bias = bias && (nsplit == 1 || first_split);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
+                const int n0 = tn * BN + c * 32;
+                if (n0 >= N) break;                      // warp-uniform
                 float v[32];
                 tmem_ld32(trow + (uint32_t)(c * 32), v);
-                const int n0 = tn * BN + c * 32;
-                if (m < M && n0 < N && nsplit > 1) {
-                    // Split-K: partial products are added into C (the host has already applied beta);
-                    // the split that owns K slice 0 also adds the bias.
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        if (vec_ok && n0 + j + 4 <= N) {
-                            float4 o = make_float4(alpha * v[j], alpha * v[j + 1], alpha * v[j + 2], alpha * v[j + 3]);
-                            if (bias && first_split) {
-                                const float4 bb = *reinterpret_cast<const float4 *>(bias + n0 + j);
-                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                            }
-                            atomicAdd(reinterpret_cast<float4 *>(crow + n0 + j), o);
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(stg + lane * EPI_PITCH + j) =
+                        make_float4(alpha * v[j], alpha * v[j + 1], alpha * v[j + 2], alpha * v[j + 3]);
+                __syncwarp();
+                const int n = n0 + sub_c;
+                const bool vec = vec_ok && (n + 4 <= N);
+                float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (add_bias && vec) bb = *reinterpret_cast<const float4 *>(bias + n);
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int row = rr * 4 + sub_r, m = row_base + row;
+                    float4 o = *reinterpret_cast<const float4 *>(stg + row * EPI_PITCH + sub_c);
+                    if (m >= M) continue;
+                    float *cp = C + (size_t)m * N + n;
+                    if (vec) {
+                        o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                        if (nsplit > 1) {
+                            // split-K: partial products are added into C (the host has applied beta already)
+                            atomicAdd(reinterpret_cast<float4 *>(cp), o);
                         } else {
-                            for (int e = 0; e < 4; ++e)
-                                if (n0 + j + e < N)
-                                    atomicAdd(crow + n0 + j + e, alpha * v[j + e] + ((bias && first_split) ? bias[n0 + j + e] : 0.0f));
-                        }
-                    }
-                } else if (m < M && n0 < N) {
-                    if (vec_ok && n0 + 32 <= N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o = make_float4(alpha * v[j], alpha * v[j + 1], alpha * v[j + 2], alpha * v[j + 3]);
-                            if (bias) {
-                                const float4 bb = *reinterpret_cast<const float4 *>(bias + n0 + j);
-                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                            }
                             if (beta != 0.0f) {
-                                const float4 cc = *reinterpret_cast<const float4 *>(crow + n0 + j);
+                                const float4 cc = *reinterpret_cast<const float4 *>(cp);
                                 o.x = fmaf(beta, cc.x, o.x); o.y = fmaf(beta, cc.y, o.y);
                                 o.z = fmaf(beta, cc.z, o.z); o.w = fmaf(beta, cc.w, o.w);
                             }
                             if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
-                            *reinterpret_cast<float4 *>(crow + n0 + j) = o;
+                            *reinterpret_cast<float4 *>(cp) = o;
                         }
                     } else {
+                        const float ov[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (n0 + j < N) {
-                                float o = alpha * v[j];
-                                if (bias) o += bias[n0 + j];
-                                if (beta != 0.0f) o = fmaf(beta, crow[n0 + j], o);
-                                crow[n0 + j] = round_c ? round_tf32(o) : o;
-                            }
+                        for (int e = 0; e < 4; ++e) {
+                            if (n + e >= N) continue;
+                            float x = ov[e] + (add_bias ? bias[n + e] : 0.0f);
+                            if (nsplit > 1) { atomicAdd(cp + e, x); continue; }
+                            if (beta != 0.0f) x = fmaf(beta, cp[e], x);
+                            cp[e] = round_c ? round_tf32(x) : x;
                         }
                     }
                 }
+                __syncwarp();
             }
             fence_before();
             __syncwarp();

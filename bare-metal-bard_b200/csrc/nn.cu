@@ -158,7 +158,7 @@ __global__ void layernorm_fwd_block_k(float *__restrict__ out, float *__restrict
 // `partial` ([gridDim.x][2*C]: dw then db).  column_add_k finishes the sum in a
 // fixed order, so the parameter gradients are reproducible run to run.
 template <int V4>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
                      const float *__restrict__ dout, const float *__restrict__ inp,
                      const float *__restrict__ weight, const float *__restrict__ mean,
@@ -167,11 +167,9 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
     const int C4 = C >> 2;
-    float4 w[V4], dw[V4], db[V4];
+    float4 dw[V4], db[V4];
 #pragma unroll
     for (int i = 0; i < V4; ++i) {
-        const int c4 = lane + 32 * i;
-        w[i] = (c4 < C4) ? LD4(weight + c4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         dw[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -180,22 +178,29 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
         const float *dy = dout + (size_t)row * C;
         float *dx = dinp + (size_t)row * C;
         const float mu = mean[row], rs = rstd[row];
-        float4 xh[V4], g[V4];
+        float4 xh[V4], g[V4], acc[V4];
         float s1 = 0.0f, s2 = 0.0f;
+        // all three rows are requested before anything is consumed: one memory round trip per row
+#pragma unroll
+        for (int i = 0; i < V4; ++i) {
+            const int c4 = lane + 32 * i;
+            if (c4 < C4) { xh[i] = LD4(x + c4 * 4); g[i] = LD4(dy + c4 * 4); acc[i] = LD4(dx + c4 * 4); }
+        }
 #pragma unroll
         for (int i = 0; i < V4; ++i) {
             const int c4 = lane + 32 * i;
             if (c4 < C4) {
-                const float4 xv = LD4(x + c4 * 4);
-                g[i] = LD4(dy + c4 * 4);
+                const float4 xv = xh[i], wv = LD4(weight + c4 * 4);   // weight row stays in L1
                 xh[i].x = (xv.x - mu) * rs; xh[i].y = (xv.y - mu) * rs;
                 xh[i].z = (xv.z - mu) * rs; xh[i].w = (xv.w - mu) * rs;
-                const float a = g[i].x * w[i].x, b = g[i].y * w[i].y, c = g[i].z * w[i].z, d = g[i].w * w[i].w;
-                s1 += (a + b) + (c + d);
-                s2 += (a * xh[i].x + b * xh[i].y) + (c * xh[i].z + d * xh[i].w);
                 dw[i].x += g[i].x * xh[i].x; dw[i].y += g[i].y * xh[i].y;
                 dw[i].z += g[i].z * xh[i].z; dw[i].w += g[i].w * xh[i].w;
                 db[i].x += g[i].x; db[i].y += g[i].y; db[i].z += g[i].z; db[i].w += g[i].w;
+                const float a = g[i].x * wv.x, b = g[i].y * wv.y, c = g[i].z * wv.z, d = g[i].w * wv.w;
+                g[i] = make_float4(a, b, c, d);                       // from here on g holds dxhat = dy * w
+                s1 += (a + b) + (c + d);
+                s2 += (a * xh[i].x + b * xh[i].y) + (c * xh[i].z + d * xh[i].w);
+
             }
         }
         const float m1 = warp_sum(s1) / C, m2 = warp_sum(s2) / C;
@@ -203,11 +208,11 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
         for (int i = 0; i < V4; ++i) {
             const int c4 = lane + 32 * i;
             if (c4 < C4) {
-                float4 d = LD4(dx + c4 * 4);
-                d.x += rs * (g[i].x * w[i].x - m1 - xh[i].x * m2);
-                d.y += rs * (g[i].y * w[i].y - m1 - xh[i].y * m2);
-                d.z += rs * (g[i].z * w[i].z - m1 - xh[i].z * m2);
-                d.w += rs * (g[i].w * w[i].w - m1 - xh[i].w * m2);
+                float4 d = acc[i];
+                d.x += rs * (g[i].x - m1 - xh[i].x * m2);
+                d.y += rs * (g[i].y - m1 - xh[i].y * m2);
+                d.z += rs * (g[i].z - m1 - xh[i].z * m2);
+                d.w += rs * (g[i].w - m1 - xh[i].w * m2);
                 ST4(dx + c4 * 4) = rnd4(d, rnd);
             }
         }
@@ -349,7 +354,20 @@ bias_bwd_partial_k(float *__restrict__ partial, const float *__restrict__ dout, 
     const int c4 = blockIdx.x * 256 + threadIdx.x;
     if (c4 * 4 >= C) return;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int n = blockIdx.y; n < N; n += gridDim.y) {
+    // rows n = blockIdx.y + k*gridDim.y, four loads in flight at a time, summed in row order
+    const int step = gridDim.y;
+    int n = blockIdx.y;
+    for (; n + 3 * step < N; n += 4 * step) {
+        const float4 g0 = LD4(dout + (size_t)n * C + c4 * 4);
+        const float4 g1 = LD4(dout + (size_t)(n + step) * C + c4 * 4);
+        const float4 g2 = LD4(dout + (size_t)(n + 2 * step) * C + c4 * 4);
+        const float4 g3 = LD4(dout + (size_t)(n + 3 * step) * C + c4 * 4);
+        s.x += g0.x; s.y += g0.y; s.z += g0.z; s.w += g0.w;
+        s.x += g1.x; s.y += g1.y; s.z += g1.z; s.w += g1.w;
+        s.x += g2.x; s.y += g2.y; s.z += g2.z; s.w += g2.w;
+        s.x += g3.x; s.y += g3.y; s.z += g3.z; s.w += g3.w;
+    }
+    for (; n < N; n += step) {
         const float4 g = LD4(dout + (size_t)n * C + c4 * 4);
         s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
     }
@@ -579,8 +597,8 @@ int launch_column_add(float *dst, float *dst2, int ncols_first, const float *par
 // Layernorm backward with the scratch supplied by the caller: `partial` holds
 // at least layernorm_bwd_blocks(N) * 2 * C floats.
 int layernorm_bwd_blocks(int N) {
-    int g = ceil_div(N, 8);
-    const int cap = 2 * sm_count();
+    int g = ceil_div(N, 4);
+    const int cap = 3 * sm_count();     // 128-thread blocks, three resident per SM
     return g > cap ? cap : (g < 1 ? 1 : g);
 }
 int layernorm_backward_with_scratch(float *dinp, float *dweight, float *dbias, const float *dout,
@@ -590,10 +608,10 @@ int layernorm_backward_with_scratch(float *dinp, float *dweight, float *dbias, c
     const int rnd = emit_rounded() ? 1 : 0;
     const size_t sm = 2 * C * sizeof(float);
     // registers follow the row length: V4 float4 per lane cover C <= 128 * V4
-    if (C <= 256) layernorm_bwd_warp_k<2><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
-    else if (C <= 512) layernorm_bwd_warp_k<4><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
-    else if (C <= 768) layernorm_bwd_warp_k<6><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
-    else layernorm_bwd_warp_k<8><<<G, 256, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    if (C <= 256) layernorm_bwd_warp_k<2><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    else if (C <= 512) layernorm_bwd_warp_k<4><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    else if (C <= 768) layernorm_bwd_warp_k<6><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+    else layernorm_bwd_warp_k<8><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
     count_launch();
     BMB_LAUNCH_CHECK();
     return launch_column_add(dweight, dbias, C, partial, G, 2 * C, st);
