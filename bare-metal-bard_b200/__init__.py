@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(HERE, "libbmb.so")
 MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2
 GEMM_A_ROUNDED, GEMM_B_ROUNDED = 1, 2
 E_UNSUPPORTED = 3
+E_LIMIT = 6
 
 _f, _i, _p, _z, _ll, _d, _u = C.c_float, C.c_int, C.c_void_p, C.c_size_t, C.c_longlong, C.c_double, C.c_uint
 
@@ -70,6 +71,7 @@ SIGNATURES = {
     "bmb_encoder_backward": (_i, [_p, _p, _p, _p, _i, _i, _i]),
     "bmb_layernorm_forward": (_i, [_p, _p, _p, _p, _p, _p, _i, _i]),
     "bmb_layernorm_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i]),
+    "bmb_layernorm_backward_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i]),
     "bmb_gelu_forward": (_i, [_p, _p, _i]),
     "bmb_gelu_backward": (_i, [_p, _p, _p, _i]),
     "bmb_residual_forward": (_i, [_p, _p, _p, _i]),

@@ -7,6 +7,7 @@
 #include "common.cuh"
 #include <cfloat>
 #include <cmath>
+#include <mutex>
 
 namespace bmb {
 namespace {
@@ -692,6 +693,54 @@ int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias, const floa
     count_launch();
     BMB_LAUNCH_CHECK();
     return launch_column_add(dweight, dbias, C, partial, parts, 2 * C, st);
+}
+
+}  // extern "C"
+
+// ---- layernorm backward without any allocation ---------------------------------
+// The two-stage parameter-gradient sum needs a block of per-CTA partial rows.
+// bmb_layernorm_backward takes it from per-device scratch that is cudaMalloc'ed on
+// first use; this variant keeps it in the library image instead: a fixed 4 MiB
+// array in device memory (every GPU that loads libbmb.so holds it until exit).
+namespace {
+constexpr int NOALLOC_MAX_C = 1024;       // widest row served
+constexpr int NOALLOC_MAX_BLOCKS = 512;   // most partial rows ever written
+static __device__ __align__(256) float g_ln_noalloc_scratch[(size_t)NOALLOC_MAX_BLOCKS * 2 * NOALLOC_MAX_C];
+float *g_ln_noalloc_ptr[64];              // device address of the array, per device, 0 = not looked up yet
+std::mutex g_ln_noalloc_mu;
+}  // namespace
+
+extern "C" {
+
+int bmb_layernorm_backward_noalloc(float *dinp, float *dweight, float *dbias, const float *dout,
+                                   const float *inp, const float *weight, const float *mean,
+                                   const float *rstd, int N, int C) {
+    if (N <= 0 || C <= 0) return BMB_OK;
+    if (C > NOALLOC_MAX_C)
+        return fail(BMB_E_LIMIT, "layernorm_backward_noalloc: C=%d exceeds the built-in scratch (C <= %d)", C, NOALLOC_MAX_C);
+    if (C % 4 != 0 || !aligned16(dinp) || !aligned16(inp) || !aligned16(dout) || !aligned16(weight))
+        return fail(BMB_E_ARG, "layernorm_backward_noalloc: needs C %% 4 == 0 and 16-byte aligned buffers");
+    const int dev = current_device();
+    if (dev < 0 || dev >= 64) return fail(BMB_E_ARG, "device index %d out of range", dev);
+    float *partial = nullptr;
+    {
+        // Set-up, once per device, with that device current: in host code the array's name is only a
+        // stand-in, the kernel needs the address the runtime reports for this device.
+        std::lock_guard<std::mutex> lk(g_ln_noalloc_mu);
+        if (!g_ln_noalloc_ptr[dev]) {
+            void *p = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&p, g_ln_noalloc_scratch);
+            if (e != cudaSuccess || !p)
+                return fail(BMB_E_CUDA, "cudaGetSymbolAddress(layernorm scratch) -> %s", cudaGetErrorString(e));
+            g_ln_noalloc_ptr[dev] = static_cast<float *>(p);
+        }
+        partial = g_ln_noalloc_ptr[dev];
+    }
+    int G = layernorm_bwd_blocks(N);
+    if (G > NOALLOC_MAX_BLOCKS) G = NOALLOC_MAX_BLOCKS;   // the kernel strides rows over any grid
+    // Every partial row that is read was written by this launch first, so nothing needs clearing.
+    return layernorm_backward_with_scratch(dinp, dweight, dbias, dout, inp, weight, mean, rstd, N, C, partial, G,
+                                           cur_stream());
 }
 
 int bmb_gelu_forward(float *out, const float *inp, int n) {

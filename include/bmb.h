@@ -138,6 +138,22 @@ int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias,
                            const float *dout, const float *inp,
                            const float *weight, const float *mean,
                            const float *rstd, int N, int C);
+/* Same result as bmb_layernorm_backward, for callers that must not allocate.  No
+ * counterpart in the reference.  A training loop that has handed all of its device memory
+ * out at start-up (as gpt_alloc does) cannot afford the library's lazy cudaMalloc in the
+ * middle of a step: it may fail on a full device, and it synchronises the whole device.
+ * This entry point calls no cudaMalloc / cudaFree or any allocating routine: its partial
+ * sums live in a fixed 4 MiB array inside the library image, present on every GPU that
+ * loads libbmb.so.  Limits: C <= 1024, C % 4 == 0, 16-byte aligned buffers; a wider row
+ * returns BMB_E_LIMIT.  The first call on each device looks up the array's device address
+ * (once, with that device current), so make that first call before any stream capture.
+ * All calls on a device share the one array: calls that overlap on the GPU (two streams,
+ * two threads) race on it and must be serialised by the caller.  Nothing in the array needs
+ * clearing between calls. */
+int bmb_layernorm_backward_noalloc(float *dinp, float *dweight, float *dbias,
+                                   const float *dout, const float *inp,
+                                   const float *weight, const float *mean,
+                                   const float *rstd, int N, int C);
 int bmb_gelu_forward(float *out, const float *inp, int n);
 int bmb_gelu_backward(float *dinp, const float *inp, const float *dout, int n);
 int bmb_residual_forward(float *out, const float *a, const float *b, int n);
