@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libbmb.so")
 
 MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2
-GEMM_A_ROUNDED, GEMM_B_ROUNDED = 1, 2
+GEMM_A_ROUNDED, GEMM_B_ROUNDED, GEMM_C_ROUNDED, GEMM_NO_SPLIT = 1, 2, 4, 8
 E_UNSUPPORTED = 3
 E_LIMIT = 6
 

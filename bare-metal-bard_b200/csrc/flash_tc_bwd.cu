@@ -375,11 +375,23 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
             const int qc0 = (ib0 + i) * QB + colhalf * 16;     // first query column of this thread
             // per-column lse (in log2 units) and D; every thread of the CTA reads the same 32 values
             float lc[16], dc[16];
+            if ((T & 3) == 0 && qc0 + 16 <= T && (((uintptr_t)lse | (uintptr_t)dsum) & 15) == 0) {
+                // 16 consecutive, 16-byte aligned values of each: four 128-bit loads
+                const float4 *lp = reinterpret_cast<const float4 *>(lse + (size_t)bh * T + qc0);
+                const float4 *dp4 = reinterpret_cast<const float4 *>(dsum + (size_t)bh * T + qc0);
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const int q = qc0 + c;
-                lc[c] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
-                dc[c] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+                for (int c = 0; c < 4; ++c) {
+                    const float4 a = __ldg(lp + c), d4 = __ldg(dp4 + c);
+                    lc[c * 4] = a.x * LOG2E; lc[c * 4 + 1] = a.y * LOG2E; lc[c * 4 + 2] = a.z * LOG2E; lc[c * 4 + 3] = a.w * LOG2E;
+                    dc[c * 4] = d4.x; dc[c * 4 + 1] = d4.y; dc[c * 4 + 2] = d4.z; dc[c * 4 + 3] = d4.w;
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int q = qc0 + c;
+                    lc[c] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
+                    dc[c] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+                }
             }
             if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((i / 2) & 1), giveup)) { ok = false; break; }
             fence_after();

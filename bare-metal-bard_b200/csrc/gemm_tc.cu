@@ -49,12 +49,13 @@ namespace {
 
 using namespace tc;
 
-constexpr int BM = 128, BN = 256, STAGES = 4, KBYTES = 128;
-constexpr int A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+// Output tile: 128 rows by 256, 192 or 128 columns (chosen per problem to fill the last wave of CTAs).
+constexpr int BM = 128, BN_WIDE = 256, BN_NARROW = 128, STAGES = 4, KBYTES = 128;
+constexpr int A_BYTES = BM * KBYTES;
 constexpr int NTHREADS = 192;
 constexpr int EPI_PITCH = 36;                       // floats per parked row: 32 + 4 keeps 128-bit accesses conflict-free
 constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;   // one 32 x 32 staging block per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES;
+constexpr int smem_bytes(int bn) { return STAGES * (A_BYTES + bn * KBYTES) + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES; }
 constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 128 bytes of M/N
 
 struct TileSched {
@@ -70,13 +71,102 @@ struct TileSched {
     }
 };
 
+// The work of one CTA, as a list of items (tile, K slices [kb0, kb1)).  Tiles [0, dp_tiles) are
+// handed out whole, round-robin.  The K slices of the remaining `sk_tiles` tiles -- the ones that
+// would otherwise form a last, partly filled wave -- are laid end to end and cut into `g_sk` equal
+// runs, one per CTA ("stream-K"), so a tile there is shared by the CTAs whose runs cross it.  Each
+// CTA walks its run first, then its whole tiles.  Producer, issuer and epilogue warps each keep
+// their own copy of this iterator and see the same sequence.
+struct WorkIter {
+    int dp_tiles, kblocks, g_sk, grid;
+    long long R;            // K slices in the stream-K region
+    long long it, hi;       // what is left of this CTA's run
+    int dp_next;
+    __device__ __forceinline__ long long run_start(int c) const { return ((long long)c * R) / g_sk; }
+    __device__ __forceinline__ void init(int cta, int grid_, int dp_tiles_, int sk_tiles, int kblocks_, int g_sk_) {
+        dp_tiles = dp_tiles_; kblocks = kblocks_; g_sk = g_sk_; grid = grid_;
+        R = (long long)sk_tiles * kblocks_;
+        if (cta < g_sk_) { it = run_start(cta); hi = run_start(cta + 1); } else { it = hi = 0; }
+        dp_next = cta;
+    }
+    __device__ __forceinline__ bool next(int &tile, int &kb0, int &kb1) {
+        if (it < hi) {
+            const long long t = it / kblocks;
+            kb0 = (int)(it - t * kblocks);
+            const long long n = min((long long)(kblocks - kb0), hi - it);
+            kb1 = kb0 + (int)n;
+            tile = dp_tiles + (int)t;
+            it += n;
+            return true;
+        }
+        if (dp_next < dp_tiles) {
+            tile = dp_next; kb0 = 0; kb1 = kblocks;
+            dp_next += grid;
+            return true;
+        }
+        return false;
+    }
+};
+
+// One 128-bit group of the result: bias, beta * C, optional TF32 rounding, store (scalar at ragged edges).
+__device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, int M, int N, int m, int n, bool vec,
+                                             float beta, const float *__restrict__ bias, int round_c) {
+    if (m >= M) return;
+    float *cp = C + (size_t)m * N + n;
+    if (vec) {
+        if (bias) {
+            const float4 bb = *reinterpret_cast<const float4 *>(bias + n);
+            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+        }
+        if (beta != 0.0f) {
+            const float4 cc = *reinterpret_cast<const float4 *>(cp);
+            o.x = fmaf(beta, cc.x, o.x); o.y = fmaf(beta, cc.y, o.y);
+            o.z = fmaf(beta, cc.z, o.z); o.w = fmaf(beta, cc.w, o.w);
+        }
+        if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
+        *reinterpret_cast<float4 *>(cp) = o;
+    } else {
+        const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (n + e >= N) continue;
+            float x = ov[e] + (bias ? bias[n + e] : 0.0f);
+            if (beta != 0.0f) x = fmaf(beta, cp[e], x);
+            cp[e] = round_c ? round_tf32(x) : x;
+        }
+    }
+}
+
+// One 128-bit group of a part of a stream-K tile: added into C, which the host has already
+// multiplied by beta; the part that holds the first K slice brings the bias.
+__device__ __forceinline__ void add_result(float4 o, float *__restrict__ C, int M, int N, int m, int n, bool vec,
+                                           const float *__restrict__ bias) {
+    if (m >= M) return;
+    float *cp = C + (size_t)m * N + n;
+    if (vec) {
+        if (bias) {
+            const float4 bb = *reinterpret_cast<const float4 *>(bias + n);
+            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+        }
+        atomicAdd(reinterpret_cast<float4 *>(cp), o);
+    } else {
+        const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (n + e < N) atomicAdd(cp + e, ov[e] + (bias ? bias[n + e] : 0.0f));
+    }
+}
+
 // KIND 0 = tf32 (fp32 operands), 1 = f16 (bf16 operands, always K-major).
 // a_mn / b_mn: the operand's tile is MN-major (TF32 only).
-template <int KIND>
+template <int KIND, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, int M, int N,
           int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
-          int vec_ok, int nsplit, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
+          int vec_ok, int dp_tiles, int g_sk, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
+    constexpr int B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t ACC_COLS = BN > 128 ? 256 : 128; // TMEM columns set aside per accumulator
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // two accumulators; allocations are powers of two
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -94,9 +184,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     sch.tiles_m = (M + BM - 1) / BM;
     sch.tiles_n = (N + BN - 1) / BN;
     sch.num_tiles = sch.tiles_m * sch.tiles_n;
-    // Split-K: a work unit is (tile, split); split s covers K slices [s*kbs, min(kblocks, (s+1)*kbs)).
-    const int num_units = sch.num_tiles * nsplit;
-    const int kbs = (kblocks + nsplit - 1) / nsplit;
+    WorkIter wi;
+    wi.init((int)blockIdx.x, (int)gridDim.x, dp_tiles, sch.num_tiles - dp_tiles, kblocks, g_sk);
+    int tile, kb0, kb1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); armed[s] = -1; }
@@ -104,7 +194,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         *giveup = 0;
         mbar_init_fence();
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     fence_before();
     __syncthreads();
     fence_after();
@@ -116,10 +206,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+            while (ok && wi.next(tile, kb0, kb1)) {
                 int tm, tn;
-                sch.coords(unit / nsplit, tm, tn);
-                const int kb0 = (unit % nsplit) * kbs, kb1 = min(kblocks, kb0 + kbs);
+                sch.coords(tile, tm, tn);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * s;
@@ -157,11 +246,10 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0, acc = 0;
             uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+            while (ok && wi.next(tile, kb0, kb1)) {
                 if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
                 fence_after();
-                const uint32_t d = tmem_base + (uint32_t)(acc * BN);
-                const int kb0 = (unit % nsplit) * kbs, kb1 = min(kblocks, kb0 + kbs);
+                const uint32_t d = tmem_base + (uint32_t)acc * ACC_COLS;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
                     fence_after();
@@ -187,20 +275,21 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+        while (ok && wi.next(tile, kb0, kb1)) {
             int tm, tn;
-            sch.coords(unit / nsplit, tm, tn);
-            const bool first_split = (unit % nsplit) == 0;
+            sch.coords(tile, tm, tn);
+            const bool whole = (kb0 == 0 && kb1 == kblocks);
             if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
             fence_after();
             // The accumulator leaves TMEM one row per thread; the rows are parked in shared memory and
             // written out four rows per instruction, each row segment a contiguous 128 bytes, so that
-            // the global stores (loads of C, atomics) are fully coalesced.
+            // the global stores (loads of C, atomics) are fully coalesced.  A whole tile is stored; a
+            // part of a stream-K tile is added into C.
             const int row_base = tm * BM + q * 32;
-            const uint32_t trow = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+            const uint32_t trow = tmem_base + (uint32_t)acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
             float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256) + (warp - 2) * (32 * EPI_PITCH);
             const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
-            const bool add_bias = bias && (nsplit == 1 || first_split);
+            const float *part_bias = (kb0 == 0) ? bias : nullptr;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int n0 = tn * BN + c * 32;
@@ -214,39 +303,12 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 __syncwarp();
                 const int n = n0 + sub_c;
                 const bool vec = vec_ok && (n + 4 <= N);
-                float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (add_bias && vec) bb = *reinterpret_cast<const float4 *>(bias + n);
 #pragma unroll
                 for (int rr = 0; rr < 8; ++rr) {
-                    const int row = rr * 4 + sub_r, m = row_base + row;
-                    float4 o = *reinterpret_cast<const float4 *>(stg + row * EPI_PITCH + sub_c);
-                    if (m >= M) continue;
-                    float *cp = C + (size_t)m * N + n;
-                    if (vec) {
-                        o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                        if (nsplit > 1) {
-                            // split-K: partial products are added into C (the host has applied beta already)
-                            atomicAdd(reinterpret_cast<float4 *>(cp), o);
-                        } else {
-                            if (beta != 0.0f) {
-                                const float4 cc = *reinterpret_cast<const float4 *>(cp);
-                                o.x = fmaf(beta, cc.x, o.x); o.y = fmaf(beta, cc.y, o.y);
-                                o.z = fmaf(beta, cc.z, o.z); o.w = fmaf(beta, cc.w, o.w);
-                            }
-                            if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
-                            *reinterpret_cast<float4 *>(cp) = o;
-                        }
-                    } else {
-                        const float ov[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            if (n + e >= N) continue;
-                            float x = ov[e] + (add_bias ? bias[n + e] : 0.0f);
-                            if (nsplit > 1) { atomicAdd(cp + e, x); continue; }
-                            if (beta != 0.0f) x = fmaf(beta, cp[e], x);
-                            cp[e] = round_c ? round_tf32(x) : x;
-                        }
-                    }
+                    const int row = rr * 4 + sub_r;
+                    const float4 o = *reinterpret_cast<const float4 *>(stg + row * EPI_PITCH + sub_c);
+                    if (whole) store_result(o, C, M, N, row_base + row, n, vec, beta, bias, round_c);
+                    else add_result(o, C, M, N, row_base + row, n, vec, part_bias);
                 }
                 __syncwarp();
             }
@@ -262,7 +324,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     if (warp == 1) {
         __syncwarp();
         fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (threadIdx.x == 0 && *giveup) {
         *reinterpret_cast<volatile int *>(status) = 1;
@@ -368,7 +430,6 @@ int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int 
     return BMB_OK;
 }
 
-bool g_attr_set[64][2];
 std::mutex g_attr_mu;
 
 }  // namespace
@@ -378,32 +439,81 @@ bool gemm_tc_accepts(int math, int, int, int batch, int M, int N, int K, const f
     if (math != BMB_MATH_TF32 && math != BMB_MATH_BF16) return false;
     if (batch != 1) return false;                // batched problems stay on the SIMT kernel
     // Problems smaller than one tile stay on the SIMT kernel (fp32-exact, so within any tensor-core tolerance).
-    if (M < BM || N < BN || K < 32 || !C) return false;
+    if (M < BM || N < BN_NARROW || K < 32 || !C) return false;
     if ((long long)M * K >= (1LL << 40) || (long long)N * K >= (1LL << 40)) return false;
     return true;
 }
 
 namespace {
-__global__ void scale_c_k(float *C, long long n, float beta) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-         i += (long long)gridDim.x * blockDim.x)
-        C[i] *= beta;
+
+// C = beta * C over the tiles [dp_tiles, num_tiles) (the stream-K tiles), before their parts are added.
+__global__ void __launch_bounds__(256) sk_prepare_k(float *__restrict__ C, int M, int N, int tiles_m, int tiles_n, int dp_tiles,
+                                                    int bn, float beta, int vec_ok) {
+    TileSched sch;
+    sch.tiles_m = tiles_m; sch.tiles_n = tiles_n; sch.num_tiles = tiles_m * tiles_n;
+    int tm, tn;
+    sch.coords(dp_tiles + (int)blockIdx.x, tm, tn);
+    const int m0 = tm * BM, n0 = tn * bn;
+    const int rows = min(BM, M - m0), cols = min(bn, N - n0);
+    if (vec_ok && cols % 4 == 0) {
+        const int c4 = cols / 4;
+        for (int i = threadIdx.x; i < rows * c4; i += blockDim.x) {
+            float4 *p = reinterpret_cast<float4 *>(C + (size_t)(m0 + i / c4) * N + n0) + i % c4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (beta != 0.0f) { v = *p; v.x *= beta; v.y *= beta; v.z *= beta; v.w *= beta; }
+            *p = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
+            float *p = C + (size_t)(m0 + i / cols) * N + n0 + i % cols;
+            *p = (beta != 0.0f) ? beta * *p : 0.0f;
+        }
+    }
 }
 
-// Number of K splits for a problem with `tiles` output tiles and `kblocks` K slices on `sms` SMs: the
-// split count that minimises (waves of work units) x (slices per unit + a fixed per-unit cost).
-int choose_split(int tiles, int kblocks, int sms) {
-    if (tiles * 4 >= sms * 3 || kblocks < 16) return 1;
-    int best = 1;
-    long long best_cost = -1;
-    for (int s = 1; s <= 16 && s * 8 <= kblocks; ++s) {
-        const int kbs = (kblocks + s - 1) / s;
-        if ((s - 1) * kbs >= kblocks) continue;            // an empty split
-        const long long waves = (tiles * s + sms - 1) / sms;
-        const long long cost = waves * (kbs + 6);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+// Relative cost of one K slice of a tile `bn` columns wide (the narrower tiles re-read A more often
+// and amortise the epilogue less well).
+double slice_cost(int bn) { return bn == 256 ? 256.0 : (bn == 192 ? 200.0 : 150.0); }
+
+// Pick the tile width and how many tiles to hand out whole; the rest (a last, partly filled wave, or a
+// problem smaller than one wave) is shared between CTAs along K.  Costs are in K-slice units of a
+// 256-wide tile; a tile pays ~4 slices for its epilogue, sharing a tile ~6 more.
+void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int force_bn, int *bn_out, int *dp_tiles_out) {
+    const int tiles_m = (M + BM - 1) / BM;
+    const int widths[3] = {256, 192, 128};
+    double best = -1.0;
+    for (int w : widths) {
+        if (force_bn ? (w != force_bn) : (w > 128 && N < w)) continue;
+        const long long tiles = (long long)tiles_m * ((N + w - 1) / w);
+        const long long full = tiles / ctas, rem = tiles % ctas;
+        const double unit = slice_cost(w) / 256.0;
+        const double whole = (double)(full + (rem ? 1 : 0)) * (kblocks + 4) * unit;
+        double cost = whole;
+        int dp = (int)tiles;
+        if (allow_split && rem && kblocks >= 8) {
+            const double shared = ((double)full * (kblocks + 4) + (double)((rem * kblocks + ctas - 1) / ctas) + 10.0) * unit;
+            if (shared < whole) { cost = shared; dp = (int)(tiles - rem); }
+        }
+        if (best < 0.0 || cost < best) { best = cost; *bn_out = w; *dp_tiles_out = dp; }
     }
-    return best;
+}
+
+template <int KIND, int BN>
+int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, int M, int N, int kblocks, int kper,
+              int amn, int bmn, float alpha, float beta, float *C, int vec_ok, int dp_tiles, int g_sk, const float *bias,
+              int round_c, int *status_dev) {
+    static bool attr_set[64];
+    {
+        std::lock_guard<std::mutex> lk(g_attr_mu);
+        const int d = current_device();
+        if (d >= 0 && d < 64 && !attr_set[d]) {
+            BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
+            attr_set[d] = true;
+        }
+    }
+    gemm_tc_k<KIND, BN><<<grid, NTHREADS, smem_bytes(BN), st>>>(mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
+                                                                dp_tiles, g_sk, bias, round_c, status_dev);
+    return BMB_OK;
 }
 
 }  // namespace
@@ -418,52 +528,50 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     if (*status_host != 0)
         return fail(BMB_E_TIMEOUT, "an earlier tensor-core kernel on this device gave up waiting on a barrier");
     const bool bf16 = (math == BMB_MATH_BF16);
+    const int esize = bf16 ? 2 : 4;
+    const int kper = KBYTES / esize;
+    const int kblocks = (K + kper - 1) / kper;
+    const int ctas = sm_count();
+    // Sharing tiles between CTAs adds parts into C in whatever order they finish, so the last bits of
+    // such a result vary from run to run, and a rounded result would need another pass: both
+    // BMB_GEMM_NO_SPLIT and BMB_GEMM_C_ROUNDED keep every tile on one CTA.
+    const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED));
+    static const int force_bn = [] { const char *e = getenv("BMB_GEMM_TILE_N"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 192 || v == 128) ? v : 0; }();
+    int bn = BN_WIDE, dp_tiles = 0;
+    choose_schedule(M, N, kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, &bn, &dp_tiles);
     Operand a, b;
     BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st));
-    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, BN, st));
-    const int esize = bf16 ? 2 : 4;
+    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st));
     CUtensorMap mapA, mapB;
     BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
     BMB_TRY(make_map_2d(&mapB, b.ptr, esize, b.rows, b.cols, b.pitch_bytes, b.box_rows, b.mn_major));
-    const int kper = KBYTES / esize;
-    const int kblocks = (K + kper - 1) / kper;
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
+    const int tiles = tiles_m * tiles_n;
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
-    // Split-K when the tiles cannot fill the GPU (the dW products of a training step: few tiles, long K).
-    // The partial products are added atomically, so the summation order -- not the result beyond fp32
-    // rounding -- varies from run to run; BMB_GEMM_NO_SPLIT keeps one CTA per tile.
-    int nsplit = (flags & BMB_GEMM_NO_SPLIT) ? 1 : choose_split(tiles, kblocks, sm_count());
-    if (nsplit > 1) {
-        if (beta == 0.0f) BMB_CUDA(cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), st));
-        else if (beta != 1.0f) {
-            scale_c_k<<<blocks_for((long long)M * N), 256, 0, st>>>(C, (long long)M * N, beta);
+    const int sk_tiles = tiles - dp_tiles;
+    int g_sk = 1;
+    if (sk_tiles > 0) {
+        const long long runs = (long long)sk_tiles * kblocks / 4;       // at least 4 K slices per run
+        g_sk = (int)(runs < 1 ? 1 : (runs > ctas ? ctas : runs));
+        if (beta != 1.0f) {
+            sk_prepare_k<<<sk_tiles, 256, 0, st>>>(C, M, N, tiles_m, tiles_n, dp_tiles, bn, beta, vec_ok);
             count_launch();
         }
     }
-    const int units = tiles * nsplit;
-    const int grid = units < sm_count() ? units : sm_count();
-    const int round_c = (flags & BMB_GEMM_C_ROUNDED) && nsplit == 1 ? 1 : 0;
-    const int kind = bf16 ? 1 : 0;
-    {
-        std::lock_guard<std::mutex> lk(g_attr_mu);
-        const int d = current_device();
-        if (d >= 0 && d < 64 && !g_attr_set[d][kind]) {
-            if (bf16) BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-            else BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-            g_attr_set[d][kind] = true;
-        }
+    const int grid = sk_tiles > 0 ? (dp_tiles >= ctas ? ctas : (dp_tiles > g_sk ? dp_tiles : g_sk)) : (tiles < ctas ? tiles : ctas);
+    const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
+    const int amn = bf16 ? 0 : (a.mn_major ? 1 : 0), bmn = bf16 ? 0 : (b.mn_major ? 1 : 0);
+#define BMB_TC_ARGS grid, st, mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
+    if (bf16) {
+        if (bn == 256) BMB_TRY((launch_tc<1, 256>(BMB_TC_ARGS)));
+        else if (bn == 192) BMB_TRY((launch_tc<1, 192>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<1, 128>(BMB_TC_ARGS)));
+    } else {
+        if (bn == 256) BMB_TRY((launch_tc<0, 256>(BMB_TC_ARGS)));
+        else if (bn == 192) BMB_TRY((launch_tc<0, 192>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<0, 128>(BMB_TC_ARGS)));
     }
-    if (bf16)
-        gemm_tc_k<1><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, 0, 0, alpha, beta, C, vec_ok, nsplit, bias,
-                                                        round_c, status_dev);
-    else
-        gemm_tc_k<0><<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, M, N, kblocks, kper, a.mn_major ? 1 : 0,
-                                                        b.mn_major ? 1 : 0, alpha, beta, C, vec_ok, nsplit, bias, round_c, status_dev);
-    if (nsplit > 1 && (flags & BMB_GEMM_C_ROUNDED)) {
-        count_launch();
-        BMB_LAUNCH_CHECK();
-        return bmb_round_tf32(C, C, (size_t)M * N, (void *)st);
-    }
+#undef BMB_TC_ARGS
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
