@@ -13,7 +13,7 @@
 //                    (K-major, 128-byte swizzle) and folds the previous block's
 //                    P V into its output registers: o = o * exp2(m_old - m_new) + PV;
 //   warp 8           producer: TMA loads of the two Q tiles, then K and V
-//                    blocks into a 2-deep ring;
+//                    blocks into a 3-deep ring;
 //   warp 9           issuer: S_t = Q_t K_j^T as soon as the group has taken
 //                    S_t(j-1) out of TMEM, PV_t = P_t V_j as soon as P_t is
 //                    written.  The two tiles interleave, so one group's
@@ -34,7 +34,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KV_STAGES = 2;
+constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KV_STAGES = 3;
 constexpr int Q_TILE_BYTES = QT * HS * 4;          // 32 KB: two halves of 128 rows x 128 B
 constexpr int KV_TILE_BYTES = KB * HS * 4;         // 16 KB: two halves / chunks of 64 rows x 128 B
 constexpr int P_TILE_BYTES = QT * KB * 4;          // 32 KB: two halves of 128 rows x 128 B
@@ -61,16 +61,19 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
     // barrier indices
-    enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, PV_FULL = 11, NBARS = 13 };
+    enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = KV_FULL + KV_STAGES, S_FULL = KV_EMPTY + KV_STAGES, S_EMPTY = S_FULL + NQ,
+           P_FULL = S_EMPTY + NQ, PV_FULL = P_FULL + NQ, NBARS = PV_FULL + NQ };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int bh = blockIdx.y, b = bh / NH, h = bh % NH;
+    const int bh = blockIdx.x, b = bh / NH, h = bh % NH;
     const int C = NH * HS;
-    const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;      // longest rows first
+    // CTAs are dispatched x first: every head's last (longest) query block, then the next, so the
+    // long CTAs start early and the short ones fill the tail.
+    const int qblk = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int q0 = qblk * (NQ * QT);
 
     int nblk[NQ];
@@ -112,7 +115,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                                     h * HS + half * 32, row0 + q0 + t * QT + rr * 64, bar(Q_FULL));
             }
             bool ok = true;
-            int armed_parity[KV_STAGES] = {-1, -1};
+            int armed_parity[KV_STAGES];
+            for (int s = 0; s < KV_STAGES; ++s) armed_parity[s] = -1;
             for (int j = 0; j < maxblk; ++j) {
                 const int st = j % KV_STAGES;
                 const uint32_t ph = (uint32_t)((j / KV_STAGES) & 1);
@@ -209,54 +213,46 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                 if (!mbar_wait(bar(S_FULL + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
                 fence_after();
                 float s[KB];
-                {
-                    float v[32];
-                    tmem_ld32(s_addr, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) s[i] = v[i];
-                    tmem_ld32(s_addr + 32, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) s[32 + i] = v[i];
-                }
+                tmem_ld64(s_addr, s);
                 fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(S_EMPTY + t));       // S_t may be overwritten
 
+                // m is the running maximum of the raw scores (the scale is positive, so the order is
+                // the same); the scale rides in the exponent's multiply-add.
                 const int k0 = j * KB;
-                const bool diag = (k0 + KB - 1 > tile_q0);
-                float mx = -INFINITY;
+                if (k0 + KB - 1 > tile_q0) {                // the block touches the diagonal (warp-uniform)
 #pragma unroll
-                for (int i = 0; i < KB; ++i) {
-                    float x = s[i] * scale_log2e;
-                    if (diag && (k0 + i > qi)) x = -INFINITY;
-                    s[i] = x;
-                    mx = fmaxf(mx, x);
+                    for (int i = 0; i < KB; ++i)
+                        if (k0 + i > qi) s[i] = -INFINITY;
                 }
-                const float m_new = fmaxf(m, mx);           // finite: key 0 is visible to every row
-                const float alpha = fast_exp2(m - m_new);
-                float sum = 0.0f;
+                float mx0 = fmax3(s[0], s[1], s[2]), mx1 = fmax3(s[3], s[4], s[5]);
 #pragma unroll
-                for (int i = 0; i < KB; ++i) {
-                    const float p = fast_exp2(s[i] - m_new);
-                    sum += p;
-                    s[i] = round_tf32(p);
+                for (int i = 6; i + 3 < KB; i += 4) {
+                    mx0 = fmax3(mx0, s[i], s[i + 1]);
+                    mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
                 }
-                l = l * alpha + sum;
+                const float m_new = fmax3(m, fmax3(mx0, mx1, s[KB - 2]), s[KB - 1]);   // finite: key 0 is visible to every row
+                const float mb = m_new * scale_log2e;
+                const float alpha = fast_exp2(fmaf(m, scale_log2e, -mb));
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < KB; i += 2) {
+                    const float p0 = fast_exp2(fmaf(s[i], scale_log2e, -mb));
+                    const float p1 = fast_exp2(fmaf(s[i + 1], scale_log2e, -mb));
+                    sum0 += p0;
+                    sum1 += p1;
+                    s[i] = round_tf32(p0);
+                    s[i + 1] = round_tf32(p1);
+                }
+                l = l * alpha + (sum0 + sum1);
                 m = m_new;
 
                 if (j > 0) {
                     // P V of the previous block is complete: the P buffer is free and PV readable.
                     if (!mbar_wait(bar(PV_FULL + t), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
                     fence_after();
-                    float v[32];
-                    tmem_ld32(pv_addr, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha_prev, v[i]);
-                    tmem_ld32(pv_addr + 32, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], alpha_prev, v[i]);
                 }
-                alpha_prev = alpha;
                 // P row -> shared memory, K-major with the 128-byte swizzle (16-byte unit c of row r at c ^ (r & 7)).
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -268,9 +264,24 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     }
                 }
                 fence_proxy_async();
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(P_FULL + t));
+                // The previous block's P V must be out of TMEM before the next product may overwrite it;
+                // its fold into the output registers then runs while the tensor core works on this block.
+                if (j > 0) {
+                    float v0[32], v1[32];
+                    tmem_ld32_nowait(pv_addr, v0);
+                    tmem_ld32_nowait(pv_addr + 32, v1);
+                    tmem_wait_ld();
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(P_FULL + t));
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { o[i] = fmaf(o[i], alpha_prev, v0[i]); o[32 + i] = fmaf(o[32 + i], alpha_prev, v1[i]); }
+                } else {
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(P_FULL + t));
+                }
+                alpha_prev = alpha;
             }
             if (ok && mbar_wait(bar(PV_FULL + t), (uint32_t)((nb - 1) & 1), giveup)) {
                 fence_after();
@@ -291,7 +302,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                         if (round_out) w = make_float4(round_tf32(w.x), round_tf32(w.y), round_tf32(w.z), round_tf32(w.w));
                         *reinterpret_cast<float4 *>(dst + d) = w;
                     }
-                    lse[(size_t)bh * T + qi] = (m + log2f(l)) * 0.6931471805599453f;
+                    lse[(size_t)bh * T + qi] = (m * scale_log2e + log2f(l)) * 0.6931471805599453f;
                 }
             }
         }
@@ -361,7 +372,7 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
         }
     }
     const float scale_log2e = (1.0f / sqrtf((float)HS)) * 1.4426950408889634f;
-    dim3 grid((T + NQ * QT - 1) / (NQ * QT), B * NH);
+    dim3 grid(B * NH, (T + NQ * QT - 1) / (NQ * QT));
     flash_fwd_tc_k<<<grid, FWD_THREADS, FWD_SMEM, st>>>(mapQK, mapV, out, lse, T, NH, scale_log2e,
                                                         emit_rounded() ? 1 : 0, status_dev);
     count_launch();

@@ -72,9 +72,9 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
     auto bar = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int bh = blockIdx.y, b = bh / NH, h = bh % NH;
+    const int bh = blockIdx.x, b = bh / NH, h = bh % NH;
     const int C = NH * HS;
-    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * QT;
+    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * QT;   // CTAs are dispatched x first: every head's longest tile, then the next
     const int nb = min(T - 1, q0 + QT - 1) / KB + 1;       // key blocks up to the diagonal
 
     if (threadIdx.x == 0) {
@@ -259,9 +259,9 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
     auto bar = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int bh = blockIdx.y, b = bh / NH, h = bh % NH;
+    const int bh = blockIdx.x, b = bh / NH, h = bh % NH;
     const int C = NH * HS;
-    const int j0 = (int)blockIdx.x * KT;                   // first key of this CTA (earliest keys walk longest)
+    const int j0 = (int)blockIdx.y * KT;                   // first key of this CTA (earliest keys walk longest)
     const int ib0 = j0 / QB;                               // first query block that can see these keys
     const int nb = (T + QB - 1) / QB - ib0;                // query blocks to walk
 
@@ -509,7 +509,9 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
         }
     }
     const float scale = 1.0f / sqrtf((float)HS);
-    dim3 gkv((T + dkv::KT - 1) / dkv::KT, B * NH), gq((T + dq::QT - 1) / dq::QT, B * NH);
+    // x = (batch, head), y = position: the dispatch order runs through all heads at the position with
+    // the most work first, so the long CTAs start early and the short ones fill the tail.
+    dim3 gkv(B * NH, (T + dkv::KT - 1) / dkv::KT), gq(B * NH, (T + dq::QT - 1) / dq::QT);
     flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qk32, qn32, gk32, gn32, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     flash_bwd_dq_tc_k<<<gq, dq::THREADS, dq::SMEM, st>>>(qk64, qn64, gk64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     count_launch(2);

@@ -335,7 +335,7 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
         BMB_CUDA(cudaMalloc(&t->shadow, pb));
         const int tids[5] = {P_WTE, P_QKVW, P_APW, P_FCW, P_FPW};
         for (int id : tids) { t->toff[id] = t->num_shadow_t; t->num_shadow_t += (t->psize[id] + 63) & ~(size_t)63; }
-        if ((size_t)c.padded_vocab / 32 + 1 < 65535 && (size_t)c.n_layer < 65535 && !getenv("BMB_DBG_NO_SHADOW_T"))
+        if ((size_t)c.padded_vocab / 32 + 1 < 65535 && (size_t)c.n_layer < 65535)
             BMB_CUDA(cudaMalloc(&t->shadow_t, t->num_shadow_t * sizeof(float)));
     }
 
