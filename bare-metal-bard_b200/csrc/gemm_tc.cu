@@ -158,7 +158,8 @@ __device__ __forceinline__ void add_result(float4 o, float *__restrict__ C, int 
 }
 
 // KIND 0 = tf32 (fp32 operands), 1 = f16 (bf16 operands, always K-major).
-// a_mn / b_mn: the operand's tile is MN-major (TF32 only).
+// a_mn / b_mn: the operand's tile is MN-major (TF32 only); 2 = its tensor map is the 3-d one that
+// brings all chunks of a slice in one copy.
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, int M, int N,
@@ -216,13 +217,17 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     armed[s] = (int)ph;
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
                     const int k0 = kb * kelems_per_block;
-                    if (a_mn) {
+                    if (a_mn == 2) {
+                        tma_load_3d(sa, &mapA, 0, k0, tm * (BM / 32), fb);        // all chunks in one copy
+                    } else if (a_mn) {
 #pragma unroll 1
                         for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * CHUNK_BYTES, &mapA, tm * BM + c * 32, k0, fb);
                     } else {
                         tma_load_2d(sa, &mapA, k0, tm * BM, fb);
                     }
-                    if (b_mn) {
+                    if (b_mn == 2) {
+                        tma_load_3d(sb, &mapB, 0, k0, tn * (BN / 32), fb);
+                    } else if (b_mn) {
 #pragma unroll 1
                         for (int c = 0; c < BN / 32; ++c) tma_load_2d(sb + c * CHUNK_BYTES, &mapB, tn * BN + c * 32, k0, fb);
                     } else {
@@ -378,6 +383,8 @@ struct Operand {
     bool mn_major;        // tile layout
     long long rows, cols, pitch_bytes;   // tensor-map geometry (cols contiguous)
     int box_rows;
+    bool map3d;           // MN-major with the extent a multiple of 32: one 3-d copy per slice
+    int tile_chunks;      // 32-wide chunks per tile (3-d map only)
 };
 
 inline int blocks_for(long long items) {
@@ -405,8 +412,10 @@ int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int 
             }
             op->ptr = use;
             op->mn_major = !kcontig;
+            op->map3d = false;
+            op->tile_chunks = 0;
             if (kcontig) { op->rows = X; op->cols = K; op->pitch_bytes = (long long)K * 4; op->box_rows = tile_rows; }
-            else { op->rows = K; op->cols = X; op->pitch_bytes = X * 4; op->box_rows = 32; }
+            else { op->rows = K; op->cols = X; op->pitch_bytes = X * 4; op->box_rows = 32; op->map3d = (X % 32 == 0); op->tile_chunks = tile_rows / 32; }
             return BMB_OK;
         }
     }
@@ -425,7 +434,7 @@ int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int 
     }
     count_launch();
     BMB_LAUNCH_CHECK();
-    op->ptr = scr; op->mn_major = false;
+    op->ptr = scr; op->mn_major = false; op->map3d = false; op->tile_chunks = 0;
     op->rows = X; op->cols = Kp; op->pitch_bytes = (long long)Kp * esize; op->box_rows = tile_rows;
     return BMB_OK;
 }
@@ -543,8 +552,10 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st));
     BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st));
     CUtensorMap mapA, mapB;
-    BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
-    BMB_TRY(make_map_2d(&mapB, b.ptr, esize, b.rows, b.cols, b.pitch_bytes, b.box_rows, b.mn_major));
+    if (a.map3d) BMB_TRY(make_map_mn3d(&mapA, a.ptr, a.rows, a.cols, a.pitch_bytes, a.tile_chunks));
+    else BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
+    if (b.map3d) BMB_TRY(make_map_mn3d(&mapB, b.ptr, b.rows, b.cols, b.pitch_bytes, b.tile_chunks));
+    else BMB_TRY(make_map_2d(&mapB, b.ptr, esize, b.rows, b.cols, b.pitch_bytes, b.box_rows, b.mn_major));
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
     const int tiles = tiles_m * tiles_n;
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
@@ -560,7 +571,7 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     }
     const int grid = sk_tiles > 0 ? (dp_tiles >= ctas ? ctas : (dp_tiles > g_sk ? dp_tiles : g_sk)) : (tiles < ctas ? tiles : ctas);
     const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
-    const int amn = bf16 ? 0 : (a.mn_major ? 1 : 0), bmn = bf16 ? 0 : (b.mn_major ? 1 : 0);
+    const int amn = bf16 ? 0 : (a.mn_major ? (a.map3d ? 2 : 1) : 0), bmn = bf16 ? 0 : (b.mn_major ? (b.map3d ? 2 : 1) : 0);
 #define BMB_TC_ARGS grid, st, mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {
         if (bn == 256) BMB_TRY((launch_tc<1, 256>(BMB_TC_ARGS)));

@@ -40,6 +40,25 @@ int make_map_2d(CUtensorMap *map, const void *ptr, int esize, long long rows, lo
     return BMB_OK;
 }
 
+// An MN-major fp32 operand (rows_k rows of K, cols_x contiguous M/N values, cols_x % 32 == 0) seen as
+// [cols_x / 32 chunks][rows_k][32 floats]: one copy of a 32 x 32 x box_chunks box lands in shared memory
+// as box_chunks consecutive chunks of 32 K rows x 128 bytes, the layout the MN-major descriptors read.
+int make_map_mn3d(CUtensorMap *map, const void *ptr, long long rows_k, long long cols_x, long long pitch_bytes, int box_chunks) {
+    EncodeFn enc = encode_fn();
+    if (!enc) return fail(BMB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {32, (cuuint64_t)rows_k, (cuuint64_t)(cols_x / 32)};
+    const cuuint64_t strides[2] = {(cuuint64_t)pitch_bytes, 128};
+    const cuuint32_t box[3] = {32, 32, (cuuint32_t)box_chunks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(BMB_E_CUDA, "cuTensorMapEncodeTiled (3-d) failed (%d) for %lld x %lld, pitch %lld", (int)r, rows_k, cols_x,
+                    pitch_bytes);
+    return BMB_OK;
+}
+
 struct Status { int *dev = nullptr; int *host = nullptr; };
 static Status g_status[64];
 static std::mutex g_status_mu;

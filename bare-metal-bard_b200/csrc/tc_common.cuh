@@ -55,6 +55,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
 // Generic-proxy shared-memory writes become visible to the async proxy (tcgen05.mma operand reads).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -190,6 +195,7 @@ EncodeFn encode_fn();
 // 2-D map over a rows x cols matrix of `esize`-byte elements, columns contiguous, row pitch `pitch_bytes`;
 // box = 128 bytes of columns x box_rows rows, zero fill outside the matrix; atom32 = false: SWIZZLE_128B,
 // atom32 = true: SWIZZLE_128B_ATOM_32B (for MN-major tiles of 32-bit elements).
+int make_map_mn3d(CUtensorMap *map, const void *ptr, long long rows_k, long long cols_x, long long pitch_bytes, int box_chunks);
 int make_map_2d(CUtensorMap *map, const void *ptr, int esize, long long rows, long long cols, long long pitch_bytes,
                 int box_rows, bool atom32 = false);
 
