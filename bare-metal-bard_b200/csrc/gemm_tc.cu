@@ -52,9 +52,9 @@ using namespace tc;
 // Output tile: 128 rows by 256, 192 or 128 columns (chosen per problem to fill the last wave of CTAs).
 constexpr int BM = 128, BN_WIDE = 256, BN_NARROW = 128, STAGES = 4, KBYTES = 128;
 constexpr int A_BYTES = BM * KBYTES;
-constexpr int NTHREADS = 192;
-constexpr int EPI_PITCH = 36;                       // floats per parked row: 32 + 4 keeps 128-bit accesses conflict-free
-constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;   // one 32 x 32 staging block per epilogue warp
+constexpr int EPI_WARPS = 8;                        // two per TMEM lane quadrant, taking alternate 32-column chunks
+constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_BYTES = EPI_WARPS * 32 * 32 * 4;  // one 32 x 32 staging block per epilogue warp, 16-byte units XOR-swizzled by row
 constexpr int smem_bytes(int bn) { return STAGES * (A_BYTES + bn * KBYTES) + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES; }
 constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 128 bytes of M/N
 
@@ -112,6 +112,7 @@ struct WorkIter {
 __device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, int M, int N, int m, int n, bool vec,
                                              float beta, const float *__restrict__ bias, int round_c) {
     if (m >= M) return;
+    if (round_c & 2) return;  // DBG
     float *cp = C + (size_t)m * N + n;
     if (vec) {
         if (bias) {
@@ -123,7 +124,7 @@ __device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, in
             o.x = fmaf(beta, cc.x, o.x); o.y = fmaf(beta, cc.y, o.y);
             o.z = fmaf(beta, cc.z, o.z); o.w = fmaf(beta, cc.w, o.w);
         }
-        if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
+        if (round_c & 1) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
         *reinterpret_cast<float4 *>(cp) = o;
     } else {
         const float ov[4] = {o.x, o.y, o.z, o.w};
@@ -132,7 +133,7 @@ __device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, in
             if (n + e >= N) continue;
             float x = ov[e] + (bias ? bias[n + e] : 0.0f);
             if (beta != 0.0f) x = fmaf(beta, cp[e], x);
-            cp[e] = round_c ? round_tf32(x) : x;
+            cp[e] = (round_c & 1) ? round_tf32(x) : x;
         }
     }
 }
@@ -191,7 +192,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); armed[s] = -1; }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, EPI_WARPS); }
         *giveup = 0;
         mbar_init_fence();
     }
@@ -277,6 +278,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                          // TMEM lane quadrant this warp may read
+        const int chunk_par = (warp - 2) >> 2;           // this warp takes the chunks of this parity
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
@@ -292,26 +294,27 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             // part of a stream-K tile is added into C.
             const int row_base = tm * BM + q * 32;
             const uint32_t trow = tmem_base + (uint32_t)acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-            float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256) + (warp - 2) * (32 * EPI_PITCH);
-            const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
+            float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256) + (warp - 2) * (32 * 32);
+            const int sub_r = lane >> 3, sub_u = lane & 7, sub_c = sub_u * 4;
             const float *part_bias = (kb0 == 0) ? bias : nullptr;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = chunk_par; c < BN / 32; c += 2) {
                 const int n0 = tn * BN + c * 32;
                 if (n0 >= N) break;                      // warp-uniform
+                if (round_c & 4) break;  // DBG
                 float v[32];
                 tmem_ld32(trow + (uint32_t)(c * 32), v);
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4 *>(stg + lane * EPI_PITCH + j) =
-                        make_float4(alpha * v[j], alpha * v[j + 1], alpha * v[j + 2], alpha * v[j + 3]);
+                for (int u = 0; u < 8; ++u)
+                    *reinterpret_cast<float4 *>(stg + lane * 32 + ((u ^ (lane & 7)) << 2)) =
+                        make_float4(alpha * v[4 * u], alpha * v[4 * u + 1], alpha * v[4 * u + 2], alpha * v[4 * u + 3]);
                 __syncwarp();
                 const int n = n0 + sub_c;
                 const bool vec = vec_ok && (n + 4 <= N);
 #pragma unroll
                 for (int rr = 0; rr < 8; ++rr) {
                     const int row = rr * 4 + sub_r;
-                    const float4 o = *reinterpret_cast<const float4 *>(stg + row * EPI_PITCH + sub_c);
+                    const float4 o = *reinterpret_cast<const float4 *>(stg + row * 32 + ((sub_u ^ (row & 7)) << 2));
                     if (whole) store_result(o, C, M, N, row_base + row, n, vec, beta, bias, round_c);
                     else add_result(o, C, M, N, row_base + row, n, vec, part_bias);
                 }
@@ -570,7 +573,8 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
         }
     }
     const int grid = sk_tiles > 0 ? (dp_tiles >= ctas ? ctas : (dp_tiles > g_sk ? dp_tiles : g_sk)) : (tiles < ctas ? tiles : ctas);
-    const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
+    static const int dbg_epi = [] { const char *e = getenv("BMB_DBG_EPI"); return e ? atoi(e) : 0; }();  // DBG
+    const int round_c = ((flags & BMB_GEMM_C_ROUNDED) ? 1 : 0) | dbg_epi;
     const int amn = bf16 ? 0 : (a.mn_major ? (a.map3d ? 2 : 1) : 0), bmn = bf16 ? 0 : (b.mn_major ? (b.map3d ? 2 : 1) : 0);
 #define BMB_TC_ARGS grid, st, mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {

@@ -33,10 +33,6 @@ struct bmb_trainer {
     size_t psize[NPT], poff[NPT], num_params = 0;
     float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
     float *shadow = nullptr;  // TF32-rounded parameters (tensor-core modes only)
-    // Transposed TF32-rounded copies of the five matrices a dX product multiplies by (token embedding
-    // and the four block weights): stored [in, out], they are K-major operands for those products.
-    float *shadow_t = nullptr;
-    size_t toff[NPT] = {0}, num_shadow_t = 0;
     float *acts = nullptr, *bacts = nullptr;
     size_t num_acts = 0, num_bacts = 0;
     int *d_tokens = nullptr, *d_targets = nullptr;
@@ -211,10 +207,8 @@ int backward(bmb_trainer *t) {
     const float *P = t->params;
     float *G = t->grads;
     set_emit_rounded(fz);
-    // dX = dY * W with W stored [out, in]: read the transposed shadow [in, out] as a K-major operand
-    // where there is one, else W itself as an MN-major one.
+    // dX = dY * W with W stored [out, in]: W is the MN-major operand of this product.
     auto dx = [&](int flags, int M_, int N_, int K_, const float *dY, int id, size_t woff, float *dX) -> int {
-        if (t->shadow_t) return mm(t, flags | BMB_GEMM_B_ROUNDED, 0, 1, M_, N_, K_, dY, t->shadow_t + t->toff[id] + woff, 0.0f, dX);
         return mm(t, flags, 0, 0, M_, N_, K_, dY, W + t->poff[id] + woff, 0.0f, dX);
     };
 
@@ -262,42 +256,9 @@ int backward(bmb_trainer *t) {
     return BMB_OK;
 }
 
-// dst[b][c][r] = tf32(src[b][r][c]) for `batch` matrices of rows x cols.
-__global__ void __launch_bounds__(256) transpose_round_k(float *__restrict__ dst, const float *__restrict__ src, int rows, int cols) {
-    __shared__ float tile[32][33];
-    src += (size_t)blockIdx.z * rows * cols;
-    dst += (size_t)blockIdx.z * rows * cols;
-    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const int r = r0 + j, c = c0 + threadIdx.x;
-        if (r < rows && c < cols) tile[j][threadIdx.x] = round_tf32(__ldg(src + (size_t)r * cols + c));
-    }
-    __syncthreads();
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const int c = c0 + j, r = r0 + threadIdx.x;
-        if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][j];
-    }
-}
-
-int refresh_shadow_t(bmb_trainer *t) {
-    if (!t->shadow_t) return BMB_OK;
-    const bmb_train_config &c = t->c;
-    const int C = c.n_embd, L = c.n_layer;
-    const struct { int id, rows, cols, batch; } mats[5] = {{P_WTE, c.padded_vocab, C, 1}, {P_QKVW, 3 * C, C, L},
-                                                          {P_APW, C, C, L}, {P_FCW, 4 * C, C, L}, {P_FPW, C, 4 * C, L}};
-    for (const auto &mt : mats) {
-        const dim3 grid((mt.cols + 31) / 32, (mt.rows + 31) / 32, mt.batch);
-        transpose_round_k<<<grid, dim3(32, 8), 0, t->st>>>(t->shadow_t + t->toff[mt.id], t->params + t->poff[mt.id], mt.rows, mt.cols);
-        count_launch();
-    }
-    BMB_LAUNCH_CHECK();
-    return BMB_OK;
-}
-
 int refresh_shadow(bmb_trainer *t) {
     if (!t->shadow) return BMB_OK;
-    BMB_TRY(bmb_round_tf32(t->shadow, t->params, t->num_params, t->st));
-    return refresh_shadow_t(t);
+    return bmb_round_tf32(t->shadow, t->params, t->num_params, t->st);
 }
 
 }  // namespace
@@ -331,13 +292,7 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
     BMB_CUDA(cudaMemset(t->m, 0, pb));
     BMB_CUDA(cudaMemset(t->v, 0, pb));
     BMB_CUDA(cudaMemset(t->grads, 0, pb));
-    if (c.math != BMB_MATH_FP32) {
-        BMB_CUDA(cudaMalloc(&t->shadow, pb));
-        const int tids[5] = {P_WTE, P_QKVW, P_APW, P_FCW, P_FPW};
-        for (int id : tids) { t->toff[id] = t->num_shadow_t; t->num_shadow_t += (t->psize[id] + 63) & ~(size_t)63; }
-        if ((size_t)c.padded_vocab / 32 + 1 < 65535 && (size_t)c.n_layer < 65535)
-            BMB_CUDA(cudaMalloc(&t->shadow_t, t->num_shadow_t * sizeof(float)));
-    }
+    if (c.math != BMB_MATH_FP32) BMB_CUDA(cudaMalloc(&t->shadow, pb));
 
     const size_t B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head, Vp = c.padded_vocab;
     const size_t BT = B * T, BTC = BT * C, BT3C = 3 * BTC, BT4C = 4 * BTC;
@@ -425,7 +380,6 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     for (cudaEvent_t e : t->ev) cudaEventDestroy(e);
     cudaFree(t->params); cudaFree(t->grads); cudaFree(t->m); cudaFree(t->v);
     if (t->shadow) cudaFree(t->shadow);
-    if (t->shadow_t) cudaFree(t->shadow_t);
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
     cudaFree(t->d_loss); cudaFree(t->d_sumsq);
     cudaStreamDestroy(t->st);
@@ -493,7 +447,6 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
     BMB_TRY(bmb_adamw_update_clipped(t->params, t->grads, t->m, t->v, t->num_params, lr, t->c.beta1, t->c.beta2,
                                      t->c.eps, t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip,
                                      (float)t->nranks, t->shadow));
-    BMB_TRY(refresh_shadow_t(t));
     return BMB_OK;
 }
 
