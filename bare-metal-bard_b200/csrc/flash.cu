@@ -170,6 +170,34 @@ __global__ void flash_dsum_k(float *__restrict__ dsum, const float *__restrict__
     if (lane == 0) dsum[w] = a;
 }
 
+// The same sums with 128-bit loads over the (B*T, C) arrays in storage order: GL = HS/4 consecutive
+// lanes hold one head of one token and add up with shuffles.  Needs 16-byte aligned rows.
+template <int GL>
+__global__ void __launch_bounds__(256) flash_dsum_vec_k(float *__restrict__ dsum, const float *__restrict__ dout,
+                                                        const float *__restrict__ out, int T, int NH, long long n4) {
+    const int c4 = NH * GL;                                // 128-bit words per token
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    // whole warps stay in the loop for the shuffles
+    const long long n4_up = (n4 + 31) & ~31LL;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n4_up; e += stride) {
+        float a = 0.0f;
+        if (e < n4) {
+            const float4 x = __ldg(reinterpret_cast<const float4 *>(dout) + e);
+            const float4 y = __ldg(reinterpret_cast<const float4 *>(out) + e);
+            a = x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+        }
+#pragma unroll
+        for (int o = GL / 2; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (e < n4 && (threadIdx.x & (GL - 1)) == 0) {
+            const long long bt = e / c4;
+            const int h = (int)(e - bt * c4) / GL;
+            const long long b = bt / T;
+            const int t = (int)(bt - b * T);
+            dsum[(b * NH + h) * T + t] = a;
+        }
+    }
+}
+
 // dQ: a row group owns a query row; keys stream through shared memory.
 template <int HS, int KC>
 __global__ void __launch_bounds__(FT)
@@ -399,7 +427,18 @@ int run_bwd(int cfg, float *dqkv, float *dsum, const float *dout, const float *q
 
 int launch_flash_dsum(float *dsum, const float *dout, const float *out, int B, int T, int NH, int HS, cudaStream_t st) {
     const long long rows = (long long)B * NH * T;
-    flash_dsum_k<<<ceil_div(rows * 32, 256), 256, 0, st>>>(dsum, dout, out, T, NH, HS, rows);
+    const bool vec = (HS == 32 || HS == 64 || HS == 128) && (((uintptr_t)dout | (uintptr_t)out) & 15) == 0;
+    if (vec) {
+        const long long n4 = rows * (HS / 4);
+        long long blocks = (n4 + 255) / 256;
+        const long long cap = 16LL * sm_count();
+        if (blocks > cap) blocks = cap;
+        if (HS == 32) flash_dsum_vec_k<8><<<(int)blocks, 256, 0, st>>>(dsum, dout, out, T, NH, n4);
+        else if (HS == 64) flash_dsum_vec_k<16><<<(int)blocks, 256, 0, st>>>(dsum, dout, out, T, NH, n4);
+        else flash_dsum_vec_k<32><<<(int)blocks, 256, 0, st>>>(dsum, dout, out, T, NH, n4);
+    } else {
+        flash_dsum_k<<<ceil_div(rows * 32, 256), 256, 0, st>>>(dsum, dout, out, T, NH, HS, rows);
+    }
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;

@@ -49,11 +49,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 namespace dq {
 constexpr int QT = 128, KB = 64, STAGES = 2;
 constexpr int OFF_Q = 0, OFF_DO = 32768, OFF_ST = 65536, STAGE_BYTES = 49152;   // Kk | Kn | Vk, 16 KB each
-constexpr int OFF_DS = OFF_ST + STAGES * STAGE_BYTES;                            // 32 KB
-constexpr int OFF_BAR = OFF_DS + 32768;
+constexpr int OFF_DS = OFF_ST + STAGES * STAGE_BYTES;                            // two buffers of 32 KB
+constexpr int OFF_BAR = OFF_DS + 2 * 32768;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 320;
-enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, SP_FULL = 5, SP_EMPTY = 7, DS_FULL = 9, DQ_DONE = 10, NBARS = 11 };
+enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, SP_FULL = 5, SP_EMPTY = 7, DS_FULL = 9, DQ_DONE = 11, NBARS = 13 };
 }  // namespace dq
 
 __global__ void __launch_bounds__(dq::THREADS, 1)
@@ -81,8 +81,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
         mbar_init(bar(Q_FULL), 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(bar(KV_FULL + s), 1); mbar_init(bar(KV_EMPTY + s), 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(SP_EMPTY + s), 8); }
-        mbar_init(bar(DS_FULL), 8);
-        mbar_init(bar(DQ_DONE), 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(DS_FULL + s), 8); mbar_init(bar(DQ_DONE + s), 1); }
         *giveup = 0;
         mbar_init_fence();
     }
@@ -155,16 +154,17 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                     issue_sp((j + 1) % STAGES, nbuf);
                     commit(bar(SP_FULL + nbuf));
                 }
-                if (!mbar_wait(bar(DS_FULL), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                const int db = j & 1;                    // dS buffer of this block
+                if (!mbar_wait(bar(DS_FULL + db), (uint32_t)((j / 2) & 1), giveup)) { ok = false; break; }
                 fence_after();
                 const uint32_t kn = base + OFF_ST + st * STAGE_BYTES + 16384;
 #pragma unroll
                 for (int ks = 0; ks < KB / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + 256, smem_desc_kmajor(base + OFF_DS + half * 16384 + off),
+                    mma_tf32(tmem_base + 256, smem_desc_kmajor(base + OFF_DS + db * 32768 + half * 16384 + off),
                              smem_desc_mnmajor32(kn + ks * 1024, 8192), idesc_kn, (j | ks) ? 1u : 0u);
                 }
-                commit(bar(DQ_DONE));
+                commit(bar(DQ_DONE + db));
                 commit(bar(KV_EMPTY + st));
             }
         }
@@ -176,7 +176,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
         const float d_r = (qi < T) ? dsum[(size_t)bh * T + qi] : 0.0f;
         const float scale_log2e = scale * LOG2E;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        uint8_t *dsrow = gen + OFF_DS + colhalf * 16384 + r * 128;
+        uint8_t *dsrow0 = gen + OFF_DS + colhalf * 16384 + r * 128;
         bool ok = true;
         for (int j = 0; j < nb; ++j) {
             const int buf = j & 1;
@@ -196,15 +196,17 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                 if (diag && (k0 + i > qi)) p = 0.0f;
                 s[i] = round_tf32(p * (dp[i] - d_r));
             }
-            if (j > 0 && !mbar_wait(bar(DQ_DONE), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
+            // dS goes into the buffer the product of two blocks ago has finished reading
+            if (j > 1 && !mbar_wait(bar(DQ_DONE + buf), (uint32_t)(((j - 2) / 2) & 1), giveup)) { ok = false; break; }
+            uint8_t *dsrow = dsrow0 + buf * 32768;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<float4 *>(dsrow + ((c ^ (r & 7)) << 4)) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(DS_FULL));
+            if (lane == 0) mbar_arrive(bar(DS_FULL + buf));
         }
-        if (ok && mbar_wait(bar(DQ_DONE), (uint32_t)((nb - 1) & 1), giveup)) {
+        if (ok && mbar_wait(bar(DQ_DONE + ((nb - 1) & 1)), (uint32_t)(((nb - 1) / 2) & 1), giveup)) {
             fence_after();
             float v[32];
             tmem_ld32(lane_addr + (uint32_t)(256 + colhalf * 32), v);
@@ -234,12 +236,12 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
 namespace dkv {
 constexpr int KT = 128, QB = 32, STAGES = 3;
 constexpr int OFF_K = 0, OFF_V = 32768, OFF_ST = 65536, STAGE_BYTES = 32768;    // Qk | Qn | dOk | dOn, 8 KB each
-constexpr int OFF_PT = OFF_ST + STAGES * STAGE_BYTES;                            // 16 KB
-constexpr int OFF_DST = OFF_PT + 16384;                                          // 16 KB
-constexpr int OFF_BAR = OFF_DST + 16384;
+constexpr int OFF_PT = OFF_ST + STAGES * STAGE_BYTES;                            // two buffers of 16 KB
+constexpr int OFF_DST = OFF_PT + 2 * 16384;                                      // two buffers of 16 KB
+constexpr int OFF_BAR = OFF_DST + 2 * 16384;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 320;
-enum { KV_FULL = 0, ST_FULL = 1, ST_EMPTY = 4, SP_FULL = 7, SP_EMPTY = 9, PD_FULL = 11, PD_DONE = 12, NBARS = 13 };
+enum { KV_FULL = 0, ST_FULL = 1, ST_EMPTY = 4, SP_FULL = 7, SP_EMPTY = 9, PD_FULL = 11, PD_DONE = 13, NBARS = 15 };
 }  // namespace dkv
 
 __global__ void __launch_bounds__(dkv::THREADS, 1)
@@ -269,8 +271,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
         mbar_init(bar(KV_FULL), 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(bar(ST_FULL + s), 1); mbar_init(bar(ST_EMPTY + s), 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(SP_EMPTY + s), 8); }
-        mbar_init(bar(PD_FULL), 8);
-        mbar_init(bar(PD_DONE), 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(PD_FULL + s), 8); mbar_init(bar(PD_DONE + s), 1); }
         *giveup = 0;
         mbar_init_fence();
     }
@@ -345,20 +346,21 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                     issue_sp((i + 1) % STAGES, nbuf);
                     commit(bar(SP_FULL + nbuf));
                 }
-                if (!mbar_wait(bar(PD_FULL), (uint32_t)(i & 1), giveup)) { ok = false; break; }
+                const int pb = i & 1;                     // P^T / dS^T buffer of this block
+                if (!mbar_wait(bar(PD_FULL + pb), (uint32_t)((i / 2) & 1), giveup)) { ok = false; break; }
                 fence_after();
                 const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < QB / 8; ++ks) {     // dV += P^T dO
-                    mma_tf32(tmem_base + 128, smem_desc_kmajor(base + OFF_PT + ks * 32),
+                    mma_tf32(tmem_base + 128, smem_desc_kmajor(base + OFF_PT + pb * 16384 + ks * 32),
                              smem_desc_mnmajor32(sb + 24576 + ks * 1024, 4096), idesc_acc, (i | ks) ? 1u : 0u);
                 }
 #pragma unroll
                 for (int ks = 0; ks < QB / 8; ++ks) {     // dK += dS^T Q
-                    mma_tf32(tmem_base + 192, smem_desc_kmajor(base + OFF_DST + ks * 32),
+                    mma_tf32(tmem_base + 192, smem_desc_kmajor(base + OFF_DST + pb * 16384 + ks * 32),
                              smem_desc_mnmajor32(sb + 8192 + ks * 1024, 4096), idesc_acc, (i | ks) ? 1u : 0u);
                 }
-                commit(bar(PD_DONE));
+                commit(bar(PD_DONE + pb));
                 commit(bar(ST_EMPTY + st));
             }
         }
@@ -368,7 +370,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
         const int kj = j0 + r;                             // this thread's key
         const float scale_log2e = scale * LOG2E;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        uint8_t *ptrow = gen + OFF_PT + r * 128, *dstrow = gen + OFF_DST + r * 128;
+        uint8_t *ptrow0 = gen + OFF_PT + r * 128, *dstrow0 = gen + OFF_DST + r * 128;
         bool ok = true;
         for (int i = 0; i < nb; ++i) {
             const int buf = i & 1;
@@ -409,7 +411,9 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                 s[c] = round_tf32(p);
                 dp[c] = round_tf32(p * (dp[c] - dc[c]));
             }
-            if (i > 0 && !mbar_wait(bar(PD_DONE), (uint32_t)((i - 1) & 1), giveup)) { ok = false; break; }
+            // P^T and dS^T go into the buffers the products of two blocks ago have finished reading
+            if (i > 1 && !mbar_wait(bar(PD_DONE + buf), (uint32_t)(((i - 2) / 2) & 1), giveup)) { ok = false; break; }
+            uint8_t *ptrow = ptrow0 + buf * 16384, *dstrow = dstrow0 + buf * 16384;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int unit = ((colhalf * 4 + c) ^ (r & 7)) << 4;
@@ -418,9 +422,9 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(PD_FULL));
+            if (lane == 0) mbar_arrive(bar(PD_FULL + buf));
         }
-        if (ok && nb > 0 && mbar_wait(bar(PD_DONE), (uint32_t)((nb - 1) & 1), giveup)) {
+        if (ok && nb > 0 && mbar_wait(bar(PD_DONE + ((nb - 1) & 1)), (uint32_t)(((nb - 1) / 2) & 1), giveup)) {
             fence_after();
             float v[32];
             tmem_ld32(lane_addr + (uint32_t)(128 + colhalf * 32), v);
