@@ -80,6 +80,7 @@ SIGNATURES = {
     "bmb_bias_backward": (_i, [_p, _p, _i, _i]),
     "bmb_softmax_crossentropy_forward": (_i, [_p, _p, _p, _p, _i, _i, _i]),
     "bmb_crossentropy_softmax_backward": (_i, [_p, _p, _p, _i, _i, _i, _f]),
+    "bmb_softmax_crossentropy_fused": (_i, [_p, _p, _p, _p, _i, _i, _i, _f]),
     "bmb_adamw_update": (_i, [_p, _p, _p, _p, _i, _f, _f, _f, _f, _f, _i, _f]),
     "bmb_grad_global_norm": (_i, [_p, _i, C.POINTER(_f)]),
     "bmb_zero_buffer": (_i, [_p, _z]),

@@ -20,7 +20,7 @@ LIB = os.path.join(HERE, "libbmb.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",
-]
+] + os.environ.get("BMB_NVCC_FLAGS", "").split()      # e.g. -DBMB_FLASH_TRACE for the developer phase timers
 
 
 def _sources():

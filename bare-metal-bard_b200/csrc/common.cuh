@@ -113,5 +113,11 @@ __device__ __forceinline__ float round_tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return __uint_as_float(r);
 }
+// The same rounding with two integer instructions instead of a conversion (which shares the
+// special-function unit with exp): add half a TF32 ulp to the magnitude, clear the low 13 bits.
+// For finite values and infinities the result equals cvt.rna.tf32.f32.
+__device__ __forceinline__ float round_tf32_alu(float x) {
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+}
 }  // namespace bmb
 #endif

@@ -13,7 +13,7 @@
 //                    (K-major, 128-byte swizzle) and folds the previous block's
 //                    P V into its output registers: o = o * exp2(m_old - m_new) + PV;
 //   warp 8           producer: TMA loads of the two Q tiles, then K and V
-//                    blocks into a 3-deep ring;
+//                    blocks into a 5-deep ring;
 //   warp 9           issuer: S_t = Q_t K_j^T as soon as the group has taken
 //                    S_t(j-1) out of TMEM, PV_t = P_t V_j as soon as P_t is
 //                    written.  The two tiles interleave, so one group's
@@ -34,15 +34,14 @@ namespace {
 
 using namespace tc;
 
-constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KV_STAGES = 3;
+constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KV_STAGES = 5;
 constexpr int Q_TILE_BYTES = QT * HS * 4;          // 32 KB: two halves of 128 rows x 128 B
 constexpr int KV_TILE_BYTES = KB * HS * 4;         // 16 KB: two halves / chunks of 64 rows x 128 B
-constexpr int P_TILE_BYTES = QT * KB * 4;          // 32 KB: two halves of 128 rows x 128 B
+constexpr int TILE_COLS = 192;                     // TMEM columns per query tile: S | P | P V, 64 each
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + NQ * Q_TILE_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
-constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE_BYTES;
-constexpr int OFF_BAR = OFF_P + NQ * P_TILE_BYTES;
+constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_TILE_BYTES;
 constexpr int FWD_SMEM = OFF_BAR + 256 + 1024;
 constexpr int FWD_THREADS = 320;
 
@@ -51,6 +50,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+#ifdef BMB_FLASH_TRACE
+__device__ long long g_trace[16];
+#define TR(i) do { if (tr) { const long long now_ = clock64(); g_trace[i] += now_ - tlast; tlast = now_; } } while (0)
+#else
+#define TR(i)
+#endif
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant__ CUtensorMap mapV,
@@ -94,7 +100,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         *giveup = 0;
         mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 256);
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
     fence_before();
     __syncthreads();
     fence_after();
@@ -143,7 +149,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             const uint32_t idesc_pv = make_idesc(2, 0, 1, HS, QT);   // P (K-major) x V (MN-major)
             auto issue_s = [&](int t, int st) {
                 const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES, ka = base + OFF_K + st * KV_TILE_BYTES;
-                const uint32_t d = tmem_base + (uint32_t)(t * 128);
+                const uint32_t d = tmem_base + (uint32_t)(t * TILE_COLS);
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
@@ -152,14 +158,12 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                 }
             };
             auto issue_pv = [&](int t, int st) {
-                const uint32_t pa = base + OFF_P + t * P_TILE_BYTES, va = base + OFF_V + st * KV_TILE_BYTES;
-                const uint32_t d = tmem_base + (uint32_t)(t * 128 + 64);
+                // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
+                const uint32_t va = base + OFF_V + st * KV_TILE_BYTES;
+                const uint32_t pa = tmem_base + (uint32_t)(t * TILE_COLS + 64), d = pa + 64;
 #pragma unroll
-                for (int ks = 0; ks < KB / 8; ++ks) {
-                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(d, smem_desc_kmajor(pa + half * (QT * 128) + off),
-                             smem_desc_mnmajor32(va + ks * 1024, KB * 128), idesc_pv, ks ? 1u : 0u);
-                }
+                for (int ks = 0; ks < KB / 8; ++ks)
+                    mma_tf32_ts(d, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KB * 128), idesc_pv, ks ? 1u : 0u);
             };
             bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
             if (ok) ok = mbar_wait(bar(KV_FULL + 0), 0, giveup);
@@ -201,19 +205,25 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         const int qi = tile_q0 + r;
         const int nb = nblk[t];
         if (nb > 0) {
-            const uint32_t s_addr = tmem_base + (uint32_t)(t * 128) + ((uint32_t)(quad * 32) << 16);
-            const uint32_t pv_addr = s_addr + 64;
-            uint8_t *prow = gen + OFF_P + t * P_TILE_BYTES + r * 128;
+            const uint32_t s_addr = tmem_base + (uint32_t)(t * TILE_COLS) + ((uint32_t)(quad * 32) << 16);
+            const uint32_t p_addr = s_addr + 64, pv_addr = s_addr + 128;
             float o[HS];
 #pragma unroll
             for (int d = 0; d < HS; ++d) o[d] = 0.0f;
             float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
             bool ok = true;
+#ifdef BMB_FLASH_TRACE
+            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 4 && lane == 0);
+            long long tlast = clock64();
+#endif
             for (int j = 0; j < nb; ++j) {
+                TR(0);
                 if (!mbar_wait(bar(S_FULL + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
                 fence_after();
+                TR(1);
                 float s[KB];
                 tmem_ld64(s_addr, s);
+                TR(2);
                 fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(S_EMPTY + t));       // S_t may be overwritten
@@ -242,28 +252,22 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     const float p1 = fast_exp2(fmaf(s[i + 1], scale_log2e, -mb));
                     sum0 += p0;
                     sum1 += p1;
-                    s[i] = round_tf32(p0);
-                    s[i + 1] = round_tf32(p1);
+                    s[i] = round_tf32_alu(p0);
+                    s[i + 1] = round_tf32_alu(p1);
                 }
                 l = l * alpha + (sum0 + sum1);
                 m = m_new;
+                TR(3);
 
                 if (j > 0) {
                     // P V of the previous block is complete: the P buffer is free and PV readable.
                     if (!mbar_wait(bar(PV_FULL + t), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
                     fence_after();
                 }
-                // P row -> shared memory, K-major with the 128-byte swizzle (16-byte unit c of row r at c ^ (r & 7)).
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const float4 val = make_float4(s[half * 32 + c * 4], s[half * 32 + c * 4 + 1],
-                                                       s[half * 32 + c * 4 + 2], s[half * 32 + c * 4 + 3]);
-                        *reinterpret_cast<float4 *>(prow + half * (QT * 128) + ((c ^ (r & 7)) << 4)) = val;
-                    }
-                }
-                fence_proxy_async();
+                TR(4);
+                // P row -> this thread's lane of tensor memory, the A operand of P V
+                tmem_st64(p_addr, s);
+                TR(5);
                 // The previous block's P V must be out of TMEM before the next product may overwrite it;
                 // its fold into the output registers then runs while the tensor core works on this block.
                 if (j > 0) {
@@ -271,6 +275,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     tmem_ld32_nowait(pv_addr, v0);
                     tmem_ld32_nowait(pv_addr + 32, v1);
                     tmem_wait_ld();
+                    TR(6);
                     fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(P_FULL + t));
@@ -282,6 +287,10 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     if (lane == 0) mbar_arrive(bar(P_FULL + t));
                 }
                 alpha_prev = alpha;
+                TR(7);
+#ifdef BMB_FLASH_TRACE
+                if (tr) g_trace[8] += 1;
+#endif
             }
             if (ok && mbar_wait(bar(PV_FULL + t), (uint32_t)((nb - 1) & 1), giveup)) {
                 fence_after();
@@ -313,7 +322,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     if (warp == 9) {
         __syncwarp();
         fence_after();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, 512);
     }
     if (threadIdx.x == 0 && *giveup) {
         *reinterpret_cast<volatile int *>(status) = 2;
@@ -381,3 +390,10 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
 }
 
 }  // namespace bmb
+
+#ifdef BMB_FLASH_TRACE
+extern "C" int bmb_dbg_flash_trace(long long *host16, int reset) {
+    if (reset) { long long z[16] = {0}; return (int)cudaMemcpyToSymbol(bmb::g_trace, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(host16, bmb::g_trace, 16 * sizeof(long long));
+}
+#endif

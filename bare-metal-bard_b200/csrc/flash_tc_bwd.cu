@@ -194,7 +194,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
             for (int i = 0; i < 32; ++i) {
                 float p = fast_exp2(fmaf(s[i], scale_log2e, -lse_r));
                 if (diag && (k0 + i > qi)) p = 0.0f;
-                s[i] = round_tf32(p * (dp[i] - d_r));
+                s[i] = round_tf32_alu(p * (dp[i] - d_r));
             }
             // dS goes into the buffer the product of two blocks ago has finished reading
             if (j > 1 && !mbar_wait(bar(DQ_DONE + buf), (uint32_t)(((j - 2) / 2) & 1), giveup)) { ok = false; break; }
@@ -408,8 +408,8 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                 const int q = qc0 + c;
                 float p = fast_exp2(fmaf(s[c], scale_log2e, -lc[c]));
                 if (q < kj || q >= T) p = 0.0f;            // causal mask and the ragged end
-                s[c] = round_tf32(p);
-                dp[c] = round_tf32(p * (dp[c] - dc[c]));
+                s[c] = round_tf32_alu(p);
+                dp[c] = round_tf32_alu(p * (dp[c] - dc[c]));
             }
             // P^T and dS^T go into the buffers the products of two blocks ago have finished reading
             if (i > 1 && !mbar_wait(bar(PD_DONE + buf), (uint32_t)(((i - 2) / 2) & 1), giveup)) { ok = false; break; }

@@ -112,7 +112,6 @@ struct WorkIter {
 __device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, int M, int N, int m, int n, bool vec,
                                              float beta, const float *__restrict__ bias, int round_c) {
     if (m >= M) return;
-    if (round_c & 2) return;  // DBG
     float *cp = C + (size_t)m * N + n;
     if (vec) {
         if (bias) {
@@ -124,7 +123,7 @@ __device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, in
             o.x = fmaf(beta, cc.x, o.x); o.y = fmaf(beta, cc.y, o.y);
             o.z = fmaf(beta, cc.z, o.z); o.w = fmaf(beta, cc.w, o.w);
         }
-        if (round_c & 1) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
+        if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
         *reinterpret_cast<float4 *>(cp) = o;
     } else {
         const float ov[4] = {o.x, o.y, o.z, o.w};
@@ -133,7 +132,7 @@ __device__ __forceinline__ void store_result(float4 o, float *__restrict__ C, in
             if (n + e >= N) continue;
             float x = ov[e] + (bias ? bias[n + e] : 0.0f);
             if (beta != 0.0f) x = fmaf(beta, cp[e], x);
-            cp[e] = (round_c & 1) ? round_tf32(x) : x;
+            cp[e] = round_c ? round_tf32(x) : x;
         }
     }
 }
@@ -301,7 +300,6 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             for (int c = chunk_par; c < BN / 32; c += 2) {
                 const int n0 = tn * BN + c * 32;
                 if (n0 >= N) break;                      // warp-uniform
-                if (round_c & 4) break;  // DBG
                 float v[32];
                 tmem_ld32(trow + (uint32_t)(c * 32), v);
 #pragma unroll
@@ -573,8 +571,7 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
         }
     }
     const int grid = sk_tiles > 0 ? (dp_tiles >= ctas ? ctas : (dp_tiles > g_sk ? dp_tiles : g_sk)) : (tiles < ctas ? tiles : ctas);
-    static const int dbg_epi = [] { const char *e = getenv("BMB_DBG_EPI"); return e ? atoi(e) : 0; }();  // DBG
-    const int round_c = ((flags & BMB_GEMM_C_ROUNDED) ? 1 : 0) | dbg_epi;
+    const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
     const int amn = bf16 ? 0 : (a.mn_major ? (a.map3d ? 2 : 1) : 0), bmn = bf16 ? 0 : (b.mn_major ? (b.map3d ? 2 : 1) : 0);
 #define BMB_TC_ARGS grid, st, mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {

@@ -389,12 +389,17 @@ __global__ void bias_bwd_scalar_k(float *__restrict__ dbias, const float *__rest
 // p = __expf(x - max) / sum, zeros in [V, Vp), loss = -logf(max(p[target], 1e-30)).
 // The row is read from DRAM once; the second and third sweeps are served by
 // L2, which holds every row in flight (2 blocks x 1024 threads per SM).
+// GRAD = true writes the gradient of the mean loss with respect to the logits,
+// (p - onehot) * grad_scale (optionally TF32-rounded), where GRAD = false writes p: the training
+// step then needs no separate backward sweep over the (N, Vp) matrix.
+template <bool GRAD>
 __global__ void __launch_bounds__(1024)
 softmax_xent_fwd_k(float *__restrict__ probs, float *__restrict__ losses,
                    const float *__restrict__ logits, const int *__restrict__ targets, int V,
-                   int Vp) {
+                   int Vp, float grad_scale, int rnd) {
     __shared__ float red[32];
     const int row = blockIdx.x;
+    const int tgt = targets[row];
     const float *x = logits + (size_t)row * Vp;
     float *p = probs + (size_t)row * Vp;
     const bool vec = (Vp & 3) == 0;
@@ -440,14 +445,24 @@ softmax_xent_fwd_k(float *__restrict__ probs, float *__restrict__ losses,
             o.y = (c + 1 < V) ? __expf(v.y - m) * inv : 0.0f;
             o.z = (c + 2 < V) ? __expf(v.z - m) * inv : 0.0f;
             o.w = (c + 3 < V) ? __expf(v.w - m) * inv : 0.0f;
+            if (GRAD) {
+                o.x = (c + 0 < V) ? (o.x - (c + 0 == tgt ? 1.0f : 0.0f)) * grad_scale : 0.0f;
+                o.y = (c + 1 < V) ? (o.y - (c + 1 == tgt ? 1.0f : 0.0f)) * grad_scale : 0.0f;
+                o.z = (c + 2 < V) ? (o.z - (c + 2 == tgt ? 1.0f : 0.0f)) * grad_scale : 0.0f;
+                o.w = (c + 3 < V) ? (o.w - (c + 3 == tgt ? 1.0f : 0.0f)) * grad_scale : 0.0f;
+                o = rnd4(o, rnd);
+            }
             ST4(p + i * 4) = o;
         }
     } else {
-        for (int i = threadIdx.x; i < Vp; i += blockDim.x)
-            p[i] = (i < V) ? __expf(x[i] - m) * inv : 0.0f;
+        for (int i = threadIdx.x; i < Vp; i += blockDim.x) {
+            float o = (i < V) ? __expf(x[i] - m) * inv : 0.0f;
+            if (GRAD) o = rnd1((i < V) ? (o - (i == tgt ? 1.0f : 0.0f)) * grad_scale : 0.0f, rnd);
+            p[i] = o;
+        }
     }
     if (threadIdx.x == 0) {
-        const int t = targets[row];
+        const int t = tgt;
         const float pt = __expf(x[t] - m) * inv;
         losses[row] = -logf(fmaxf(pt, 1e-30f));
     }
@@ -804,7 +819,17 @@ int bmb_softmax_crossentropy_forward(float *probs, float *losses, const float *l
                                      const int *targets, int N, int V, int Vp) {
     if (N <= 0) return BMB_OK;
     if (V <= 0 || V > Vp) return fail(BMB_E_ARG, "softmax_xent: need 0 < V <= Vp (V=%d Vp=%d)", V, Vp);
-    softmax_xent_fwd_k<<<N, Vp >= 4096 ? 1024 : 128, 0, cur_stream()>>>(probs, losses, logits, targets, V, Vp);
+    softmax_xent_fwd_k<false><<<N, Vp >= 4096 ? 1024 : 128, 0, cur_stream()>>>(probs, losses, logits, targets, V, Vp, 0.0f, 0);
+    count_launch();
+    BMB_LAUNCH_CHECK();
+    return BMB_OK;
+}
+int bmb_softmax_crossentropy_fused(float *dlogits, float *losses, const float *logits,
+                                   const int *targets, int N, int V, int Vp, float dloss_scale) {
+    if (N <= 0) return BMB_OK;
+    if (V <= 0 || V > Vp) return fail(BMB_E_ARG, "softmax_xent: need 0 < V <= Vp (V=%d Vp=%d)", V, Vp);
+    softmax_xent_fwd_k<true><<<N, Vp >= 4096 ? 1024 : 128, 0, cur_stream()>>>(dlogits, losses, logits, targets, V, Vp, dloss_scale,
+                                                                               emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;

@@ -187,7 +187,8 @@ int forward(bmb_trainer *t) {
     BMB_TRY(bmb_layernorm_forward(t->lnf, t->lnf_mean, t->lnf_rstd, residual, P + t->poff[P_LNFW],
                                   P + t->poff[P_LNFB], N, C));
     BMB_TRY(mm(t, wflag, 0, 1, N, Vp, C, t->lnf, W + t->poff[P_WTE], 0.0f, t->logits));
-    BMB_TRY(bmb_softmax_crossentropy_forward(t->probs, t->losses, t->logits, t->d_targets, N, V, Vp));
+    // Loss and its gradient with respect to the logits in one sweep (mean loss: dloss = 1/N).
+    BMB_TRY(bmb_softmax_crossentropy_fused(t->dlogits, t->losses, t->logits, t->d_targets, N, V, Vp, 1.0f / N));
     BMB_TRY(bmb_reduce_mean_device(t->losses, N, t->d_loss));
     return BMB_OK;
 }
@@ -213,7 +214,6 @@ int backward(bmb_trainer *t) {
     };
 
     BMB_CUDA(cudaMemsetAsync(G, 0, t->num_params * sizeof(float), t->st));
-    BMB_TRY(bmb_crossentropy_softmax_backward(t->dlogits, t->probs, t->d_targets, N, V, Vp, 1.0f / N));
     BMB_TRY(dx(wflag, N, C, Vp, t->dlogits, P_WTE, 0, t->dlnf));
     BMB_TRY(mm(t, gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
     float *last_res = t->residual3 + (size_t)(L - 1) * BTC;
@@ -313,7 +313,7 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
         t->fch = take(BT4C * L); t->fch_gelu = take(BT4C * L); t->fcproj = take(BTC * L);
         t->residual3 = take(BTC * L);
         t->lnf = take(BTC); t->lnf_mean = take(BT); t->lnf_rstd = take(BT);
-        t->logits = take(BT * Vp); t->probs = take(BT * Vp); t->losses = take(BT);
+        t->logits = take(BT * Vp); t->probs = nullptr; t->losses = take(BT);
         return off;
     };
     auto layout_bwd = [&](float *base) -> size_t {

@@ -167,6 +167,13 @@ int bmb_softmax_crossentropy_forward(float *probs, float *losses,
 int bmb_crossentropy_softmax_backward(float *dlogits, const float *probs,
                                       const int *targets, int N, int V, int Vp,
                                       float dloss_scale);
+/* No counterpart in the reference: softmax_crossentropy_forward and
+ * crossentropy_softmax_backward (src/nn.cu:197-237) in one sweep.  losses as
+ * the forward writes them; dlogits = (softmax(logits) - onehot) * dloss_scale
+ * on the V real columns, 0 on the padding.  The probabilities are not kept. */
+int bmb_softmax_crossentropy_fused(float *dlogits, float *losses,
+                                   const float *logits, const int *targets,
+                                   int N, int V, int Vp, float dloss_scale);
 int bmb_adamw_update(float *params, float *grads, float *m, float *v, int n,
                      float lr, float beta1, float beta2, float eps,
                      float weight_decay, int step, float grad_scale);
