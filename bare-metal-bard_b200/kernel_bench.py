@@ -1,6 +1,7 @@
 """Per-kernel timings of libbmb.so on one GPU, one JSON line per case.
 
     python bare-metal-bard_b200/kernel_bench.py [gemm] [bgemm] [flash] [nn] [--small]
+    python bare-metal-bard_b200/kernel_bench.py one:tf32:nt:8192x3072x768:rounded      (a single GEMM case)
 
 Timing follows the reference harness (src/bench.cu:75-105): 5 warm-up calls,
 then 20 calls bracketed by CUDA events one at a time; best and median are
@@ -151,12 +152,41 @@ def bench_nn(bmb, small):
              gbs_best=round(nbytes / best / 1e6, 1), gbs_median=round(nbytes / med / 1e6, 1))
 
 
+def bench_one(bmb, spec):
+    """One GEMM case, for a profiler capture or a quick comparison:
+        one:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][:nosplit]
+    math = fp32 | tf32 | bf16; ta/tb = n or t; `rounded` feeds operands already rounded to TF32
+    (what the training step does), `nosplit` keeps every tile on one CTA."""
+    parts = spec.split(":")
+    math = {"fp32": bmb.MATH_FP32, "tf32": bmb.MATH_TF32, "bf16": bmb.MATH_BF16}[parts[1]]
+    ta, tb = (1 if ch == "t" else 0 for ch in parts[2])
+    M, N, K = (int(x) for x in parts[3].split("x"))
+    opts = parts[4:]
+    A = torch.rand(M * K, device="cuda") * 2 - 1
+    B = torch.rand(K * N, device="cuda") * 2 - 1
+    Cm = torch.zeros(M * N, device="cuda")
+    flags = 0
+    if "rounded" in opts:
+        bmb.call("bmb_round_tf32", A, A, M * K, None)
+        bmb.call("bmb_round_tf32", B, B, K * N, None)
+        flags |= bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED
+    if "nosplit" in opts:
+        flags |= bmb.GEMM_NO_SPLIT
+    best, med = timed(lambda: bmb.call("bmb_gemm_ex", math, flags, ta, tb, M, N, K, 1.0, A, B, 0.0, Cm, None),
+                      warmup=3, iters=5)
+    emit(kernel="gemm_ex", spec=spec, best_ms=round(best, 4), median_ms=round(med, 4),
+         tflops_best=round(2.0 * M * N * K / best / 1e9, 2))
+
+
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     small = "--small" in sys.argv
     which = args or ["gemm", "bgemm", "flash", "nn"]
     bmb = load_package()
     torch.cuda.set_device(0)
+    for w in [x for x in which if x.startswith("one:")]:
+        bench_one(bmb, w)
+    which = [x for x in which if not x.startswith("one:")]
     for w in which:
         {"gemm": bench_gemm, "bgemm": bench_bgemm, "flash": bench_flash, "nn": bench_nn}[w](bmb, small)
 
