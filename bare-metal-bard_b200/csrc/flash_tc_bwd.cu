@@ -234,22 +234,31 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
 
 // ============================================================ dK/dV kernel
 namespace dkv {
-constexpr int KT = 128, QB = 32, STAGES = 3;
-constexpr int OFF_K = 0, OFF_V = 32768, OFF_ST = 65536, STAGE_BYTES = 32768;    // Qk | Qn | dOk | dOn, 8 KB each
-constexpr int OFF_PT = OFF_ST + STAGES * STAGE_BYTES;                            // two buffers of 16 KB
-constexpr int OFF_DST = OFF_PT + 2 * 16384;                                      // two buffers of 16 KB
-constexpr int OFF_BAR = OFF_DST + 2 * 16384;
+constexpr int KT = 128, QB = 64, STAGES = 2;
+constexpr int OFF_K = 0, OFF_V = 32768;
+constexpr int OFF_STK = 65536, STK_BYTES = 32768;       // per stage: Q then dO, K-major, 16 KB each
+constexpr int OFF_STN = OFF_STK + STAGES * STK_BYTES;   // per stage: Q then dO, MN-major, 16 KB each
+constexpr int STN_BYTES = 32768;
+constexpr int OFF_BAR = OFF_STN + STAGES * STN_BYTES;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 320;
-enum { KV_FULL = 0, ST_FULL = 1, ST_EMPTY = 4, SP_FULL = 7, SP_EMPTY = 9, PD_FULL = 11, PD_DONE = 13, NBARS = 15 };
+enum { KV_FULL = 0, STK_FULL = 1, STK_EMPTY = 3, STN_FULL = 5, STN_EMPTY = 7, SP_FULL = 9, PD_FULL = 11, ACC_DONE = 13, NBARS = 14 };
+// TMEM columns: S^T / P^T [2] at 0 / 64, dP^T / dS^T [2] at 128 / 192, dV at 256, dK at 320
+constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320;
 }  // namespace dkv
 
+// A CTA owns 128 keys and walks query blocks of 64 from the diagonal to the end.  S^T = K Q^T and
+// dP^T = V dO^T land in tensor memory; 256 threads (a key row each, 32 of the 64 query columns)
+// turn them into P^T and dS^T and write those back over S^T and dP^T, where the tensor core reads
+// them as the A operand of dV += P^T dO and dK += dS^T Q.  Nothing of the (T x T) matrices touches
+// shared memory.  The K-major copies of a query block (operands of the first two products) and its
+// MN-major copies (operands of the last two) ride in separate 2-deep rings, so each is refilled as
+// soon as its own consumers are done.
 __global__ void __launch_bounds__(dkv::THREADS, 1)
-flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_k32,
-                   const __grid_constant__ CUtensorMap mapQKV_n32, const __grid_constant__ CUtensorMap mapDO_k32,
-                   const __grid_constant__ CUtensorMap mapDO_n32, float *__restrict__ dqkv,
-                   const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
-                   int round_out, int *__restrict__ status) {
+flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
+                   const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
+                   float *__restrict__ dqkv, const float *__restrict__ lse, const float *__restrict__ dsum,
+                   int T, int NH, float scale, int round_out, int *__restrict__ status) {
     using namespace dkv;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -269,20 +278,23 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
 
     if (threadIdx.x == 0) {
         mbar_init(bar(KV_FULL), 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(bar(ST_FULL + s), 1); mbar_init(bar(ST_EMPTY + s), 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(SP_EMPTY + s), 8); }
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(PD_FULL + s), 8); mbar_init(bar(PD_DONE + s), 1); }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar(STK_FULL + s), 1); mbar_init(bar(STK_EMPTY + s), 1);
+            mbar_init(bar(STN_FULL + s), 1); mbar_init(bar(STN_EMPTY + s), 1);
+            mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(PD_FULL + s), 8);
+        }
+        mbar_init(bar(ACC_DONE), 1);
         *giveup = 0;
         mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 256);
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
     fence_before();
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S^T[2] at 0 / 32, dP^T[2] at 64 / 96, dV at 128, dK at 192
 
     if (warp == 8) {
+        // ------------------------------------------------------------ producer
         if (lane == 0) {
             const int row0 = b * T;
             mbar_arrive_expect_tx(bar(KV_FULL), 65536);
@@ -292,149 +304,160 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                     tma_load_2d(base + OFF_V + half * 16384 + rr * 8192, &mapQKV_k64, 2 * C + h * HS + half * 32, row0 + j0 + rr * 64, bar(KV_FULL));
                 }
             bool ok = true;
-            int armed[STAGES] = {-1, -1, -1};
+            int armed_k[STAGES] = {-1, -1}, armed_n[STAGES] = {-1, -1};
             for (int i = 0; i < nb; ++i) {
                 const int st = i % STAGES;
                 const uint32_t ph = (uint32_t)((i / STAGES) & 1);
-                if (!mbar_wait(bar(ST_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(ST_FULL + st), STAGE_BYTES);
-                armed[st] = (int)ph;
-                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
                 const int qrow = row0 + (ib0 + i) * QB;
+                if (!mbar_wait(bar(STK_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(STK_FULL + st), STK_BYTES);
+                armed_k[st] = (int)ph;
+                const uint32_t sk = base + OFF_STK + st * STK_BYTES;
                 for (int half = 0; half < 2; ++half) {
-                    tma_load_2d(sb + half * 4096, &mapQKV_k32, h * HS + half * 32, qrow, bar(ST_FULL + st));
-                    tma_load_2d(sb + 8192 + half * 4096, &mapQKV_n32, h * HS + half * 32, qrow, bar(ST_FULL + st));
-                    tma_load_2d(sb + 16384 + half * 4096, &mapDO_k32, h * HS + half * 32, qrow, bar(ST_FULL + st));
-                    tma_load_2d(sb + 24576 + half * 4096, &mapDO_n32, h * HS + half * 32, qrow, bar(ST_FULL + st));
+                    tma_load_2d(sk + half * 8192, &mapQKV_k64, h * HS + half * 32, qrow, bar(STK_FULL + st));
+                    tma_load_2d(sk + 16384 + half * 8192, &mapDO_k64, h * HS + half * 32, qrow, bar(STK_FULL + st));
+                }
+                if (!mbar_wait(bar(STN_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(STN_FULL + st), STN_BYTES);
+                armed_n[st] = (int)ph;
+                const uint32_t sn = base + OFF_STN + st * STN_BYTES;
+                for (int half = 0; half < 2; ++half) {
+                    tma_load_2d(sn + half * 8192, &mapQKV_n64, h * HS + half * 32, qrow, bar(STN_FULL + st));
+                    tma_load_2d(sn + 16384 + half * 8192, &mapDO_n64, h * HS + half * 32, qrow, bar(STN_FULL + st));
                 }
             }
             if (!ok) {
                 mbar_drain(bar(KV_FULL), 0);
-                for (int s = 0; s < STAGES; ++s)
-                    if (armed[s] >= 0) mbar_drain(bar(ST_FULL + s), (uint32_t)armed[s]);
+                for (int s = 0; s < STAGES; ++s) {
+                    if (armed_k[s] >= 0) mbar_drain(bar(STK_FULL + s), (uint32_t)armed_k[s]);
+                    if (armed_n[s] >= 0) mbar_drain(bar(STN_FULL + s), (uint32_t)armed_n[s]);
+                }
             }
         }
     } else if (warp == 9) {
+        // -------------------------------------------------------------- issuer
         if (lane == 0) {
-            const uint32_t idesc_st = make_idesc(2, 0, 0, QB, KT);     // [128 keys x 32 queries]
-            const uint32_t idesc_acc = make_idesc(2, 0, 1, HS, KT);    // [128 keys x 64] = A (K-major) x B (MN-major)
-            auto issue_sp = [&](int st, int buf) {
-                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+            const uint32_t idesc_st = make_idesc(2, 0, 0, QB, KT);     // [128 keys x 64 queries], both operands K-major
+            const uint32_t idesc_acc = make_idesc(2, 0, 1, HS, KT);    // [128 keys x 64] = A (tensor memory) x B (MN-major)
+            auto issue_sp = [&](int st) {
+                const uint32_t sk = base + OFF_STK + st * STK_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + (uint32_t)(buf * 32), smem_desc_kmajor(base + OFF_K + half * 16384 + off),
-                             smem_desc_kmajor(sb + half * 4096 + off), idesc_st, ks ? 1u : 0u);
+                    mma_tf32(tmem_base + COL_S + (uint32_t)(st * 64), smem_desc_kmajor(base + OFF_K + half * 16384 + off),
+                             smem_desc_kmajor(sk + half * 8192 + off), idesc_st, ks ? 1u : 0u);
                 }
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + (uint32_t)(64 + buf * 32), smem_desc_kmajor(base + OFF_V + half * 16384 + off),
-                             smem_desc_kmajor(sb + 16384 + half * 4096 + off), idesc_st, ks ? 1u : 0u);
+                    mma_tf32(tmem_base + COL_DP + (uint32_t)(st * 64), smem_desc_kmajor(base + OFF_V + half * 16384 + off),
+                             smem_desc_kmajor(sk + 16384 + half * 8192 + off), idesc_st, ks ? 1u : 0u);
                 }
             };
             bool ok = mbar_wait(bar(KV_FULL), 0, giveup);
-            if (ok) ok = mbar_wait(bar(ST_FULL + 0), 0, giveup);
-            if (ok) { fence_after(); issue_sp(0, 0); commit(bar(SP_FULL + 0)); }
-            for (int i = 0; ok && i < nb; ++i) {
-                const int st = i % STAGES;
-                if (i + 1 < nb) {
-                    const int nbuf = (i + 1) & 1;
-                    if (!mbar_wait(bar(ST_FULL + (i + 1) % STAGES), (uint32_t)(((i + 1) / STAGES) & 1), giveup)) { ok = false; break; }
-                    if (i >= 1 && !mbar_wait(bar(SP_EMPTY + nbuf), (uint32_t)(((i - 1) / 2) & 1), giveup)) { ok = false; break; }
-                    fence_after();
-                    issue_sp((i + 1) % STAGES, nbuf);
-                    commit(bar(SP_FULL + nbuf));
-                }
-                const int pb = i & 1;                     // P^T / dS^T buffer of this block
-                if (!mbar_wait(bar(PD_FULL + pb), (uint32_t)((i / 2) & 1), giveup)) { ok = false; break; }
+            if (ok && nb > 0) ok = mbar_wait(bar(STK_FULL + 0), 0, giveup);
+            if (ok && nb > 0) {
                 fence_after();
-                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < QB / 8; ++ks) {     // dV += P^T dO
-                    mma_tf32(tmem_base + 128, smem_desc_kmajor(base + OFF_PT + pb * 16384 + ks * 32),
-                             smem_desc_mnmajor32(sb + 24576 + ks * 1024, 4096), idesc_acc, (i | ks) ? 1u : 0u);
-                }
-#pragma unroll
-                for (int ks = 0; ks < QB / 8; ++ks) {     // dK += dS^T Q
-                    mma_tf32(tmem_base + 192, smem_desc_kmajor(base + OFF_DST + pb * 16384 + ks * 32),
-                             smem_desc_mnmajor32(sb + 8192 + ks * 1024, 4096), idesc_acc, (i | ks) ? 1u : 0u);
-                }
-                commit(bar(PD_DONE + pb));
-                commit(bar(ST_EMPTY + st));
+                issue_sp(0);
+                commit(bar(SP_FULL + 0));
+                commit(bar(STK_EMPTY + 0));
             }
+            for (int i = 0; ok && i < nb; ++i) {
+                const int st = i & 1;
+                const uint32_t ph = (uint32_t)((i >> 1) & 1);
+                if (i + 1 < nb) {
+                    // block i+1 goes into the other S^T / dP^T buffer; the products that read that buffer's
+                    // P^T / dS^T (block i-1) were issued before this point, and the tensor core runs in order
+                    const int s1 = (i + 1) & 1;
+                    if (!mbar_wait(bar(STK_FULL + s1), (uint32_t)(((i + 1) >> 1) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    issue_sp(s1);
+                    commit(bar(SP_FULL + s1));
+                    commit(bar(STK_EMPTY + s1));
+                }
+                if (!mbar_wait(bar(STN_FULL + st), ph, giveup)) { ok = false; break; }
+                if (!mbar_wait(bar(PD_FULL + st), ph, giveup)) { ok = false; break; }
+                fence_after();
+                const uint32_t sn = base + OFF_STN + st * STN_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < QB / 8; ++ks)       // dV += P^T dO
+                    mma_tf32_ts(tmem_base + COL_DV, tmem_base + COL_S + (uint32_t)(st * 64 + ks * 8),
+                                smem_desc_mnmajor32(sn + 16384 + ks * 1024, 8192), idesc_acc, (i | ks) ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < QB / 8; ++ks)       // dK += dS^T Q
+                    mma_tf32_ts(tmem_base + COL_DK, tmem_base + COL_DP + (uint32_t)(st * 64 + ks * 8),
+                                smem_desc_mnmajor32(sn + ks * 1024, 8192), idesc_acc, (i | ks) ? 1u : 0u);
+                commit(bar(STN_EMPTY + st));
+            }
+            if (ok) commit(bar(ACC_DONE));
         }
     } else {
+        // ------------------------------------------------------- P^T and dS^T
         const int quad = warp & 3, colhalf = warp >> 2;
         const int r = quad * 32 + lane;
         const int kj = j0 + r;                             // this thread's key
         const float scale_log2e = scale * LOG2E;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        uint8_t *ptrow0 = gen + OFF_PT + r * 128, *dstrow0 = gen + OFF_DST + r * 128;
+        const bool vec_stats = (T & 3) == 0 && (((uintptr_t)lse | (uintptr_t)dsum) & 15) == 0;
         bool ok = true;
         for (int i = 0; i < nb; ++i) {
             const int buf = i & 1;
-            const int qc0 = (ib0 + i) * QB + colhalf * 16;     // first query column of this thread
-            // per-column lse (in log2 units) and D; every thread of the CTA reads the same 32 values
-            float lc[16], dc[16];
-            if ((T & 3) == 0 && qc0 + 16 <= T && (((uintptr_t)lse | (uintptr_t)dsum) & 15) == 0) {
-                // 16 consecutive, 16-byte aligned values of each: four 128-bit loads
+            const int qc0 = (ib0 + i) * QB + colhalf * 32;     // first query column of this thread
+            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((i >> 1) & 1), giveup)) { ok = false; break; }
+            fence_after();
+            float s[32], dp[32];
+            const uint32_t s_addr = lane_addr + COL_S + (uint32_t)(buf * 64 + colhalf * 32);
+            const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(buf * 64 + colhalf * 32);
+            tmem_ld32_nowait(s_addr, s);
+            tmem_ld32_nowait(dp_addr, dp);
+            tmem_wait_ld();
+            // per-column lse and D: every thread of the CTA reads the same 64 values, so these hit L1
+            if (vec_stats && qc0 + 32 <= T) {
                 const float4 *lp = reinterpret_cast<const float4 *>(lse + (size_t)bh * T + qc0);
                 const float4 *dp4 = reinterpret_cast<const float4 *>(dsum + (size_t)bh * T + qc0);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float4 a = __ldg(lp + c), d4 = __ldg(dp4 + c);
-                    lc[c * 4] = a.x * LOG2E; lc[c * 4 + 1] = a.y * LOG2E; lc[c * 4 + 2] = a.z * LOG2E; lc[c * 4 + 3] = a.w * LOG2E;
-                    dc[c * 4] = d4.x; dc[c * 4 + 1] = d4.y; dc[c * 4 + 2] = d4.z; dc[c * 4 + 3] = d4.w;
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 l4 = __ldg(lp + c4), d4 = __ldg(dp4 + c4);
+                    const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = c4 * 4 + e;
+                        float p = fast_exp2(fmaf(s[c], scale_log2e, -lv[e] * LOG2E));
+                        if (qc0 + c < kj) p = 0.0f;        // causal mask
+                        s[c] = round_tf32_alu(p);
+                        dp[c] = round_tf32_alu(p * (dp[c] - dv[e]));
+                    }
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
+                for (int c = 0; c < 32; ++c) {
                     const int q = qc0 + c;
-                    lc[c] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
-                    dc[c] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+                    const float lq = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
+                    const float dq_ = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+                    float p = fast_exp2(fmaf(s[c], scale_log2e, -lq));
+                    if (q < kj || q >= T) p = 0.0f;        // causal mask and the ragged end
+                    s[c] = round_tf32_alu(p);
+                    dp[c] = round_tf32_alu(p * (dp[c] - dq_));
                 }
             }
-            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((i / 2) & 1), giveup)) { ok = false; break; }
-            fence_after();
-            float s[16], dp[16];
-            tmem_ld16(lane_addr + (uint32_t)(buf * 32 + colhalf * 16), s);
-            tmem_ld16(lane_addr + (uint32_t)(64 + buf * 32 + colhalf * 16), dp);
+            tmem_st32_nowait(s_addr, s);
+            tmem_st32_nowait(dp_addr, dp);
+            tmem_wait_st();
             fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(SP_EMPTY + buf));
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const int q = qc0 + c;
-                float p = fast_exp2(fmaf(s[c], scale_log2e, -lc[c]));
-                if (q < kj || q >= T) p = 0.0f;            // causal mask and the ragged end
-                s[c] = round_tf32_alu(p);
-                dp[c] = round_tf32_alu(p * (dp[c] - dc[c]));
-            }
-            // P^T and dS^T go into the buffers the products of two blocks ago have finished reading
-            if (i > 1 && !mbar_wait(bar(PD_DONE + buf), (uint32_t)(((i - 2) / 2) & 1), giveup)) { ok = false; break; }
-            uint8_t *ptrow = ptrow0 + buf * 16384, *dstrow = dstrow0 + buf * 16384;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int unit = ((colhalf * 4 + c) ^ (r & 7)) << 4;
-                *reinterpret_cast<float4 *>(ptrow + unit) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
-                *reinterpret_cast<float4 *>(dstrow + unit) = make_float4(dp[c * 4], dp[c * 4 + 1], dp[c * 4 + 2], dp[c * 4 + 3]);
-            }
-            fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(PD_FULL + buf));
         }
-        if (ok && nb > 0 && mbar_wait(bar(PD_DONE + ((nb - 1) & 1)), (uint32_t)(((nb - 1) / 2) & 1), giveup)) {
+        if (ok && nb > 0 && mbar_wait(bar(ACC_DONE), 0, giveup)) {
             fence_after();
             float v[32];
-            tmem_ld32(lane_addr + (uint32_t)(128 + colhalf * 32), v);
+            tmem_ld32(lane_addr + COL_DV + (uint32_t)(colhalf * 32), v);
             if (kj < T) {
                 float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + 2 * C + h * HS + colhalf * 32;
 #pragma unroll
                 for (int d = 0; d < 32; d += 4)
                     *reinterpret_cast<float4 *>(dst + d) = out4(v[d], v[d + 1], v[d + 2], v[d + 3], round_out);
             }
-            tmem_ld32(lane_addr + (uint32_t)(192 + colhalf * 32), v);
+            tmem_ld32(lane_addr + COL_DK + (uint32_t)(colhalf * 32), v);
             if (kj < T) {
                 float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + C + h * HS + colhalf * 32;
 #pragma unroll
@@ -449,7 +472,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
     if (warp == 9) {
         __syncwarp();
         fence_after();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, 512);
     }
     if (threadIdx.x == 0 && *giveup) {
         *reinterpret_cast<volatile int *>(status) = 4;
@@ -495,14 +518,11 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
         q = sq; g = sg;
     }
     const long long rows = (long long)B * T;
-    CUtensorMap qk64, qn64, qk32, qn32, gk64, gk32, gn32;
+    CUtensorMap qk64, qn64, gk64, gn64;
     BMB_TRY(make_map_2d(&qk64, q, 4, rows, 3LL * C, 3LL * C * 4, 64, false));
     BMB_TRY(make_map_2d(&qn64, q, 4, rows, 3LL * C, 3LL * C * 4, 64, true));
-    BMB_TRY(make_map_2d(&qk32, q, 4, rows, 3LL * C, 3LL * C * 4, 32, false));
-    BMB_TRY(make_map_2d(&qn32, q, 4, rows, 3LL * C, 3LL * C * 4, 32, true));
     BMB_TRY(make_map_2d(&gk64, g, 4, rows, C, (long long)C * 4, 64, false));
-    BMB_TRY(make_map_2d(&gk32, g, 4, rows, C, (long long)C * 4, 32, false));
-    BMB_TRY(make_map_2d(&gn32, g, 4, rows, C, (long long)C * 4, 32, true));
+    BMB_TRY(make_map_2d(&gn64, g, 4, rows, C, (long long)C * 4, 64, true));
     {
         std::lock_guard<std::mutex> lk(g_mu);
         const int d = current_device();
@@ -516,7 +536,7 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
     // x = (batch, head), y = position: the dispatch order runs through all heads at the position with
     // the most work first, so the long CTAs start early and the short ones fill the tail.
     dim3 gkv(B * NH, (T + dkv::KT - 1) / dkv::KT), gq(B * NH, (T + dq::QT - 1) / dq::QT);
-    flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qk32, qn32, gk32, gn32, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
+    flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     flash_bwd_dq_tc_k<<<gq, dq::THREADS, dq::SMEM, st>>>(qk64, qn64, gk64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     count_launch(2);
     BMB_LAUNCH_CHECK();
