@@ -71,6 +71,9 @@ SIGNATURES = {
     "bmb_encoder_backward": (_i, [_p, _p, _p, _p, _i, _i, _i]),
     "bmb_layernorm_forward": (_i, [_p, _p, _p, _p, _p, _p, _i, _i]),
     "bmb_layernorm_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i]),
+    "bmb_gelu_backward_colsum": (_i, [_p, _p, _p, _p, _i, _i]),
+    "bmb_residual_layernorm_forward": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i]),
+    "bmb_layernorm_backward_colsum": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i]),
     "bmb_layernorm_backward_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i]),
     "bmb_gelu_forward": (_i, [_p, _p, _i]),
     "bmb_gelu_backward": (_i, [_p, _p, _p, _i]),

@@ -82,11 +82,14 @@ __global__ void encoder_bwd_wte_k(float *__restrict__ dwte, const float *__restr
 // One warp per row, the row held in registers between the mean pass, the
 // variance pass and the write (src/nn.cu:54-78: two-pass biased variance,
 // rsqrtf(var + 1e-5)).  C % 4 == 0 and C <= 32*4*V4 floats.
+// With `addend`: the row normalised is inp + addend, and that sum is also stored to `sum_out`
+// (the residual add of a transformer block riding in the layernorm that follows it).
 template <int V4>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_warp_k(float *__restrict__ out, float *__restrict__ mean, float *__restrict__ rstd,
                      const float *__restrict__ inp, const float *__restrict__ weight,
-                     const float *__restrict__ bias, int N, int C, int rnd) {
+                     const float *__restrict__ bias, int N, int C, int rnd,
+                     const float *__restrict__ addend = nullptr, float *__restrict__ sum_out = nullptr) {
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int C4 = C >> 2;
@@ -99,6 +102,11 @@ layernorm_fwd_warp_k(float *__restrict__ out, float *__restrict__ mean, float *_
         for (int i = 0; i < V4; ++i) {
             const int c4 = lane + 32 * i;
             v[i] = (c4 < C4) ? LD4(x + c4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (addend && c4 < C4) {
+                const float4 a = LD4(addend + (size_t)row * C + c4 * 4);
+                v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+                ST4(sum_out + (size_t)row * C + c4 * 4) = v[i];
+            }
             sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
         const float mu = warp_sum(sum) / C;
@@ -158,21 +166,24 @@ __global__ void layernorm_fwd_block_k(float *__restrict__ out, float *__restrict
 // fold their partials through shared memory, and the block writes one row of
 // `partial` ([gridDim.x][2*C]: dw then db).  column_add_k finishes the sum in a
 // fixed order, so the parameter gradients are reproducible run to run.
-template <int V4>
+// COLSUM: `partial` rows are 3*C wide and the third part holds the column sums of the updated dinp
+// (as stored), which is the bias gradient of the projection that produced this layer's input.
+template <int V4, bool COLSUM>
 __global__ void __launch_bounds__(128)
 layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
                      const float *__restrict__ dout, const float *__restrict__ inp,
                      const float *__restrict__ weight, const float *__restrict__ mean,
                      const float *__restrict__ rstd, int N, int C, int rnd) {
-    extern __shared__ float fold[];  // 2*C floats
+    extern __shared__ float fold[];  // 2*C floats (3*C with COLSUM)
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
     const int C4 = C >> 2;
-    float4 dw[V4], db[V4];
+    float4 dw[V4], db[V4], dc[COLSUM ? V4 : 1];
 #pragma unroll
     for (int i = 0; i < V4; ++i) {
         dw[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (COLSUM) dc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     for (int row = blockIdx.x * warps_per_block + wid; row < N; row += gridDim.x * warps_per_block) {
         const float *x = inp + (size_t)row * C;
@@ -214,7 +225,9 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
                 d.y += rs * (g[i].y - m1 - xh[i].y * m2);
                 d.z += rs * (g[i].z - m1 - xh[i].z * m2);
                 d.w += rs * (g[i].w - m1 - xh[i].w * m2);
-                ST4(dx + c4 * 4) = rnd4(d, rnd);
+                d = rnd4(d, rnd);
+                ST4(dx + c4 * 4) = d;
+                if (COLSUM) { dc[i].x += d.x; dc[i].y += d.y; dc[i].z += d.z; dc[i].w += d.w; }
             }
         }
     }
@@ -233,13 +246,22 @@ layernorm_bwd_warp_k(float *__restrict__ dinp, float *__restrict__ partial,
                     }
                     ST4(fold + c4 * 4) = a;
                     ST4(fold + C + c4 * 4) = b;
+                    if (COLSUM) {
+                        float4 c = dc[i];
+                        if (turn > 0) {
+                            const float4 pc = LD4(fold + 2 * C + c4 * 4);
+                            c.x += pc.x; c.y += pc.y; c.z += pc.z; c.w += pc.w;
+                        }
+                        ST4(fold + 2 * C + c4 * 4) = c;
+                    }
                 }
             }
         }
         __syncthreads();
     }
-    float *dst = partial + (size_t)blockIdx.x * 2 * C;
-    for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) dst[i] = fold[i];
+    constexpr int PARTS = COLSUM ? 3 : 2;
+    float *dst = partial + (size_t)blockIdx.x * PARTS * C;
+    for (int i = threadIdx.x; i < PARTS * C; i += blockDim.x) dst[i] = fold[i];
 }
 
 // Any C: block per row, parameter-gradient partials through atomics on a
@@ -272,10 +294,10 @@ __global__ void layernorm_bwd_block_k(float *__restrict__ dinp, float *__restric
 // dst[c] += sum_{g < G} partial[g][c]   for c < ncols, in a fixed order: a block
 // covers 32 columns, its 8 warps each sum every 8th row of `partial`, and the 8
 // sub-sums are added in warp order.  If dst2 != nullptr the columns
-// [ncols_first, ncols) go to dst2.
+// [ncols_first, ncols) go to dst2; if dst3 != nullptr those from 2 * ncols_first on go to dst3.
 __global__ void __launch_bounds__(256)
 column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
-             const float *__restrict__ partial, int G, int ncols) {
+             const float *__restrict__ partial, int G, int ncols, float *__restrict__ dst3 = nullptr) {
     __shared__ float red[8][33];
     const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + cx;
@@ -288,7 +310,8 @@ column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
         float t = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) t += red[i][cx];
-        if (dst2 && c >= ncols_first) dst2[c - ncols_first] += t;
+        if (dst3 && c >= 2 * ncols_first) dst3[c - 2 * ncols_first] += t;
+        else if (dst2 && c >= ncols_first) dst2[c - ncols_first] += t;
         else dst[c] += t;
     }
 }
@@ -336,6 +359,10 @@ __global__ void add3_k(float *__restrict__ out, const float *__restrict__ a,
         ST4(out + i * 4) = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
     }
 }
+__global__ void add3_scalar_k(float *__restrict__ out, const float *__restrict__ a, const float *__restrict__ b, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = a[i] + b[i];
+}
 __global__ void bias_fwd_k(float *__restrict__ out, const float *__restrict__ bias, int C,
                            long long n4, int rnd) {
     const int C4 = C >> 2;
@@ -371,6 +398,39 @@ bias_bwd_partial_k(float *__restrict__ partial, const float *__restrict__ dout, 
     for (; n < N; n += step) {
         const float4 g = LD4(dout + (size_t)n * C + c4 * 4);
         s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
+    }
+    ST4(partial + (size_t)blockIdx.y * C + c4 * 4) = s;
+}
+// GELU backward over an (N x C) matrix that also leaves the column sums of its result (the bias
+// gradient of the projection that produced the GELU input) in partial[blockIdx.y][C]: the grid is
+// that of bias_bwd_partial_k, each thread walks its float4 column down a residue class of rows.
+__global__ void __launch_bounds__(256)
+gelu_bwd_colsum_k(float *__restrict__ partial, float *__restrict__ dinp, const float *__restrict__ inp,
+                  const float *__restrict__ dout, int N, int C, int rnd) {
+    const int c4 = blockIdx.x * 256 + threadIdx.x;
+    if (c4 * 4 >= C) return;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int step = gridDim.y;
+    int n = blockIdx.y;
+    for (; n + step < N; n += 2 * step) {          // two rows in flight
+        const size_t o0 = (size_t)n * C + c4 * 4, o1 = (size_t)(n + step) * C + c4 * 4;
+        const float4 x0 = LD4(inp + o0), g0 = LD4(dout + o0), x1 = LD4(inp + o1), g1 = LD4(dout + o1);
+        float4 d0, d1;
+        d0.x = dgelu1(x0.x, g0.x); d0.y = dgelu1(x0.y, g0.y); d0.z = dgelu1(x0.z, g0.z); d0.w = dgelu1(x0.w, g0.w);
+        d1.x = dgelu1(x1.x, g1.x); d1.y = dgelu1(x1.y, g1.y); d1.z = dgelu1(x1.z, g1.z); d1.w = dgelu1(x1.w, g1.w);
+        d0 = rnd4(d0, rnd); d1 = rnd4(d1, rnd);
+        ST4(dinp + o0) = d0; ST4(dinp + o1) = d1;
+        s.x += d0.x; s.y += d0.y; s.z += d0.z; s.w += d0.w;
+        s.x += d1.x; s.y += d1.y; s.z += d1.z; s.w += d1.w;
+    }
+    for (; n < N; n += step) {
+        const size_t o0 = (size_t)n * C + c4 * 4;
+        const float4 x0 = LD4(inp + o0), g0 = LD4(dout + o0);
+        float4 d0;
+        d0.x = dgelu1(x0.x, g0.x); d0.y = dgelu1(x0.y, g0.y); d0.z = dgelu1(x0.z, g0.z); d0.w = dgelu1(x0.w, g0.w);
+        d0 = rnd4(d0, rnd);
+        ST4(dinp + o0) = d0;
+        s.x += d0.x; s.y += d0.y; s.z += d0.z; s.w += d0.w;
     }
     ST4(partial + (size_t)blockIdx.y * C + c4 * 4) = s;
 }
@@ -603,8 +663,8 @@ bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 // Shared with other translation units of the library.
 int launch_column_add(float *dst, float *dst2, int ncols_first, const float *partial, int G,
-                      int ncols, cudaStream_t st) {
-    column_add_k<<<ceil_div(ncols, 32), 256, 0, st>>>(dst, dst2, ncols_first, partial, G, ncols);
+                      int ncols, cudaStream_t st, float *dst3 = nullptr) {
+    column_add_k<<<ceil_div(ncols, 32), 256, 0, st>>>(dst, dst2, ncols_first, partial, G, ncols, dst3);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -617,20 +677,27 @@ int layernorm_bwd_blocks(int N) {
     const int cap = 3 * sm_count();     // 128-thread blocks, three resident per SM
     return g > cap ? cap : (g < 1 ? 1 : g);
 }
+// dcolsum != nullptr: also dcolsum += column sums of the updated dinp; `partial` then holds
+// G * 3 * C floats.
 int layernorm_backward_with_scratch(float *dinp, float *dweight, float *dbias, const float *dout,
                                     const float *inp, const float *weight, const float *mean,
                                     const float *rstd, int N, int C, float *partial, int G,
-                                    cudaStream_t st) {
+                                    cudaStream_t st, float *dcolsum = nullptr) {
     const int rnd = emit_rounded() ? 1 : 0;
-    const size_t sm = 2 * C * sizeof(float);
     // registers follow the row length: V4 float4 per lane cover C <= 128 * V4
-    if (C <= 256) layernorm_bwd_warp_k<2><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
-    else if (C <= 512) layernorm_bwd_warp_k<4><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
-    else if (C <= 768) layernorm_bwd_warp_k<6><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
-    else layernorm_bwd_warp_k<8><<<G, 128, sm, st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);
+#define BMB_LN_BWD(V4_)                                                                                                   \
+    do {                                                                                                                  \
+        if (dcolsum) layernorm_bwd_warp_k<V4_, true><<<G, 128, 3 * C * sizeof(float), st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd); \
+        else layernorm_bwd_warp_k<V4_, false><<<G, 128, 2 * C * sizeof(float), st>>>(dinp, partial, dout, inp, weight, mean, rstd, N, C, rnd);        \
+    } while (0)
+    if (C <= 256) BMB_LN_BWD(2);
+    else if (C <= 512) BMB_LN_BWD(4);
+    else if (C <= 768) BMB_LN_BWD(6);
+    else BMB_LN_BWD(8);
+#undef BMB_LN_BWD
     count_launch();
     BMB_LAUNCH_CHECK();
-    return launch_column_add(dweight, dbias, C, partial, G, 2 * C, st);
+    return launch_column_add(dweight, dbias, C, partial, G, (dcolsum ? 3 : 2) * C, st, dcolsum);
 }
 
 }  // namespace bmb
@@ -684,6 +751,49 @@ int bmb_layernorm_forward(float *out, float *mean, float *rstd, const float *inp
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
+}
+
+int bmb_residual_layernorm_forward(float *sum_out, float *out, float *mean, float *rstd, const float *a,
+                                   const float *b, const float *weight, const float *bias, int N, int C) {
+    if (N <= 0 || C <= 0) return BMB_OK;
+    cudaStream_t st = cur_stream();
+    const bool fast = (C % 4 == 0) && C <= 1024 && aligned16(out) && aligned16(a) && aligned16(b) &&
+                      aligned16(sum_out) && aligned16(weight) && aligned16(bias);
+    if (!fast) {
+        const long long n = (long long)N * C;
+        add3_scalar_k<<<grid_for(n, 256, 8), 256, 0, st>>>(sum_out, a, b, n);
+        count_launch();
+        BMB_LAUNCH_CHECK();
+        return bmb_layernorm_forward(out, mean, rstd, sum_out, weight, bias, N, C);
+    }
+    int g = ceil_div(N, 8);
+    const int cap = sm_count() * 8;
+    if (g > cap) g = cap;
+    const int rnd = emit_rounded() ? 1 : 0;
+    if (C <= 256) layernorm_fwd_warp_k<2><<<g, 256, 0, st>>>(out, mean, rstd, a, weight, bias, N, C, rnd, b, sum_out);
+    else if (C <= 512) layernorm_fwd_warp_k<4><<<g, 256, 0, st>>>(out, mean, rstd, a, weight, bias, N, C, rnd, b, sum_out);
+    else if (C <= 768) layernorm_fwd_warp_k<6><<<g, 256, 0, st>>>(out, mean, rstd, a, weight, bias, N, C, rnd, b, sum_out);
+    else layernorm_fwd_warp_k<8><<<g, 256, 0, st>>>(out, mean, rstd, a, weight, bias, N, C, rnd, b, sum_out);
+    count_launch();
+    BMB_LAUNCH_CHECK();
+    return BMB_OK;
+}
+
+int bmb_layernorm_backward_colsum(float *dinp, float *dweight, float *dbias, float *dcolsum, const float *dout,
+                                  const float *inp, const float *weight, const float *mean,
+                                  const float *rstd, int N, int C) {
+    if (N <= 0 || C <= 0) return BMB_OK;
+    cudaStream_t st = cur_stream();
+    const bool fast = (C % 4 == 0) && C <= 1024 && aligned16(dinp) && aligned16(inp) &&
+                      aligned16(dout) && aligned16(weight);
+    if (!fast || !dcolsum) {
+        BMB_TRY(bmb_layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, N, C));
+        return dcolsum ? bmb_bias_backward(dcolsum, dinp, N, C) : BMB_OK;
+    }
+    const int G = layernorm_bwd_blocks(N);
+    float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)G * 3 * C * sizeof(float));
+    if (!partial) return BMB_E_CUDA;
+    return layernorm_backward_with_scratch(dinp, dweight, dbias, dout, inp, weight, mean, rstd, N, C, partial, G, st, dcolsum);
 }
 
 int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias, const float *dout,
@@ -773,6 +883,25 @@ int bmb_gelu_backward(float *dinp, const float *inp, const float *dout, int n) {
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
+}
+int bmb_gelu_backward_colsum(float *dinp, float *dcolsum, const float *inp, const float *dout, int N, int C) {
+    if (N <= 0 || C <= 0) return BMB_OK;
+    cudaStream_t st = cur_stream();
+    if (C % 4 != 0 || !aligned16(dinp) || !aligned16(inp) || !aligned16(dout) || !dcolsum) {
+        if ((long long)N * C % 4) return fail(BMB_E_ARG, "gelu_backward_colsum: N*C must be a multiple of 4");
+        BMB_TRY(bmb_gelu_backward(dinp, inp, dout, N * C));
+        return dcolsum ? bmb_bias_backward(dcolsum, dinp, N, C) : BMB_OK;
+    }
+    const int strips = ceil_div(C / 4, 256);
+    int gy = (4 * sm_count()) / strips;
+    if (gy < 1) gy = 1;
+    if (gy > N) gy = N;
+    float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)gy * C * sizeof(float));
+    if (!partial) return BMB_E_CUDA;
+    gelu_bwd_colsum_k<<<dim3(strips, gy), 256, 0, st>>>(partial, dinp, inp, dout, N, C, emit_rounded() ? 1 : 0);
+    count_launch();
+    BMB_LAUNCH_CHECK();
+    return launch_column_add(dcolsum, nullptr, C, partial, gy, C, st);
 }
 int bmb_residual_forward(float *out, const float *a, const float *b, int n) {
     if (n % 4) return fail(BMB_E_ARG, "residual_forward: n=%d must be a multiple of 4", n);

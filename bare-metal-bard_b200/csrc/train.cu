@@ -136,13 +136,14 @@ int forward(bmb_trainer *t) {
 
     BMB_TRY(bmb_encoder_forward(t->encoded, t->d_tokens, P + t->poff[P_WTE], P + t->poff[P_WPE], B, T, C));
     float *residual = t->encoded;
+    // The first layernorm stands alone; every later one (and the final one) rides with the
+    // residual add that produces its input.
+    BMB_TRY(bmb_layernorm_forward(t->ln1, t->ln1_mean, t->ln1_rstd, residual, P + t->poff[P_LN1W], P + t->poff[P_LN1B], N, C));
     for (int l = 0; l < L; ++l) {
         float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * BT3C, *atty = t->atty + l * BTC;
         float *attproj = t->attproj + l * BTC, *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
         float *fch = t->fch + l * BT4C, *fchg = t->fch_gelu + l * BT4C, *fcproj = t->fcproj + l * BTC;
         float *res3 = t->residual3 + l * BTC;
-        BMB_TRY(bmb_layernorm_forward(ln1, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, residual,
-                                      P + t->poff[P_LN1W] + (size_t)l * C, P + t->poff[P_LN1B] + (size_t)l * C, N, C));
         if (fz) {
             BMB_TRY(mm(t, wflag | BMB_GEMM_C_ROUNDED, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv,
                        P + t->poff[P_QKVB] + (size_t)l * 3 * C));
@@ -163,9 +164,8 @@ int forward(bmb_trainer *t) {
             BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
             BMB_TRY(bmb_bias_forward(attproj, P + t->poff[P_APB] + (size_t)l * C, N, C));
         }
-        BMB_TRY(bmb_residual_forward(res2, residual, attproj, (int)BTC));
-        BMB_TRY(bmb_layernorm_forward(ln2, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, res2,
-                                      P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
+        BMB_TRY(bmb_residual_layernorm_forward(res2, ln2, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, residual, attproj,
+                                               P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
         if (fz) {
             BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch,
                        P + t->poff[P_FCB] + (size_t)l * 4 * C));
@@ -181,11 +181,15 @@ int forward(bmb_trainer *t) {
             BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj));
             BMB_TRY(bmb_bias_forward(fcproj, P + t->poff[P_FPB] + (size_t)l * C, N, C));
         }
-        BMB_TRY(bmb_residual_forward(res3, res2, fcproj, (int)BTC));
+        if (l + 1 < L)
+            BMB_TRY(bmb_residual_layernorm_forward(res3, t->ln1 + (l + 1) * BTC, t->ln1_mean + (l + 1) * BT, t->ln1_rstd + (l + 1) * BT,
+                                                   res2, fcproj, P + t->poff[P_LN1W] + (size_t)(l + 1) * C,
+                                                   P + t->poff[P_LN1B] + (size_t)(l + 1) * C, N, C));
+        else
+            BMB_TRY(bmb_residual_layernorm_forward(res3, t->lnf, t->lnf_mean, t->lnf_rstd, res2, fcproj, P + t->poff[P_LNFW],
+                                                   P + t->poff[P_LNFB], N, C));
         residual = res3;
     }
-    BMB_TRY(bmb_layernorm_forward(t->lnf, t->lnf_mean, t->lnf_rstd, residual, P + t->poff[P_LNFW],
-                                  P + t->poff[P_LNFB], N, C));
     BMB_TRY(mm(t, wflag, 0, 1, N, Vp, C, t->lnf, W + t->poff[P_WTE], 0.0f, t->logits));
     // Loss and its gradient with respect to the logits in one sweep (mean loss: dloss = 1/N).
     BMB_TRY(bmb_softmax_crossentropy_fused(t->dlogits, t->losses, t->logits, t->d_targets, N, V, Vp, 1.0f / N));
@@ -218,8 +222,11 @@ int backward(bmb_trainer *t) {
     BMB_TRY(mm(t, gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
     float *last_res = t->residual3 + (size_t)(L - 1) * BTC;
     BMB_CUDA(cudaMemsetAsync(t->dres, 0, BTC * sizeof(float), t->st));
-    BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LNFW], G + t->poff[P_LNFB], t->dlnf, last_res,
-                                   P + t->poff[P_LNFW], t->lnf_mean, t->lnf_rstd, N, C));
+    // Each layernorm backward also sums the columns of the residual-stream gradient it leaves behind:
+    // that is the bias gradient of the projection feeding that point of the stream.
+    BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LNFW], G + t->poff[P_LNFB],
+                                          G + t->poff[P_FPB] + (size_t)(L - 1) * C, t->dlnf, last_res,
+                                          P + t->poff[P_LNFW], t->lnf_mean, t->lnf_rstd, N, C));
     for (int l = L - 1; l >= 0; --l) {
         float *residual = (l == 0) ? t->encoded : t->residual3 + (size_t)(l - 1) * BTC;
         float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * BT3C, *atty = t->atty + l * BTC;
@@ -229,16 +236,14 @@ int backward(bmb_trainer *t) {
 
         BMB_TRY(dx(wflag, N, 4 * C, C, t->dres, P_FPW, (size_t)l * C * 4 * C, t->dfch_gelu));
         BMB_TRY(mm(t, gflag, 1, 0, C, 4 * C, N, t->dres, fchg, 1.0f, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
-        BMB_TRY(bmb_bias_backward(G + t->poff[P_FPB] + lC, t->dres, N, C));
-        BMB_TRY(bmb_gelu_backward(t->dfch, fch, t->dfch_gelu, (int)BT4C));
+        BMB_TRY(bmb_gelu_backward_colsum(t->dfch, G + t->poff[P_FCB] + 4 * lC, fch, t->dfch_gelu, N, 4 * C));
         BMB_TRY(dx(wflag, N, C, 4 * C, t->dfch, P_FCW, (size_t)l * 4 * C * C, t->dln2));
         BMB_TRY(mm(t, gflag, 1, 0, 4 * C, C, N, t->dfch, ln2, 1.0f, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
-        BMB_TRY(bmb_bias_backward(G + t->poff[P_FCB] + 4 * lC, t->dfch, N, 4 * C));
-        BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC, t->dln2, res2,
-                                       P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
+        BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC,
+                                              G + t->poff[P_APB] + lC, t->dln2, res2,
+                                              P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
         BMB_TRY(dx(wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), N, C, C, t->dres, P_APW, (size_t)l * C * C, t->datty));
         BMB_TRY(mm(t, gflag, 1, 0, C, C, N, t->dres, atty, 1.0f, G + t->poff[P_APW] + (size_t)l * C * C));
-        BMB_TRY(bmb_bias_backward(G + t->poff[P_APB] + lC, t->dres, N, C));
         if (c.use_flash && fz && attn_cfg(c) == 2)
             BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH, true, t->st));
         else if (c.use_flash)
@@ -249,8 +254,9 @@ int backward(bmb_trainer *t) {
         BMB_TRY(dx(wflag, N, C, 3 * C, t->dqkv, P_QKVW, (size_t)l * 3 * C * C, t->dln1));
         BMB_TRY(mm(t, gflag, 1, 0, 3 * C, C, N, t->dqkv, ln1, 1.0f, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
-        BMB_TRY(bmb_layernorm_backward(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC, t->dln1, residual,
-                                       P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C));
+        BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC,
+                                              l > 0 ? G + t->poff[P_FPB] + lC - C : nullptr, t->dln1, residual,
+                                              P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C));
     }
     BMB_TRY(bmb_encoder_backward(G + t->poff[P_WTE], G + t->poff[P_WPE], t->dres, t->d_tokens, B, T, C));
     return BMB_OK;

@@ -154,6 +154,22 @@ int bmb_layernorm_backward_noalloc(float *dinp, float *dweight, float *dbias,
                                    const float *dout, const float *inp,
                                    const float *weight, const float *mean,
                                    const float *rstd, int N, int C);
+/* No counterparts in the reference (fusions the training step uses):
+ * residual_layernorm_forward: sum_out = a + b, then layernorm_forward(out, mean, rstd, sum_out, ...)
+ *   (residual_forward + layernorm_forward, src/nn.cu:54-81, 152-159) in one pass over the rows.
+ * layernorm_backward_colsum: layernorm_backward, and dcolsum += column sums of the updated dinp --
+ *   the bias gradient (bias_backward, src/nn.cu:184-191) of the projection whose output gradient
+ *   dinp is.  dcolsum may be NULL. */
+/* gelu_backward over an (N x C) matrix, and dcolsum += column sums of dinp (the bias gradient
+ * of the projection that produced the GELU input).  No counterpart in the reference. */
+int bmb_gelu_backward_colsum(float *dinp, float *dcolsum, const float *inp,
+                             const float *dout, int N, int C);
+int bmb_residual_layernorm_forward(float *sum_out, float *out, float *mean, float *rstd,
+                                   const float *a, const float *b, const float *weight,
+                                   const float *bias, int N, int C);
+int bmb_layernorm_backward_colsum(float *dinp, float *dweight, float *dbias, float *dcolsum,
+                                  const float *dout, const float *inp, const float *weight,
+                                  const float *mean, const float *rstd, int N, int C);
 int bmb_gelu_forward(float *out, const float *inp, int n);
 int bmb_gelu_backward(float *dinp, const float *inp, const float *dout, int n);
 int bmb_residual_forward(float *out, const float *a, const float *b, int n);

@@ -231,6 +231,20 @@ def test_layernorm_vs_oracle(bmb, orc, cuda, N, Cc):
     bmb.call("bmb_layernorm_backward", tdx, tdw, tdb, tdy, tx, tw, tm, tr, N, Cc)
     assert normwise(host(cuda, tdx), wdx) < 1e-5
     assert normwise(host(cuda, tdw), wdw) < 1e-5 and normwise(host(cuda, tdb), wdb) < 1e-5
+    # the fused forms the training step uses: residual add + layernorm, and backward + column sums of dinp
+    ta, tb2 = dev(cuda, x - dy), dev(cuda, dy)                 # a + b == x up to fp32 rounding of the split
+    ts, fo, fm, fr = (cuda.zeros(n, device="cuda") for n in (N * Cc, N * Cc, N, N))
+    bmb.call("bmb_residual_layernorm_forward", ts, fo, fm, fr, ta, tb2, tw, tb, N, Cc)
+    ssum = ((x - dy) + dy).astype(np.float32)
+    assert np.array_equal(host(cuda, ts).reshape(N, Cc), ssum)
+    uo, um, ur = cuda.zeros(N * Cc, device="cuda"), cuda.zeros(N, device="cuda"), cuda.zeros(N, device="cuda")
+    bmb.call("bmb_layernorm_forward", uo, um, ur, ts, tw, tb, N, Cc)
+    assert np.array_equal(host(cuda, fo), host(cuda, uo)) and np.array_equal(host(cuda, fm), host(cuda, um))
+    cdx, cdw, cdb, ccs = dev(cuda, dx), dev(cuda, dw), dev(cuda, db), dev(cuda, normal(Cc, 8))
+    bmb.call("bmb_layernorm_backward_colsum", cdx, cdw, cdb, ccs, tdy, tx, tw, tm, tr, N, Cc)
+    assert np.array_equal(host(cuda, cdx), host(cuda, tdx)) and np.array_equal(host(cuda, cdw), host(cuda, tdw))
+    want_cs = normal(Cc, 8).astype(np.float64) + host(cuda, tdx).reshape(N, Cc).astype(np.float64).sum(0)
+    assert normwise(host(cuda, ccs), want_cs.astype(np.float32)) < 1e-5
 
 
 def test_layernorm_backward_is_reproducible(bmb, cuda):
@@ -258,6 +272,12 @@ def test_elementwise_bias_encoder_vs_oracle(bmb, orc, cuda):
     bmb.call("bmb_gelu_forward", tg, tx, N * Cc)
     bmb.call("bmb_gelu_backward", tdg, tx, tdy, N * Cc)
     assert normwise(host(cuda, tg), g) < 1e-6 and normwise(host(cuda, tdg), dg) < 1e-6
+    # fused with the bias gradient of the projection that fed the GELU
+    fdg, fcs = cuda.zeros(N * Cc, device="cuda"), dev(cuda, bias)
+    bmb.call("bmb_gelu_backward_colsum", fdg, fcs, tx, tdy, N, Cc)
+    assert np.array_equal(host(cuda, fdg), host(cuda, tdg))
+    want = bias.astype(np.float64) + host(cuda, tdg).reshape(N, Cc).astype(np.float64).sum(0)
+    assert normwise(host(cuda, fcs), want.astype(np.float32)) < 1e-5
     r = cuda.zeros(N * Cc, device="cuda")
     bmb.call("bmb_residual_forward", r, tx, tdy, N * Cc)
     assert np.array_equal(host(cuda, r), (x + dy).ravel())
