@@ -162,7 +162,8 @@ __device__ __forceinline__ void add_result(float4 o, float *__restrict__ C, int 
 // brings all chunks of a slice in one copy.
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, int M, int N,
+gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+          const __grid_constant__ CUtensorMap mapC, int c_mode, int M, int N,
           int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
           int vec_ok, int dp_tiles, int g_sk, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
     constexpr int B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -171,7 +172,8 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(gen + STAGES * STAGE_BYTES);
+    // operand ring | epilogue staging (1024-byte aligned: it is a TMA store source) | barriers
+    uint64_t *bars = reinterpret_cast<uint64_t *>(gen + STAGES * STAGE_BYTES + EPI_BYTES);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -293,15 +295,70 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             // part of a stream-K tile is added into C.
             const int row_base = tm * BM + q * 32;
             const uint32_t trow = tmem_base + (uint32_t)acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-            float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES + 256) + (warp - 2) * (32 * 32);
+            float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES) + (warp - 2) * (32 * 32);
             const int sub_r = lane >> 3, sub_u = lane & 7, sub_c = sub_u * 4;
             const float *part_bias = (kb0 == 0) ? bias : nullptr;
 #pragma unroll 1
             for (int c = chunk_par; c < BN / 32; c += 2) {
                 const int n0 = tn * BN + c * 32;
                 if (n0 >= N) break;                      // warp-uniform
+                if (whole && c_mode == 3) {
+                    // Direct path (beta 0, aligned C): the accumulator leaves TMEM in the 16x256b shape,
+                    // where four neighbouring lanes hold 32 contiguous bytes of a row, so the registers
+                    // go straight to global memory in whole sectors -- no trip through shared memory,
+                    // whose bandwidth the main loop needs.
+                    float lo[16], hi[16];
+                    tmem_ld_16x256b_x4_nowait(trow + (uint32_t)(c * 32), lo);                       // rows 0..15 of this quadrant
+                    tmem_ld_16x256b_x4_nowait(trow + (uint32_t)(c * 32) + (16u << 16), hi);         // rows 16..31
+                    tmem_wait_ld();
+                    const int r0 = row_base + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int n = n0 + 8 * j + cq;
+                        if (n >= N) continue;
+                        float2 bb = make_float2(0.f, 0.f);
+                        if (bias) bb = *reinterpret_cast<const float2 *>(bias + n);
+                        float2 o[4] = {make_float2(lo[4 * j], lo[4 * j + 1]), make_float2(lo[4 * j + 2], lo[4 * j + 3]),
+                                       make_float2(hi[4 * j], hi[4 * j + 1]), make_float2(hi[4 * j + 2], hi[4 * j + 3])};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int m = r0 + 8 * k;
+                            float2 x = make_float2(fmaf(alpha, o[k].x, bb.x), fmaf(alpha, o[k].y, bb.y));
+                            if (round_c) x = make_float2(round_tf32(x.x), round_tf32(x.y));
+                            if (m < M) *reinterpret_cast<float2 *>(C + (size_t)m * N + n) = x;
+                        }
+                    }
+                    continue;
+                }
                 float v[32];
                 tmem_ld32(trow + (uint32_t)(c * 32), v);
+                if (c_mode) {
+                    // TMA path (C 16-byte aligned, N % 4 == 0, beta 0 or 1): finish the values in registers,
+                    // park the 32 x 32 block in the swizzled layout the tensor map expects and let the
+                    // copy engine store it (beta 0, whole tile) or add it into C (beta 1, stream-K parts).
+                    if (row_base >= M) continue;         // warp-uniform; the box would lie outside C
+                    const float *bsrc = whole ? bias : part_bias;
+                    if (lane == 0) tma_store_wait_read();   // the previous block has left the staging buffer
+                    __syncwarp();
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        float4 o = make_float4(alpha * v[4 * u], alpha * v[4 * u + 1], alpha * v[4 * u + 2], alpha * v[4 * u + 3]);
+                        if (bsrc && n0 + 4 * u < N) {
+                            const float4 bb = *reinterpret_cast<const float4 *>(bsrc + n0 + 4 * u);
+                            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                        }
+                        if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
+                        *reinterpret_cast<float4 *>(stg + lane * 32 + ((u ^ (lane & 7)) << 2)) = o;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (whole && c_mode == 1) tma_store_2d(&mapC, smem_u32(stg), n0, row_base);
+                        else tma_reduce_add_2d(&mapC, smem_u32(stg), n0, row_base);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
                     *reinterpret_cast<float4 *>(stg + lane * 32 + ((u ^ (lane & 7)) << 2)) =
@@ -323,6 +380,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+        if (c_mode && lane == 0) tma_store_wait_all();   // every block this warp handed to the copy engine has landed
     }
 
     fence_before();
@@ -509,7 +567,8 @@ void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int 
 }
 
 template <int KIND, int BN>
-int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, int M, int N, int kblocks, int kper,
+int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, int c_mode,
+              int M, int N, int kblocks, int kper,
               int amn, int bmn, float alpha, float beta, float *C, int vec_ok, int dp_tiles, int g_sk, const float *bias,
               int round_c, int *status_dev) {
     static bool attr_set[64];
@@ -521,7 +580,7 @@ int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensor
             attr_set[d] = true;
         }
     }
-    gemm_tc_k<KIND, BN><<<grid, NTHREADS, smem_bytes(BN), st>>>(mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
+    gemm_tc_k<KIND, BN><<<grid, NTHREADS, smem_bytes(BN), st>>>(mapA, mapB, mapC, c_mode, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
                                                                 dp_tiles, g_sk, bias, round_c, status_dev);
     return BMB_OK;
 }
@@ -573,7 +632,16 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     const int grid = sk_tiles > 0 ? (dp_tiles >= ctas ? ctas : (dp_tiles > g_sk ? dp_tiles : g_sk)) : (tiles < ctas ? tiles : ctas);
     const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
     const int amn = bf16 ? 0 : (a.mn_major ? (a.map3d ? 2 : 1) : 0), bmn = bf16 ? 0 : (b.mn_major ? (b.map3d ? 2 : 1) : 0);
-#define BMB_TC_ARGS grid, st, mapA, mapB, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
+    // The epilogue hands finished 32 x 32 blocks to the copy engine when C allows a tensor map
+    // (16-byte aligned rows) and beta is 0 (store) or 1 (add); otherwise the warps store themselves.
+    CUtensorMap mapC;
+    memset(&mapC, 0, sizeof(mapC));
+    static const bool no_tma_store = getenv("BMB_GEMM_NO_TMA_STORE") != nullptr;
+    static const bool no_direct = getenv("BMB_GEMM_NO_DIRECT") != nullptr;
+    // 3 = whole tiles stored straight from registers (beta 0), parts of shared tiles added by the copy engine
+    const int c_mode = (!no_tma_store && vec_ok && (beta == 0.0f || beta == 1.0f)) ? (beta == 0.0f ? (no_direct ? 1 : 3) : 2) : 0;
+    if (c_mode) BMB_TRY(make_map_2d(&mapC, C, 4, M, N, (long long)N * 4, 32, false));
+#define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {
         if (bn == 256) BMB_TRY((launch_tc<1, 256>(BMB_TC_ARGS)));
         else if (bn == 192) BMB_TRY((launch_tc<1, 192>(BMB_TC_ARGS)));
