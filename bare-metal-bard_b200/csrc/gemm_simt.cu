@@ -92,6 +92,20 @@ __device__ __forceinline__ void store_slice(float *__restrict__ s, const float4 
     }
 }
 
+// Two fp32 fused multiply-adds in one instruction (sm_100): each half is an IEEE fma.rn, so results
+// are bit-identical to fmaf; it halves the issue slots the inner product needs.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void ffma2(unsigned long long &d, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+
 template <bool TA, bool TB, bool GUARD>
 __global__ void __launch_bounds__(NTHREADS, 2)
 gemm_simt_k(int M, int N, int K, float alpha, const float *__restrict__ A, long long sA,
@@ -112,11 +126,12 @@ gemm_simt_k(int M, int N, int K, float alpha, const float *__restrict__ A, long 
     constexpr bool A_KC = !TA, B_KC = TB;
     const long long lda = TA ? M : K, ldb = TB ? K : N;
 
-    float acc[8][8];
+    // acc2[i][jp] holds columns 2*jp and 2*jp+1 of row i of the 8 x 8 micro-tile
+    unsigned long long acc2[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) acc2[i][j] = 0ull;
 
     float4 ra[2], rb[2];
     fetch_slice<A_KC, GUARD>(ra, A, lda, m0, 0, M, K, tid);
@@ -147,11 +162,13 @@ gemm_simt_k(int M, int N, int K, float alpha, const float *__restrict__ A, long 
             const float4 b0 = *reinterpret_cast<const float4 *>(&bs[k * 128 + bn[c]]);
             const float4 b1 = *reinterpret_cast<const float4 *>(&bs[k * 128 + 64 + bn[c]]);
             const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const unsigned long long bp[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 8; ++i) {
+                const unsigned long long aa = pack2(av[i], av[i]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) ffma2(acc2[i][j], aa, bp[j]);
+            }
         }
         if (more) {
             store_slice<A_KC>(As[cur ^ 1], ra, tid);
@@ -160,6 +177,11 @@ gemm_simt_k(int M, int N, int K, float alpha, const float *__restrict__ A, long 
         __syncthreads();
     }
 
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) unpack2(acc2[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
     // Epilogue.  Rows ty*4+{0..3} and 64+ty*4+{0..3}; columns likewise in tx.
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
