@@ -41,6 +41,10 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 GPT124M = dict(max_seq_len=1024, vocab_size=50304, padded_vocab=50304, n_layer=12, n_head=12, n_embd=768)
 B_PER_GPU, T = 8, 1024
+# ncu, one training step: 25.06 GB read + written by the 147 tensor-core GEMM launches; algorithmic (each
+# operand and result once, C twice where beta = 1): 21.4 GB
+GEMM_DRAM_BYTES_PER_LAUNCH = 170.5e6
+GEMM_ALGO_BYTES_PER_LAUNCH = 145.6e6
 HP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, grad_clip=1.0)
 
 
@@ -297,7 +301,11 @@ def run_bmb(args):
         "model_tflops": round(flops_per_step_per_gpu(tr.num_params) * world / (ms_step * 1e-3) / 1e12, 1),
         "roofline": {"bound": "tensor", "kernel": "GEMMs of the step (%d calls)" % prof["gemm_calls"],
                      "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
-                     "frac": round(achieved / peak, 3) if peak else None, "traffic": None,
+                     "frac": round(achieved / peak, 3) if peak else None,
+                     # DRAM bytes per GEMM launch, mean over the 147 launches of one TF32 step, from the ncu
+                     # capture summarised in profiles/train_step_gpt124m_tf32_gemm_dram.md (not measured live)
+                     "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if (math == bmb.MATH_TF32 and not args.unfused) else None,
+                     "algorithmic_bytes_per_launch": GEMM_ALGO_BYTES_PER_LAUNCH,
                      "gemm_ms_per_step": round(prof["gemm_ms"] / args.steps, 3), "peak_note": peak_note,
                      "bound_detail": bound},
         "clocks": clocks,
