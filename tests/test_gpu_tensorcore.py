@@ -58,6 +58,39 @@ def test_tensorcore_gemm_vs_oracle(bmb, orc, cuda, kind, ta, tb, M, N, K):
     assert normwise(got, want32) < (5e-4 if kind == "tf32" else 8e-3)
 
 
+@pytest.mark.parametrize("ta,tb,M,N,K,beta", [
+    (0, 1, 8192, 3072, 768, 0.0),      # 192-column tiles, whole tiles stored from registers
+    (0, 1, 8192, 768, 3072, 0.0),      # last wave shared between CTAs along K
+    (0, 0, 8192, 768, 3072, 0.0),      # B MN-major through the 3-d tensor map
+    (1, 0, 3072, 768, 8192, 1.0),      # both MN-major, fewer tiles than SMs, accumulate into C
+    (1, 0, 768, 768, 8192, 1.0),
+    (0, 1, 4096, 160, 512, 0.0),       # 128-column tiles (N < 192)
+])
+def test_training_step_shapes_at_full_size(bmb, cuda, ta, tb, M, N, K, beta):
+    """The GEMM shapes of the 124M training step, operands pre-rounded as the step feeds them,
+    against a float64 product on the device (the CPU oracle needs minutes at these sizes):
+    2e-5 normwise, which only the accumulation order may use up.  Sharing tiles between CTAs
+    must agree with keeping every tile on one CTA to the same bound."""
+    g = cuda.Generator(device="cuda").manual_seed(5)
+    A = cuda.rand(M * K, device="cuda", generator=g) * 2 - 1
+    B = cuda.rand(K * N, device="cuda", generator=g) * 2 - 1
+    C0 = cuda.rand(M * N, device="cuda", generator=g)
+    bmb.call("bmb_round_tf32", A, A, M * K, None)
+    bmb.call("bmb_round_tf32", B, B, K * N, None)
+    Am = A.view(K, M).t() if ta else A.view(M, K)
+    Bm = B.view(N, K).t() if tb else B.view(K, N)
+    want = (Am.double() @ Bm.double() + beta * C0.view(M, N).double())
+    outs = []
+    for extra in (0, bmb.GEMM_NO_SPLIT):
+        Cm = C0.clone()
+        bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED | extra, ta, tb, M, N, K, 1.0, A, B, beta, Cm, None)
+        cuda.cuda.synchronize()
+        err = ((Cm.view(M, N).double() - want).norm() / want.norm()).item()
+        assert err < 2e-5, (extra, err)
+        outs.append(Cm)
+    assert ((outs[0] - outs[1]).double().norm() / want.norm()).item() < 2e-5
+
+
 def test_registry_tf32_entry_at_2048(bmb, orc, cuda):
     """Registry entry 2 at the harness's verification setting alpha 0.5, beta 3
     (src/bench.cu:261), inputs uniform [-1,1): normwise below the entry's tol."""
