@@ -49,8 +49,9 @@ namespace {
 
 using namespace tc;
 
-// Output tile: 128 rows by 256, 192 or 128 columns (chosen per problem to fill the last wave of CTAs).
-constexpr int BM = 128, BN_WIDE = 256, BN_NARROW = 128, STAGES = 4, KBYTES = 128;
+// Output tile: 128 rows by 256, 192, 128 or 64 columns (chosen per problem to fill the last wave of CTAs;
+// 64 serves outputs narrower than 128, e.g. the head-size-wide products of unfused attention).
+constexpr int BM = 128, BN_WIDE = 256, BN_NARROW = 64, STAGES = 4, KBYTES = 128;
 constexpr int A_BYTES = BM * KBYTES;
 constexpr int EPI_WARPS = 8;                        // two per TMEM lane quadrant, taking alternate 32-column chunks
 constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
@@ -163,7 +164,7 @@ __device__ __forceinline__ void add_result(float4 o, float *__restrict__ C, int 
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-          const __grid_constant__ CUtensorMap mapC, int c_mode, int M, int N,
+          const __grid_constant__ CUtensorMap mapC, int c_mode, int batch, int M, int N,
           int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
           int vec_ok, int dp_tiles, int g_sk, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
     constexpr int B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -186,7 +187,10 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     TileSched sch;
     sch.tiles_m = (M + BM - 1) / BM;
     sch.tiles_n = (N + BN - 1) / BN;
-    sch.num_tiles = sch.tiles_m * sch.tiles_n;
+    // A batch of dense problems is one long list of tiles; its operands are seen as the 2-d matrices
+    // [batch * rows][K] (K-major) or [batch * K][rows] (MN-major), so only a row offset tells batches apart.
+    const int tiles_per_problem = sch.tiles_m * sch.tiles_n;
+    sch.num_tiles = tiles_per_problem * batch;
     WorkIter wi;
     wi.init((int)blockIdx.x, (int)gridDim.x, dp_tiles, sch.num_tiles - dp_tiles, kblocks, g_sk);
     int tile, kb0, kb1;
@@ -211,7 +215,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             bool ok = true;
             while (ok && wi.next(tile, kb0, kb1)) {
                 int tm, tn;
-                sch.coords(tile, tm, tn);
+                const int bi = tile / tiles_per_problem;
+                sch.coords(tile - bi * tiles_per_problem, tm, tn);
+                const int a_row0 = bi * M, b_row0 = bi * N, k_row0 = bi * (kblocks * kelems_per_block);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; }
                     const uint32_t fb = full0 + 8 * s;
@@ -220,20 +226,20 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
                     const int k0 = kb * kelems_per_block;
                     if (a_mn == 2) {
-                        tma_load_3d(sa, &mapA, 0, k0, tm * (BM / 32), fb);        // all chunks in one copy
+                        tma_load_3d(sa, &mapA, 0, k_row0 + k0, tm * (BM / 32), fb);        // all chunks in one copy
                     } else if (a_mn) {
 #pragma unroll 1
-                        for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * CHUNK_BYTES, &mapA, tm * BM + c * 32, k0, fb);
+                        for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * CHUNK_BYTES, &mapA, tm * BM + c * 32, k_row0 + k0, fb);
                     } else {
-                        tma_load_2d(sa, &mapA, k0, tm * BM, fb);
+                        tma_load_2d(sa, &mapA, k0, a_row0 + tm * BM, fb);
                     }
                     if (b_mn == 2) {
-                        tma_load_3d(sb, &mapB, 0, k0, tn * (BN / 32), fb);
+                        tma_load_3d(sb, &mapB, 0, k_row0 + k0, tn * (BN / 32), fb);
                     } else if (b_mn) {
 #pragma unroll 1
-                        for (int c = 0; c < BN / 32; ++c) tma_load_2d(sb + c * CHUNK_BYTES, &mapB, tn * BN + c * 32, k0, fb);
+                        for (int c = 0; c < BN / 32; ++c) tma_load_2d(sb + c * CHUNK_BYTES, &mapB, tn * BN + c * 32, k_row0 + k0, fb);
                     } else {
-                        tma_load_2d(sb, &mapB, k0, tn * BN, fb);
+                        tma_load_2d(sb, &mapB, k0, b_row0 + tn * BN, fb);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -283,9 +289,12 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
+        float *const C0 = C;
         while (ok && wi.next(tile, kb0, kb1)) {
             int tm, tn;
-            sch.coords(tile, tm, tn);
+            const int bi = tile / tiles_per_problem;
+            sch.coords(tile - bi * tiles_per_problem, tm, tn);
+            float *C = C0 + (size_t)bi * M * N;          // this problem's result
             const bool whole = (kb0 == 0 && kb1 == kblocks);
             if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
             fence_after();
@@ -453,17 +462,18 @@ inline int blocks_for(long long items) {
 
 // Decide how an operand reaches the tensor core.  X = its M or N extent, kcontig =
 // element (x,k) at src[x*K + k], otherwise at src[k*X + x].
+// `batch` dense problems one after the other (batch > 1 only reaches here with geometry the direct route takes).
 int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int K, bool bf16, bool rounded,
-                  ScratchSlot slot, int tile_rows, cudaStream_t st) {
+                  ScratchSlot slot, int tile_rows, cudaStream_t st, int batch = 1) {
     const bool aligned = ((uintptr_t)src % 16) == 0;
     if (!bf16) {
         const bool geom_ok = aligned && (kcontig ? (K % 4 == 0) : (X % 4 == 0));
         if (geom_ok) {
             const float *use = src;
             if (!rounded) {
-                float *scr = (float *)device_scratch(slot, (size_t)X * K * sizeof(float));
+                float *scr = (float *)device_scratch(slot, (size_t)batch * X * K * sizeof(float));
                 if (!scr) return BMB_E_CUDA;
-                const long long n4 = X * (long long)K / 4;
+                const long long n4 = (long long)batch * X * (long long)K / 4;
                 prep_round_vec4_k<<<blocks_for(n4), 256, 0, st>>>(scr, src, n4);
                 count_launch();
                 BMB_LAUNCH_CHECK();
@@ -473,8 +483,8 @@ int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int 
             op->mn_major = !kcontig;
             op->map3d = false;
             op->tile_chunks = 0;
-            if (kcontig) { op->rows = X; op->cols = K; op->pitch_bytes = (long long)K * 4; op->box_rows = tile_rows; }
-            else { op->rows = K; op->cols = X; op->pitch_bytes = X * 4; op->box_rows = 32; op->map3d = (X % 32 == 0); op->tile_chunks = tile_rows / 32; }
+            if (kcontig) { op->rows = X * batch; op->cols = K; op->pitch_bytes = (long long)K * 4; op->box_rows = tile_rows; }
+            else { op->rows = (long long)K * batch; op->cols = X; op->pitch_bytes = X * 4; op->box_rows = 32; op->map3d = (X % 32 == 0); op->tile_chunks = tile_rows / 32; }
             return BMB_OK;
         }
     }
@@ -502,13 +512,23 @@ std::mutex g_attr_mu;
 
 }  // namespace
 
-bool gemm_tc_accepts(int math, int, int, int batch, int M, int N, int K, const float *, long long, const float *,
-                     long long, const float *C, long long) {
+bool gemm_tc_accepts(int math, int transA, int transB, int batch, int M, int N, int K, const float *A, long long sA,
+                     const float *B, long long sB, const float *C, long long sC) {
     if (math != BMB_MATH_TF32 && math != BMB_MATH_BF16) return false;
-    if (batch != 1) return false;                // batched problems stay on the SIMT kernel
     // Problems smaller than one tile stay on the SIMT kernel (fp32-exact, so within any tensor-core tolerance).
     if (M < BM || N < BN_NARROW || K < 32 || !C) return false;
     if ((long long)M * K >= (1LL << 40) || (long long)N * K >= (1LL << 40)) return false;
+    if (batch != 1) {
+        // Batched: TF32, dense strides, operands the tensor maps can read where they lie; an MN-major
+        // operand additionally needs K % 32 == 0 so that a K slice never runs into the next problem.
+        if (math != BMB_MATH_TF32) return false;
+        if (sA != (long long)M * K || sB != (long long)K * N || sC != (long long)M * N) return false;
+        const bool a_kc = !transA, b_kc = transB != 0;
+        if ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0) return false;
+        if ((a_kc ? K : M) % 4 != 0 || (b_kc ? K : N) % 4 != 0) return false;
+        if ((!a_kc || !b_kc) && K % 32 != 0) return false;
+        if ((long long)batch * M >= (1LL << 31) || (long long)batch * N >= (1LL << 31) || (long long)batch * K >= (1LL << 31)) return false;
+    }
     return true;
 }
 
@@ -541,17 +561,17 @@ __global__ void __launch_bounds__(256) sk_prepare_k(float *__restrict__ C, int M
 
 // Relative cost of one K slice of a tile `bn` columns wide (the narrower tiles re-read A more often
 // and amortise the epilogue less well).
-double slice_cost(int bn) { return bn == 256 ? 256.0 : (bn == 192 ? 200.0 : 150.0); }
+double slice_cost(int bn) { return bn == 256 ? 256.0 : (bn == 192 ? 200.0 : (bn == 128 ? 150.0 : 110.0)); }
 
 // Pick the tile width and how many tiles to hand out whole; the rest (a last, partly filled wave, or a
 // problem smaller than one wave) is shared between CTAs along K.  Costs are in K-slice units of a
 // 256-wide tile; a tile pays ~4 slices for its epilogue, sharing a tile ~6 more.
 void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int force_bn, int *bn_out, int *dp_tiles_out) {
     const int tiles_m = (M + BM - 1) / BM;
-    const int widths[3] = {256, 192, 128};
+    const int widths[4] = {256, 192, 128, 64};
     double best = -1.0;
     for (int w : widths) {
-        if (force_bn ? (w != force_bn) : (w > 128 && N < w)) continue;
+        if (force_bn ? (w != force_bn) : ((w > 64 && N < w) || (w == 64 && N >= 128))) continue;
         const long long tiles = (long long)tiles_m * ((N + w - 1) / w);
         const long long full = tiles / ctas, rem = tiles % ctas;
         const double unit = slice_cost(w) / 256.0;
@@ -568,7 +588,7 @@ void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int 
 
 template <int KIND, int BN>
 int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, int c_mode,
-              int M, int N, int kblocks, int kper,
+              int batch, int M, int N, int kblocks, int kper,
               int amn, int bmn, float alpha, float beta, float *C, int vec_ok, int dp_tiles, int g_sk, const float *bias,
               int round_c, int *status_dev) {
     static bool attr_set[64];
@@ -580,7 +600,7 @@ int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensor
             attr_set[d] = true;
         }
     }
-    gemm_tc_k<KIND, BN><<<grid, NTHREADS, smem_bytes(BN), st>>>(mapA, mapB, mapC, c_mode, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
+    gemm_tc_k<KIND, BN><<<grid, NTHREADS, smem_bytes(BN), st>>>(mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
                                                                 dp_tiles, g_sk, bias, round_c, status_dev);
     return BMB_OK;
 }
@@ -590,7 +610,6 @@ int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensor
 int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N, int K, float alpha,
             const float *A, long long, const float *B, long long, float beta, float *C, long long,
             const float *bias, cudaStream_t st) {
-    (void)batch;
     int *status_dev = nullptr;
     volatile int *status_host = nullptr;
     BMB_TRY(tc::status_word(&status_dev, &status_host));
@@ -604,20 +623,23 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     // Sharing tiles between CTAs adds parts into C in whatever order they finish, so the last bits of
     // such a result vary from run to run, and a rounded result would need another pass: both
     // BMB_GEMM_NO_SPLIT and BMB_GEMM_C_ROUNDED keep every tile on one CTA.
-    const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED));
-    static const int force_bn = [] { const char *e = getenv("BMB_GEMM_TILE_N"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 192 || v == 128) ? v : 0; }();
+    const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED)) && batch == 1;
+    static const int force_bn = [] { const char *e = getenv("BMB_GEMM_TILE_N"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 192 || v == 128 || v == 64) ? v : 0; }();
     int bn = BN_WIDE, dp_tiles = 0;
     choose_schedule(M, N, kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, &bn, &dp_tiles);
     Operand a, b;
-    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st));
-    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st));
+    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st, batch));
+    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st, batch));
     CUtensorMap mapA, mapB;
     if (a.map3d) BMB_TRY(make_map_mn3d(&mapA, a.ptr, a.rows, a.cols, a.pitch_bytes, a.tile_chunks));
     else BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
     if (b.map3d) BMB_TRY(make_map_mn3d(&mapB, b.ptr, b.rows, b.cols, b.pitch_bytes, b.tile_chunks));
     else BMB_TRY(make_map_2d(&mapB, b.ptr, esize, b.rows, b.cols, b.pitch_bytes, b.box_rows, b.mn_major));
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
-    const int tiles = tiles_m * tiles_n;
+    const long long tiles_ll = (long long)tiles_m * tiles_n * batch;
+    if (tiles_ll >= (1LL << 31)) return fail(BMB_E_LIMIT, "gemm_tc: %lld tiles", tiles_ll);
+    const int tiles = (int)tiles_ll;
+    if (batch > 1) dp_tiles = tiles;                 // batched problems: every tile on one CTA
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
     const int sk_tiles = tiles - dp_tiles;
     int g_sk = 1;
@@ -639,17 +661,20 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     static const bool no_tma_store = getenv("BMB_GEMM_NO_TMA_STORE") != nullptr;
     static const bool no_direct = getenv("BMB_GEMM_NO_DIRECT") != nullptr;
     // 3 = whole tiles stored straight from registers (beta 0), parts of shared tiles added by the copy engine
-    const int c_mode = (!no_tma_store && vec_ok && (beta == 0.0f || beta == 1.0f)) ? (beta == 0.0f ? (no_direct ? 1 : 3) : 2) : 0;
+    int c_mode = (!no_tma_store && vec_ok && (beta == 0.0f || beta == 1.0f)) ? (beta == 0.0f ? (no_direct ? 1 : 3) : 2) : 0;
+    if (batch > 1 && c_mode != 3) c_mode = 0;        // the tensor map over C describes one problem only
     if (c_mode) BMB_TRY(make_map_2d(&mapC, C, 4, M, N, (long long)N * 4, 32, false));
-#define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
+#define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {
         if (bn == 256) BMB_TRY((launch_tc<1, 256>(BMB_TC_ARGS)));
         else if (bn == 192) BMB_TRY((launch_tc<1, 192>(BMB_TC_ARGS)));
-        else BMB_TRY((launch_tc<1, 128>(BMB_TC_ARGS)));
+        else if (bn == 128) BMB_TRY((launch_tc<1, 128>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<1, 64>(BMB_TC_ARGS)));
     } else {
         if (bn == 256) BMB_TRY((launch_tc<0, 256>(BMB_TC_ARGS)));
         else if (bn == 192) BMB_TRY((launch_tc<0, 192>(BMB_TC_ARGS)));
-        else BMB_TRY((launch_tc<0, 128>(BMB_TC_ARGS)));
+        else if (bn == 128) BMB_TRY((launch_tc<0, 128>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<0, 64>(BMB_TC_ARGS)));
     }
 #undef BMB_TC_ARGS
     count_launch();

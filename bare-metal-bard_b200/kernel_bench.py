@@ -88,9 +88,13 @@ def bench_bgemm(bmb, small):
              2.0 * batch * T * T * hs, 4.0 * batch * (2 * T * hs + T * T)),
             ("PV NN", lambda: bmb.call("bmb_batched_gemm", 0, 0, batch, T, hs, T, 1.0, att, T * T, k, T * hs, 0.0, o, T * hs, None),
              2.0 * batch * T * T * hs, 4.0 * batch * (2 * T * hs + T * T))):
-        best, med = timed(fn)
-        emit(kernel="bgemm_simt_fp32", shape=tag, batch=batch, best_ms=round(best, 4), median_ms=round(med, 4),
-             tflops_best=round(flop / best / 1e9, 2), gbs_best=round(nbytes / best / 1e6, 1))
+        prev = bmb.lib().bmb_get_math_mode()
+        for mode, name in ((bmb.MATH_FP32, "bgemm_simt_fp32"), (bmb.MATH_TF32, "bgemm_tcgen05_tf32")):
+            bmb.lib().bmb_set_math_mode(mode)
+            best, med = timed(fn)
+            emit(kernel=name, shape=tag, batch=batch, best_ms=round(best, 4), median_ms=round(med, 4),
+                 tflops_best=round(flop / best / 1e9, 2), gbs_best=round(nbytes / best / 1e6, 1))
+        bmb.lib().bmb_set_math_mode(prev)
 
 
 def bench_flash(bmb, small):

@@ -91,6 +91,42 @@ def test_training_step_shapes_at_full_size(bmb, cuda, ta, tb, M, N, K, beta):
     assert ((outs[0] - outs[1]).double().norm() / want.norm()).item() < 2e-5
 
 
+@pytest.mark.parametrize("ta,tb,batch,M,N,K", [
+    (0, 1, 12, 256, 256, 64),      # Q K^T of unfused attention: both operands K-major
+    (0, 0, 12, 256, 64, 256),      # P V: 64-column tiles, B MN-major
+    (1, 0, 6, 256, 64, 128),       # att^T dvaccum: A MN-major
+    (0, 1, 5, 200, 136, 96),       # ragged M and N: tiles run past a problem's end
+    (0, 0, 3, 128, 64, 40),        # MN-major with K % 32 != 0: stays on the SIMT kernel
+])
+def test_batched_tensorcore_gemm_vs_oracle(bmb, orc, cuda, ta, tb, batch, M, N, K):
+    """batched_gemm (src/gemm.h:26-29) in TF32 mode against the float64 product of the rounded
+    operands (2e-5: accumulation order only) and the fp32 product of the raw ones (5e-4)."""
+    A, B, C0 = uniform(batch * M * K, 1), uniform(batch * K * N, 2), uniform(batch * M * N, 3)
+    Ar, Br = rounded(orc, A, "tf32"), rounded(orc, B, "tf32")
+    want_r, want32 = C0.copy(), C0.copy()
+    orc.orc_batched_gemm(ta, tb, batch, M, N, K, 0.5, _np(A), M * K, _np(B), K * N, 2.0, _np(want32), M * N)
+    for i in range(batch):
+        c = want_r[i * M * N:(i + 1) * M * N]
+        orc.orc_gemm_f64(ta, tb, M, N, K, 0.5, _np(np.ascontiguousarray(Ar[i * M * K:(i + 1) * M * K])),
+                         _np(np.ascontiguousarray(Br[i * K * N:(i + 1) * K * N])), 2.0, _np(c))
+    dA, dB, dC = dev(cuda, A), dev(cuda, B), dev(cuda, C0)
+    prev = bmb.lib().bmb_get_math_mode()
+    bmb.lib().bmb_set_math_mode(bmb.MATH_TF32)
+    try:
+        bmb.call("bmb_batched_gemm", ta, tb, batch, M, N, K, 0.5, dA, M * K, dB, K * N, 2.0, dC, M * N, None)
+        got = host(cuda, dC)
+        # beta = 0 leg: C poisoned first
+        dP = cuda.full((batch * M * N,), float("nan"), device="cuda")
+        bmb.call("bmb_batched_gemm", ta, tb, batch, M, N, K, 1.0, dA, M * K, dB, K * N, 0.0, dP, M * N, None)
+        assert np.all(np.isfinite(host(cuda, dP)))
+    finally:
+        bmb.lib().bmb_set_math_mode(prev)
+    on_tensor_cores = ta == 0 and tb == 1 or K % 32 == 0     # else the fp32 kernel serves it, exact in fp32
+    if on_tensor_cores:
+        assert normwise(got, want_r) < 2e-5
+    assert normwise(got, want32) < (5e-4 if on_tensor_cores else 1e-6)
+
+
 def test_registry_tf32_entry_at_2048(bmb, orc, cuda):
     """Registry entry 2 at the harness's verification setting alpha 0.5, beta 3
     (src/bench.cu:261), inputs uniform [-1,1): normwise below the entry's tol."""
