@@ -45,17 +45,34 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+#ifdef BMB_FLASH_TRACE
+__device__ long long g_trace_bwd[16];
+#define TRB(i) do { if (tr) { const long long now_ = clock64(); g_trace_bwd[i] += now_ - tlast; tlast = now_; } } while (0)
+#else
+#define TRB(i)
+#endif
+
 // ============================================================== dQ kernel
 namespace dq {
-constexpr int QT = 128, KB = 64, STAGES = 2;
-constexpr int OFF_Q = 0, OFF_DO = 32768, OFF_ST = 65536, STAGE_BYTES = 49152;   // Kk | Kn | Vk, 16 KB each
-constexpr int OFF_DS = OFF_ST + STAGES * STAGE_BYTES;                            // two buffers of 32 KB
-constexpr int OFF_BAR = OFF_DS + 2 * 32768;
+constexpr int QT = 128, KB = 64, STAGES = 3;
+constexpr int OFF_Q = 0, OFF_DO = 32768;
+constexpr int OFF_KK = 65536, KK_BYTES = 32768;         // per stage: K then V, K-major, 16 KB each
+constexpr int OFF_KN = OFF_KK + STAGES * KK_BYTES;      // per stage: K, MN-major, 16 KB
+constexpr int KN_BYTES = 16384;
+constexpr int OFF_BAR = OFF_KN + STAGES * KN_BYTES;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 320;
-enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, SP_FULL = 5, SP_EMPTY = 7, DS_FULL = 9, DQ_DONE = 11, NBARS = 13 };
+enum { Q_FULL = 0, KK_FULL = 1, KK_EMPTY = 4, KN_FULL = 7, KN_EMPTY = 10, SP_FULL = 13, DS_FULL = 15, DQ_DONE = 17, NBARS = 18 };
+// TMEM columns: S [2] at 0 / 64, dP / dS [2] at 128 / 192, dQ at 256
+constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
 }  // namespace dq
 
+// A CTA owns 128 queries and walks key blocks of 64 up to the diagonal.  S = Q K^T and dP = dO V^T
+// land in tensor memory (double buffered); 256 threads (a query row each, 32 of the 64 key columns)
+// turn them into dS, written back over dP, where the tensor core reads it as the A operand of
+// dQ += dS K.  The K-major copies of a key block (K and V: operands of the first two products) and
+// the MN-major copy of K (operand of the last) ride in separate 3-deep rings, each refilled as soon
+// as its own consumer is done.
 __global__ void __launch_bounds__(dq::THREADS, 1)
 flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_constant__ CUtensorMap mapQKV_n,
                   const __grid_constant__ CUtensorMap mapDO_k, float *__restrict__ dqkv,
@@ -79,9 +96,12 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(bar(KV_FULL + s), 1); mbar_init(bar(KV_EMPTY + s), 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(SP_EMPTY + s), 8); }
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(DS_FULL + s), 8); mbar_init(bar(DQ_DONE + s), 1); }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar(KK_FULL + s), 1); mbar_init(bar(KK_EMPTY + s), 1);
+            mbar_init(bar(KN_FULL + s), 1); mbar_init(bar(KN_EMPTY + s), 1);
+        }
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(DS_FULL + s), 8); }
+        mbar_init(bar(DQ_DONE), 1);
         *giveup = 0;
         mbar_init_fence();
     }
@@ -90,9 +110,9 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S[2] at 0 / 64, dP[2] at 128 / 192, dQ at 256
 
     if (warp == 8) {
+        // ------------------------------------------------------------ producer
         if (lane == 0) {
             const int row0 = b * T;
             mbar_arrive_expect_tx(bar(Q_FULL), 65536);
@@ -102,73 +122,83 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                     tma_load_2d(base + OFF_DO + half * 16384 + rr * 8192, &mapDO_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(Q_FULL));
                 }
             bool ok = true;
-            int armed[STAGES] = {-1, -1};
+            int armed_k[STAGES], armed_n[STAGES];
+            for (int s = 0; s < STAGES; ++s) { armed_k[s] = -1; armed_n[s] = -1; }
             for (int j = 0; j < nb; ++j) {
                 const int st = j % STAGES;
                 const uint32_t ph = (uint32_t)((j / STAGES) & 1);
-                if (!mbar_wait(bar(KV_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(KV_FULL + st), STAGE_BYTES);
-                armed[st] = (int)ph;
-                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+                if (!mbar_wait(bar(KK_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(KK_FULL + st), KK_BYTES);
+                armed_k[st] = (int)ph;
+                const uint32_t sk = base + OFF_KK + st * KK_BYTES;
                 for (int half = 0; half < 2; ++half) {
-                    tma_load_2d(sb + half * 8192, &mapQKV_k, C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
-                    tma_load_2d(sb + 16384 + half * 8192, &mapQKV_n, C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
-                    tma_load_2d(sb + 32768 + half * 8192, &mapQKV_k, 2 * C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
+                    tma_load_2d(sk + half * 8192, &mapQKV_k, C + h * HS + half * 32, row0 + j * KB, bar(KK_FULL + st));
+                    tma_load_2d(sk + 16384 + half * 8192, &mapQKV_k, 2 * C + h * HS + half * 32, row0 + j * KB, bar(KK_FULL + st));
                 }
+                if (!mbar_wait(bar(KN_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(KN_FULL + st), KN_BYTES);
+                armed_n[st] = (int)ph;
+                const uint32_t sn = base + OFF_KN + st * KN_BYTES;
+                for (int half = 0; half < 2; ++half)
+                    tma_load_2d(sn + half * 8192, &mapQKV_n, C + h * HS + half * 32, row0 + j * KB, bar(KN_FULL + st));
             }
             if (!ok) {
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < STAGES; ++s)
-                    if (armed[s] >= 0) mbar_drain(bar(KV_FULL + s), (uint32_t)armed[s]);
+                for (int s = 0; s < STAGES; ++s) {
+                    if (armed_k[s] >= 0) mbar_drain(bar(KK_FULL + s), (uint32_t)armed_k[s]);
+                    if (armed_n[s] >= 0) mbar_drain(bar(KN_FULL + s), (uint32_t)armed_n[s]);
+                }
             }
         }
     } else if (warp == 9) {
+        // -------------------------------------------------------------- issuer
         if (lane == 0) {
             const uint32_t idesc_kk = make_idesc(2, 0, 0, KB, QT);     // [128 x 64] = A(K-major) x B(K-major)
-            const uint32_t idesc_kn = make_idesc(2, 0, 1, HS, QT);     // dQ: dS (K-major) x K (MN-major)
+            const uint32_t idesc_kn = make_idesc(2, 0, 1, HS, QT);     // dQ: dS (tensor memory) x K (MN-major)
             auto issue_sp = [&](int st, int buf) {
-                const uint32_t sb = base + OFF_ST + st * STAGE_BYTES;
+                const uint32_t sk = base + OFF_KK + st * KK_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + (uint32_t)(buf * 64), smem_desc_kmajor(base + OFF_Q + half * 16384 + off),
-                             smem_desc_kmajor(sb + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
+                    mma_tf32(tmem_base + COL_S + (uint32_t)(buf * 64), smem_desc_kmajor(base + OFF_Q + half * 16384 + off),
+                             smem_desc_kmajor(sk + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
                 }
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + (uint32_t)(128 + buf * 64), smem_desc_kmajor(base + OFF_DO + half * 16384 + off),
-                             smem_desc_kmajor(sb + 32768 + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
+                    mma_tf32(tmem_base + COL_DP + (uint32_t)(buf * 64), smem_desc_kmajor(base + OFF_DO + half * 16384 + off),
+                             smem_desc_kmajor(sk + 16384 + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
                 }
             };
             bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
-            if (ok) ok = mbar_wait(bar(KV_FULL + 0), 0, giveup);
-            if (ok) { fence_after(); issue_sp(0, 0); commit(bar(SP_FULL + 0)); }
+            if (ok) ok = mbar_wait(bar(KK_FULL + 0), 0, giveup);
+            if (ok) { fence_after(); issue_sp(0, 0); commit(bar(SP_FULL + 0)); commit(bar(KK_EMPTY + 0)); }
             for (int j = 0; ok && j < nb; ++j) {
-                const int st = j % STAGES;
+                const int st = j % STAGES, buf = j & 1;
                 if (j + 1 < nb) {
-                    const int nbuf = (j + 1) & 1;
-                    if (!mbar_wait(bar(KV_FULL + (j + 1) % STAGES), (uint32_t)(((j + 1) / STAGES) & 1), giveup)) { ok = false; break; }
-                    if (j >= 1 && !mbar_wait(bar(SP_EMPTY + nbuf), (uint32_t)(((j - 1) / 2) & 1), giveup)) { ok = false; break; }
+                    // block j+1 goes into the other S / dP buffer; the product that read that buffer's dS
+                    // (block j-1) was issued before this point, and the tensor core runs in order
+                    const int s1 = (j + 1) % STAGES;
+                    if (!mbar_wait(bar(KK_FULL + s1), (uint32_t)(((j + 1) / STAGES) & 1), giveup)) { ok = false; break; }
                     fence_after();
-                    issue_sp((j + 1) % STAGES, nbuf);
-                    commit(bar(SP_FULL + nbuf));
+                    issue_sp(s1, (j + 1) & 1);
+                    commit(bar(SP_FULL + ((j + 1) & 1)));
+                    commit(bar(KK_EMPTY + s1));
                 }
-                const int db = j & 1;                    // dS buffer of this block
-                if (!mbar_wait(bar(DS_FULL + db), (uint32_t)((j / 2) & 1), giveup)) { ok = false; break; }
+                if (!mbar_wait(bar(KN_FULL + st), (uint32_t)((j / STAGES) & 1), giveup)) { ok = false; break; }
+                if (!mbar_wait(bar(DS_FULL + buf), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
                 fence_after();
-                const uint32_t kn = base + OFF_ST + st * STAGE_BYTES + 16384;
+                const uint32_t kn = base + OFF_KN + st * KN_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < KB / 8; ++ks) {
-                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + 256, smem_desc_kmajor(base + OFF_DS + db * 32768 + half * 16384 + off),
-                             smem_desc_mnmajor32(kn + ks * 1024, 8192), idesc_kn, (j | ks) ? 1u : 0u);
-                }
-                commit(bar(DQ_DONE + db));
-                commit(bar(KV_EMPTY + st));
+                for (int ks = 0; ks < KB / 8; ++ks)
+                    mma_tf32_ts(tmem_base + COL_DQ, tmem_base + COL_DP + (uint32_t)(buf * 64 + ks * 8),
+                                smem_desc_mnmajor32(kn + ks * 1024, 8192), idesc_kn, (j | ks) ? 1u : 0u);
+                commit(bar(KN_EMPTY + st));
             }
+            if (ok) commit(bar(DQ_DONE));
         }
     } else {
+        // ----------------------------------------------------------------- dS
         const int quad = warp & 3, colhalf = warp >> 2;
         const int r = quad * 32 + lane;
         const int qi = q0 + r;
@@ -176,18 +206,23 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
         const float d_r = (qi < T) ? dsum[(size_t)bh * T + qi] : 0.0f;
         const float scale_log2e = scale * LOG2E;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        uint8_t *dsrow0 = gen + OFF_DS + colhalf * 16384 + r * 128;
         bool ok = true;
+#ifdef BMB_FLASH_TRACE
+        const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && lane == 0);
+        long long tlast = clock64();
+#endif
         for (int j = 0; j < nb; ++j) {
             const int buf = j & 1;
-            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((j / 2) & 1), giveup)) { ok = false; break; }
+            TRB(0);
+            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
             fence_after();
+            TRB(1);
             float s[32], dp[32];
-            tmem_ld32(lane_addr + (uint32_t)(buf * 64 + colhalf * 32), s);
-            tmem_ld32(lane_addr + (uint32_t)(128 + buf * 64 + colhalf * 32), dp);
-            fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(SP_EMPTY + buf));
+            const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(buf * 64 + colhalf * 32);
+            tmem_ld32_nowait(lane_addr + COL_S + (uint32_t)(buf * 64 + colhalf * 32), s);
+            tmem_ld32_nowait(dp_addr, dp);
+            tmem_wait_ld();
+            TRB(2);
             const int k0 = j * KB + colhalf * 32;
             const bool diag = (k0 + 31 > q0);
 #pragma unroll
@@ -196,20 +231,21 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                 if (diag && (k0 + i > qi)) p = 0.0f;
                 s[i] = round_tf32_alu(p * (dp[i] - d_r));
             }
-            // dS goes into the buffer the product of two blocks ago has finished reading
-            if (j > 1 && !mbar_wait(bar(DQ_DONE + buf), (uint32_t)(((j - 2) / 2) & 1), giveup)) { ok = false; break; }
-            uint8_t *dsrow = dsrow0 + buf * 32768;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<float4 *>(dsrow + ((c ^ (r & 7)) << 4)) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
-            fence_proxy_async();
+            TRB(3);
+            tmem_st32_nowait(dp_addr, s);                 // dS over dP: the A operand of dQ += dS K
+            tmem_wait_st();
+            fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(DS_FULL + buf));
+            TRB(4);
+#ifdef BMB_FLASH_TRACE
+            if (tr) g_trace_bwd[8] += 1;
+#endif
         }
-        if (ok && mbar_wait(bar(DQ_DONE + ((nb - 1) & 1)), (uint32_t)(((nb - 1) / 2) & 1), giveup)) {
+        if (ok && mbar_wait(bar(DQ_DONE), 0, giveup)) {
             fence_after();
             float v[32];
-            tmem_ld32(lane_addr + (uint32_t)(256 + colhalf * 32), v);
+            tmem_ld32(lane_addr + COL_DQ + (uint32_t)(colhalf * 32), v);
             if (qi < T) {
                 float *dst = dqkv + ((size_t)b * T + qi) * 3 * C + h * HS + colhalf * 32;
 #pragma unroll
@@ -240,7 +276,9 @@ constexpr int OFF_STK = 65536, STK_BYTES = 32768;       // per stage: Q then dO,
 constexpr int OFF_STN = OFF_STK + STAGES * STK_BYTES;   // per stage: Q then dO, MN-major, 16 KB each
 constexpr int STN_BYTES = 32768;
 constexpr int OFF_BAR = OFF_STN + STAGES * STN_BYTES;
-constexpr int SMEM = OFF_BAR + 256 + 1024;
+constexpr int STAT_MAX = 4096;                          // queries whose lse and D fit in shared memory
+constexpr int OFF_STAT = OFF_BAR + 256;                 // lse * log2(e), then D, STAT_MAX floats each
+constexpr int SMEM = OFF_STAT + 2 * STAT_MAX * 4 + 1024;
 constexpr int THREADS = 320;
 enum { KV_FULL = 0, STK_FULL = 1, STK_EMPTY = 3, STN_FULL = 5, STN_EMPTY = 7, SP_FULL = 9, PD_FULL = 11, ACC_DONE = 13, NBARS = 14 };
 // TMEM columns: S^T / P^T [2] at 0 / 64, dP^T / dS^T [2] at 128 / 192, dV at 256, dK at 320
@@ -288,6 +326,18 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
         mbar_init_fence();
     }
     if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
+    // Every thread needs the lse and D of every query the CTA walks: park them in shared memory once
+    // (zero beyond the end of the sequence), lse already in log2 units.
+    float *stat_l = reinterpret_cast<float *>(gen + OFF_STAT), *stat_d = stat_l + STAT_MAX;
+    const int nstat = nb * QB;
+    const bool stats_in_smem = nstat <= STAT_MAX;
+    if (stats_in_smem) {
+        for (int i = threadIdx.x; i < nstat; i += blockDim.x) {
+            const int q = ib0 * QB + i;
+            stat_l[i] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
+            stat_d[i] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+        }
+    }
     fence_before();
     __syncthreads();
     fence_after();
@@ -398,32 +448,38 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
         const int kj = j0 + r;                             // this thread's key
         const float scale_log2e = scale * LOG2E;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const bool vec_stats = (T & 3) == 0 && (((uintptr_t)lse | (uintptr_t)dsum) & 15) == 0;
         bool ok = true;
+#ifdef BMB_FLASH_TRACE
+        const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && lane == 0);
+        long long tlast = clock64();
+#endif
         for (int i = 0; i < nb; ++i) {
             const int buf = i & 1;
             const int qc0 = (ib0 + i) * QB + colhalf * 32;     // first query column of this thread
+            TRB(9);
             if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((i >> 1) & 1), giveup)) { ok = false; break; }
             fence_after();
+            TRB(10);
             float s[32], dp[32];
             const uint32_t s_addr = lane_addr + COL_S + (uint32_t)(buf * 64 + colhalf * 32);
             const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(buf * 64 + colhalf * 32);
             tmem_ld32_nowait(s_addr, s);
             tmem_ld32_nowait(dp_addr, dp);
             tmem_wait_ld();
-            // per-column lse and D: every thread of the CTA reads the same 64 values, so these hit L1
-            if (vec_stats && qc0 + 32 <= T) {
-                const float4 *lp = reinterpret_cast<const float4 *>(lse + (size_t)bh * T + qc0);
-                const float4 *dp4 = reinterpret_cast<const float4 *>(dsum + (size_t)bh * T + qc0);
+            TRB(11);
+            // per-column lse and D
+            if (stats_in_smem) {
+                const float4 *lp = reinterpret_cast<const float4 *>(stat_l + i * QB + colhalf * 32);
+                const float4 *dp4 = reinterpret_cast<const float4 *>(stat_d + i * QB + colhalf * 32);
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4) {
-                    const float4 l4 = __ldg(lp + c4), d4 = __ldg(dp4 + c4);
+                    const float4 l4 = lp[c4], d4 = dp4[c4];          // the same address for the whole warp: broadcast
                     const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int c = c4 * 4 + e;
-                        float p = fast_exp2(fmaf(s[c], scale_log2e, -lv[e] * LOG2E));
-                        if (qc0 + c < kj) p = 0.0f;        // causal mask
+                        float p = fast_exp2(fmaf(s[c], scale_log2e, -lv[e]));
+                        if (qc0 + c < kj || qc0 + c >= T) p = 0.0f;        // causal mask and the ragged end
                         s[c] = round_tf32_alu(p);
                         dp[c] = round_tf32_alu(p * (dp[c] - dv[e]));
                     }
@@ -440,12 +496,17 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                     dp[c] = round_tf32_alu(p * (dp[c] - dq_));
                 }
             }
+            TRB(12);
             tmem_st32_nowait(s_addr, s);
             tmem_st32_nowait(dp_addr, dp);
             tmem_wait_st();
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(PD_FULL + buf));
+            TRB(13);
+#ifdef BMB_FLASH_TRACE
+            if (tr) g_trace_bwd[14] += 1;
+#endif
         }
         if (ok && nb > 0 && mbar_wait(bar(ACC_DONE), 0, giveup)) {
             fence_after();
@@ -544,3 +605,10 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
 }
 
 }  // namespace bmb
+
+#ifdef BMB_FLASH_TRACE
+extern "C" int bmb_dbg_flash_bwd_trace(long long *host16, int reset) {
+    if (reset) { long long z[16] = {0}; return (int)cudaMemcpyToSymbol(bmb::g_trace_bwd, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(host16, bmb::g_trace_bwd, 16 * sizeof(long long));
+}
+#endif
