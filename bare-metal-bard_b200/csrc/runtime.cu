@@ -76,6 +76,7 @@ void *device_scratch(ScratchSlot slot, size_t bytes) {
 extern "C" {
 
 const char *bmb_last_error(void) { return bmb::g_err; }
+long long bmb_launch_count(void) { return bmb::launches_total(); }
 const char *bmb_version(void) { return "bmb-b200 0.1 (sm_100a)"; }
 
 int bmb_set_stream(void *s) { bmb::g_stream = (cudaStream_t)s; return BMB_OK; }

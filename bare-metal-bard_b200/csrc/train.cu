@@ -19,6 +19,9 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
                      cudaStream_t st);
 int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
                       const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st);
+namespace tc {
+int status_word(int **dev_ptr, volatile int **host_ptr);
+}
 }
 using namespace bmb;
 
@@ -45,6 +48,12 @@ struct bmb_trainer {
         *ln2, *ln2_mean, *ln2_rstd, *fch, *fch_gelu, *fcproj, *residual3, *lnf, *lnf_mean, *lnf_rstd,
         *logits, *probs, *losses;
     float *dres, *dln1, *dln2, *datty, *dqkv, *dqkvr, *datt, *dsum, *dfch, *dfch_gelu, *dlogits, *dlnf;
+    // The forward and backward pass of a step, captured once into a CUDA graph and replayed: the
+    // ~370 launches of a step then follow one another without a host round trip each.
+    bool use_graph = true, graph_failed = false;
+    int eager_passes = 0;                 // the first pass runs eagerly (it sizes the library's scratch)
+    cudaGraphExec_t graph_exec = nullptr;
+    long long graph_launches = 0;
     // profiling
     bool prof = false;
     std::vector<cudaEvent_t> ev;
@@ -262,6 +271,60 @@ int backward(bmb_trainer *t) {
     return BMB_OK;
 }
 
+// forward + backward of one step on t->st: replay of the captured graph, or eager launches while
+// there is no graph (first pass, GEMM event profiling on, graphs switched off, or capture failed).
+int forward_backward_step(bmb_trainer *t) {
+    if (!t->use_graph || t->graph_failed || t->prof) {
+        BMB_TRY(forward(t));
+        return backward(t);
+    }
+    if (!t->graph_exec) {
+        if (t->eager_passes < 1) {
+            t->eager_passes++;
+            BMB_TRY(forward(t));
+            return backward(t);
+        }
+        const long long before = launches_total();
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(t->st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            t->graph_failed = true;
+            BMB_TRY(forward(t));
+            return backward(t);
+        }
+        int rc = forward(t);
+        if (rc == BMB_OK) rc = backward(t);
+        const cudaError_t e = cudaStreamEndCapture(t->st, &graph);
+        if (rc != BMB_OK || e != cudaSuccess || !graph ||
+            cudaGraphInstantiate(&t->graph_exec, graph, 0) != cudaSuccess) {
+            // nothing ran during the capture: fall back to eager launches for good and run this pass now
+            cudaGetLastError();
+            if (graph) cudaGraphDestroy(graph);
+            t->graph_exec = nullptr;
+            t->graph_failed = true;
+            BMB_TRY(forward(t));
+            return backward(t);
+        }
+        cudaGraphDestroy(graph);
+        t->graph_launches = launches_total() - before;
+        count_launch((int)-t->graph_launches);        // counted again at every replay, this first one included
+    }
+    BMB_CUDA(cudaGraphLaunch(t->graph_exec, t->st));
+    count_launch((int)t->graph_launches);
+    return BMB_OK;
+}
+
+// The tensor-core kernels report a bounded wait that ran out through a host-mapped word; the eager
+// entry points look at it before every launch, a replayed graph does not, so the trainer looks after
+// it has synchronised.
+int check_kernel_status() {
+    int *dev = nullptr;
+    volatile int *host = nullptr;
+    BMB_TRY(tc::status_word(&dev, &host));
+    if (*host != 0) return fail(BMB_E_TIMEOUT, "a tensor-core kernel gave up waiting on a barrier (status %d)", *host);
+    return BMB_OK;
+}
+
 int refresh_shadow(bmb_trainer *t) {
     if (!t->shadow) return BMB_OK;
     return bmb_round_tf32(t->shadow, t->params, t->num_params, t->st);
@@ -285,6 +348,7 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
 
     bmb_trainer *t = new bmb_trainer();
     t->c = c;
+    if (const char *g = getenv("BMB_TRAINER_GRAPH")) t->use_graph = atoi(g) != 0;
     BMB_CUDA(cudaGetDevice(&t->dev));
     BMB_CUDA(cudaStreamCreateWithFlags(&t->st, cudaStreamNonBlocking));
     param_sizes(t->psize, c);
@@ -384,6 +448,7 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     cudaSetDevice(t->dev);
     cudaStreamSynchronize(t->st);
     for (cudaEvent_t e : t->ev) cudaEventDestroy(e);
+    if (t->graph_exec) cudaGraphExecDestroy(t->graph_exec);
     cudaFree(t->params); cudaFree(t->grads); cudaFree(t->m); cudaFree(t->v);
     if (t->shadow) cudaFree(t->shadow);
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
@@ -446,8 +511,7 @@ int bmb_trainer_forward_backward(bmb_trainer *t) {
 int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
     if (!t || step < 1) return fail(BMB_E_ARG, "trainer_step: bad argument");
     Scope sc(t);
-    BMB_TRY(forward(t));
-    BMB_TRY(backward(t));
+    BMB_TRY(forward_backward_step(t));
     if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
     BMB_TRY(bmb_grad_sumsq_device(t->grads, t->num_params, t->d_sumsq));
     BMB_TRY(bmb_adamw_update_clipped(t->params, t->grads, t->m, t->v, t->num_params, lr, t->c.beta1, t->c.beta2,
@@ -461,7 +525,7 @@ int bmb_trainer_loss(bmb_trainer *t, float *host_loss) {
     Scope sc(t);
     BMB_CUDA(cudaMemcpyAsync(host_loss, t->d_loss, sizeof(float), cudaMemcpyDeviceToHost, t->st));
     BMB_CUDA(cudaStreamSynchronize(t->st));
-    return BMB_OK;
+    return check_kernel_status();
 }
 
 void *bmb_trainer_stream(bmb_trainer *t) { return t ? (void *)t->st : nullptr; }

@@ -33,6 +33,9 @@ extern "C" {
 
 const char *bmb_last_error(void);
 const char *bmb_version(void);
+/* Kernels this library has launched in this process so far (launches replayed from a CUDA
+ * graph included).  No counterpart in the reference; bench.py reports it. */
+long long bmb_launch_count(void);
 
 /* ---- per-thread launch context ---------------------------------------- */
 /* Stream used by every entry point without a `stream` parameter.  Thread

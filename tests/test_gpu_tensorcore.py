@@ -252,3 +252,27 @@ def test_train_step_tf32_loss_vs_oracle(bmb, orc, cuda, fused):
         assert abs(tr.loss() - want) < 2e-2, s
     orc.orc_gpt_destroy(g)
     tr.close()
+
+
+def test_graph_replay_equals_eager_launches(bmb, cuda, monkeypatch):
+    """From its second step on the trainer replays forward + backward from a CUDA graph; with
+    BMB_TRAINER_GRAPH=0 it launches kernel by kernel.  Same seeds, same batches: both ways
+    must give the same losses up to the run-to-run wobble of the sums that use atomics (the token
+    embedding gradient; tiles shared between CTAs in the tensor-core GEMM): 1e-5 fp32, 1e-3 TF32."""
+    rng = np.random.default_rng(7)
+    toks = rng.integers(0, TINY["vocab_size"], (6, TINY["B"], TINY["T"]), dtype=np.int32)
+    tgts = rng.integers(0, TINY["vocab_size"], (6, TINY["B"], TINY["T"]), dtype=np.int32)
+    for math, tol in ((bmb.MATH_FP32, 1e-5), (bmb.MATH_TF32, 1e-3)):
+        runs = []
+        for graph in ("1", "0"):
+            monkeypatch.setenv("BMB_TRAINER_GRAPH", graph)
+            tr = bmb.Trainer(seed=1337, use_flash=1, math=math, fused=1 if math == bmb.MATH_TF32 else 0, **TINY)
+            losses = []
+            for s in range(6):
+                tr.upload(toks[s], tgts[s])
+                tr.step(3e-4, s + 1)
+                losses.append(tr.loss())
+            tr.close()
+            runs.append(losses)
+        assert max(abs(a - b) for a, b in zip(*runs)) <= tol, runs
+
