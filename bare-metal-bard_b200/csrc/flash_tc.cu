@@ -2,26 +2,31 @@
 // S = Q K^T and O += P V as tcgen05.mma kind::tf32 with S and P V in tensor
 // memory, Q / K / V tiles brought in by TMA straight out of the fused
 // (B,T,3C) projection, softmax in registers with one query row per thread.
-// The (T x T) score matrix never leaves the SM (src/flash.h:1-34).
+// The (T x T) score matrix never leaves tensor memory and registers (src/flash.h:1-34).
 //
 // One CTA owns 256 consecutive queries of one (batch, head) as two tiles of
 // 128 and walks the keys in blocks of 64 up to the diagonal.  320 threads:
 //   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: a thread reads its row
-//                    of S from TMEM (tcgen05.ld), scales, masks the diagonal
-//                    block, updates the running max and sum, writes
-//                    P = exp2(s - max) rounded to TF32 into shared memory
-//                    (K-major, 128-byte swizzle) and folds the previous block's
-//                    P V into its output registers: o = o * exp2(m_old - m_new) + PV;
+//                    of S from TMEM (tcgen05.ld), masks the diagonal block,
+//                    updates the running max and sum (the scale rides in the
+//                    exponent's multiply-add), writes P = exp2(.) rounded to
+//                    TF32 back into tensor memory (tcgen05.st) and, after
+//                    handing P to the tensor core, folds the previous block's
+//                    P V into its output registers:
+//                    o = o * exp2(m_old - m_new) + PV;
 //   warp 8           producer: TMA loads of the two Q tiles, then K and V
 //                    blocks into a 5-deep ring;
 //   warp 9           issuer: S_t = Q_t K_j^T as soon as the group has taken
-//                    S_t(j-1) out of TMEM, PV_t = P_t V_j as soon as P_t is
-//                    written.  The two tiles interleave, so one group's
-//                    exponentials overlap the other's matrix products.
+//                    S_t(j-1) out of TMEM, PV_t = P_t V_j (A operand read from
+//                    tensor memory) as soon as P_t is written.  The two tiles
+//                    interleave, so one group's exponentials overlap the
+//                    other's matrix products.
 // V is the B operand of P V with the head dimension contiguous, i.e. MN-major:
 // its TMA map uses the 128-byte swizzle with 32-byte atoms.  K and Q are
 // K-major.  Keys beyond the end of a sequence are never seen unmasked: a key
 // index >= T exceeds every valid query index, so the causal mask covers it.
+// CTAs are dispatched longest first (grid x = (batch, head), y = query block
+// counted from the end).
 //
 // All mbarrier waits are bounded (tc_common.cuh); on expiry the CTA drains its
 // copies in flight, frees its TMEM columns and raises the device status word.

@@ -9,16 +9,18 @@
 //   diagonal.  Per block the issuer forms S = Q K^T and dP = dO V^T in TMEM
 //   (double buffered, so block j+1 is being multiplied while block j is in the
 //   registers); 256 threads -- a row of 128 per 32-column half -- turn them
-//   into dS, rounded to TF32 and written K-major into shared memory; then
-//   dQ += dS K accumulates in TMEM over the whole walk.
-// dK/dV kernel: a CTA owns 128 keys and walks query blocks of 32 from the
+//   into dS, rounded to TF32 and written back over dP in tensor memory, which
+//   dQ += dS K (accumulated in TMEM over the whole walk) reads as its A operand.
+// dK/dV kernel: a CTA owns 128 keys and walks query blocks of 64 from the
 //   diagonal to the end, with everything transposed so that the owned keys are
-//   again the rows: S^T = K Q^T, dP^T = V dO^T, then dV += P^T dO and
-//   dK += dS^T Q accumulate in TMEM.  lse and D now vary along the columns.
+//   again the rows: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T written back in
+//   place, then dV += P^T dO and dK += dS^T Q accumulate in TMEM.  lse and D
+//   now vary along the columns; those of the whole walk sit in shared memory.
 // K (dQ kernel) and Q, dO (dK/dV kernel) serve twice, once as a K-major operand
 // and once with the head dimension as N, i.e. MN-major; the two uses need
 // different swizzles (128-byte, and 128-byte with 32-byte atoms), so TMA brings
-// each of those tiles in twice.
+// each of those tiles in twice, into separate rings that are refilled as soon
+// as their own consumer is done.
 // Products are TF32 with fp32 accumulation; the exponentials, the subtraction
 // of D and the scaling are fp32.  Waits are bounded as in the other kernels.
 #include "tc_common.cuh"

@@ -19,21 +19,31 @@
 // tensor core takes this only in the 128-byte swizzle with 32-byte atoms),
 // and the instruction descriptor says which.
 //
-// Kernel shape.  One persistent CTA per SM, 192 threads in three roles:
+// Kernel shape.  One persistent CTA per SM, 320 threads in three roles:
 //   warp 0      producer: one lane issues the TMA loads of a K-slice (32 fp32
-//               or 64 bf16 of K: A 16 KB, B 32 KB) into a 4-deep ring, each
-//               slice armed on an mbarrier with its byte count;
+//               or 64 bf16 of K: A 16 KB, B 8..32 KB) into a 4-deep ring, each
+//               slice armed on an mbarrier with its byte count.  A K-major
+//               operand is one 2-d copy; an MN-major one is one 3-d copy that
+//               lands all its 32-wide chunks (one copy per chunk starved the
+//               tensor pipe);
 //   warp 1      issuer: one lane waits for a slice, issues 4 tcgen05.mma
-//               (128 x 256 x 32 bytes of K each) and commits them to the
-//               slice's "empty" barrier; after the last slice of a tile it
+//               (128 x BN x 32 bytes of K each) and commits them to the
+//               slice's "empty" barrier; after the last slice of a work item it
 //               commits to the accumulator's "full" barrier.  This warp owns
-//               the TMEM allocation (512 columns: two 128 x 256 fp32
-//               accumulators, so the epilogue of tile i overlaps the main loop
-//               of tile i+1);
-//   warps 2..5  epilogue: each warp reads its 32 TMEM lanes 32 columns at a
-//               time (tcgen05.ld 32x32b.x32), applies alpha/beta and stores.
-// Tiles are visited in groups of 8 M-tiles so that concurrently resident CTAs
-// share A and B slices in L2.
+//               the TMEM allocation (two fp32 accumulators, so the epilogue of
+//               one item overlaps the main loop of the next);
+//   warps 2..9  epilogue, two per TMEM lane quadrant taking alternate
+//               32-column chunks.  Whole tiles with beta = 0 leave TMEM in the
+//               16x256b shape and go straight from registers to global memory
+//               in whole sectors; parts of tiles shared between CTAs, and
+//               beta = 1, are parked in swizzled shared memory and added into C
+//               by the copy engine (TMA reduce); any other case takes the
+//               generic path (staging, then coalesced loads/stores/atomics).
+// Tile width BN is 256, 192, 128 or 64 columns, chosen per problem; tiles are
+// visited in groups of 8 M-tiles so that concurrently resident CTAs share A and
+// B slices in L2; the tiles of a partly filled last wave are cut along K and
+// shared between CTAs (WorkIter below).  A batch of dense problems is one long
+// tile list.
 //
 // Every wait on an mbarrier is bounded: when one runs out, the CTA raises a
 // flag all roles poll, the producer waits (bounded again) for the copies it
