@@ -53,6 +53,7 @@
 #include "tc_common.cuh"
 #include <cuda_bf16.h>
 #include <mutex>
+#include <vector>
 
 namespace bmb {
 namespace {
@@ -71,11 +72,11 @@ constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 12
 
 struct TileSched {
     int tiles_m, tiles_n, num_tiles;
-    __device__ __forceinline__ void coords(int tile, int &tm, int &tn) const {
+    __host__ __device__ __forceinline__ void coords(int tile, int &tm, int &tn) const {
         constexpr int GM = 8;
         const int per_group = GM * tiles_n;
         const int g = tile / per_group, first_m = g * GM;
-        const int gsz = min(GM, tiles_m - first_m);
+        const int gsz = (tiles_m - first_m < GM) ? tiles_m - first_m : GM;
         const int r = tile - g * per_group;
         tm = first_m + r % gsz;
         tn = r / gsz;
@@ -93,18 +94,18 @@ struct WorkIter {
     long long R;            // K slices in the stream-K region
     long long it, hi;       // what is left of this CTA's run
     int dp_next;
-    __device__ __forceinline__ long long run_start(int c) const { return ((long long)c * R) / g_sk; }
-    __device__ __forceinline__ void init(int cta, int grid_, int dp_tiles_, int sk_tiles, int kblocks_, int g_sk_) {
+    __host__ __device__ __forceinline__ long long run_start(int c) const { return ((long long)c * R) / g_sk; }
+    __host__ __device__ __forceinline__ void init(int cta, int grid_, int dp_tiles_, int sk_tiles, int kblocks_, int g_sk_) {
         dp_tiles = dp_tiles_; kblocks = kblocks_; g_sk = g_sk_; grid = grid_;
         R = (long long)sk_tiles * kblocks_;
         if (cta < g_sk_) { it = run_start(cta); hi = run_start(cta + 1); } else { it = hi = 0; }
         dp_next = cta;
     }
-    __device__ __forceinline__ bool next(int &tile, int &kb0, int &kb1) {
+    __host__ __device__ __forceinline__ bool next(int &tile, int &kb0, int &kb1) {
         if (it < hi) {
             const long long t = it / kblocks;
             kb0 = (int)(it - t * kblocks);
-            const long long n = min((long long)(kblocks - kb0), hi - it);
+            const long long n = ((long long)(kblocks - kb0) < hi - it) ? (long long)(kblocks - kb0) : hi - it;
             kb1 = kb0 + (int)n;
             tile = dp_tiles + (int)t;
             it += n;
@@ -596,6 +597,37 @@ void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int 
     }
 }
 
+// Everything the launch decides about how the tiles are handed out.
+struct Plan { int bn, kblocks, tiles_m, tiles_n, tiles, dp_tiles, sk_tiles, g_sk, grid; };
+
+int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int ctas) {
+    const int kper = KBYTES / (bf16 ? 2 : 4);
+    p->kblocks = (K + kper - 1) / kper;
+    // Sharing tiles between CTAs adds parts into C in whatever order they finish, so the last bits of
+    // such a result vary from run to run, and a rounded result would need another pass: both
+    // BMB_GEMM_NO_SPLIT and BMB_GEMM_C_ROUNDED keep every tile on one CTA; so do batched problems.
+    const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED)) && batch == 1;
+    static const int force_bn = [] { const char *e = getenv("BMB_GEMM_TILE_N"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 192 || v == 128 || v == 64) ? v : 0; }();
+    p->bn = BN_WIDE;
+    p->dp_tiles = 0;
+    choose_schedule(M, N, p->kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, &p->bn, &p->dp_tiles);
+    p->tiles_m = (M + BM - 1) / BM;
+    p->tiles_n = (N + p->bn - 1) / p->bn;
+    const long long tiles_ll = (long long)p->tiles_m * p->tiles_n * batch;
+    if (tiles_ll >= (1LL << 31)) return fail(BMB_E_LIMIT, "gemm_tc: %lld tiles", tiles_ll);
+    p->tiles = (int)tiles_ll;
+    if (batch > 1) p->dp_tiles = p->tiles;
+    p->sk_tiles = p->tiles - p->dp_tiles;
+    p->g_sk = 1;
+    if (p->sk_tiles > 0) {
+        const long long runs = (long long)p->sk_tiles * p->kblocks / 4;       // at least 4 K slices per run
+        p->g_sk = (int)(runs < 1 ? 1 : (runs > ctas ? ctas : runs));
+    }
+    p->grid = p->sk_tiles > 0 ? (p->dp_tiles >= ctas ? ctas : (p->dp_tiles > p->g_sk ? p->dp_tiles : p->g_sk))
+                              : (p->tiles < ctas ? p->tiles : ctas);
+    return BMB_OK;
+}
+
 template <int KIND, int BN>
 int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, int c_mode,
               int batch, int M, int N, int kblocks, int kper,
@@ -628,15 +660,10 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     const bool bf16 = (math == BMB_MATH_BF16);
     const int esize = bf16 ? 2 : 4;
     const int kper = KBYTES / esize;
-    const int kblocks = (K + kper - 1) / kper;
     const int ctas = sm_count();
-    // Sharing tiles between CTAs adds parts into C in whatever order they finish, so the last bits of
-    // such a result vary from run to run, and a rounded result would need another pass: both
-    // BMB_GEMM_NO_SPLIT and BMB_GEMM_C_ROUNDED keep every tile on one CTA.
-    const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED)) && batch == 1;
-    static const int force_bn = [] { const char *e = getenv("BMB_GEMM_TILE_N"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 192 || v == 128 || v == 64) ? v : 0; }();
-    int bn = BN_WIDE, dp_tiles = 0;
-    choose_schedule(M, N, kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, &bn, &dp_tiles);
+    Plan plan;
+    BMB_TRY(plan_gemm(&plan, bf16, flags, batch, M, N, K, ctas));
+    const int kblocks = plan.kblocks, bn = plan.bn, dp_tiles = plan.dp_tiles;
     Operand a, b;
     BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st, batch));
     BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st, batch));
@@ -645,23 +672,13 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     else BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
     if (b.map3d) BMB_TRY(make_map_mn3d(&mapB, b.ptr, b.rows, b.cols, b.pitch_bytes, b.tile_chunks));
     else BMB_TRY(make_map_2d(&mapB, b.ptr, esize, b.rows, b.cols, b.pitch_bytes, b.box_rows, b.mn_major));
-    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
-    const long long tiles_ll = (long long)tiles_m * tiles_n * batch;
-    if (tiles_ll >= (1LL << 31)) return fail(BMB_E_LIMIT, "gemm_tc: %lld tiles", tiles_ll);
-    const int tiles = (int)tiles_ll;
-    if (batch > 1) dp_tiles = tiles;                 // batched problems: every tile on one CTA
+    const int tiles_m = plan.tiles_m, tiles_n = plan.tiles_n;
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
-    const int sk_tiles = tiles - dp_tiles;
-    int g_sk = 1;
-    if (sk_tiles > 0) {
-        const long long runs = (long long)sk_tiles * kblocks / 4;       // at least 4 K slices per run
-        g_sk = (int)(runs < 1 ? 1 : (runs > ctas ? ctas : runs));
-        if (beta != 1.0f) {
-            sk_prepare_k<<<sk_tiles, 256, 0, st>>>(C, M, N, tiles_m, tiles_n, dp_tiles, bn, beta, vec_ok);
-            count_launch();
-        }
+    const int sk_tiles = plan.sk_tiles, g_sk = plan.g_sk, grid = plan.grid;
+    if (sk_tiles > 0 && beta != 1.0f) {
+        sk_prepare_k<<<sk_tiles, 256, 0, st>>>(C, M, N, tiles_m, tiles_n, dp_tiles, bn, beta, vec_ok);
+        count_launch();
     }
-    const int grid = sk_tiles > 0 ? (dp_tiles >= ctas ? ctas : (dp_tiles > g_sk ? dp_tiles : g_sk)) : (tiles < ctas ? tiles : ctas);
     const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
     const int amn = bf16 ? 0 : (a.mn_major ? (a.map3d ? 2 : 1) : 0), bmn = bf16 ? 0 : (b.mn_major ? (b.map3d ? 2 : 1) : 0);
     // The epilogue hands finished 32 x 32 blocks to the copy engine when C allows a tensor map
@@ -693,3 +710,36 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
 }
 
 }  // namespace bmb
+
+// Host-side replay of the tile schedule a tensor-core GEMM of this shape would use on `ctas` SMs:
+// returns BMB_OK when the work items of all CTAs cover every (tile, K slice) exactly once, whole
+// tiles only where no tile is shared.  Runs no kernel; the CPU tests sweep shapes through it.
+extern "C" int bmb_gemm_schedule_check(int math, int flags, int batch, int M, int N, int K, int ctas, int *bn_out,
+                                       int *dp_tiles_out, int *grid_out) {
+    using namespace bmb;
+    if (M < 1 || N < 1 || K < 1 || batch < 1 || ctas < 1) return fail(BMB_E_ARG, "schedule_check: bad argument");
+    Plan p;
+    BMB_TRY(plan_gemm(&p, math == BMB_MATH_BF16, flags, batch, M, N, K, ctas));
+    if (bn_out) *bn_out = p.bn;
+    if (dp_tiles_out) *dp_tiles_out = p.dp_tiles;
+    if (grid_out) *grid_out = p.grid;
+    if (p.grid < 1 || p.grid > ctas) return fail(BMB_E_LIMIT, "schedule_check: grid %d", p.grid);
+    if ((long long)p.tiles * p.kblocks > (1LL << 28)) return fail(BMB_E_LIMIT, "schedule_check: problem too large to replay");
+    std::vector<unsigned char> seen((size_t)p.tiles * p.kblocks, 0);
+    for (int c = 0; c < p.grid; ++c) {
+        WorkIter wi;
+        wi.init(c, p.grid, p.dp_tiles, p.sk_tiles, p.kblocks, p.g_sk);
+        int tile, kb0, kb1;
+        while (wi.next(tile, kb0, kb1)) {
+            if (tile < 0 || tile >= p.tiles || kb0 < 0 || kb1 > p.kblocks || kb0 >= kb1)
+                return fail(BMB_E_LIMIT, "schedule_check: CTA %d got item (%d, %d, %d)", c, tile, kb0, kb1);
+            if (tile < p.dp_tiles && !(kb0 == 0 && kb1 == p.kblocks))
+                return fail(BMB_E_LIMIT, "schedule_check: whole tile %d cut", tile);
+            for (int k = kb0; k < kb1; ++k)
+                if (seen[(size_t)tile * p.kblocks + k]++) return fail(BMB_E_LIMIT, "schedule_check: tile %d slice %d twice", tile, k);
+        }
+    }
+    for (size_t i = 0; i < seen.size(); ++i)
+        if (!seen[i]) return fail(BMB_E_LIMIT, "schedule_check: tile %zu slice %zu never computed", i / p.kblocks, i % p.kblocks);
+    return BMB_OK;
+}

@@ -87,3 +87,32 @@ def test_missing_library_fails_loudly(bmb, tmp_path, monkeypatch):
     monkeypatch.setattr(bmb, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(bmb.BmbError, match="no CPU or PyTorch fallback"):
         bmb.lib()
+
+
+def test_tensorcore_gemm_schedule_covers_every_slice_once(bmb):
+    """The tile plan of the tcgen05 GEMM (tile width, whole tiles, tiles shared along K between CTAs),
+    replayed on the host for the training step's shapes, odd shapes and random ones, on several SM
+    counts: every (tile, K slice) must be computed exactly once."""
+    import ctypes as C
+    import random
+    lib = bmb.lib()
+    rng = random.Random(11)
+    shapes = [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072), (8192, 50304, 768),
+              (8192, 768, 50304), (3072, 768, 8192), (768, 768, 8192), (50304, 768, 8192), (8192, 8192, 8192),
+              (128, 64, 32), (129, 65, 33), (1000, 1000, 1000), (4096, 160, 512)]
+    shapes += [(rng.randrange(128, 5000), rng.randrange(64, 5000), rng.randrange(32, 5000)) for _ in range(60)]
+    shared = 0
+    for ctas in (148, 132, 7, 1):
+        for (M, N, K) in shapes:
+            for flags in (0, bmb.GEMM_NO_SPLIT):
+                bn, dp, grid = C.c_int(), C.c_int(), C.c_int()
+                st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flags, 1, M, N, K, ctas, C.byref(bn), C.byref(dp), C.byref(grid))
+                assert st == 0, (M, N, K, ctas, flags, lib.bmb_last_error())
+                tiles = -(-M // 128) * -(-N // bn.value)
+                assert bn.value in (64, 128, 192, 256) and 1 <= grid.value <= ctas and 0 <= dp.value <= tiles
+                if flags:
+                    assert dp.value == tiles
+                shared += dp.value < tiles
+    assert shared > 20                      # the sweep does exercise shared tiles
+    st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 96, 1024, 64, 1024, 148, None, None, None)   # batched
+    assert st == 0, lib.bmb_last_error()
