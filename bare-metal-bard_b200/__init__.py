@@ -115,6 +115,7 @@ SIGNATURES = {
     "bmb_trainer_step": (_i, [_p, _f, _i]),
     "bmb_trainer_forward_backward": (_i, [_p]),
     "bmb_trainer_loss": (_i, [_p, C.POINTER(_f)]),
+    "bmb_trainer_loss_async": (_i, [_p, _p]),
     "bmb_trainer_sync": (_i, [_p]),
     "bmb_trainer_stream": (_p, [_p]),
     "bmb_trainer_profile": (_i, [_p, _i]),
@@ -193,6 +194,10 @@ class Trainer:
         v = _f()
         check(lib().bmb_trainer_loss(self.h, C.byref(v)), "bmb_trainer_loss")
         return v.value
+
+    def loss_async(self, pinned_scalar):
+        """Enqueue the read of the last step's loss into a pinned float32 tensor / array element."""
+        check(lib().bmb_trainer_loss_async(self.h, ptr(pinned_scalar)), "bmb_trainer_loss_async")
 
     def sync(self):
         check(lib().bmb_trainer_sync(self.h), "bmb_trainer_sync")

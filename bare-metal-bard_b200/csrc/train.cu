@@ -520,6 +520,13 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
     return BMB_OK;
 }
 
+int bmb_trainer_loss_async(bmb_trainer *t, float *pinned_host_loss) {
+    if (!t || !pinned_host_loss) return fail(BMB_E_ARG, "trainer_loss_async: null argument");
+    Scope sc(t);
+    BMB_CUDA(cudaMemcpyAsync(pinned_host_loss, t->d_loss, sizeof(float), cudaMemcpyDeviceToHost, t->st));
+    return BMB_OK;
+}
+
 int bmb_trainer_loss(bmb_trainer *t, float *host_loss) {
     if (!t || !host_loss) return fail(BMB_E_ARG, "trainer_loss: null argument");
     Scope sc(t);

@@ -289,6 +289,11 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step);
 int bmb_trainer_forward_backward(bmb_trainer *t);
 /* Blocks: waits for the stream and returns the last step's mean loss. */
 int bmb_trainer_loss(bmb_trainer *t, float *host_loss);
+/* The same read without the wait: enqueues the 4-byte device-to-host copy of the last step's mean
+ * loss on the trainer's stream and returns; `pinned_host_loss` must be page-locked and is valid once
+ * the stream has passed this point (an event recorded after the call, or bmb_trainer_sync).  Lets a
+ * training loop read every step's loss one step late instead of draining the GPU every step. */
+int bmb_trainer_loss_async(bmb_trainer *t, float *pinned_host_loss);
 int bmb_trainer_sync(bmb_trainer *t);
 /* The CUDA stream every step of this trainer is enqueued on (for events). */
 void *bmb_trainer_stream(bmb_trainer *t);
