@@ -104,9 +104,12 @@ SIGNATURES = {
     "bmb_comm_create": (_i, [C.POINTER(_p), C.POINTER(C.c_ubyte), _i, _i]),
     "bmb_comm_destroy": (_i, [_p]),
     "bmb_comm_allreduce": (_i, [_p, _p, _z, _p]),
+    "bmb_comm_allreduce_f64": (_i, [_p, _p, _z, _p]),
     "bmb_trainer_create": (_i, [C.POINTER(_p), C.POINTER(TrainConfig), _u]),
     "bmb_trainer_destroy": (_i, [_p]),
     "bmb_trainer_attach_comm": (_i, [_p, _p, _i]),
+    "bmb_trainer_ipc_export": (_i, [_p, _p]),
+    "bmb_trainer_attach_peers": (_i, [_p, _i, _i, _p]),
     "bmb_trainer_num_params": (_z, [_p]),
     "bmb_trainer_get_params": (_i, [_p, _p]),
     "bmb_trainer_set_params": (_i, [_p, _p]),
@@ -194,6 +197,17 @@ class Trainer:
         v = _f()
         check(lib().bmb_trainer_loss(self.h, C.byref(v)), "bmb_trainer_loss")
         return v.value
+
+    def ipc_export(self):
+        """This rank's 192-byte record of CUDA IPC handles (gradients, parameters, shadow)."""
+        rec = (C.c_ubyte * 192)()
+        check(lib().bmb_trainer_ipc_export(self.h, rec), "bmb_trainer_ipc_export")
+        return bytes(rec)
+
+    def attach_peers(self, rank, nranks, records):
+        """records: the ranks' ipc_export() results concatenated in rank order."""
+        buf = (C.c_ubyte * len(records)).from_buffer_copy(records)
+        check(lib().bmb_trainer_attach_peers(self.h, rank, nranks, buf), "bmb_trainer_attach_peers")
 
     def loss_async(self, pinned_scalar):
         """Enqueue the read of the last step's loss into a pinned float32 tensor / array element."""

@@ -505,4 +505,13 @@ int bmb_comm_allreduce(bmb_comm *c, float *buf, size_t count, void *stream) {
     return BMB_OK;
 }
 
+// Sum of `count` doubles across the ranks (the squared-norm exchange of the fused data-parallel step).
+int bmb_comm_allreduce_f64(bmb_comm *c, double *buf, size_t count, void *stream) {
+    if (!c || !c->comm) return fail(BMB_E_ARG, "comm_allreduce_f64: null communicator");
+    if (count == 0 || c->nranks == 1) return BMB_OK;
+    const int rc = g_nccl.AllReduce(buf, buf, count, /*ncclFloat64*/ 8, /*ncclSum*/ 0, c->comm, (cudaStream_t)stream);
+    if (rc) return nccl_fail("ncclAllReduce", rc);
+    return BMB_OK;
+}
+
 }  // extern "C"

@@ -22,6 +22,14 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
 namespace tc {
 int status_word(int **dev_ptr, volatile int **host_ptr);
 }
+struct DpFused;
+int dp_fused_export(const float *grads, const float *params, const float *shadow, void *out192);
+int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads, float *params, float *shadow,
+                    const void *all_handles);
+void dp_fused_destroy(DpFused *d);
+int dp_fused_reduce(DpFused *d, size_t n, float *grads, double *d_sumsq_slice, cudaStream_t st);
+int dp_fused_update(DpFused *d, size_t n, const float *grads, float *m, float *v, float lr, float beta1, float beta2,
+                    float eps, float wd, int step, const double *d_sumsq_total, float clip, cudaStream_t st);
 }
 using namespace bmb;
 
@@ -43,6 +51,8 @@ struct bmb_trainer {
     double *d_sumsq = nullptr;
     bmb_comm *comm = nullptr;
     int nranks = 1;
+    DpFused *dp = nullptr;        // fused gradient exchange + optimiser over peer memory, when attached
+    float *d_token = nullptr;     // one float the ranks all-reduce where the step only needs a barrier
     // activation pointers
     float *encoded, *ln1, *ln1_mean, *ln1_rstd, *qkv, *qkvr, *att, *lse, *atty, *attproj, *residual2,
         *ln2, *ln2_mean, *ln2_rstd, *fch, *fch_gelu, *fcproj, *residual3, *lnf, *lnf_mean, *lnf_rstd,
@@ -412,6 +422,8 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
     BMB_CUDA(cudaMalloc(&t->d_loss, sizeof(float)));
     BMB_CUDA(cudaMalloc(&t->d_sumsq, sizeof(double)));
     BMB_CUDA(cudaMemset(t->d_loss, 0, sizeof(float)));
+    BMB_CUDA(cudaMalloc(&t->d_token, sizeof(float)));
+    BMB_CUDA(cudaMemset(t->d_token, 0, sizeof(float)));
 
     // GPT-2 initialisation with the reference's draw order (src/gpt.cu:189-218):
     // one mt19937 stream; a fresh normal_distribution per tensor; N(0, 0.02)
@@ -452,7 +464,8 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     cudaFree(t->params); cudaFree(t->grads); cudaFree(t->m); cudaFree(t->v);
     if (t->shadow) cudaFree(t->shadow);
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
-    cudaFree(t->d_loss); cudaFree(t->d_sumsq);
+    cudaFree(t->d_loss); cudaFree(t->d_sumsq); cudaFree(t->d_token);
+    dp_fused_destroy(t->dp);
     cudaStreamDestroy(t->st);
     delete t;
     return BMB_OK;
@@ -463,6 +476,22 @@ int bmb_trainer_attach_comm(bmb_trainer *t, bmb_comm *c, int nranks) {
     t->comm = c;
     t->nranks = nranks;
     return BMB_OK;
+}
+
+int bmb_trainer_ipc_export(bmb_trainer *t, void *record192) {
+    if (!t || !record192) return fail(BMB_E_ARG, "trainer_ipc_export: null argument");
+    Scope sc(t);
+    return dp_fused_export(t->grads, t->params, t->shadow, record192);
+}
+
+int bmb_trainer_attach_peers(bmb_trainer *t, int rank, int nranks, const void *records) {
+    if (!t || !records) return fail(BMB_E_ARG, "trainer_attach_peers: null argument");
+    if (!t->comm || t->nranks != nranks) return fail(BMB_E_ARG, "trainer_attach_peers: attach the communicator of %d ranks first", nranks);
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    dp_fused_destroy(t->dp);
+    t->dp = nullptr;
+    return dp_fused_create(&t->dp, rank, nranks, t->num_params, t->grads, t->params, t->shadow, records);
 }
 
 size_t bmb_trainer_num_params(const bmb_trainer *t) { return t ? t->num_params : 0; }
@@ -512,6 +541,18 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
     if (!t || step < 1) return fail(BMB_E_ARG, "trainer_step: bad argument");
     Scope sc(t);
     BMB_TRY(forward_backward_step(t));
+    if (t->dp) {
+        // Collectives on this stream order the phases across ranks: no rank's reduce starts before
+        // every rank's backward is done, no update before every slice is summed, and the next
+        // forward not before every rank has received every slice of the new parameters.
+        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st));
+        BMB_TRY(dp_fused_reduce(t->dp, t->num_params, t->grads, t->d_sumsq, t->st));
+        BMB_TRY(bmb_comm_allreduce_f64(t->comm, t->d_sumsq, 1, t->st));
+        BMB_TRY(dp_fused_update(t->dp, t->num_params, t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
+                                t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, t->st));
+        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st));
+        return BMB_OK;
+    }
     if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
     BMB_TRY(bmb_grad_sumsq_device(t->grads, t->num_params, t->d_sumsq));
     BMB_TRY(bmb_adamw_update_clipped(t->params, t->grads, t->m, t->v, t->num_params, lr, t->c.beta1, t->c.beta2,

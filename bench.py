@@ -205,6 +205,11 @@ def run_bmb(args):
         comm = C.c_void_p()
         bmb.check(lib.bmb_comm_create(C.byref(comm), ident, world, rank), "bmb_comm_create")
         tr.attach_comm(comm, world)
+        if not args.nccl_dp:
+            # fused gradient exchange + optimiser over peer memory: hand every rank's IPC record to every rank
+            mine = tr.ipc_export()
+            records = b"".join(dist_mod.broadcast_bytes(mine, 192, src=r) for r in range(world))
+            tr.attach_peers(rank, world, records)
 
     PROF_STEPS = 2
     nsteps = args.warmup + 2 * args.steps + PROF_STEPS
@@ -319,6 +324,8 @@ def run_bmb(args):
         "config": {"workload": "GPT-2-small-shaped train step: 12 layers, d_model 768, 12 heads, ctx 1024, "
                                "vocab 50304, batch 8 sequences per GPU, AdamW lr 3e-4 betas 0.9/0.95 wd 0.1 clip 1.0",
                    "global_batch": B_PER_GPU * world, "seq_len": T, "parallelism": "dp%d" % world,
+                   "gradient_exchange": ("none" if world == 1 else "NCCL all-reduce, full optimiser per rank" if args.nccl_dp
+                                         else "fused over peer memory: slice reduce, slice AdamW, parameter broadcast"),
                    "l2": "per-step working set (~10 GB of activations) exceeds the 126 MB L2",
                    "flop_per_step_per_gpu": flops_per_step_per_gpu(tr.num_params)},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B_PER_GPU * T * 4,
@@ -422,6 +429,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the square GEMM sweep")
     ap.add_argument("--unfused", action="store_true", help="the reference's op list: separate bias kernels, "
                     "operands rounded by a prepass instead of by their producers")
+    ap.add_argument("--nccl-dp", action="store_true", help="N > 1: sum gradients with one NCCL all-reduce and run the "
+                    "whole optimiser on every rank, instead of the fused exchange over peer memory")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.warmup < 3:

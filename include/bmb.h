@@ -258,6 +258,7 @@ int bmb_comm_create(bmb_comm **out, const unsigned char id[128], int nranks,
 int bmb_comm_destroy(bmb_comm *c);
 /* In-place sum of count floats over all ranks, asynchronous on `stream`. */
 int bmb_comm_allreduce(bmb_comm *c, float *buf, size_t count, void *stream);
+int bmb_comm_allreduce_f64(bmb_comm *c, double *buf, size_t count, void *stream);
 
 /* ---- GPT training step (caller of all of the above; src/gpt.h:10-79,
  *      src/train_gpt.cu:397-464) ---------------------------------------- */
@@ -274,6 +275,17 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg,
                        unsigned seed);
 int bmb_trainer_destroy(bmb_trainer *t);
 int bmb_trainer_attach_comm(bmb_trainer *t, bmb_comm *c, int nranks);
+/* Fused gradient exchange + optimiser over peer memory (one process per GPU, 2..8 ranks; replaces
+ * ddp_allreduce + grad norm + adamw_update of src/train_gpt.cu:431-451 inside bmb_trainer_step):
+ * every rank sums its slice of all ranks' gradients by reading the peers' buffers, the ranks add
+ * their squared norms, every rank updates its slice and stores the new parameters into all
+ * ranks' buffers.  bmb_trainer_ipc_export writes this rank's 192-byte handle record; the launcher
+ * gathers the records of all ranks in rank order and hands them to bmb_trainer_attach_peers
+ * (after bmb_trainer_attach_comm, whose communicator carries the small collectives that order
+ * the phases).  After a fused step bmb_trainer_get_grads returns summed values only inside this
+ * rank's slice. */
+int bmb_trainer_ipc_export(bmb_trainer *t, void *record192);
+int bmb_trainer_attach_peers(bmb_trainer *t, int rank, int nranks, const void *records);
 size_t bmb_trainer_num_params(const bmb_trainer *t);
 int bmb_trainer_get_params(bmb_trainer *t, float *host_out);
 int bmb_trainer_set_params(bmb_trainer *t, const float *host_in);

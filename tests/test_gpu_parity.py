@@ -543,3 +543,21 @@ def test_golden_fixtures_on_gpu(bmb, orc, cuda):
                 tr.step(float(z["lr"]), s + 1)
                 assert abs(tr.loss() - float(z["losses"][s])) < 2e-3, (f, s)
             tr.close()
+
+
+def test_fused_data_parallel_step_matches_nccl(cuda):
+    """Two ranks (one per GPU) train a small model with the NCCL all-reduce + full optimiser and with
+    the fused exchange over peer memory: same losses, same parameters on every rank
+    (tests/dp_fused_check.py).  Needs two GPUs."""
+    import os
+    import subprocess
+    import sys
+    if cuda.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29577", os.path.join(here, "dp_fused_check.py")],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
