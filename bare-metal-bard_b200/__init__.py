@@ -206,7 +206,7 @@ class Trainer:
 
     def attach_peers(self, rank, nranks, records):
         """records: the ranks' ipc_export() results concatenated in rank order."""
-        buf = (C.c_ubyte * len(records)).from_buffer_copy(records)
+        buf = (C.c_ubyte * len(records)).from_buffer_copy(records) if records is not None else None
         check(lib().bmb_trainer_attach_peers(self.h, rank, nranks, buf), "bmb_trainer_attach_peers")
 
     def loss_async(self, pinned_scalar):

@@ -485,7 +485,14 @@ int bmb_trainer_ipc_export(bmb_trainer *t, void *record192) {
 }
 
 int bmb_trainer_attach_peers(bmb_trainer *t, int rank, int nranks, const void *records) {
-    if (!t || !records) return fail(BMB_E_ARG, "trainer_attach_peers: null argument");
+    if (!t) return fail(BMB_E_ARG, "trainer_attach_peers: null handle");
+    if (!records) {                       // detach: back to the communicator's all-reduce
+        Scope sc(t);
+        BMB_CUDA(cudaStreamSynchronize(t->st));
+        dp_fused_destroy(t->dp);
+        t->dp = nullptr;
+        return BMB_OK;
+    }
     if (!t->comm || t->nranks != nranks) return fail(BMB_E_ARG, "trainer_attach_peers: attach the communicator of %d ranks first", nranks);
     Scope sc(t);
     BMB_CUDA(cudaStreamSynchronize(t->st));

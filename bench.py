@@ -209,7 +209,15 @@ def run_bmb(args):
             # fused gradient exchange + optimiser over peer memory: hand every rank's IPC record to every rank
             mine = tr.ipc_export()
             records = b"".join(dist_mod.broadcast_bytes(mine, 192, src=r) for r in range(world))
-            tr.attach_peers(rank, world, records)
+            try:
+                tr.attach_peers(rank, world, records)
+                attached = 1.0
+            except bmb.BmbError as e:           # e.g. no peer access between two of the GPUs
+                sys.stderr.write("rank %d: fused exchange unavailable (%s)\n" % (rank, e))
+                attached = 0.0
+            if -dist_mod.max_over_ranks(-attached) < 1.0:      # all ranks or none
+                tr.attach_peers(rank, world, None)
+                args.nccl_dp = True
 
     PROF_STEPS = 2
     nsteps = args.warmup + 2 * args.steps + PROF_STEPS

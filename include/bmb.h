@@ -282,8 +282,9 @@ int bmb_trainer_attach_comm(bmb_trainer *t, bmb_comm *c, int nranks);
  * ranks' buffers.  bmb_trainer_ipc_export writes this rank's 192-byte handle record; the launcher
  * gathers the records of all ranks in rank order and hands them to bmb_trainer_attach_peers
  * (after bmb_trainer_attach_comm, whose communicator carries the small collectives that order
- * the phases).  After a fused step bmb_trainer_get_grads returns summed values only inside this
- * rank's slice. */
+ * the phases).  records = NULL detaches (back to the communicator's all-reduce); all ranks must
+ * attach or none.  After a fused step bmb_trainer_get_grads returns summed values only inside
+ * this rank's slice. */
 int bmb_trainer_ipc_export(bmb_trainer *t, void *record192);
 int bmb_trainer_attach_peers(bmb_trainer *t, int rank, int nranks, const void *records);
 size_t bmb_trainer_num_params(const bmb_trainer *t);
