@@ -9,8 +9,9 @@
 //   2. the ranks add their sums of squares (one 8-byte all-reduce, which is also the barrier between
 //      the phases);
 //   3. update + broadcast: it runs AdamW (with the clip factor of src/train_gpt.cu:442-448) on its
-//      slice only and stores the new parameters -- and their TF32-rounded shadow -- straight into every
-//      rank's buffers.
+//      slice only and stores the new parameters straight into every rank's buffers (each rank rounds
+//      its own TF32 shadow copy from them afterwards: a local pass is cheaper than a second trip
+//      over NVLink).
 // Per rank that is (n-1)/n of the buffer read and (n-1)/n written over NVLink, as in a ring
 // all-reduce, but the optimiser touches 1/n of the parameters and no separate norm pass is needed.
 // The peers' buffers are reached through CUDA IPC handles exchanged by the launcher.  The kernels only
@@ -27,7 +28,6 @@ constexpr int MAX_RANKS = 8;
 struct PeerBufs {
     const float *grads[MAX_RANKS];
     float *params[MAX_RANKS];
-    float *shadow[MAX_RANKS];
 };
 
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
@@ -82,7 +82,7 @@ __device__ __forceinline__ float adamw_one(float p, float g, float &m, float &v,
 
 // AdamW (src/nn.cu:240-254) on [off, off + len) of this rank's buffers, gradient = the reduced slice
 // scaled by the clip rule evaluated from the global squared norm *d_sumsq (sum over all ranks'
-// slices); the new parameters and their TF32 shadow go to every rank.
+// slices); the new parameters go to every rank.
 __global__ void __launch_bounds__(256)
 dp_adamw_broadcast_k(PeerBufs pb, int nranks, int rank, const float *__restrict__ grads, float *__restrict__ m,
                      float *__restrict__ v, size_t off, size_t len, float lr, float b1, float b2, float eps, float wd,
@@ -101,13 +101,9 @@ dp_adamw_broadcast_k(PeerBufs pb, int nranks, int rank, const float *__restrict_
         p.w = adamw_one(p.w, g.w * gscale, mm.w, vv.w, lr, b1, b2, eps, wd, bc1, bc2);
         st4(m + e, mm);
         st4(v + e, vv);
-        const float4 ps = make_float4(round_tf32(p.x), round_tf32(p.y), round_tf32(p.z), round_tf32(p.w));
 #pragma unroll
         for (int r = 0; r < MAX_RANKS; ++r)
-            if (r < nranks) {
-                st4(pb.params[r] + e, p);
-                if (pb.shadow[r]) st4(pb.shadow[r] + e, ps);
-            }
+            if (r < nranks) st4(pb.params[r] + e, p);
     }
 }
 
@@ -127,12 +123,12 @@ int dp_fused_export(const float *grads, const float *params, const float *shadow
     memset(h, 0, sizeof(h));
     BMB_CUDA(cudaIpcGetMemHandle(&h[0], const_cast<float *>(grads)));
     BMB_CUDA(cudaIpcGetMemHandle(&h[1], const_cast<float *>(params)));
-    if (shadow) BMB_CUDA(cudaIpcGetMemHandle(&h[2], const_cast<float *>(shadow)));
+    (void)shadow;          // the third handle slot of the record stays empty: shadows are rounded locally
     memcpy(out192, h, sizeof(h));
     return BMB_OK;
 }
 
-int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads, float *params, float *shadow,
+int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads, float *params, float * /*shadow*/,
                     const void *all_handles) {
     if (nranks < 2 || nranks > MAX_RANKS || rank < 0 || rank >= nranks)
         return fail(BMB_E_ARG, "fused data-parallel step: rank %d of %d (2..%d ranks)", rank, nranks, MAX_RANKS);
@@ -143,14 +139,13 @@ int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads,
     const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(all_handles);
     for (int r = 0; r < nranks; ++r) {
         if (r == rank) {
-            d->pb.grads[r] = grads; d->pb.params[r] = params; d->pb.shadow[r] = shadow;
+            d->pb.grads[r] = grads; d->pb.params[r] = params;
             continue;
         }
-        void *pg = nullptr, *pp = nullptr, *ps = nullptr;
+        void *pg = nullptr, *pp = nullptr;
         cudaError_t e = cudaIpcOpenMemHandle(&pg, h[3 * r + 0], cudaIpcMemLazyEnablePeerAccess);
         if (e == cudaSuccess) { d->opened[d->nopened++] = pg; e = cudaIpcOpenMemHandle(&pp, h[3 * r + 1], cudaIpcMemLazyEnablePeerAccess); }
-        if (e == cudaSuccess) { d->opened[d->nopened++] = pp; if (shadow) e = cudaIpcOpenMemHandle(&ps, h[3 * r + 2], cudaIpcMemLazyEnablePeerAccess); }
-        if (e == cudaSuccess && ps) d->opened[d->nopened++] = ps;
+        if (e == cudaSuccess) d->opened[d->nopened++] = pp;
         if (e != cudaSuccess) {
             const int rc = fail(BMB_E_CUDA, "cudaIpcOpenMemHandle for rank %d -> %s", r, cudaGetErrorString(e));
             for (int i = 0; i < d->nopened; ++i) cudaIpcCloseMemHandle(d->opened[i]);
@@ -160,7 +155,6 @@ int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads,
         }
         d->pb.grads[r] = static_cast<const float *>(pg);
         d->pb.params[r] = static_cast<float *>(pp);
-        d->pb.shadow[r] = static_cast<float *>(ps);
     }
     *out = d;
     return BMB_OK;

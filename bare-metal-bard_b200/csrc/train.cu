@@ -558,7 +558,7 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
         BMB_TRY(dp_fused_update(t->dp, t->num_params, t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
                                 t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, t->st));
         BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st));
-        return BMB_OK;
+        return refresh_shadow(t);         // every slice of the new parameters has arrived
     }
     if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
     BMB_TRY(bmb_grad_sumsq_device(t->grads, t->num_params, t->d_sumsq));
