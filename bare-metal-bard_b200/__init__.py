@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(HERE, "libbmb.so")
 
 MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2
 GEMM_A_ROUNDED, GEMM_B_ROUNDED, GEMM_C_ROUNDED, GEMM_NO_SPLIT = 1, 2, 4, 8
+FLASH_OPERANDS_ROUNDED = 1
 E_UNSUPPORTED = 3
 E_LIMIT = 6
 
@@ -63,10 +64,12 @@ SIGNATURES = {
     "bmb_flash_config_name": (C.c_char_p, [_i]),
     "bmb_flash_default_config": (_i, []),
     "bmb_flash_attention_forward_cfg": (_i, [_i, _p, _p, _p, _i, _i, _i, _i]),
+    "bmb_flash_attention_forward_ex": (_i, [_i, _i, _p, _p, _p, _i, _i, _i, _i]),
     "bmb_flash_num_bwd_configs": (_i, []),
     "bmb_flash_bwd_config_name": (C.c_char_p, [_i]),
     "bmb_flash_default_bwd_config": (_i, []),
     "bmb_flash_attention_backward_cfg": (_i, [_i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i]),
+    "bmb_flash_attention_backward_ex": (_i, [_i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i]),
     "bmb_attention_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i]),
     "bmb_attention_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i]),
     "bmb_encoder_forward": (_i, [_p, _p, _p, _p, _i, _i, _i]),

@@ -385,7 +385,7 @@ const FwdCfg FWD[] = {{16, "simt-fp32 rowgroup keys16"}, {8, "simt-fp32 rowgroup
                       {0, "tcgen05-tf32 q2x128 k64"}};
 // Backward config 2 is the tensor-core kernel pair (flash_tc_bwd.cu), head size 64 only.
 const BwdCfg BWD[] = {{4, "simt-fp32 rowgroup keys4"}, {8, "simt-fp32 rowgroup keys8"},
-                      {0, "tcgen05-tf32 dq128x64 dkv128x32"}};
+                      {0, "tcgen05-tf32 dq128x64 dkv128x64"}};
 constexpr int NFWD = 3, NBWD = 3, FWD_TC = 2, BWD_TC = 2;
 
 bool shape_ok(const float *a, const float *b, int C, int NH) {
@@ -456,6 +456,11 @@ int bmb_flash_default_config(void) { return bmb_get_math_mode() == BMB_MATH_FP32
 
 int bmb_flash_attention_forward_cfg(int cfg, float *out, float *lse, const float *qkv, int B, int T,
                                     int C, int NH) {
+    return bmb_flash_attention_forward_ex(cfg, 0, out, lse, qkv, B, T, C, NH);
+}
+
+int bmb_flash_attention_forward_ex(int cfg, int flags, float *out, float *lse, const float *qkv, int B, int T,
+                                   int C, int NH) {
     if (cfg < 0 || cfg >= NFWD) return fail(BMB_E_UNSUPPORTED, "flash: no forward config %d", cfg);
     if (B <= 0 || T <= 0) return BMB_OK;
     if (!shape_ok(out, qkv, C, NH)) return fail(BMB_E_ARG, "flash: bad shape or alignment (C=%d NH=%d)", C, NH);
@@ -465,7 +470,7 @@ int bmb_flash_attention_forward_cfg(int cfg, float *out, float *lse, const float
     if (cfg == FWD_TC) {
         if (!flash_tc_supported(T, C, NH, qkv, out))
             return fail(BMB_E_UNSUPPORTED, "flash: the tensor-core config needs head size 64 (got %d)", hs);
-        return flash_forward_tc(out, lse, qkv, B, T, C, NH, false, st);
+        return flash_forward_tc(out, lse, qkv, B, T, C, NH, (flags & BMB_FLASH_OPERANDS_ROUNDED) != 0, st);
     }
     switch (hs) {
     case 32:  return run_fwd<32>(cfg, out, lse, qkv, B, T, NH, scale, st);
@@ -490,6 +495,12 @@ int bmb_flash_default_bwd_config(void) { return bmb_get_math_mode() == BMB_MATH_
 int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum, const float *dout,
                                      const float *qkv, const float *out, const float *lse, int B,
                                      int T, int C, int NH) {
+    return bmb_flash_attention_backward_ex(cfg, 0, dqkv, dsum, dout, qkv, out, lse, B, T, C, NH);
+}
+
+int bmb_flash_attention_backward_ex(int cfg, int flags, float *dqkv, float *dsum, const float *dout,
+                                    const float *qkv, const float *out, const float *lse, int B,
+                                    int T, int C, int NH) {
     if (cfg < 0 || cfg >= NBWD) return fail(BMB_E_UNSUPPORTED, "flash: no backward config %d", cfg);
     if (B <= 0 || T <= 0) return BMB_OK;
     if (!shape_ok(dqkv, qkv, C, NH) || !shape_ok(dout, out, C, NH))
@@ -500,7 +511,7 @@ int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum, const fl
     if (cfg == BWD_TC) {
         if (!flash_tc_supported(T, C, NH, qkv, dqkv))
             return fail(BMB_E_UNSUPPORTED, "flash: the tensor-core config needs head size 64 (got %d)", hs);
-        return flash_backward_tc(dqkv, dsum, dout, qkv, out, lse, B, T, C, NH, false, st);
+        return flash_backward_tc(dqkv, dsum, dout, qkv, out, lse, B, T, C, NH, (flags & BMB_FLASH_OPERANDS_ROUNDED) != 0, st);
     }
     switch (hs) {
     case 32:  return run_bwd<32>(cfg, dqkv, dsum, dout, qkv, out, lse, B, T, NH, scale, st);

@@ -112,6 +112,15 @@ def bench_flash(bmb, small):
         best, med = timed(lambda: bmb.call("bmb_flash_attention_forward_cfg", cfg, out, lse, qkv, B, T, C, NH))
         emit(kernel="flash_fwd", config=name, B=B, NH=NH, T=T, hs=hs, best_ms=round(best, 4), median_ms=round(med, 4),
              useful_tflops_best=round(useful / best / 1e9, 2), gbs_best=round(fbytes / best / 1e6, 1))
+    # the tensor-core kernels alone, on operands already rounded to TF32 (how the training step runs them)
+    tc_fwd = lib.bmb_flash_num_configs() - 1
+    qr, dr = qkv.clone(), dout.clone()
+    bmb.call("bmb_round_tf32", qr, qr, qr.numel(), None)
+    bmb.call("bmb_round_tf32", dr, dr, dr.numel(), None)
+    best, med = timed(lambda: bmb.call("bmb_flash_attention_forward_ex", tc_fwd, bmb.FLASH_OPERANDS_ROUNDED, out, lse, qr, B, T, C, NH))
+    emit(kernel="flash_fwd", config=lib.bmb_flash_config_name(tc_fwd).decode() + ", operands pre-rounded", B=B, NH=NH, T=T, hs=hs,
+         best_ms=round(best, 4), median_ms=round(med, 4), useful_tflops_best=round(useful / best / 1e9, 2),
+         gbs_best=round(fbytes / best / 1e6, 1))
     bmb.call("bmb_flash_attention_forward_cfg", 0, out, lse, qkv, B, T, C, NH)
     bbytes = 4.0 * (2 * B * T * 3 * C + 2 * B * T * C + 2 * B * NH * T)
     for cfg in range(lib.bmb_flash_num_bwd_configs()):
@@ -120,6 +129,11 @@ def bench_flash(bmb, small):
         emit(kernel="flash_bwd", config=name, B=B, NH=NH, T=T, hs=hs, best_ms=round(best, 4), median_ms=round(med, 4),
              tflops_2p5x_best=round(2.5 * useful / best / 1e9, 2), tflops_3p5x_best=round(3.5 * useful / best / 1e9, 2),
              gbs_best=round(bbytes / best / 1e6, 1))
+    tc_bwd = lib.bmb_flash_num_bwd_configs() - 1
+    best, med = timed(lambda: bmb.call("bmb_flash_attention_backward_ex", tc_bwd, bmb.FLASH_OPERANDS_ROUNDED, dqkv, dsum, dr, qr, out, lse, B, T, C, NH))
+    emit(kernel="flash_bwd", config=lib.bmb_flash_bwd_config_name(tc_bwd).decode() + ", operands pre-rounded", B=B, NH=NH, T=T, hs=hs,
+         best_ms=round(best, 4), median_ms=round(med, 4), tflops_2p5x_best=round(2.5 * useful / best / 1e9, 2),
+         tflops_3p5x_best=round(3.5 * useful / best / 1e9, 2), gbs_best=round(bbytes / best / 1e6, 1))
 
 
 def bench_nn(bmb, small):

@@ -124,6 +124,16 @@ int bmb_flash_attention_backward_cfg(int cfg, float *dqkv, float *dsum,
                                      const float *dout, const float *qkv,
                                      const float *out, const float *lse, int B,
                                      int T, int C, int NH);
+/* No counterpart in the reference: the _cfg calls with a flag word.  BMB_FLASH_OPERANDS_ROUNDED
+ * tells the TF32 tensor-core configuration that qkv (and dout) already hold TF32-representable
+ * values, as the training step's producers leave them: the kernels then read them where they
+ * lie instead of rounding copies first.  Ignored by the fp32 configurations. */
+#define BMB_FLASH_OPERANDS_ROUNDED 1
+int bmb_flash_attention_forward_ex(int cfg, int flags, float *out, float *lse,
+                                   const float *qkv, int B, int T, int C, int NH);
+int bmb_flash_attention_backward_ex(int cfg, int flags, float *dqkv, float *dsum,
+                                    const float *dout, const float *qkv, const float *out,
+                                    const float *lse, int B, int T, int C, int NH);
 
 /* ---- unfused attention (src/attention.h:18-24) ------------------------- */
 int bmb_attention_forward(float *out, float *qkvr, float *att,

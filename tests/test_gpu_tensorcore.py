@@ -11,7 +11,7 @@ Two bars per case:
 import numpy as np
 import pytest
 
-from helpers import _np, normwise, uniform
+from helpers import _np, normal, normwise, uniform
 
 pytestmark = pytest.mark.gpu
 
@@ -217,6 +217,26 @@ def test_tensorcore_flash_backward_vs_oracle(bmb, orc, cuda, B, T, C, NH):
     errs = [float(np.max(np.abs(g[:, i].astype(np.float64) - w[:, i])) / max(float(np.max(np.abs(w[:, i]))), floor))
             for i in range(3)]
     assert np.all(np.isfinite(g)) and max(errs) < 5e-3, errs
+
+
+def test_tensorcore_flash_reads_prerounded_operands_in_place(bmb, orc, cuda):
+    """With BMB_FLASH_OPERANDS_ROUNDED the tensor-core kernels skip their rounding copies; on operands
+    that are already TF32-representable the results must equal the copying route bit for bit."""
+    B, T, C, NH = 2, 256, 256, 4
+    lib = bmb.lib()
+    qkv = rounded(orc, normal(B * T * 3 * C, 5), "tf32")
+    dout = rounded(orc, normal(B * T * C, 6), "tf32")
+    dq, dd = dev(cuda, qkv), dev(cuda, dout)
+    fwd, bwd = lib.bmb_flash_num_configs() - 1, lib.bmb_flash_num_bwd_configs() - 1
+    o1, l1, o2, l2 = (cuda.zeros(n, device="cuda") for n in (B * T * C, B * NH * T, B * T * C, B * NH * T))
+    bmb.call("bmb_flash_attention_forward_cfg", fwd, o1, l1, dq, B, T, C, NH)
+    bmb.call("bmb_flash_attention_forward_ex", fwd, bmb.FLASH_OPERANDS_ROUNDED, o2, l2, dq, B, T, C, NH)
+    assert np.array_equal(host(cuda, o1), host(cuda, o2)) and np.array_equal(host(cuda, l1), host(cuda, l2))
+    g1, g2 = cuda.zeros(B * T * 3 * C, device="cuda"), cuda.zeros(B * T * 3 * C, device="cuda")
+    s1, s2 = cuda.zeros(B * NH * T, device="cuda"), cuda.zeros(B * NH * T, device="cuda")
+    bmb.call("bmb_flash_attention_backward_cfg", bwd, g1, s1, dd, dq, o1, l1, B, T, C, NH)
+    bmb.call("bmb_flash_attention_backward_ex", bwd, bmb.FLASH_OPERANDS_ROUNDED, g2, s2, dd, dq, o1, l1, B, T, C, NH)
+    assert np.array_equal(host(cuda, g1), host(cuda, g2))
 
 
 def test_tensorcore_flash_rejects_other_head_sizes(bmb, cuda):
