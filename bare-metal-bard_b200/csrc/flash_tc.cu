@@ -5,22 +5,27 @@
 // The (T x T) score matrix never leaves tensor memory and registers (src/flash.h:1-34).
 //
 // One CTA owns 256 consecutive queries of one (batch, head) as two tiles of
-// 128 and walks the keys in blocks of 64 up to the diagonal.  320 threads:
-//   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: a thread reads its row
-//                    of S from TMEM (tcgen05.ld), masks the diagonal block,
+// 128 and walks the keys up to the diagonal: shared-memory stages and S
+// products cover 128 keys, softmax steps 64.  352 threads:
+//   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: a thread reads 64 scores
+//                    of its row from TMEM (tcgen05.ld), masks the diagonal,
 //                    updates the running max and sum (the scale rides in the
 //                    exponent's multiply-add), writes P = exp2(.) rounded to
 //                    TF32 back into tensor memory (tcgen05.st) and, after
-//                    handing P to the tensor core, folds the previous block's
+//                    handing P to the tensor core, folds the previous step's
 //                    P V into its output registers:
 //                    o = o * exp2(m_old - m_new) + PV;
-//   warp 8           producer: TMA loads of the two Q tiles, then K and V
-//                    blocks into a 5-deep ring;
-//   warp 9           issuer: S_t = Q_t K_j^T as soon as the group has taken
-//                    S_t(j-1) out of TMEM, PV_t = P_t V_j (A operand read from
-//                    tensor memory) as soon as P_t is written.  The two tiles
-//                    interleave, so one group's exponentials overlap the
-//                    other's matrix products.
+//   warp 8           producer: TMA loads of the two Q tiles, then K blocks into
+//                    a 2-deep ring and V blocks into a 3-deep ring;
+//   warp 9           issuer of S_t = Q_t K_j^T (N = 128: one instruction costs
+//                    the tensor pipe its 64 cycles, whereas a thread cannot
+//                    issue N = 64 instructions as fast as the pipe retires
+//                    them), as soon as the group has taken S_t(j-1) out of TMEM;
+//   warp 10          issuer of PV_t = P_t V (A operand read from tensor memory,
+//                    64 keys per step) as soon as P_t is written.
+// Two issuing threads keep the next block's scores from queueing behind a wait
+// for the other tile's P; the two tiles interleave, so one group's exponentials
+// overlap the other's matrix products.
 // V is the B operand of P V with the head dimension contiguous, i.e. MN-major:
 // its TMA map uses the 128-byte swizzle with 32-byte atoms.  K and Q are
 // K-major.  Keys beyond the end of a sequence are never seen unmasked: a key
@@ -39,16 +44,18 @@ namespace {
 
 using namespace tc;
 
-constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KV_STAGES = 5;
+// KB keys per softmax step, KBLK = 2 KB keys per shared-memory stage and per S product
+constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KBLK = 128, K_STAGES = 2, V_STAGES = 3;
 constexpr int Q_TILE_BYTES = QT * HS * 4;          // 32 KB: two halves of 128 rows x 128 B
-constexpr int KV_TILE_BYTES = KB * HS * 4;         // 16 KB: two halves / chunks of 64 rows x 128 B
-constexpr int TILE_COLS = 192;                     // TMEM columns per query tile: S | P | P V, 64 each
+constexpr int KV_TILE_BYTES = KBLK * HS * 4;       // 32 KB: two halves / chunks of 128 rows x 128 B
+constexpr int TILE_COLS = 256;                     // TMEM columns per query tile: S (128) | P (64) | P V (64)
+constexpr int COL_P = 128, COL_PV = 192;
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + NQ * Q_TILE_BYTES;
-constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
-constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_TILE_BYTES;
+constexpr int OFF_V = OFF_K + K_STAGES * KV_TILE_BYTES;
+constexpr int OFF_BAR = OFF_V + V_STAGES * KV_TILE_BYTES;
 constexpr int FWD_SMEM = OFF_BAR + 256 + 1024;
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 352;
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -58,9 +65,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 #ifdef BMB_FLASH_TRACE
 __device__ long long g_trace[16];
-#define TR(i) do { if (tr) { const long long now_ = clock64(); g_trace[i] += now_ - tlast; tlast = now_; } } while (0)
+// phase times are summed in registers and written once, so a timer costs one clock read
+#define TR(i) do { const long long now_ = clock64(); tacc[(i) & 7] += now_ - tlast; tlast = now_; } while (0)
+#define TRI(i) TR(i)
+#define TR_FLUSH(first, n) do { if (tr) for (int i_ = 0; i_ < (n); ++i_) g_trace[(first) + i_] += tacc[((first) + i_) & 7]; } while (0)
 #else
 #define TR(i)
+#define TRI(i)
+#define TR_FLUSH(first, n)
 #endif
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -72,8 +84,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
     // barrier indices
-    enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = KV_FULL + KV_STAGES, S_FULL = KV_EMPTY + KV_STAGES, S_EMPTY = S_FULL + NQ,
-           P_FULL = S_EMPTY + NQ, PV_FULL = P_FULL + NQ, NBARS = PV_FULL + NQ };
+    enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + K_STAGES, V_FULL = K_EMPTY + K_STAGES, V_EMPTY = V_FULL + V_STAGES,
+           S_FULL = V_EMPTY + V_STAGES, S_EMPTY = S_FULL + NQ, P_FULL = S_EMPTY + NQ, PV_FULL = P_FULL + NQ, NBARS = PV_FULL + NQ };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -87,17 +99,20 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     const int qblk = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int q0 = qblk * (NQ * QT);
 
-    int nblk[NQ];
+    // per tile: softmax steps of KB keys up to the diagonal, and the blocks of KBLK keys that hold them
+    int nstep[NQ], nblk[NQ];
 #pragma unroll
     for (int t = 0; t < NQ; ++t) {
         const int first = q0 + t * QT;
-        nblk[t] = (first < T) ? (min(T - 1, first + QT - 1) / KB + 1) : 0;
+        nstep[t] = (first < T) ? (min(T - 1, first + QT - 1) / KB + 1) : 0;
+        nblk[t] = (nstep[t] + 1) / 2;
     }
     const int maxblk = max(nblk[0], nblk[1]);
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(bar(KV_FULL + s), 1); mbar_init(bar(KV_EMPTY + s), 1); }
+        for (int s = 0; s < K_STAGES; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
+        for (int s = 0; s < V_STAGES; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1); }
         for (int t = 0; t < NQ; ++t) {
             mbar_init(bar(S_FULL + t), 1); mbar_init(bar(S_EMPTY + t), 4);
             mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_FULL + t), 1);
@@ -126,81 +141,108 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                                     h * HS + half * 32, row0 + q0 + t * QT + rr * 64, bar(Q_FULL));
             }
             bool ok = true;
-            int armed_parity[KV_STAGES];
-            for (int s = 0; s < KV_STAGES; ++s) armed_parity[s] = -1;
+            int armed_k[K_STAGES], armed_v[V_STAGES];
+            for (int s = 0; s < K_STAGES; ++s) armed_k[s] = -1;
+            for (int s = 0; s < V_STAGES; ++s) armed_v[s] = -1;
             for (int j = 0; j < maxblk; ++j) {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (uint32_t)((j / KV_STAGES) & 1);
-                if (!mbar_wait(bar(KV_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(KV_FULL + st), 2 * KV_TILE_BYTES);
-                armed_parity[st] = (int)ph;
-                for (int half = 0; half < 2; ++half) {
-                    tma_load_2d(base + OFF_K + st * KV_TILE_BYTES + half * (KB * 128), &mapQK,
-                                C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
-                    tma_load_2d(base + OFF_V + st * KV_TILE_BYTES + half * (KB * 128), &mapV,
-                                2 * C + h * HS + half * 32, row0 + j * KB, bar(KV_FULL + st));
-                }
+                const int sk = j % K_STAGES, sv = j % V_STAGES;
+                const uint32_t pk = (uint32_t)((j / K_STAGES) & 1), pv = (uint32_t)((j / V_STAGES) & 1);
+                if (!mbar_wait(bar(K_EMPTY + sk), pk ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(K_FULL + sk), KV_TILE_BYTES);
+                armed_k[sk] = (int)pk;
+                for (int half = 0; half < 2; ++half)
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_K + sk * KV_TILE_BYTES + half * (KBLK * 128) + rr * (64 * 128), &mapQK,
+                                    C + h * HS + half * 32, row0 + j * KBLK + rr * 64, bar(K_FULL + sk));
+                if (!mbar_wait(bar(V_EMPTY + sv), pv ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(V_FULL + sv), KV_TILE_BYTES);
+                armed_v[sv] = (int)pv;
+                for (int half = 0; half < 2; ++half)
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_V + sv * KV_TILE_BYTES + half * (KBLK * 128) + rr * (64 * 128), &mapV,
+                                    2 * C + h * HS + half * 32, row0 + j * KBLK + rr * 64, bar(V_FULL + sv));
             }
             if (!ok) {
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < KV_STAGES; ++s)
-                    if (armed_parity[s] >= 0) mbar_drain(bar(KV_FULL + s), (uint32_t)armed_parity[s]);
+                for (int s = 0; s < K_STAGES; ++s)
+                    if (armed_k[s] >= 0) mbar_drain(bar(K_FULL + s), (uint32_t)armed_k[s]);
+                for (int s = 0; s < V_STAGES; ++s)
+                    if (armed_v[s] >= 0) mbar_drain(bar(V_FULL + s), (uint32_t)armed_v[s]);
             }
         }
     } else if (warp == 9) {
-        // -------------------------------------------------------------- issuer
+        // ----------------------------------------------------- issuer of S = Q K^T
         if (lane == 0) {
-            const uint32_t idesc_s = make_idesc(2, 0, 0, KB, QT);    // Q (K-major) x K (K-major)
-            const uint32_t idesc_pv = make_idesc(2, 0, 1, HS, QT);   // P (K-major) x V (MN-major)
-            auto issue_s = [&](int t, int st) {
-                const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES, ka = base + OFF_K + st * KV_TILE_BYTES;
-                const uint32_t d = tmem_base + (uint32_t)(t * TILE_COLS);
-#pragma unroll
-                for (int ks = 0; ks < HS / 8; ++ks) {
-                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(d, smem_desc_kmajor(qa + half * (QT * 128) + off),
-                             smem_desc_kmajor(ka + half * (KB * 128) + off), idesc_s, ks ? 1u : 0u);
-                }
-            };
-            auto issue_pv = [&](int t, int st) {
-                // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
-                const uint32_t va = base + OFF_V + st * KV_TILE_BYTES;
-                const uint32_t pa = tmem_base + (uint32_t)(t * TILE_COLS + 64), d = pa + 64;
-#pragma unroll
-                for (int ks = 0; ks < KB / 8; ++ks)
-                    mma_tf32_ts(d, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KB * 128), idesc_pv, ks ? 1u : 0u);
-            };
+            const uint32_t idesc_s = make_idesc(2, 0, 0, KBLK, QT);    // Q (K-major) x K (K-major), 128 keys at a time
+#ifdef BMB_FLASH_TRACE
+            // issuer phases of CTA (0, 0): 9 wait K, 10 wait S_EMPTY, 11 issue S
+            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0);
+            long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            long long tlast = clock64();
+#endif
             bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
-            if (ok) ok = mbar_wait(bar(KV_FULL + 0), 0, giveup);
-            if (ok) {
-                fence_after();
-                for (int t = 0; t < NQ; ++t)
-                    if (nblk[t] > 0) { issue_s(t, 0); commit(bar(S_FULL + t)); }
-            }
+            TRI(15);
             for (int j = 0; ok && j < maxblk; ++j) {
-                const int st = j % KV_STAGES;
-                if (j + 1 < maxblk) {
-                    if (!mbar_wait(bar(KV_FULL + (j + 1) % KV_STAGES), (uint32_t)(((j + 1) / KV_STAGES) & 1), giveup)) { ok = false; break; }
-                }
-                for (int t = 0; ok && t < NQ; ++t) {
-                    if (j + 1 < nblk[t]) {
-                        if (!mbar_wait(bar(S_EMPTY + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
-                        fence_after();
-                        issue_s(t, (j + 1) % KV_STAGES);
-                        commit(bar(S_FULL + t));
+                const int st = j % K_STAGES;
+                if (!mbar_wait(bar(K_FULL + st), (uint32_t)((j / K_STAGES) & 1), giveup)) { ok = false; break; }
+                TRI(9);
+                const uint32_t ka = base + OFF_K + st * KV_TILE_BYTES;
+                for (int t = 0; t < NQ; ++t) {
+                    if (j >= nblk[t]) continue;
+                    // the group has taken block j-1's scores out of tensor memory
+                    if (j > 0 && !mbar_wait(bar(S_EMPTY + t), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    TRI(10);
+                    const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES;
+                    const uint32_t d = tmem_base + (uint32_t)(t * TILE_COLS);
+#pragma unroll
+                    for (int ks = 0; ks < HS / 8; ++ks) {
+                        const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                        mma_tf32(d, smem_desc_kmajor(qa + half * (QT * 128) + off),
+                                 smem_desc_kmajor(ka + half * (KBLK * 128) + off), idesc_s, ks ? 1u : 0u);
                     }
-                }
-                for (int t = 0; ok && t < NQ; ++t) {
-                    if (j < nblk[t]) {
-                        if (!mbar_wait(bar(P_FULL + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
-                        fence_after();
-                        issue_pv(t, st);
-                        commit(bar(PV_FULL + t));
-                    }
+                    commit(bar(S_FULL + t));
+                    TRI(11);
                 }
                 if (!ok) break;
-                commit(bar(KV_EMPTY + st));     // every MMA that read this K/V block has been issued
+                commit(bar(K_EMPTY + st));      // every product that reads this K block has been issued
             }
+            TR_FLUSH(9, 3);
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------- issuer of O += P V
+        if (lane == 0) {
+            const uint32_t idesc_pv = make_idesc(2, 0, 1, HS, QT);   // P (tensor memory) x V (MN-major)
+#ifdef BMB_FLASH_TRACE
+            // 12 wait V, 13 wait P_FULL, 14 issue PV
+            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0);
+            long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            long long tlast = clock64();
+#endif
+            bool ok = true;
+            const int maxstep = max(nstep[0], nstep[1]);
+            for (int i = 0; ok && i < maxstep; ++i) {
+                const int j = i >> 1, st = j % V_STAGES;
+                if (!(i & 1) && !mbar_wait(bar(V_FULL + st), (uint32_t)((j / V_STAGES) & 1), giveup)) { ok = false; break; }
+                TRI(12);
+                // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
+                const uint32_t va = base + OFF_V + st * KV_TILE_BYTES + (uint32_t)((i & 1) * (KB * 128));
+                for (int t = 0; t < NQ; ++t) {
+                    if (i >= nstep[t]) continue;
+                    if (!mbar_wait(bar(P_FULL + t), (uint32_t)(i & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    TRI(13);
+                    const uint32_t pa = tmem_base + (uint32_t)(t * TILE_COLS + COL_P), d = tmem_base + (uint32_t)(t * TILE_COLS + COL_PV);
+#pragma unroll
+                    for (int ks = 0; ks < KB / 8; ++ks)
+                        mma_tf32_ts(d, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, ks ? 1u : 0u);
+                    commit(bar(PV_FULL + t));
+                    TRI(14);
+                }
+                if (!ok) break;
+                if ((i & 1) || i + 1 == maxstep) commit(bar(V_EMPTY + st));     // every product that reads this V block has been issued
+            }
+            TR_FLUSH(12, 3);
         }
     } else {
         // ------------------------------------------------------ softmax groups
@@ -208,10 +250,10 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         const int r = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const int tile_q0 = q0 + t * QT;
         const int qi = tile_q0 + r;
-        const int nb = nblk[t];
+        const int nb = nstep[t];
         if (nb > 0) {
             const uint32_t s_addr = tmem_base + (uint32_t)(t * TILE_COLS) + ((uint32_t)(quad * 32) << 16);
-            const uint32_t p_addr = s_addr + 64, pv_addr = s_addr + 128;
+            const uint32_t p_addr = s_addr + COL_P, pv_addr = s_addr + COL_PV;
             float o[HS];
 #pragma unroll
             for (int d = 0; d < HS; ++d) o[d] = 0.0f;
@@ -219,19 +261,25 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             bool ok = true;
 #ifdef BMB_FLASH_TRACE
             const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 4 && lane == 0);
+            long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long tlast = clock64();
 #endif
             for (int j = 0; j < nb; ++j) {
                 TR(0);
-                if (!mbar_wait(bar(S_FULL + t), (uint32_t)(j & 1), giveup)) { ok = false; break; }
-                fence_after();
+                // one S product covers two steps: wait for it on the even step, release it on the odd (or last) one
+                if (!(j & 1)) {
+                    if (!mbar_wait(bar(S_FULL + t), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                }
                 TR(1);
                 float s[KB];
-                tmem_ld64(s_addr, s);
+                tmem_ld64(s_addr + (uint32_t)((j & 1) * KB), s);
                 TR(2);
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(S_EMPTY + t));       // S_t may be overwritten
+                if ((j & 1) || j + 1 == nb) {
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(S_EMPTY + t));       // S_t may be overwritten
+                }
 
                 // m is the running maximum of the raw scores (the scale is positive, so the order is
                 // the same); the scale rides in the exponent's multiply-add.
@@ -293,10 +341,11 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                 }
                 alpha_prev = alpha;
                 TR(7);
-#ifdef BMB_FLASH_TRACE
-                if (tr) g_trace[8] += 1;
-#endif
             }
+#ifdef BMB_FLASH_TRACE
+            TR_FLUSH(0, 8);
+            if (tr) g_trace[8] += nb;
+#endif
             if (ok && mbar_wait(bar(PV_FULL + t), (uint32_t)((nb - 1) & 1), giveup)) {
                 fence_after();
                 float v[32];
