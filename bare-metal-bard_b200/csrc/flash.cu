@@ -385,7 +385,7 @@ const FwdCfg FWD[] = {{16, "simt-fp32 rowgroup keys16"}, {8, "simt-fp32 rowgroup
                       {0, "tcgen05-tf32 q2x128 k64"}};
 // Backward config 2 is the tensor-core kernel pair (flash_tc_bwd.cu), head size 64 only.
 const BwdCfg BWD[] = {{4, "simt-fp32 rowgroup keys4"}, {8, "simt-fp32 rowgroup keys8"},
-                      {0, "tcgen05-tf32 dq128x64 dkv128x64"}};
+                      {0, "tcgen05-tf32 dq128x128 dkv128x128"}};
 constexpr int NFWD = 3, NBWD = 3, FWD_TC = 2, BWD_TC = 2;
 
 bool shape_ok(const float *a, const float *b, int C, int NH) {

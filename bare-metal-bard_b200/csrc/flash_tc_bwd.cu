@@ -48,33 +48,40 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 #ifdef BMB_FLASH_TRACE
-__device__ long long g_trace_bwd[16];
-#define TRB(i) do { if (tr) { const long long now_ = clock64(); g_trace_bwd[i] += now_ - tlast; tlast = now_; } } while (0)
+__device__ long long g_trace_bwd[32];
+// phase times are summed in registers and written once, so a timer costs one clock read
+#define TRB(i) do { const long long now_ = clock64(); tacc[(i) & 7] += now_ - tlast; tlast = now_; } while (0)
+#define TRB_FLUSH(first, n) do { if (tr) for (int i_ = 0; i_ < (n); ++i_) g_trace_bwd[(first) + i_] += tacc[((first) + i_) & 7]; } while (0)
 #else
 #define TRB(i)
+#define TRB_FLUSH(first, n)
 #endif
 
 // ============================================================== dQ kernel
 namespace dq {
-constexpr int QT = 128, KB = 64, STAGES = 3;
+constexpr int QT = 128, KB = 128, G = 64;               // keys per block (one S / dP product) and per granule (one dQ product)
 constexpr int OFF_Q = 0, OFF_DO = 32768;
-constexpr int OFF_KK = 65536, KK_BYTES = 32768;         // per stage: K then V, K-major, 16 KB each
-constexpr int OFF_KN = OFF_KK + STAGES * KK_BYTES;      // per stage: K, MN-major, 16 KB
-constexpr int KN_BYTES = 16384;
-constexpr int OFF_BAR = OFF_KN + STAGES * KN_BYTES;
+constexpr int OFF_KS = 65536, OFF_VK = OFF_KS + 2 * 32768;   // K and V blocks, K-major, two stages of 32 KB each
+constexpr int OFF_KN = OFF_VK + 2 * 32768;              // K granules, MN-major, two slots of 16 KB
+constexpr int OFF_BAR = OFF_KN + 2 * 16384;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
-constexpr int THREADS = 320;
-enum { Q_FULL = 0, KK_FULL = 1, KK_EMPTY = 4, KN_FULL = 7, KN_EMPTY = 10, SP_FULL = 13, DS_FULL = 15, DQ_DONE = 17, NBARS = 18 };
-// TMEM columns: S [2] at 0 / 64, dP / dS [2] at 128 / 192, dQ at 256
-constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
+constexpr int THREADS = 384;
+enum { Q_FULL = 0, KS_FULL = 1, KS_EMPTY = 3, VK_FULL = 5, VK_EMPTY = 7, KN_FULL = 9, KN_EMPTY = 11, S_FULL = 13, DP_FULL = 15,
+       DS_FULL = 16, DQ_DONE = 18, S_EMPTY = 19, NBARS = 21 };
+// TMEM columns: S [2] at 0 / 128, dP / dS at 256 (two granules of 64), dQ at 384
+constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DQ = 384;
 }  // namespace dq
 
-// A CTA owns 128 queries and walks key blocks of 64 up to the diagonal.  S = Q K^T and dP = dO V^T
-// land in tensor memory (double buffered); 256 threads (a query row each, 32 of the 64 key columns)
-// turn them into dS, written back over dP, where the tensor core reads it as the A operand of
-// dQ += dS K.  The K-major copies of a key block (K and V: operands of the first two products) and
-// the MN-major copy of K (operand of the last) ride in separate 3-deep rings, each refilled as soon
-// as its own consumer is done.
+// A CTA owns 128 queries and walks key blocks of 128 up to the diagonal.  S = Q K^T (double
+// buffered) and dP = dO V^T land in tensor memory as N = 128 products: an instruction of that width
+// costs the tensor pipe its 64 cycles, whereas one thread cannot issue N = 64 instructions as fast as
+// the pipe retires them.  256 threads (a query row each, 32 columns of each 64-key granule) rebuild P
+// from S while dP is still being multiplied, then turn dP into dS granule by granule, written back
+// over dP, where the tensor core reads it as the A operand of dQ += dS K; the second granule is
+// computed while the first is multiplied.  The K-major copies of K and V (operands of S and dP) sit
+// in 2-deep rings of whole blocks, the MN-major copy of K (operand of dQ) in two granule slots, each
+// refilled as soon as its own consumer is done, by two loading threads so that neither ring waits
+// for the other.
 __global__ void __launch_bounds__(dq::THREADS, 1)
 flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_constant__ CUtensorMap mapQKV_n,
                   const __grid_constant__ CUtensorMap mapDO_k, float *__restrict__ dqkv,
@@ -95,14 +102,17 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
     const int C = NH * HS;
     const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * QT;   // CTAs are dispatched x first: every head's longest tile, then the next
     const int nb = min(T - 1, q0 + QT - 1) / KB + 1;       // key blocks up to the diagonal
+    const int row0 = b * T;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar(KK_FULL + s), 1); mbar_init(bar(KK_EMPTY + s), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(KS_FULL + s), 1); mbar_init(bar(KS_EMPTY + s), 1);
+            mbar_init(bar(VK_FULL + s), 1); mbar_init(bar(VK_EMPTY + s), 1);
             mbar_init(bar(KN_FULL + s), 1); mbar_init(bar(KN_EMPTY + s), 1);
+            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(DS_FULL + s), 8); mbar_init(bar(S_EMPTY + s), 8);
         }
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(DS_FULL + s), 8); }
+        mbar_init(bar(DP_FULL), 1);
         mbar_init(bar(DQ_DONE), 1);
         *giveup = 0;
         mbar_init_fence();
@@ -114,9 +124,8 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 8) {
-        // ------------------------------------------------------------ producer
+        // ------------------------------------- loads of Q, dO and the K-major K / V blocks
         if (lane == 0) {
-            const int row0 = b * T;
             mbar_arrive_expect_tx(bar(Q_FULL), 65536);
             for (int half = 0; half < 2; ++half)
                 for (int rr = 0; rr < 2; ++rr) {
@@ -124,82 +133,133 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                     tma_load_2d(base + OFF_DO + half * 16384 + rr * 8192, &mapDO_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(Q_FULL));
                 }
             bool ok = true;
-            int armed_k[STAGES], armed_n[STAGES];
-            for (int s = 0; s < STAGES; ++s) { armed_k[s] = -1; armed_n[s] = -1; }
+            int armed_k[2] = {-1, -1}, armed_v[2] = {-1, -1};
             for (int j = 0; j < nb; ++j) {
-                const int st = j % STAGES;
-                const uint32_t ph = (uint32_t)((j / STAGES) & 1);
-                if (!mbar_wait(bar(KK_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(KK_FULL + st), KK_BYTES);
+                const int st = j & 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1);
+                if (!mbar_wait(bar(KS_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(KS_FULL + st), 32768);
                 armed_k[st] = (int)ph;
-                const uint32_t sk = base + OFF_KK + st * KK_BYTES;
-                for (int half = 0; half < 2; ++half) {
-                    tma_load_2d(sk + half * 8192, &mapQKV_k, C + h * HS + half * 32, row0 + j * KB, bar(KK_FULL + st));
-                    tma_load_2d(sk + 16384 + half * 8192, &mapQKV_k, 2 * C + h * HS + half * 32, row0 + j * KB, bar(KK_FULL + st));
-                }
-                if (!mbar_wait(bar(KN_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(KN_FULL + st), KN_BYTES);
-                armed_n[st] = (int)ph;
-                const uint32_t sn = base + OFF_KN + st * KN_BYTES;
                 for (int half = 0; half < 2; ++half)
-                    tma_load_2d(sn + half * 8192, &mapQKV_n, C + h * HS + half * 32, row0 + j * KB, bar(KN_FULL + st));
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_KS + st * 32768 + half * 16384 + rr * 8192, &mapQKV_k, C + h * HS + half * 32,
+                                    row0 + j * KB + rr * 64, bar(KS_FULL + st));
+                if (!mbar_wait(bar(VK_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(VK_FULL + st), 32768);
+                armed_v[st] = (int)ph;
+                for (int half = 0; half < 2; ++half)
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_VK + st * 32768 + half * 16384 + rr * 8192, &mapQKV_k, 2 * C + h * HS + half * 32,
+                                    row0 + j * KB + rr * 64, bar(VK_FULL + st));
             }
             if (!ok) {
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < STAGES; ++s) {
-                    if (armed_k[s] >= 0) mbar_drain(bar(KK_FULL + s), (uint32_t)armed_k[s]);
-                    if (armed_n[s] >= 0) mbar_drain(bar(KN_FULL + s), (uint32_t)armed_n[s]);
+                for (int s = 0; s < 2; ++s) {
+                    if (armed_k[s] >= 0) mbar_drain(bar(KS_FULL + s), (uint32_t)armed_k[s]);
+                    if (armed_v[s] >= 0) mbar_drain(bar(VK_FULL + s), (uint32_t)armed_v[s]);
                 }
             }
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------- loads of the MN-major K granules
+        if (lane == 0) {
+            bool ok = true;
+            int armed_n[2] = {-1, -1};
+            for (int j = 0; ok && j < nb; ++j)
+                for (int g = 0; g < 2; ++g) {
+                    const uint32_t ph = (uint32_t)(j & 1);
+                    if (!mbar_wait(bar(KN_EMPTY + g), ph ^ 1, giveup)) { ok = false; break; }
+                    mbar_arrive_expect_tx(bar(KN_FULL + g), 16384);
+                    armed_n[g] = (int)ph;
+                    for (int half = 0; half < 2; ++half)
+                        tma_load_2d(base + OFF_KN + g * 16384 + half * 8192, &mapQKV_n, C + h * HS + half * 32,
+                                    row0 + j * KB + g * G, bar(KN_FULL + g));
+                }
+            if (!ok)
+                for (int g = 0; g < 2; ++g)
+                    if (armed_n[g] >= 0) mbar_drain(bar(KN_FULL + g), (uint32_t)armed_n[g]);
         }
     } else if (warp == 9) {
-        // -------------------------------------------------------------- issuer
+        // ------------------------------------------------- issuer of S = Q K^T
+        // Two threads feed the tensor core, because one cannot issue N = 64 instructions as fast as the
+        // pipe retires them; this one runs ahead with the scores of the next block.
         if (lane == 0) {
-            const uint32_t idesc_kk = make_idesc(2, 0, 0, KB, QT);     // [128 x 64] = A(K-major) x B(K-major)
-            const uint32_t idesc_kn = make_idesc(2, 0, 1, HS, QT);     // dQ: dS (tensor memory) x K (MN-major)
-            auto issue_sp = [&](int st, int buf) {
-                const uint32_t sk = base + OFF_KK + st * KK_BYTES;
+            const uint32_t idesc_kk = make_idesc(2, 0, 0, KB, QT);     // [128 x 128] = A(K-major) x B(K-major)
+            bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
+            for (int j = 0; ok && j < nb; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(bar(KS_FULL + st), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
+                // the threads have taken block j-2 out of this S buffer
+                if (j >= 2 && !mbar_wait(bar(S_EMPTY + st), (uint32_t)(((j >> 1) & 1) ^ 1), giveup)) { ok = false; break; }
+                fence_after();
+                const uint32_t d = tmem_base + COL_S + (uint32_t)(st * 128), bsm = base + OFF_KS + st * 32768;
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + COL_S + (uint32_t)(buf * 64), smem_desc_kmajor(base + OFF_Q + half * 16384 + off),
-                             smem_desc_kmajor(sk + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
+                    mma_tf32(d, smem_desc_kmajor(base + OFF_Q + half * 16384 + off), smem_desc_kmajor(bsm + half * 16384 + off), idesc_kk, ks ? 1u : 0u);
                 }
+                commit(bar(S_FULL + st));
+                commit(bar(KS_EMPTY + st));
+            }
+        }
+    } else if (warp == 11) {
+        // ----------------------------- issuer of dP = dO V^T and dQ += dS K
+        if (lane == 0) {
+            const uint32_t idesc_kk = make_idesc(2, 0, 0, KB, QT);     // [128 x 128] = A(K-major) x B(K-major)
+            const uint32_t idesc_kn = make_idesc(2, 0, 1, HS, QT);     // dQ: dS (tensor memory) x K (MN-major)
+            auto issue_dp = [&](uint32_t bsm) {
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + COL_DP + (uint32_t)(buf * 64), smem_desc_kmajor(base + OFF_DO + half * 16384 + off),
-                             smem_desc_kmajor(sk + 16384 + half * 8192 + off), idesc_kk, ks ? 1u : 0u);
+                    mma_tf32(tmem_base + COL_DP, smem_desc_kmajor(base + OFF_DO + half * 16384 + off), smem_desc_kmajor(bsm + half * 16384 + off), idesc_kk, ks ? 1u : 0u);
                 }
             };
+#ifdef BMB_FLASH_TRACE
+            // phases of this thread in CTA (0, 0): 16 prologue, 19 wait dS and K granule, 20 issue dQ, 21 wait V block, 22 issue dP
+            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0);
+            long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            long long tlast = clock64();
+#endif
             bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
-            if (ok) ok = mbar_wait(bar(KK_FULL + 0), 0, giveup);
-            if (ok) { fence_after(); issue_sp(0, 0); commit(bar(SP_FULL + 0)); commit(bar(KK_EMPTY + 0)); }
-            for (int j = 0; ok && j < nb; ++j) {
-                const int st = j % STAGES, buf = j & 1;
-                if (j + 1 < nb) {
-                    // block j+1 goes into the other S / dP buffer; the product that read that buffer's dS
-                    // (block j-1) was issued before this point, and the tensor core runs in order
-                    const int s1 = (j + 1) % STAGES;
-                    if (!mbar_wait(bar(KK_FULL + s1), (uint32_t)(((j + 1) / STAGES) & 1), giveup)) { ok = false; break; }
-                    fence_after();
-                    issue_sp(s1, (j + 1) & 1);
-                    commit(bar(SP_FULL + ((j + 1) & 1)));
-                    commit(bar(KK_EMPTY + s1));
-                }
-                if (!mbar_wait(bar(KN_FULL + st), (uint32_t)((j / STAGES) & 1), giveup)) { ok = false; break; }
-                if (!mbar_wait(bar(DS_FULL + buf), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
+            if (ok) ok = mbar_wait(bar(VK_FULL + 0), 0, giveup);
+            if (ok) {
                 fence_after();
-                const uint32_t kn = base + OFF_KN + st * KN_BYTES;
+                issue_dp(base + OFF_VK);
+                commit(bar(DP_FULL));
+                commit(bar(VK_EMPTY + 0));
+            }
+            TRB(16);
+            for (int j = 0; ok && j < nb; ++j) {
+                const int s1 = (j + 1) & 1;
+                for (int g = 0; g < 2; ++g) {
+                    if (!mbar_wait(bar(KN_FULL + g), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                    if (!mbar_wait(bar(DS_FULL + g), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    TRB(19);
+                    const uint32_t kn = base + OFF_KN + g * 16384;
 #pragma unroll
-                for (int ks = 0; ks < KB / 8; ++ks)
-                    mma_tf32_ts(tmem_base + COL_DQ, tmem_base + COL_DP + (uint32_t)(buf * 64 + ks * 8),
-                                smem_desc_mnmajor32(kn + ks * 1024, 8192), idesc_kn, (j | ks) ? 1u : 0u);
-                commit(bar(KN_EMPTY + st));
+                    for (int ks = 0; ks < G / 8; ++ks)
+                        mma_tf32_ts(tmem_base + COL_DQ, tmem_base + COL_DP + (uint32_t)(g * G + ks * 8),
+                                    smem_desc_mnmajor32(kn + ks * 1024, 8192), idesc_kn, (j | g | ks) ? 1u : 0u);
+                    commit(bar(KN_EMPTY + g));
+                    TRB(20);
+                }
+                if (!ok) break;
+                if (j + 1 < nb) {
+                    // dP of block j+1 overwrites the dS just multiplied: the tensor core runs this thread's products in order
+                    if (!mbar_wait(bar(VK_FULL + s1), (uint32_t)(((j + 1) >> 1) & 1), giveup)) { ok = false; break; }
+                    fence_after();
+                    TRB(21);
+                    issue_dp(base + OFF_VK + s1 * 32768);
+                    commit(bar(DP_FULL));
+                    commit(bar(VK_EMPTY + s1));
+                }
+                TRB(22);
             }
             if (ok) commit(bar(DQ_DONE));
+            TRB_FLUSH(16, 7);
         }
-    } else {
+    } else if (warp < 8) {
         // ----------------------------------------------------------------- dS
         const int quad = warp & 3, colhalf = warp >> 2;
         const int r = quad * 32 + lane;
@@ -210,40 +270,69 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         bool ok = true;
 #ifdef BMB_FLASH_TRACE
+        // phases of one thread of CTA (0, 0): 0 wait S, 1 load S + rebuild P, 2 wait dP, 3 dS of both granules
         const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && lane == 0);
+        long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tlast = clock64();
 #endif
         for (int j = 0; j < nb; ++j) {
             const int buf = j & 1;
-            TRB(0);
-            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
+            if (!mbar_wait(bar(S_FULL + buf), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
             fence_after();
-            TRB(1);
-            float s[32], dp[32];
-            const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(buf * 64 + colhalf * 32);
-            tmem_ld32_nowait(lane_addr + COL_S + (uint32_t)(buf * 64 + colhalf * 32), s);
-            tmem_ld32_nowait(dp_addr, dp);
+            TRB(0);
+            // P of this thread's 32 + 32 columns, kept in registers until dP arrives
+            float p0[32], p1[32];
+            const uint32_t s_addr = lane_addr + COL_S + (uint32_t)(buf * 128 + colhalf * 32);
+            tmem_ld32_nowait(s_addr, p0);
+            tmem_ld32_nowait(s_addr + G, p1);
             tmem_wait_ld();
-            TRB(2);
-            const int k0 = j * KB + colhalf * 32;
-            const bool diag = (k0 + 31 > q0);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float p = fast_exp2(fmaf(s[i], scale_log2e, -lse_r));
-                if (diag && (k0 + i > qi)) p = 0.0f;
-                s[i] = round_tf32_alu(p * (dp[i] - d_r));
-            }
-            TRB(3);
-            tmem_st32_nowait(dp_addr, s);                 // dS over dP: the A operand of dQ += dS K
-            tmem_wait_st();
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(DS_FULL + buf));
-            TRB(4);
-#ifdef BMB_FLASH_TRACE
-            if (tr) g_trace_bwd[8] += 1;
-#endif
+            if (lane == 0) mbar_arrive(bar(S_EMPTY + buf));       // the S buffer may take block j+2
+            const int k0 = j * KB + colhalf * 32;
+            const bool diag = (k0 + G + 31 > q0);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float a = fast_exp2(fmaf(p0[i], scale_log2e, -lse_r));
+                float c = fast_exp2(fmaf(p1[i], scale_log2e, -lse_r));
+                if (diag && (k0 + i > qi)) a = 0.0f;
+                if (diag && (k0 + G + i > qi)) c = 0.0f;
+                p0[i] = a;
+                p1[i] = c;
+            }
+            TRB(1);
+            if (!mbar_wait(bar(DP_FULL), (uint32_t)(j & 1), giveup)) { ok = false; break; }
+            fence_after();
+            TRB(2);
+            const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(colhalf * 32);
+            {
+                float dp[32];
+                tmem_ld32(dp_addr, dp);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dp[i] = round_tf32_alu(p0[i] * (dp[i] - d_r));
+                tmem_st32_nowait(dp_addr, dp);                 // dS over dP: the A operand of dQ += dS K
+                tmem_wait_st();
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(DS_FULL + 0));
+            }
+            {
+                float dp[32];
+                tmem_ld32(dp_addr + G, dp);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dp[i] = round_tf32_alu(p1[i] * (dp[i] - d_r));
+                tmem_st32_nowait(dp_addr + G, dp);
+                tmem_wait_st();
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(DS_FULL + 1));
+            }
+            TRB(3);
         }
+#ifdef BMB_FLASH_TRACE
+        TRB_FLUSH(0, 4);
+        if (tr) g_trace_bwd[8] += nb;
+#endif
         if (ok && mbar_wait(bar(DQ_DONE), 0, giveup)) {
             fence_after();
             float v[32];
@@ -272,28 +361,31 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
 
 // ============================================================ dK/dV kernel
 namespace dkv {
-constexpr int KT = 128, QB = 64, STAGES = 2;
+constexpr int KT = 128, QB = 128, G = 64;               // queries per block (one S^T / dP^T product) and per granule
 constexpr int OFF_K = 0, OFF_V = 32768;
-constexpr int OFF_STK = 65536, STK_BYTES = 32768;       // per stage: Q then dO, K-major, 16 KB each
-constexpr int OFF_STN = OFF_STK + STAGES * STK_BYTES;   // per stage: Q then dO, MN-major, 16 KB each
-constexpr int STN_BYTES = 32768;
-constexpr int OFF_BAR = OFF_STN + STAGES * STN_BYTES;
+constexpr int OFF_QK = 65536, OFF_DOK = OFF_QK + 32768; // Q and dO blocks, K-major, 32 KB each
+constexpr int OFF_QN = OFF_DOK + 32768;                 // Q granules, MN-major, two slots of 16 KB
+constexpr int OFF_DON = OFF_QN + 2 * 16384;             // dO granules, MN-major, two slots of 16 KB
+constexpr int OFF_BAR = OFF_DON + 2 * 16384;
 constexpr int STAT_MAX = 4096;                          // queries whose lse and D fit in shared memory
 constexpr int OFF_STAT = OFF_BAR + 256;                 // lse * log2(e), then D, STAT_MAX floats each
 constexpr int SMEM = OFF_STAT + 2 * STAT_MAX * 4 + 1024;
-constexpr int THREADS = 320;
-enum { KV_FULL = 0, STK_FULL = 1, STK_EMPTY = 3, STN_FULL = 5, STN_EMPTY = 7, SP_FULL = 9, PD_FULL = 11, ACC_DONE = 13, NBARS = 14 };
-// TMEM columns: S^T / P^T [2] at 0 / 64, dP^T / dS^T [2] at 128 / 192, dV at 256, dK at 320
-constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320;
+constexpr int THREADS = 384;
+enum { KV_FULL = 0, QK_FULL = 1, QK_EMPTY = 2, DOK_FULL = 3, DOK_EMPTY = 4, N_FULL = 5, N_EMPTY = 7, S_FULL = 9, DP_FULL = 11,
+       PD_FULL = 12, ACC_DONE = 14, NBARS = 15 };
+// TMEM columns: S^T / P^T [2] at 0 / 128, dP^T / dS^T at 256, dV at 384, dK at 448
+constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DV = 384, COL_DK = 448;
 }  // namespace dkv
 
-// A CTA owns 128 keys and walks query blocks of 64 from the diagonal to the end.  S^T = K Q^T and
-// dP^T = V dO^T land in tensor memory; 256 threads (a key row each, 32 of the 64 query columns)
-// turn them into P^T and dS^T and write those back over S^T and dP^T, where the tensor core reads
-// them as the A operand of dV += P^T dO and dK += dS^T Q.  Nothing of the (T x T) matrices touches
-// shared memory.  The K-major copies of a query block (operands of the first two products) and its
-// MN-major copies (operands of the last two) ride in separate 2-deep rings, so each is refilled as
-// soon as its own consumers are done.
+// A CTA owns 128 keys and walks query blocks of 128 from the diagonal to the end.  S^T = K Q^T
+// (double buffered) and dP^T = V dO^T land in tensor memory as N = 128 products; 256 threads (a key
+// row each, 32 columns of each 64-query granule) write P^T over S^T while dP^T is still being
+// multiplied, then turn dP^T into dS^T granule by granule, in place, and the tensor core reads both
+// as the A operands of dV += P^T dO and dK += dS^T Q; the second granule is computed while the first
+// is multiplied.  Nothing of the (T x T) matrices touches shared memory.  The K-major copies of a
+// query block (operands of the first two products) have one buffer each, refilled while the block
+// is worked on; the MN-major copies (operands of the last two) sit in two granule slots, loaded by
+// a thread of their own.
 __global__ void __launch_bounds__(dkv::THREADS, 1)
 flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
                    const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
@@ -315,15 +407,18 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
     const int j0 = (int)blockIdx.y * KT;                   // first key of this CTA (earliest keys walk longest)
     const int ib0 = j0 / QB;                               // first query block that can see these keys
     const int nb = (T + QB - 1) / QB - ib0;                // query blocks to walk
+    const int row0 = b * T;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(KV_FULL), 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar(STK_FULL + s), 1); mbar_init(bar(STK_EMPTY + s), 1);
-            mbar_init(bar(STN_FULL + s), 1); mbar_init(bar(STN_EMPTY + s), 1);
-            mbar_init(bar(SP_FULL + s), 1); mbar_init(bar(PD_FULL + s), 8);
+        mbar_init(bar(QK_FULL), 1); mbar_init(bar(QK_EMPTY), 1);
+        mbar_init(bar(DOK_FULL), 1); mbar_init(bar(DOK_EMPTY), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(N_FULL + s), 1); mbar_init(bar(N_EMPTY + s), 2);     // both issuing threads release a granule slot
+            mbar_init(bar(S_FULL + s), 1); mbar_init(bar(PD_FULL + s), 8);
         }
-        mbar_init(bar(ACC_DONE), 1);
+        mbar_init(bar(DP_FULL), 1);
+        mbar_init(bar(ACC_DONE), 2);
         *giveup = 0;
         mbar_init_fence();
     }
@@ -346,9 +441,8 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 8) {
-        // ------------------------------------------------------------ producer
+        // --------------------------- loads of K, V and the K-major Q / dO blocks
         if (lane == 0) {
-            const int row0 = b * T;
             mbar_arrive_expect_tx(bar(KV_FULL), 65536);
             for (int half = 0; half < 2; ++half)
                 for (int rr = 0; rr < 2; ++rr) {
@@ -356,94 +450,129 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                     tma_load_2d(base + OFF_V + half * 16384 + rr * 8192, &mapQKV_k64, 2 * C + h * HS + half * 32, row0 + j0 + rr * 64, bar(KV_FULL));
                 }
             bool ok = true;
-            int armed_k[STAGES] = {-1, -1}, armed_n[STAGES] = {-1, -1};
+            int armed_q = -1, armed_g = -1;
             for (int i = 0; i < nb; ++i) {
-                const int st = i % STAGES;
-                const uint32_t ph = (uint32_t)((i / STAGES) & 1);
+                const uint32_t ph = (uint32_t)(i & 1);
                 const int qrow = row0 + (ib0 + i) * QB;
-                if (!mbar_wait(bar(STK_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(STK_FULL + st), STK_BYTES);
-                armed_k[st] = (int)ph;
-                const uint32_t sk = base + OFF_STK + st * STK_BYTES;
-                for (int half = 0; half < 2; ++half) {
-                    tma_load_2d(sk + half * 8192, &mapQKV_k64, h * HS + half * 32, qrow, bar(STK_FULL + st));
-                    tma_load_2d(sk + 16384 + half * 8192, &mapDO_k64, h * HS + half * 32, qrow, bar(STK_FULL + st));
-                }
-                if (!mbar_wait(bar(STN_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(STN_FULL + st), STN_BYTES);
-                armed_n[st] = (int)ph;
-                const uint32_t sn = base + OFF_STN + st * STN_BYTES;
-                for (int half = 0; half < 2; ++half) {
-                    tma_load_2d(sn + half * 8192, &mapQKV_n64, h * HS + half * 32, qrow, bar(STN_FULL + st));
-                    tma_load_2d(sn + 16384 + half * 8192, &mapDO_n64, h * HS + half * 32, qrow, bar(STN_FULL + st));
-                }
+                if (!mbar_wait(bar(QK_EMPTY), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(QK_FULL), 32768);
+                armed_q = (int)ph;
+                for (int half = 0; half < 2; ++half)
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_QK + half * 16384 + rr * 8192, &mapQKV_k64, h * HS + half * 32, qrow + rr * 64, bar(QK_FULL));
+                if (!mbar_wait(bar(DOK_EMPTY), ph ^ 1, giveup)) { ok = false; break; }
+                mbar_arrive_expect_tx(bar(DOK_FULL), 32768);
+                armed_g = (int)ph;
+                for (int half = 0; half < 2; ++half)
+                    for (int rr = 0; rr < 2; ++rr)
+                        tma_load_2d(base + OFF_DOK + half * 16384 + rr * 8192, &mapDO_k64, h * HS + half * 32, qrow + rr * 64, bar(DOK_FULL));
             }
             if (!ok) {
                 mbar_drain(bar(KV_FULL), 0);
-                for (int s = 0; s < STAGES; ++s) {
-                    if (armed_k[s] >= 0) mbar_drain(bar(STK_FULL + s), (uint32_t)armed_k[s]);
-                    if (armed_n[s] >= 0) mbar_drain(bar(STN_FULL + s), (uint32_t)armed_n[s]);
-                }
+                if (armed_q >= 0) mbar_drain(bar(QK_FULL), (uint32_t)armed_q);
+                if (armed_g >= 0) mbar_drain(bar(DOK_FULL), (uint32_t)armed_g);
             }
         }
-    } else if (warp == 9) {
-        // -------------------------------------------------------------- issuer
+    } else if (warp == 10) {
+        // ------------------------------ loads of the MN-major Q and dO granules
         if (lane == 0) {
-            const uint32_t idesc_st = make_idesc(2, 0, 0, QB, KT);     // [128 keys x 64 queries], both operands K-major
-            const uint32_t idesc_acc = make_idesc(2, 0, 1, HS, KT);    // [128 keys x 64] = A (tensor memory) x B (MN-major)
-            auto issue_sp = [&](int st) {
-                const uint32_t sk = base + OFF_STK + st * STK_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < HS / 8; ++ks) {
-                    const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + COL_S + (uint32_t)(st * 64), smem_desc_kmajor(base + OFF_K + half * 16384 + off),
-                             smem_desc_kmajor(sk + half * 8192 + off), idesc_st, ks ? 1u : 0u);
+            bool ok = true;
+            int armed_n[2] = {-1, -1};
+            for (int i = 0; ok && i < nb; ++i)
+                for (int g = 0; g < 2; ++g) {
+                    const uint32_t ph = (uint32_t)(i & 1);
+                    const int qrow = row0 + (ib0 + i) * QB + g * G;
+                    if (!mbar_wait(bar(N_EMPTY + g), ph ^ 1, giveup)) { ok = false; break; }
+                    mbar_arrive_expect_tx(bar(N_FULL + g), 32768);
+                    armed_n[g] = (int)ph;
+                    for (int half = 0; half < 2; ++half) {
+                        tma_load_2d(base + OFF_QN + g * 16384 + half * 8192, &mapQKV_n64, h * HS + half * 32, qrow, bar(N_FULL + g));
+                        tma_load_2d(base + OFF_DON + g * 16384 + half * 8192, &mapDO_n64, h * HS + half * 32, qrow, bar(N_FULL + g));
+                    }
                 }
+            if (!ok)
+                for (int g = 0; g < 2; ++g)
+                    if (armed_n[g] >= 0) mbar_drain(bar(N_FULL + g), (uint32_t)armed_n[g]);
+        }
+    } else if (warp == 9 || warp == 11) {
+        // ------------------------------------------------------------- issuers
+        // Two threads feed the tensor core, because one cannot issue N = 64 instructions as fast as the
+        // pipe retires them.  Warp 9 owns the S^T / P^T buffers: it issues S^T = K Q^T and dV += P^T dO.
+        // Warp 11 owns the dP^T / dS^T buffer: dP^T = V dO^T and dK += dS^T Q.  Each buffer is written and
+        // read by the products of one thread only, and the tensor core runs a thread's products in order.
+        if (lane == 0) {
+            const bool first = (warp == 9);
+            const uint32_t idesc_st = make_idesc(2, 0, 0, QB, KT);     // [128 keys x 128 queries], both operands K-major
+            const uint32_t idesc_acc = make_idesc(2, 0, 1, HS, KT);    // [128 keys x 64] = A (tensor memory) x B (MN-major)
+            const int IN_FULL = first ? QK_FULL : DOK_FULL, IN_EMPTY = first ? QK_EMPTY : DOK_EMPTY;
+            const uint32_t a_res = base + (first ? OFF_K : OFF_V), b_blk = base + (first ? OFF_QK : OFF_DOK);
+            const uint32_t b_gran = base + (first ? OFF_DON : OFF_QN);
+            const uint32_t acc = tmem_base + (first ? COL_DV : COL_DK);
+            // D[128 x 128] = A (K or V, resident) x B^T (a K-major block of 128 queries)
+            auto issue_st = [&](uint32_t d) {
 #pragma unroll
                 for (int ks = 0; ks < HS / 8; ++ks) {
                     const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                    mma_tf32(tmem_base + COL_DP + (uint32_t)(st * 64), smem_desc_kmajor(base + OFF_V + half * 16384 + off),
-                             smem_desc_kmajor(sk + 16384 + half * 8192 + off), idesc_st, ks ? 1u : 0u);
+                    mma_tf32(d, smem_desc_kmajor(a_res + half * 16384 + off), smem_desc_kmajor(b_blk + half * 16384 + off), idesc_st, ks ? 1u : 0u);
                 }
             };
+#ifdef BMB_FLASH_TRACE
+            // phases of warp 9 of CTA (0, 0): 24 prologue, 25 wait Q block, 26 issue S^T, 27 wait P^T / dS^T and granules, 28 issue dV
+            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && first);
+            long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            long long tlast = clock64();
+#endif
             bool ok = mbar_wait(bar(KV_FULL), 0, giveup);
-            if (ok && nb > 0) ok = mbar_wait(bar(STK_FULL + 0), 0, giveup);
+            if (ok && nb > 0) ok = mbar_wait(bar(IN_FULL), 0, giveup);
             if (ok && nb > 0) {
                 fence_after();
-                issue_sp(0);
-                commit(bar(SP_FULL + 0));
-                commit(bar(STK_EMPTY + 0));
+                issue_st(tmem_base + (first ? COL_S : COL_DP));
+                commit(bar(first ? S_FULL + 0 : DP_FULL));
+                commit(bar(IN_EMPTY));
             }
+            TRB(24);
             for (int i = 0; ok && i < nb; ++i) {
-                const int st = i & 1;
-                const uint32_t ph = (uint32_t)((i >> 1) & 1);
-                if (i + 1 < nb) {
-                    // block i+1 goes into the other S^T / dP^T buffer; the products that read that buffer's
-                    // P^T / dS^T (block i-1) were issued before this point, and the tensor core runs in order
-                    const int s1 = (i + 1) & 1;
-                    if (!mbar_wait(bar(STK_FULL + s1), (uint32_t)(((i + 1) >> 1) & 1), giveup)) { ok = false; break; }
+                const int buf = i & 1, b1 = (i + 1) & 1;
+                const uint32_t ph = (uint32_t)(i & 1), p1 = (uint32_t)((i + 1) & 1);
+                if (first && i + 1 < nb) {
+                    // S^T of block i+1 goes into the other buffer: the product that read its P^T (block i-1)
+                    // was issued by this thread before this point
+                    if (!mbar_wait(bar(QK_FULL), p1, giveup)) { ok = false; break; }
                     fence_after();
-                    issue_sp(s1);
-                    commit(bar(SP_FULL + s1));
-                    commit(bar(STK_EMPTY + s1));
+                    TRB(25);
+                    issue_st(tmem_base + COL_S + (uint32_t)(b1 * 128));
+                    commit(bar(S_FULL + b1));
+                    commit(bar(QK_EMPTY));
                 }
-                if (!mbar_wait(bar(STN_FULL + st), ph, giveup)) { ok = false; break; }
-                if (!mbar_wait(bar(PD_FULL + st), ph, giveup)) { ok = false; break; }
-                fence_after();
-                const uint32_t sn = base + OFF_STN + st * STN_BYTES;
+                TRB(26);
+                for (int g = 0; g < 2; ++g) {
+                    if (!mbar_wait(bar(N_FULL + g), ph, giveup)) { ok = false; break; }
+                    if (!mbar_wait(bar(PD_FULL + g), ph, giveup)) { ok = false; break; }
+                    fence_after();
+                    TRB(27);
+                    // dV += P^T dO   or   dK += dS^T Q
+                    const uint32_t a_tm = tmem_base + (first ? COL_S + (uint32_t)(buf * 128) : COL_DP) + (uint32_t)(g * G);
+                    const uint32_t bn = b_gran + g * 16384;
 #pragma unroll
-                for (int ks = 0; ks < QB / 8; ++ks)       // dV += P^T dO
-                    mma_tf32_ts(tmem_base + COL_DV, tmem_base + COL_S + (uint32_t)(st * 64 + ks * 8),
-                                smem_desc_mnmajor32(sn + 16384 + ks * 1024, 8192), idesc_acc, (i | ks) ? 1u : 0u);
-#pragma unroll
-                for (int ks = 0; ks < QB / 8; ++ks)       // dK += dS^T Q
-                    mma_tf32_ts(tmem_base + COL_DK, tmem_base + COL_DP + (uint32_t)(st * 64 + ks * 8),
-                                smem_desc_mnmajor32(sn + ks * 1024, 8192), idesc_acc, (i | ks) ? 1u : 0u);
-                commit(bar(STN_EMPTY + st));
+                    for (int ks = 0; ks < G / 8; ++ks)
+                        mma_tf32_ts(acc, a_tm + (uint32_t)(ks * 8), smem_desc_mnmajor32(bn + ks * 1024, 8192), idesc_acc, (i | g | ks) ? 1u : 0u);
+                    commit(bar(N_EMPTY + g));
+                    TRB(28);
+                }
+                if (!ok) break;
+                if (!first && i + 1 < nb) {
+                    // dP^T of block i+1 overwrites the dS^T this thread has just had multiplied
+                    if (!mbar_wait(bar(DOK_FULL), p1, giveup)) { ok = false; break; }
+                    fence_after();
+                    issue_st(tmem_base + COL_DP);
+                    commit(bar(DP_FULL));
+                    commit(bar(DOK_EMPTY));
+                }
             }
             if (ok) commit(bar(ACC_DONE));
+            TRB_FLUSH(24, 5);
         }
-    } else {
+    } else if (warp < 8) {
         // ------------------------------------------------------- P^T and dS^T
         const int quad = warp & 3, colhalf = warp >> 2;
         const int r = quad * 32 + lane;
@@ -452,64 +581,94 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         bool ok = true;
 #ifdef BMB_FLASH_TRACE
+        // phases of one thread of CTA (0, 0): 9 wait S^T, 10 P^T of both granules, 11 wait dP^T, 12 dS^T of both granules
         const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && lane == 0);
+        long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tlast = clock64();
 #endif
         for (int i = 0; i < nb; ++i) {
             const int buf = i & 1;
-            const int qc0 = (ib0 + i) * QB + colhalf * 32;     // first query column of this thread
-            TRB(9);
-            if (!mbar_wait(bar(SP_FULL + buf), (uint32_t)((i >> 1) & 1), giveup)) { ok = false; break; }
+            if (!mbar_wait(bar(S_FULL + buf), (uint32_t)((i >> 1) & 1), giveup)) { ok = false; break; }
             fence_after();
-            TRB(10);
-            float s[32], dp[32];
-            const uint32_t s_addr = lane_addr + COL_S + (uint32_t)(buf * 64 + colhalf * 32);
-            const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(buf * 64 + colhalf * 32);
-            tmem_ld32_nowait(s_addr, s);
-            tmem_ld32_nowait(dp_addr, dp);
-            tmem_wait_ld();
-            TRB(11);
-            // per-column lse and D
-            if (stats_in_smem) {
-                const float4 *lp = reinterpret_cast<const float4 *>(stat_l + i * QB + colhalf * 32);
-                const float4 *dp4 = reinterpret_cast<const float4 *>(stat_d + i * QB + colhalf * 32);
+            TRB(9);
+            // P^T of this thread's 32 + 32 query columns: unrounded in registers for dS^T, rounded into tensor memory
+            float p[2][32];
 #pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) {
-                    const float4 l4 = lp[c4], d4 = dp4[c4];          // the same address for the whole warp: broadcast
-                    const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+            for (int g = 0; g < 2; ++g) {
+                const int qc0 = (ib0 + i) * QB + g * G + colhalf * 32;       // first query column
+                const uint32_t s_addr = lane_addr + COL_S + (uint32_t)(buf * 128 + g * G + colhalf * 32);
+                float s[32];
+                tmem_ld32(s_addr, s);
+                if (stats_in_smem) {
+                    const float4 *lp = reinterpret_cast<const float4 *>(stat_l + i * QB + g * G + colhalf * 32);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = c4 * 4 + e;
-                        float p = fast_exp2(fmaf(s[c], scale_log2e, -lv[e]));
-                        if (qc0 + c < kj || qc0 + c >= T) p = 0.0f;        // causal mask and the ragged end
-                        s[c] = round_tf32_alu(p);
-                        dp[c] = round_tf32_alu(p * (dp[c] - dv[e]));
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = lp[c4];                    // the same address for the whole warp: broadcast
+                        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = c4 * 4 + e;
+                            float v = fast_exp2(fmaf(s[c], scale_log2e, -lv[e]));
+                            if (qc0 + c < kj || qc0 + c >= T) v = 0.0f;        // causal mask and the ragged end
+                            p[g][c] = v;
+                            s[c] = round_tf32_alu(v);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int q = qc0 + c;
+                        const float lq = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
+                        float v = fast_exp2(fmaf(s[c], scale_log2e, -lq));
+                        if (q < kj || q >= T) v = 0.0f;
+                        p[g][c] = v;
+                        s[c] = round_tf32_alu(v);
                     }
                 }
-            } else {
+                tmem_st32_nowait(s_addr, s);
+            }
+            TRB(10);
+            if (!mbar_wait(bar(DP_FULL), (uint32_t)(i & 1), giveup)) { ok = false; break; }
+            fence_after();
+            TRB(11);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int q = qc0 + c;
-                    const float lq = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
-                    const float dq_ = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
-                    float p = fast_exp2(fmaf(s[c], scale_log2e, -lq));
-                    if (q < kj || q >= T) p = 0.0f;        // causal mask and the ragged end
-                    s[c] = round_tf32_alu(p);
-                    dp[c] = round_tf32_alu(p * (dp[c] - dq_));
+            for (int g = 0; g < 2; ++g) {
+                const int qc0 = (ib0 + i) * QB + g * G + colhalf * 32;
+                const uint32_t dp_addr = lane_addr + COL_DP + (uint32_t)(g * G + colhalf * 32);
+                float dp[32];
+                tmem_ld32(dp_addr, dp);
+                if (stats_in_smem) {
+                    const float4 *dp4 = reinterpret_cast<const float4 *>(stat_d + i * QB + g * G + colhalf * 32);
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 d4 = dp4[c4];
+                        const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = c4 * 4 + e;
+                            dp[c] = round_tf32_alu(p[g][c] * (dp[c] - dv[e]));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int q = qc0 + c;
+                        const float dq_ = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+                        dp[c] = round_tf32_alu(p[g][c] * (dp[c] - dq_));
+                    }
                 }
+                tmem_st32_nowait(dp_addr, dp);
+                tmem_wait_st();                 // also covers this granule's P^T, stored above
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(PD_FULL + g));
             }
             TRB(12);
-            tmem_st32_nowait(s_addr, s);
-            tmem_st32_nowait(dp_addr, dp);
-            tmem_wait_st();
-            fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(PD_FULL + buf));
-            TRB(13);
-#ifdef BMB_FLASH_TRACE
-            if (tr) g_trace_bwd[14] += 1;
-#endif
         }
+#ifdef BMB_FLASH_TRACE
+        TRB_FLUSH(9, 4);
+        if (tr) g_trace_bwd[14] += nb;
+#endif
         if (ok && nb > 0 && mbar_wait(bar(ACC_DONE), 0, giveup)) {
             fence_after();
             float v[32];
@@ -609,8 +768,8 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
 }  // namespace bmb
 
 #ifdef BMB_FLASH_TRACE
-extern "C" int bmb_dbg_flash_bwd_trace(long long *host16, int reset) {
-    if (reset) { long long z[16] = {0}; return (int)cudaMemcpyToSymbol(bmb::g_trace_bwd, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(host16, bmb::g_trace_bwd, 16 * sizeof(long long));
+extern "C" int bmb_dbg_flash_bwd_trace(long long *host16, int reset) {   // 32 counters
+    if (reset) { long long z[32] = {0}; return (int)cudaMemcpyToSymbol(bmb::g_trace_bwd, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(host16, bmb::g_trace_bwd, 32 * sizeof(long long));
 }
 #endif
