@@ -43,7 +43,7 @@ SIGNATURES = {
     "bmb_last_error": (C.c_char_p, []),
     "bmb_version": (C.c_char_p, []),
     "bmb_launch_count": (_ll, []),
-    "bmb_gemm_schedule_check": (_i, [_i, _i, _i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "bmb_gemm_schedule_check": (_i, [_i, _i, _i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "bmb_set_stream": (_i, [_p]),
     "bmb_get_stream": (_p, []),
     "bmb_set_math_mode": (_i, [_i]),

@@ -67,7 +67,13 @@ constexpr int A_BYTES = BM * KBYTES;
 constexpr int EPI_WARPS = 8;                        // two per TMEM lane quadrant, taking alternate 32-column chunks
 constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
 constexpr int EPI_BYTES = EPI_WARPS * 32 * 32 * 4;  // one 32 x 32 staging block per epilogue warp, 16-byte units XOR-swizzled by row
-constexpr int smem_bytes(int bn) { return STAGES * (A_BYTES + bn * KBYTES) + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES; }
+// A tile is MH (1 or 2) blocks of 128 rows tall.  Two blocks share every B slice: per K slice the SM then
+// writes 64 KB and reads 96 KB of shared memory for 8 instructions, against 48 KB + 48 KB for 4 -- with
+// fp32 operands it is shared-memory bandwidth, not the tensor pipe, that bounds the main loop.  The price:
+// the two accumulators fill tensor memory, so the epilogue no longer overlaps the next tile, and the
+// ring is 3 slices deep.
+__host__ __device__ constexpr int stages_for(int mh) { return mh == 2 ? 3 : STAGES; }
+constexpr int smem_bytes(int bn, int mh = 1) { return stages_for(mh) * (mh * A_BYTES + bn * KBYTES) + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES; }
 constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 128 bytes of M/N
 
 struct TileSched {
@@ -172,15 +178,18 @@ __device__ __forceinline__ void add_result(float4 o, float *__restrict__ C, int 
 // KIND 0 = tf32 (fp32 operands), 1 = f16 (bf16 operands, always K-major).
 // a_mn / b_mn: the operand's tile is MN-major (TF32 only); 2 = its tensor map is the 3-d one that
 // brings all chunks of a slice in one copy.
-template <int KIND, int BN>
+template <int KIND, int BN, int MH>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
           const __grid_constant__ CUtensorMap mapC, int c_mode, int batch, int M, int N,
           int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
           int vec_ok, int dp_tiles, int g_sk, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
-    constexpr int B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t ACC_COLS = BN > 128 ? 256 : 128; // TMEM columns set aside per accumulator
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // two accumulators; allocations are powers of two
+    static_assert(MH == 1 || (MH == 2 && BN == 256), "two-block tiles are 256 columns wide");
+    constexpr int STAGES = stages_for(MH), BMT = BM * MH;
+    constexpr int B_BYTES = BN * KBYTES, STAGE_BYTES = MH * A_BYTES + B_BYTES;
+    constexpr uint32_t ACC_COLS = BN > 128 ? 256 : 128; // TMEM columns set aside per 128-row accumulator
+    constexpr int NACC = MH == 2 ? 1 : 2;               // accumulator sets: two blocks of rows fill tensor memory
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // allocations are powers of two
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -196,7 +205,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
 
     TileSched sch;
-    sch.tiles_m = (M + BM - 1) / BM;
+    sch.tiles_m = (M + BMT - 1) / BMT;
     sch.tiles_n = (N + BN - 1) / BN;
     // A batch of dense problems is one long list of tiles; its operands are seen as the 2-d matrices
     // [batch * rows][K] (K-major) or [batch * K][rows] (MN-major), so only a row offset tells batches apart.
@@ -234,15 +243,15 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     const uint32_t fb = full0 + 8 * s;
                     mbar_arrive_expect_tx(fb, STAGE_BYTES);
                     armed[s] = (int)ph;
-                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + MH * A_BYTES;
                     const int k0 = kb * kelems_per_block;
                     if (a_mn == 2) {
-                        tma_load_3d(sa, &mapA, 0, k_row0 + k0, tm * (BM / 32), fb);        // all chunks in one copy
+                        tma_load_3d(sa, &mapA, 0, k_row0 + k0, tm * (BMT / 32), fb);       // all chunks in one copy
                     } else if (a_mn) {
 #pragma unroll 1
-                        for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * CHUNK_BYTES, &mapA, tm * BM + c * 32, k_row0 + k0, fb);
+                        for (int c = 0; c < BMT / 32; ++c) tma_load_2d(sa + c * CHUNK_BYTES, &mapA, tm * BMT + c * 32, k_row0 + k0, fb);
                     } else {
-                        tma_load_2d(sa, &mapA, k0, a_row0 + tm * BM, fb);
+                        tma_load_2d(sa, &mapA, k0, a_row0 + tm * BMT, fb);
                     }
                     if (b_mn == 2) {
                         tma_load_3d(sb, &mapB, 0, k_row0 + k0, tn * (BN / 32), fb);
@@ -277,26 +286,32 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
                     fence_after();
-                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + MH * A_BYTES;
 #pragma unroll
                     for (int k = 0; k < KBYTES / 32; ++k) {
-                        const uint64_t da = a_mn ? smem_desc_mnmajor32(sa + k * a_step, CHUNK_BYTES) : smem_desc_kmajor(sa + k * a_step);
                         const uint64_t db = b_mn ? smem_desc_mnmajor32(sb + k * b_step, CHUNK_BYTES) : smem_desc_kmajor(sb + k * b_step);
-                        if (KIND == 0) mma_tf32(d, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
-                        else mma_f16(d, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
+#pragma unroll
+                        for (int hb = 0; hb < MH; ++hb) {       // the blocks of 128 rows, 16 KB apart in either layout
+                            const uint32_t sah = sa + hb * A_BYTES + k * a_step;
+                            const uint64_t da = a_mn ? smem_desc_mnmajor32(sah, CHUNK_BYTES) : smem_desc_kmajor(sah);
+                            if (KIND == 0) mma_tf32(d + (uint32_t)hb * ACC_COLS, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
+                            else mma_f16(d + (uint32_t)hb * ACC_COLS, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
+                        }
                     }
                     commit(empty0 + 8 * s);             // slice reusable once these MMAs retire
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
                 commit(tfull0 + 8 * acc);               // accumulator complete
-                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                          // TMEM lane quadrant this warp may read
-        const int chunk_par = (warp - 2) >> 2;           // this warp takes the chunks of this parity
+        // the two warps of a quadrant take alternate 32-column chunks of one accumulator, or one block of rows each
+        const int wgroup = (warp - 2) >> 2;
+        const int chunk_first = MH == 2 ? 0 : wgroup, chunk_step = MH == 2 ? 1 : 2, hblock = MH == 2 ? wgroup : 0;
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
@@ -313,13 +328,13 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             // written out four rows per instruction, each row segment a contiguous 128 bytes, so that
             // the global stores (loads of C, atomics) are fully coalesced.  A whole tile is stored; a
             // part of a stream-K tile is added into C.
-            const int row_base = tm * BM + q * 32;
-            const uint32_t trow = tmem_base + (uint32_t)acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+            const int row_base = tm * BMT + hblock * BM + q * 32;
+            const uint32_t trow = tmem_base + (uint32_t)(acc + hblock) * ACC_COLS + ((uint32_t)(q * 32) << 16);
             float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES) + (warp - 2) * (32 * 32);
             const int sub_r = lane >> 3, sub_u = lane & 7, sub_c = sub_u * 4;
             const float *part_bias = (kb0 == 0) ? bias : nullptr;
 #pragma unroll 1
-            for (int c = chunk_par; c < BN / 32; c += 2) {
+            for (int c = chunk_first; c < BN / 32; c += chunk_step) {
                 const int n0 = tn * BN + c * 32;
                 if (n0 >= N) break;                      // warp-uniform
                 if (whole && c_mode == 3) {
@@ -398,7 +413,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
         }
         if (c_mode && lane == 0) tma_store_wait_all();   // every block this warp handed to the copy engine has landed
     }
@@ -547,13 +562,13 @@ namespace {
 
 // C = beta * C over the tiles [dp_tiles, num_tiles) (the stream-K tiles), before their parts are added.
 __global__ void __launch_bounds__(256) sk_prepare_k(float *__restrict__ C, int M, int N, int tiles_m, int tiles_n, int dp_tiles,
-                                                    int bn, float beta, int vec_ok) {
+                                                    int bm, int bn, float beta, int vec_ok) {
     TileSched sch;
     sch.tiles_m = tiles_m; sch.tiles_n = tiles_n; sch.num_tiles = tiles_m * tiles_n;
     int tm, tn;
     sch.coords(dp_tiles + (int)blockIdx.x, tm, tn);
-    const int m0 = tm * BM, n0 = tn * bn;
-    const int rows = min(BM, M - m0), cols = min(bn, N - n0);
+    const int m0 = tm * bm, n0 = tn * bn;
+    const int rows = min(bm, M - m0), cols = min(bn, N - n0);
     if (vec_ok && cols % 4 == 0) {
         const int c4 = cols / 4;
         for (int i = threadIdx.x; i < rows * c4; i += blockDim.x) {
@@ -577,28 +592,39 @@ double slice_cost(int bn) { return bn == 256 ? 256.0 : (bn == 192 ? 200.0 : (bn 
 // Pick the tile width and how many tiles to hand out whole; the rest (a last, partly filled wave, or a
 // problem smaller than one wave) is shared between CTAs along K.  Costs are in K-slice units of a
 // 256-wide tile; a tile pays ~4 slices for its epilogue, sharing a tile ~6 more.
-void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int force_bn, int *bn_out, int *dp_tiles_out) {
-    const int tiles_m = (M + BM - 1) / BM;
-    const int widths[4] = {256, 192, 128, 64};
+// A tile of two row blocks (256 x 256) costs `tall_slice` slices of a 128 x 256 tile per slice (fitted to
+// measurements: 1.72 for twice the work) and, its epilogue no longer hidden, `tall_epi` slices more per
+// tile; sharing such tiles between CTAs costs more than sharing the small ones.
+void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int force_bn, int force_mh, bool tall_ok,
+                     int *bn_out, int *mh_out, int *dp_tiles_out) {
+    static const double tall_slice = [] { const char *e = getenv("BMB_GEMM_TALL_SLICE"); return e ? atof(e) : 1.72; }();
+    static const double tall_epi = [] { const char *e = getenv("BMB_GEMM_TALL_EPI"); return e ? atof(e) : 8.0; }();
+    const int widths[5] = {256, 256, 192, 128, 64};
     double best = -1.0;
-    for (int w : widths) {
+    for (int cand = 0; cand < 5; ++cand) {
+        const int w = widths[cand], mh = cand == 0 ? 2 : 1;
+        const bool tall_possible = tall_ok && M >= 2 * BM && N >= 256;
+        if (mh == 2 && (!tall_possible || force_mh == 1)) continue;
+        if (mh == 1 && force_mh == 2 && tall_possible) continue;
         if (force_bn ? (w != force_bn) : ((w > 64 && N < w) || (w == 64 && N >= 128))) continue;
+        const int tiles_m = (M + mh * BM - 1) / (mh * BM);
         const long long tiles = (long long)tiles_m * ((N + w - 1) / w);
         const long long full = tiles / ctas, rem = tiles % ctas;
-        const double unit = slice_cost(w) / 256.0;
-        const double whole = (double)(full + (rem ? 1 : 0)) * (kblocks + 4) * unit;
+        const double unit = mh == 2 ? tall_slice : slice_cost(w) / 256.0;
+        const double epi = mh == 2 ? tall_epi : 4.0;
+        const double whole = (double)(full + (rem ? 1 : 0)) * (kblocks + epi) * unit;
         double cost = whole;
         int dp = (int)tiles;
         if (allow_split && rem && kblocks >= 8) {
-            const double shared = ((double)full * (kblocks + 4) + (double)((rem * kblocks + ctas - 1) / ctas) + 10.0) * unit;
+            const double shared = ((double)full * (kblocks + epi) + (double)((rem * kblocks + ctas - 1) / ctas) + (mh == 2 ? 24.0 : 10.0)) * unit;
             if (shared < whole) { cost = shared; dp = (int)(tiles - rem); }
         }
-        if (best < 0.0 || cost < best) { best = cost; *bn_out = w; *dp_tiles_out = dp; }
+        if (best < 0.0 || cost < best) { best = cost; *bn_out = w; *mh_out = mh; *dp_tiles_out = dp; }
     }
 }
 
 // Everything the launch decides about how the tiles are handed out.
-struct Plan { int bn, kblocks, tiles_m, tiles_n, tiles, dp_tiles, sk_tiles, g_sk, grid; };
+struct Plan { int bn, mh, kblocks, tiles_m, tiles_n, tiles, dp_tiles, sk_tiles, g_sk, grid; };
 
 int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int ctas) {
     const int kper = KBYTES / (bf16 ? 2 : 4);
@@ -608,10 +634,14 @@ int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int
     // BMB_GEMM_NO_SPLIT and BMB_GEMM_C_ROUNDED keep every tile on one CTA; so do batched problems.
     const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED)) && batch == 1;
     static const int force_bn = [] { const char *e = getenv("BMB_GEMM_TILE_N"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 192 || v == 128 || v == 64) ? v : 0; }();
+    // BMB_GEMM_TILE_M = 128 or 256 forces the tile height where the shape allows it
+    static const int force_mh = [] { const char *e = getenv("BMB_GEMM_TILE_M"); const int v = e ? atoi(e) : 0; return v == 256 ? 2 : (v == 128 ? 1 : 0); }();
     p->bn = BN_WIDE;
+    p->mh = 1;
     p->dp_tiles = 0;
-    choose_schedule(M, N, p->kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, &p->bn, &p->dp_tiles);
-    p->tiles_m = (M + BM - 1) / BM;
+    choose_schedule(M, N, p->kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, force_mh, batch == 1, &p->bn, &p->mh,
+                    &p->dp_tiles);
+    p->tiles_m = (M + p->mh * BM - 1) / (p->mh * BM);
     p->tiles_n = (N + p->bn - 1) / p->bn;
     const long long tiles_ll = (long long)p->tiles_m * p->tiles_n * batch;
     if (tiles_ll >= (1LL << 31)) return fail(BMB_E_LIMIT, "gemm_tc: %lld tiles", tiles_ll);
@@ -628,7 +658,7 @@ int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int
     return BMB_OK;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, int MH>
 int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, int c_mode,
               int batch, int M, int N, int kblocks, int kper,
               int amn, int bmn, float alpha, float beta, float *C, int vec_ok, int dp_tiles, int g_sk, const float *bias,
@@ -638,11 +668,11 @@ int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensor
         std::lock_guard<std::mutex> lk(g_attr_mu);
         const int d = current_device();
         if (d >= 0 && d < 64 && !attr_set[d]) {
-            BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
+            BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<KIND, BN, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN, MH)));
             attr_set[d] = true;
         }
     }
-    gemm_tc_k<KIND, BN><<<grid, NTHREADS, smem_bytes(BN), st>>>(mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
+    gemm_tc_k<KIND, BN, MH><<<grid, NTHREADS, smem_bytes(BN, MH), st>>>(mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
                                                                 dp_tiles, g_sk, bias, round_c, status_dev);
     return BMB_OK;
 }
@@ -665,7 +695,7 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     BMB_TRY(plan_gemm(&plan, bf16, flags, batch, M, N, K, ctas));
     const int kblocks = plan.kblocks, bn = plan.bn, dp_tiles = plan.dp_tiles;
     Operand a, b;
-    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, BM, st, batch));
+    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, plan.mh * BM, st, batch));
     BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st, batch));
     CUtensorMap mapA, mapB;
     if (a.map3d) BMB_TRY(make_map_mn3d(&mapA, a.ptr, a.rows, a.cols, a.pitch_bytes, a.tile_chunks));
@@ -676,7 +706,7 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     const int vec_ok = ((uintptr_t)C % 16 == 0) && (N % 4 == 0);
     const int sk_tiles = plan.sk_tiles, g_sk = plan.g_sk, grid = plan.grid;
     if (sk_tiles > 0 && beta != 1.0f) {
-        sk_prepare_k<<<sk_tiles, 256, 0, st>>>(C, M, N, tiles_m, tiles_n, dp_tiles, bn, beta, vec_ok);
+        sk_prepare_k<<<sk_tiles, 256, 0, st>>>(C, M, N, tiles_m, tiles_n, dp_tiles, plan.mh * BM, bn, beta, vec_ok);
         count_launch();
     }
     const int round_c = (flags & BMB_GEMM_C_ROUNDED) ? 1 : 0;
@@ -693,15 +723,17 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     if (c_mode) BMB_TRY(make_map_2d(&mapC, C, 4, M, N, (long long)N * 4, 32, false));
 #define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {
-        if (bn == 256) BMB_TRY((launch_tc<1, 256>(BMB_TC_ARGS)));
-        else if (bn == 192) BMB_TRY((launch_tc<1, 192>(BMB_TC_ARGS)));
-        else if (bn == 128) BMB_TRY((launch_tc<1, 128>(BMB_TC_ARGS)));
-        else BMB_TRY((launch_tc<1, 64>(BMB_TC_ARGS)));
+        if (plan.mh == 2) BMB_TRY((launch_tc<1, 256, 2>(BMB_TC_ARGS)));
+        else if (bn == 256) BMB_TRY((launch_tc<1, 256, 1>(BMB_TC_ARGS)));
+        else if (bn == 192) BMB_TRY((launch_tc<1, 192, 1>(BMB_TC_ARGS)));
+        else if (bn == 128) BMB_TRY((launch_tc<1, 128, 1>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<1, 64, 1>(BMB_TC_ARGS)));
     } else {
-        if (bn == 256) BMB_TRY((launch_tc<0, 256>(BMB_TC_ARGS)));
-        else if (bn == 192) BMB_TRY((launch_tc<0, 192>(BMB_TC_ARGS)));
-        else if (bn == 128) BMB_TRY((launch_tc<0, 128>(BMB_TC_ARGS)));
-        else BMB_TRY((launch_tc<0, 64>(BMB_TC_ARGS)));
+        if (plan.mh == 2) BMB_TRY((launch_tc<0, 256, 2>(BMB_TC_ARGS)));
+        else if (bn == 256) BMB_TRY((launch_tc<0, 256, 1>(BMB_TC_ARGS)));
+        else if (bn == 192) BMB_TRY((launch_tc<0, 192, 1>(BMB_TC_ARGS)));
+        else if (bn == 128) BMB_TRY((launch_tc<0, 128, 1>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<0, 64, 1>(BMB_TC_ARGS)));
     }
 #undef BMB_TC_ARGS
     count_launch();
@@ -714,12 +746,13 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
 // Host-side replay of the tile schedule a tensor-core GEMM of this shape would use on `ctas` SMs:
 // returns BMB_OK when the work items of all CTAs cover every (tile, K slice) exactly once, whole
 // tiles only where no tile is shared.  Runs no kernel; the CPU tests sweep shapes through it.
-extern "C" int bmb_gemm_schedule_check(int math, int flags, int batch, int M, int N, int K, int ctas, int *bn_out,
+extern "C" int bmb_gemm_schedule_check(int math, int flags, int batch, int M, int N, int K, int ctas, int *bm_out, int *bn_out,
                                        int *dp_tiles_out, int *grid_out) {
     using namespace bmb;
     if (M < 1 || N < 1 || K < 1 || batch < 1 || ctas < 1) return fail(BMB_E_ARG, "schedule_check: bad argument");
     Plan p;
     BMB_TRY(plan_gemm(&p, math == BMB_MATH_BF16, flags, batch, M, N, K, ctas));
+    if (bm_out) *bm_out = p.mh * BM;
     if (bn_out) *bn_out = p.bn;
     if (dp_tiles_out) *dp_tiles_out = p.dp_tiles;
     if (grid_out) *grid_out = p.grid;

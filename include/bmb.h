@@ -34,10 +34,10 @@ extern "C" {
 const char *bmb_last_error(void);
 const char *bmb_version(void);
 /* No counterpart in the reference.  Replays on the host the tile schedule a tensor-core GEMM of
- * this shape would use on `ctas` SMs (tile width, whole tiles, tiles shared along K) and returns 0
+ * this shape would use on `ctas` SMs (tile height and width, whole tiles, tiles shared along K) and returns 0
  * when every (tile, K slice) is computed exactly once.  Launches nothing; usable without a GPU. */
 int bmb_gemm_schedule_check(int math, int flags, int batch, int M, int N, int K, int ctas,
-                            int *tile_n_out, int *whole_tiles_out, int *grid_out);
+                            int *tile_m_out, int *tile_n_out, int *whole_tiles_out, int *grid_out);
 /* Kernels this library has launched in this process so far (launches replayed from a CUDA
  * graph included).  No counterpart in the reference; bench.py reports it. */
 long long bmb_launch_count(void);

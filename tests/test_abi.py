@@ -105,14 +105,15 @@ def test_tensorcore_gemm_schedule_covers_every_slice_once(bmb):
     for ctas in (148, 132, 7, 1):
         for (M, N, K) in shapes:
             for flags in (0, bmb.GEMM_NO_SPLIT):
-                bn, dp, grid = C.c_int(), C.c_int(), C.c_int()
-                st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flags, 1, M, N, K, ctas, C.byref(bn), C.byref(dp), C.byref(grid))
+                bm, bn, dp, grid = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+                st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flags, 1, M, N, K, ctas, C.byref(bm), C.byref(bn), C.byref(dp), C.byref(grid))
                 assert st == 0, (M, N, K, ctas, flags, lib.bmb_last_error())
-                tiles = -(-M // 128) * -(-N // bn.value)
-                assert bn.value in (64, 128, 192, 256) and 1 <= grid.value <= ctas and 0 <= dp.value <= tiles
+                tiles = -(-M // bm.value) * -(-N // bn.value)
+                assert (bm.value, bn.value) in ((128, 64), (128, 128), (128, 192), (128, 256), (256, 256))
+                assert 1 <= grid.value <= ctas and 0 <= dp.value <= tiles
                 if flags:
                     assert dp.value == tiles
                 shared += dp.value < tiles
     assert shared > 20                      # the sweep does exercise shared tiles
-    st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 96, 1024, 64, 1024, 148, None, None, None)   # batched
+    st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 96, 1024, 64, 1024, 148, None, None, None, None)   # batched
     assert st == 0, lib.bmb_last_error()
