@@ -119,5 +119,8 @@ __device__ __forceinline__ float round_tf32(float x) {
 __device__ __forceinline__ float round_tf32_alu(float x) {
     return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
+// For a value that only the tensor core will read: kind::tf32 ignores the low 13 bits of an operand,
+// so adding half a TF32 ulp is all it takes to turn that truncation into rounding to nearest.
+__device__ __forceinline__ float round_tf32_for_mma(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
 }  // namespace bmb
 #endif

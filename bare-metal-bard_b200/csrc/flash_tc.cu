@@ -305,8 +305,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     const float p1 = fast_exp2(fmaf(s[i + 1], scale_log2e, -mb));
                     sum0 += p0;
                     sum1 += p1;
-                    s[i] = round_tf32_alu(p0);
-                    s[i + 1] = round_tf32_alu(p1);
+                    s[i] = round_tf32_for_mma(p0);
+                    s[i + 1] = round_tf32_for_mma(p1);
                 }
                 l = l * alpha + (sum0 + sum1);
                 m = m_new;

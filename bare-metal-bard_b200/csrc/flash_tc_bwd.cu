@@ -309,7 +309,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                 float dp[32];
                 tmem_ld32(dp_addr, dp);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) dp[i] = round_tf32_alu(p0[i] * (dp[i] - d_r));
+                for (int i = 0; i < 32; ++i) dp[i] = round_tf32_for_mma(p0[i] * (dp[i] - d_r));
                 tmem_st32_nowait(dp_addr, dp);                 // dS over dP: the A operand of dQ += dS K
                 tmem_wait_st();
                 fence_before();
@@ -320,7 +320,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
                 float dp[32];
                 tmem_ld32(dp_addr + G, dp);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) dp[i] = round_tf32_alu(p1[i] * (dp[i] - d_r));
+                for (int i = 0; i < 32; ++i) dp[i] = round_tf32_for_mma(p1[i] * (dp[i] - d_r));
                 tmem_st32_nowait(dp_addr + G, dp);
                 tmem_wait_st();
                 fence_before();
@@ -611,7 +611,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                             float v = fast_exp2(fmaf(s[c], scale_log2e, -lv[e]));
                             if (qc0 + c < kj || qc0 + c >= T) v = 0.0f;        // causal mask and the ragged end
                             p[g][c] = v;
-                            s[c] = round_tf32_alu(v);
+                            s[c] = round_tf32_for_mma(v);
                         }
                     }
                 } else {
@@ -622,7 +622,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                         float v = fast_exp2(fmaf(s[c], scale_log2e, -lq));
                         if (q < kj || q >= T) v = 0.0f;
                         p[g][c] = v;
-                        s[c] = round_tf32_alu(v);
+                        s[c] = round_tf32_for_mma(v);
                     }
                 }
                 tmem_st32_nowait(s_addr, s);
@@ -646,7 +646,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int c = c4 * 4 + e;
-                            dp[c] = round_tf32_alu(p[g][c] * (dp[c] - dv[e]));
+                            dp[c] = round_tf32_for_mma(p[g][c] * (dp[c] - dv[e]));
                         }
                     }
                 } else {
@@ -654,7 +654,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                     for (int c = 0; c < 32; ++c) {
                         const int q = qc0 + c;
                         const float dq_ = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
-                        dp[c] = round_tf32_alu(p[g][c] * (dp[c] - dq_));
+                        dp[c] = round_tf32_for_mma(p[g][c] * (dp[c] - dq_));
                     }
                 }
                 tmem_st32_nowait(dp_addr, dp);

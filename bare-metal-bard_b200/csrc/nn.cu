@@ -292,24 +292,32 @@ __global__ void layernorm_bwd_block_k(float *__restrict__ dinp, float *__restric
 }
 
 // dst[c] += sum_{g < G} partial[g][c]   for c < ncols, in a fixed order: a block
-// covers 32 columns, its 8 warps each sum every 8th row of `partial`, and the 8
+// covers 32 columns, its 32 warps each sum every 32nd row of `partial`, and the 32
 // sub-sums are added in warp order.  If dst2 != nullptr the columns
 // [ncols_first, ncols) go to dst2; if dst3 != nullptr those from 2 * ncols_first on go to dst3.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
              const float *__restrict__ partial, int G, int ncols, float *__restrict__ dst3 = nullptr) {
-    __shared__ float red[8][33];
+    __shared__ float red[32][33];
     const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + cx;
+    // 32 warps share the G rows; four loads are in flight per thread before the first add
     float s = 0.0f;
-    if (c < ncols)
-        for (int g = gy; g < G; g += 8) s += partial[(size_t)g * ncols + c];
+    if (c < ncols) {
+        int g = gy;
+        for (; g + 96 < G; g += 128) {
+            const float a0 = partial[(size_t)g * ncols + c], a1 = partial[(size_t)(g + 32) * ncols + c];
+            const float a2 = partial[(size_t)(g + 64) * ncols + c], a3 = partial[(size_t)(g + 96) * ncols + c];
+            s += a0; s += a1; s += a2; s += a3;
+        }
+        for (; g < G; g += 32) s += partial[(size_t)g * ncols + c];
+    }
     red[gy][cx] = s;
     __syncthreads();
     if (gy == 0 && c < ncols) {
         float t = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t += red[i][cx];
+        for (int i = 0; i < 32; ++i) t += red[i][cx];
         if (dst3 && c >= 2 * ncols_first) dst3[c - 2 * ncols_first] += t;
         else if (dst2 && c >= ncols_first) dst2[c - ncols_first] += t;
         else dst[c] += t;
@@ -664,7 +672,7 @@ bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 // Shared with other translation units of the library.
 int launch_column_add(float *dst, float *dst2, int ncols_first, const float *partial, int G,
                       int ncols, cudaStream_t st, float *dst3 = nullptr) {
-    column_add_k<<<ceil_div(ncols, 32), 256, 0, st>>>(dst, dst2, ncols_first, partial, G, ncols, dst3);
+    column_add_k<<<ceil_div(ncols, 32), 1024, 0, st>>>(dst, dst2, ncols_first, partial, G, ncols, dst3);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
