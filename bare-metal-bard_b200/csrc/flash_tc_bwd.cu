@@ -599,6 +599,8 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
                 const uint32_t s_addr = lane_addr + COL_S + (uint32_t)(buf * 128 + g * G + colhalf * 32);
                 float s[32];
                 tmem_ld32(s_addr, s);
+                // only the first block (the diagonal) and the last (the ragged end) have anything to mask
+                const bool masked = (i == 0) || ((ib0 + i + 1) * QB > T);
                 if (stats_in_smem) {
                     const float4 *lp = reinterpret_cast<const float4 *>(stat_l + i * QB + g * G + colhalf * 32);
 #pragma unroll
@@ -608,12 +610,16 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int c = c4 * 4 + e;
-                            float v = fast_exp2(fmaf(s[c], scale_log2e, -lv[e]));
-                            if (qc0 + c < kj || qc0 + c >= T) v = 0.0f;        // causal mask and the ragged end
-                            p[g][c] = v;
-                            s[c] = round_tf32_for_mma(v);
+                            p[g][c] = fast_exp2(fmaf(s[c], scale_log2e, -lv[e]));
                         }
                     }
+                    if (masked) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (qc0 + c < kj || qc0 + c >= T) p[g][c] = 0.0f;  // causal mask and the ragged end
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) s[c] = round_tf32_for_mma(p[g][c]);
                 } else {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
