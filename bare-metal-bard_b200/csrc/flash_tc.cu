@@ -6,7 +6,7 @@
 //
 // One CTA owns 256 consecutive queries of one (batch, head) as two tiles of
 // 128 and walks the keys up to the diagonal: shared-memory stages and S
-// products cover 128 keys, softmax steps 64.  352 threads:
+// products cover 128 keys, softmax steps 64.  384 threads:
 //   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: a thread reads 64 scores
 //                    of its row from TMEM (tcgen05.ld), masks the diagonal,
 //                    updates the running max and sum (the scale rides in the
@@ -21,11 +21,12 @@
 //                    the tensor pipe its 64 cycles, whereas a thread cannot
 //                    issue N = 64 instructions as fast as the pipe retires
 //                    them), as soon as the group has taken S_t(j-1) out of TMEM;
-//   warp 10          issuer of PV_t = P_t V (A operand read from tensor memory,
-//                    64 keys per step) as soon as P_t is written.
-// Two issuing threads keep the next block's scores from queueing behind a wait
-// for the other tile's P; the two tiles interleave, so one group's exponentials
-// overlap the other's matrix products.
+//   warps 10, 11     issuers of PV_t = P_t V for tile 0 / tile 1 (A operand read from
+//                    tensor memory, 64 keys per step) as soon as P_t is written.
+// Three issuing threads keep the next block's scores from queueing behind a wait
+// for the other tile's P and feed the N = 64 products to the pipe from two
+// schedulers; the two tiles interleave, so one group's exponentials overlap the
+// other's matrix products.
 // V is the B operand of P V with the head dimension contiguous, i.e. MN-major:
 // its TMA map uses the 128-byte swizzle with 32-byte atoms.  K and Q are
 // K-major.  Keys beyond the end of a sequence are never seen unmasked: a key
@@ -55,7 +56,7 @@ constexpr int OFF_K = OFF_Q + NQ * Q_TILE_BYTES;
 constexpr int OFF_V = OFF_K + K_STAGES * KV_TILE_BYTES;
 constexpr int OFF_BAR = OFF_V + V_STAGES * KV_TILE_BYTES;
 constexpr int FWD_SMEM = OFF_BAR + 256 + 1024;
-constexpr int FWD_THREADS = 352;
+constexpr int FWD_THREADS = 384;
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -112,7 +113,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
-        for (int s = 0; s < V_STAGES; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1); }
+        for (int s = 0; s < V_STAGES; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), NQ); }   // one release per P V issuer
         for (int t = 0; t < NQ; ++t) {
             mbar_init(bar(S_FULL + t), 1); mbar_init(bar(S_EMPTY + t), 4);
             mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_FULL + t), 1);
@@ -209,38 +210,38 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             }
             TR_FLUSH(9, 3);
         }
-    } else if (warp == 10) {
-        // ------------------------------------------------------- issuer of O += P V
+    } else if (warp == 10 || warp == 11) {
+        // ------------------------------------- issuers of O += P V, one per query tile
         if (lane == 0) {
+            const int t = warp - 10;
             const uint32_t idesc_pv = make_idesc(2, 0, 1, HS, QT);   // P (tensor memory) x V (MN-major)
 #ifdef BMB_FLASH_TRACE
-            // 12 wait V, 13 wait P_FULL, 14 issue PV
-            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0);
+            // tile 1's issuer: 12 wait V, 13 wait P_FULL, 14 issue PV
+            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && t == 1);
             long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long tlast = clock64();
 #endif
             bool ok = true;
             const int maxstep = max(nstep[0], nstep[1]);
+            const uint32_t pa = tmem_base + (uint32_t)(t * TILE_COLS + COL_P), d = tmem_base + (uint32_t)(t * TILE_COLS + COL_PV);
             for (int i = 0; ok && i < maxstep; ++i) {
                 const int j = i >> 1, st = j % V_STAGES;
                 if (!(i & 1) && !mbar_wait(bar(V_FULL + st), (uint32_t)((j / V_STAGES) & 1), giveup)) { ok = false; break; }
                 TRI(12);
-                // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
-                const uint32_t va = base + OFF_V + st * KV_TILE_BYTES + (uint32_t)((i & 1) * (KB * 128));
-                for (int t = 0; t < NQ; ++t) {
-                    if (i >= nstep[t]) continue;
+                if (i < nstep[t]) {
                     if (!mbar_wait(bar(P_FULL + t), (uint32_t)(i & 1), giveup)) { ok = false; break; }
                     fence_after();
                     TRI(13);
-                    const uint32_t pa = tmem_base + (uint32_t)(t * TILE_COLS + COL_P), d = tmem_base + (uint32_t)(t * TILE_COLS + COL_PV);
+                    // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
+                    const uint32_t va = base + OFF_V + st * KV_TILE_BYTES + (uint32_t)((i & 1) * (KB * 128));
 #pragma unroll
                     for (int ks = 0; ks < KB / 8; ++ks)
                         mma_tf32_ts(d, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, ks ? 1u : 0u);
                     commit(bar(PV_FULL + t));
                     TRI(14);
                 }
-                if (!ok) break;
-                if ((i & 1) || i + 1 == maxstep) commit(bar(V_EMPTY + st));     // every product that reads this V block has been issued
+                // this tile's products that read the V block have been issued (none, past the tile's diagonal)
+                if ((i & 1) || i + 1 == maxstep) commit(bar(V_EMPTY + st));
             }
             TR_FLUSH(12, 3);
         }
