@@ -64,15 +64,17 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 50 ms while alive (the two timed regions of
-    the default run last about 0.2 s each)."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clocks and throttle reasons, sampled every 50 ms while alive.  nvidia-smi takes a few
+    tenths of a second to start, about as long as the timed regions of the default run, so it is started
+    before the warm-up steps and only the samples stamped inside [mark(), stop()] are used."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.path = "/tmp/bmb_clocks_%d_%d.csv" % (os.getpid(), gpu_index)
         self.proc = None
+        self.t_mark = None
         try:
             self.f = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q,
@@ -81,10 +83,23 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def mark(self):
+        """The timed region starts now."""
+        self.t_mark = time.time()
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def stop(self):
         out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
         if self.proc is None:
             return out
+        t_stop = time.time()
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -96,6 +111,9 @@ class ClockSampler:
         for line in open(self.path):
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 9:
+                continue
+            ts = self._stamp(parts[0])
+            if ts is not None and self.t_mark is not None and not (self.t_mark - 0.05 <= ts <= t_stop + 0.05):
                 continue
             try:
                 sm.append(float(parts[1]))
@@ -241,13 +259,15 @@ def run_bmb(args):
             return tr.loss()
         return None
 
+    sampler = ClockSampler(local) if rank == 0 else None
     # warm-up (with IO, so every path has run), then leave a batch resident
     for i in range(args.warmup):
         one_step(i, True)
     tr.upload(*pinned[args.warmup])
     tr.sync()
     dist_mod.barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.mark()
 
     # ---- timed region 1: kernel throughput, inputs resident (forward + backward replayed as a CUDA graph)
     launches_before = lib.bmb_launch_count()
