@@ -175,7 +175,8 @@ def test_unrounded_operands_show_why_rounding_is_needed(bmb, orc, cuda, capsys):
 
 
 ATT_SHAPES = [(2, 64, 128, 2), (1, 256, 128, 2), (2, 300, 192, 3), (3, 100, 384, 6), (2, 33, 384, 6), (1, 1, 384, 6),
-              (2, 129, 128, 2), (1, 1024, 128, 2), (2, 513, 64, 1)]
+              (2, 129, 128, 2), (1, 1024, 128, 2), (2, 513, 64, 1),
+              (1, 4224, 64, 1)]       # longer than the 4096 queries whose lse / D the dK/dV kernel parks in shared memory
 
 
 @pytest.mark.parametrize("B,T,C,NH", ATT_SHAPES)
