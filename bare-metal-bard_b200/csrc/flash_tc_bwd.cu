@@ -1,17 +1,19 @@
-// Fused causal attention backward on the tensor cores (head size 64), two
-// kernels as in the reference (src/flash.cu:434-470): dQ reduces over keys,
-// dK and dV reduce over queries, so each keeps its accumulators on chip -- here
-// in tensor memory -- and writes its part of dqkv with plain stores.
+// Fused causal attention backward on the tensor cores (head size 64), split
+// as in the reference (src/flash.cu:434-470): dQ reduces over keys, dK and dV
+// reduce over queries, so each keeps its accumulators on chip -- here in tensor
+// memory -- and writes its part of dqkv with plain stores.  The reference
+// launches the two as separate kernels; here they are two kinds of CTA in one
+// grid (flash_bwd_tc_k at the end of this file).
 // P is rebuilt from the saved lse, P = exp(S - lse), and
 // dS = P * (dP - D) with D = rowsum(dO * O)   (src/flash.cu:447-453).
 //
-// dQ kernel: a CTA owns 128 queries and walks key blocks of 64 up to the
-//   diagonal.  Per block the issuer forms S = Q K^T and dP = dO V^T in TMEM
-//   (double buffered, so block j+1 is being multiplied while block j is in the
-//   registers); 256 threads -- a row of 128 per 32-column half -- turn them
-//   into dS, rounded to TF32 and written back over dP in tensor memory, which
-//   dQ += dS K (accumulated in TMEM over the whole walk) reads as its A operand.
-// dK/dV kernel: a CTA owns 128 keys and walks query blocks of 64 from the
+// dQ CTAs: a CTA owns 128 queries and walks key blocks of 128 up to the
+//   diagonal.  Per block S = Q K^T (double buffered) and dP = dO V^T land in
+//   TMEM; 256 threads -- a row of 128 per 32-column half of each 64-key
+//   granule -- turn them into dS, rounded to TF32 and written back over dP in
+//   tensor memory, which dQ += dS K (accumulated in TMEM over the whole walk)
+//   reads as its A operand.
+// dK/dV CTAs: a CTA owns 128 keys and walks query blocks of 128 from the
 //   diagonal to the end, with everything transposed so that the owned keys are
 //   again the rows: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T written back in
 //   place, then dV += P^T dO and dK += dS^T Q accumulate in TMEM.  lse and D
@@ -82,11 +84,10 @@ constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DQ = 384;
 // in 2-deep rings of whole blocks, the MN-major copy of K (operand of dQ) in two granule slots, each
 // refilled as soon as its own consumer is done, by two loading threads so that neither ring waits
 // for the other.
-__global__ void __launch_bounds__(dq::THREADS, 1)
-flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_constant__ CUtensorMap mapQKV_n,
-                  const __grid_constant__ CUtensorMap mapDO_k, float *__restrict__ dqkv,
+__device__ __forceinline__ void
+flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, const CUtensorMap &mapDO_k, float *__restrict__ dqkv,
                   const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
-                  int round_out, int *__restrict__ status) {
+                  int round_out, int *__restrict__ status, int ypos, int ny) {
     using namespace dq;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -100,7 +101,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bh = blockIdx.x, b = bh / NH, h = bh % NH;
     const int C = NH * HS;
-    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * QT;   // CTAs are dispatched x first: every head's longest tile, then the next
+    const int q0 = (ny - 1 - ypos) * QT;                  // CTAs are dispatched x first: every head's longest tile, then the next
     const int nb = min(T - 1, q0 + QT - 1) / KB + 1;       // key blocks up to the diagonal
     const int row0 = b * T;
 
@@ -216,7 +217,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
             };
 #ifdef BMB_FLASH_TRACE
             // phases of this thread in CTA (0, 0): 16 prologue, 19 wait dS and K granule, 20 issue dQ, 21 wait V block, 22 issue dP
-            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0);
+            const bool tr = (blockIdx.x == 0 && ypos == 0);
             long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long tlast = clock64();
 #endif
@@ -271,7 +272,7 @@ flash_bwd_dq_tc_k(const __grid_constant__ CUtensorMap mapQKV_k, const __grid_con
         bool ok = true;
 #ifdef BMB_FLASH_TRACE
         // phases of one thread of CTA (0, 0): 0 wait S, 1 load S + rebuild P, 2 wait dP, 3 dS of both granules
-        const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && lane == 0);
+        const bool tr = (blockIdx.x == 0 && ypos == 0 && warp == 0 && lane == 0);
         long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tlast = clock64();
 #endif
@@ -386,11 +387,10 @@ constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DV = 384, COL_DK = 448;
 // query block (operands of the first two products) have one buffer each, refilled while the block
 // is worked on; the MN-major copies (operands of the last two) sit in two granule slots, loaded by
 // a thread of their own.
-__global__ void __launch_bounds__(dkv::THREADS, 1)
-flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
-                   const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
+__device__ __forceinline__ void
+flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64, const CUtensorMap &mapDO_k64, const CUtensorMap &mapDO_n64,
                    float *__restrict__ dqkv, const float *__restrict__ lse, const float *__restrict__ dsum,
-                   int T, int NH, float scale, int round_out, int *__restrict__ status) {
+                   int T, int NH, float scale, int round_out, int *__restrict__ status, int ypos) {
     using namespace dkv;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -404,7 +404,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bh = blockIdx.x, b = bh / NH, h = bh % NH;
     const int C = NH * HS;
-    const int j0 = (int)blockIdx.y * KT;                   // first key of this CTA (earliest keys walk longest)
+    const int j0 = ypos * KT;                              // first key of this CTA (earliest keys walk longest)
     const int ib0 = j0 / QB;                               // first query block that can see these keys
     const int nb = (T + QB - 1) / QB - ib0;                // query blocks to walk
     const int row0 = b * T;
@@ -518,7 +518,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
             };
 #ifdef BMB_FLASH_TRACE
             // phases of warp 9 of CTA (0, 0): 24 prologue, 25 wait Q block, 26 issue S^T, 27 wait P^T / dS^T and granules, 28 issue dV
-            const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && first);
+            const bool tr = (blockIdx.x == 0 && ypos == 0 && first);
             long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long tlast = clock64();
 #endif
@@ -582,7 +582,7 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
         bool ok = true;
 #ifdef BMB_FLASH_TRACE
         // phases of one thread of CTA (0, 0): 9 wait S^T, 10 P^T of both granules, 11 wait dP^T, 12 dS^T of both granules
-        const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && lane == 0);
+        const bool tr = (blockIdx.x == 0 && ypos == 0 && warp == 0 && lane == 0);
         long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tlast = clock64();
 #endif
@@ -708,6 +708,21 @@ flash_bwd_dkv_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_
     }
 }
 
+// Both backward kernels as one grid: CTAs with even blockIdx.y own 128 keys (dK/dV), those with odd
+// blockIdx.y 128 queries (dQ), each family ordered from its longest walk to its shortest.  As two
+// launches each would end in a partly filled wave of its own (768 CTAs on 148 SMs at B8 H12 T1024);
+// together they end in one, and the short CTAs of either fill the gaps left by the long ones of both.
+static_assert(dq::THREADS == dkv::THREADS && dq::SMEM == dkv::SMEM, "the two bodies share one launch configuration");
+__global__ void __launch_bounds__(dkv::THREADS, 1)
+flash_bwd_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
+               const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
+               float *__restrict__ dqkv, const float *__restrict__ lse, const float *__restrict__ dsum,
+               int T, int NH, float scale, int round_out, int *__restrict__ status) {
+    const int ypos = (int)blockIdx.y >> 1, ny = (int)gridDim.y >> 1;
+    if (blockIdx.y & 1) flash_bwd_dq_body(mapQKV_k64, mapQKV_n64, mapDO_k64, dqkv, lse, dsum, T, NH, scale, round_out, status, ypos, ny);
+    else flash_bwd_dkv_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapDO_n64, dqkv, lse, dsum, T, NH, scale, round_out, status, ypos);
+}
+
 __global__ void round_copy2_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
          i += (long long)gridDim.x * blockDim.x) {
@@ -755,18 +770,17 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
         std::lock_guard<std::mutex> lk(g_mu);
         const int d = current_device();
         if (d >= 0 && d < 64 && !g_attr[d]) {
-            BMB_CUDA(cudaFuncSetAttribute(flash_bwd_dq_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::SMEM));
-            BMB_CUDA(cudaFuncSetAttribute(flash_bwd_dkv_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM));
+            BMB_CUDA(cudaFuncSetAttribute(flash_bwd_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM));
             g_attr[d] = true;
         }
     }
     const float scale = 1.0f / sqrtf((float)HS);
     // x = (batch, head), y = position: the dispatch order runs through all heads at the position with
     // the most work first, so the long CTAs start early and the short ones fill the tail.
-    dim3 gkv(B * NH, (T + dkv::KT - 1) / dkv::KT), gq(B * NH, (T + dq::QT - 1) / dq::QT);
-    flash_bwd_dkv_tc_k<<<gkv, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
-    flash_bwd_dq_tc_k<<<gq, dq::THREADS, dq::SMEM, st>>>(qk64, qn64, gk64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
-    count_launch(2);
+    static_assert(dkv::KT == dq::QT, "one grid row pair per 128 positions");
+    dim3 grid(B * NH, 2 * ((T + dkv::KT - 1) / dkv::KT));
+    flash_bwd_tc_k<<<grid, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
+    count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
 }
