@@ -17,8 +17,10 @@ LIB_PATH = os.path.join(HERE, "libbmb.so")
 
 MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2
 GEMM_A_ROUNDED, GEMM_B_ROUNDED, GEMM_C_ROUNDED, GEMM_NO_SPLIT = 1, 2, 4, 8
+GEMM_TILE_M128, GEMM_TILE_M256 = 16, 32
 FLASH_OPERANDS_ROUNDED = 1
 E_UNSUPPORTED = 3
+E_TIMEOUT = 4
 E_LIMIT = 6
 
 _f, _i, _p, _z, _ll, _d, _u = C.c_float, C.c_int, C.c_void_p, C.c_size_t, C.c_longlong, C.c_double, C.c_uint
@@ -44,6 +46,9 @@ SIGNATURES = {
     "bmb_version": (C.c_char_p, []),
     "bmb_launch_count": (_ll, []),
     "bmb_gemm_schedule_check": (_i, [_i, _i, _i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "bmb_kernel_status": (_i, [C.POINTER(_i)]),
+    "bmb_kernel_status_clear": (_i, []),
+    "bmb_selftest_wait_expiry": (_i, [_ll, C.POINTER(_ll)]),
     "bmb_set_stream": (_i, [_p]),
     "bmb_get_stream": (_p, []),
     "bmb_set_math_mode": (_i, [_i]),

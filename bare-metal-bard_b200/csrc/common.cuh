@@ -52,6 +52,9 @@ void set_emit_rounded(bool on);
 // Returns nullptr (and records an error) on failure.
 enum ScratchSlot { SCR_REDUCE = 0, SCR_GEMM_A = 1, SCR_GEMM_B = 2, SCR_MISC = 3, SCR_SLOTS = 4 };
 void *device_scratch(ScratchSlot slot, size_t bytes);
+// Counts the times any scratch block of the current device was (re)allocated.  A caller that keeps
+// scratch addresses beyond one call (the trainer's captured graph) compares it before reusing them.
+unsigned long long scratch_generation();
 int current_device();
 int sm_count();
 

@@ -95,9 +95,9 @@ struct bmb_ddp {
     int dev[MAXR];
     bool peer[MAXR][MAXR];
     bool any_peer = false, all_peer = false;
-    cudaStream_t stream[MAXR];
-    cudaEvent_t ready[MAXR], reduced[MAXR], done[MAXR];
-    cudaEvent_t t0, t1, t2;
+    cudaStream_t stream[MAXR] = {};
+    cudaEvent_t ready[MAXR] = {}, reduced[MAXR] = {}, done[MAXR] = {};
+    cudaEvent_t t0 = nullptr, t1 = nullptr, t2 = nullptr;
     float *recv[MAXR];
     size_t recv_cap = 0;
     float *host_stage = nullptr;
@@ -134,6 +134,8 @@ static int ddp_probe_pair(bmb_ddp *d, int i, int j) {
     return BMB_OK;
 }
 
+static int ddp_build(bmb_ddp *d);
+
 extern "C" {
 
 int bmb_ddp_create(bmb_ddp **out, int n, const int *devices) {
@@ -147,13 +149,29 @@ int bmb_ddp_create(bmb_ddp **out, int n, const int *devices) {
     bmb_ddp *d = new bmb_ddp();
     d->n = n;
     for (int r = 0; r < n; ++r) { d->dev[r] = devices[r]; d->recv[r] = nullptr; }
+    const int rc = ddp_build(d);
+    cudaSetDevice(prev);
+    if (rc != BMB_OK) {
+        bmb_ddp_destroy(d);               // streams and events made so far go with it
+        return rc;
+    }
+    *out = d;
+    return BMB_OK;
+}
+
+}  // extern "C"
+
+static int ddp_build(bmb_ddp *d) {
+    const int n = d->n;
     const bool no_p2p = getenv("DDP_NO_P2P") != nullptr;
     for (int i = 0; i < n; ++i)
         for (int j = 0; j < n; ++j) {
             d->peer[i][j] = false;
             if (i == j) continue;
-            if (d->dev[i] == d->dev[j]) { d->peer[i][j] = true; continue; }
+            // DDP_NO_P2P stages EVERY transfer through host memory, ranks sharing a device included
+            // (src/ddp.cu:116-120 clears the whole matrix), so the staged route can be exercised anywhere.
             if (no_p2p) continue;
+            if (d->dev[i] == d->dev[j]) { d->peer[i][j] = true; continue; }
             int can = 0;
             BMB_CUDA(cudaDeviceCanAccessPeer(&can, d->dev[i], d->dev[j]));
             if (can) {
@@ -169,7 +187,7 @@ int bmb_ddp_create(bmb_ddp **out, int n, const int *devices) {
         for (int j = 0; j < n; ++j)
             if (d->peer[i][j] && d->dev[i] != d->dev[j]) {
                 const int s = ddp_probe_pair(d, i, j);
-                if (s != BMB_OK) { delete d; return s; }
+                if (s != BMB_OK) return s;
             }
     d->any_peer = false; d->all_peer = true;
     for (int i = 0; i < n; ++i)
@@ -186,10 +204,10 @@ int bmb_ddp_create(bmb_ddp **out, int n, const int *devices) {
     BMB_CUDA(cudaEventCreate(&d->t0));
     BMB_CUDA(cudaEventCreate(&d->t1));
     BMB_CUDA(cudaEventCreate(&d->t2));
-    BMB_CUDA(cudaSetDevice(prev));
-    *out = d;
     return BMB_OK;
 }
+
+extern "C" {
 
 int bmb_ddp_destroy(bmb_ddp *d) {
     if (!d) return BMB_OK;
@@ -198,13 +216,15 @@ int bmb_ddp_destroy(bmb_ddp *d) {
     for (int r = 0; r < d->n; ++r) {
         cudaSetDevice(d->dev[r]);
         if (d->recv[r]) cudaFree(d->recv[r]);
-        cudaStreamDestroy(d->stream[r]);
-        cudaEventDestroy(d->ready[r]);
-        cudaEventDestroy(d->reduced[r]);
-        cudaEventDestroy(d->done[r]);
+        if (d->stream[r]) cudaStreamDestroy(d->stream[r]);
+        if (d->ready[r]) cudaEventDestroy(d->ready[r]);
+        if (d->reduced[r]) cudaEventDestroy(d->reduced[r]);
+        if (d->done[r]) cudaEventDestroy(d->done[r]);
     }
     cudaSetDevice(d->dev[0]);
-    cudaEventDestroy(d->t0); cudaEventDestroy(d->t1); cudaEventDestroy(d->t2);
+    if (d->t0) cudaEventDestroy(d->t0);
+    if (d->t1) cudaEventDestroy(d->t1);
+    if (d->t2) cudaEventDestroy(d->t2);
     if (d->host_stage) cudaFreeHost(d->host_stage);
     cudaSetDevice(prev);
     delete d;

@@ -640,7 +640,9 @@ int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int
     p->bn = BN_WIDE;
     p->mh = 1;
     p->dp_tiles = 0;
-    choose_schedule(M, N, p->kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, force_mh, batch == 1 && !bf16, &p->bn, &p->mh,
+    // A call may force the height itself (BMB_GEMM_TILE_M128 / _M256), which wins over the environment.
+    const int call_mh = (flags & BMB_GEMM_TILE_M256) ? 2 : ((flags & BMB_GEMM_TILE_M128) ? 1 : force_mh);
+    choose_schedule(M, N, p->kblocks, ctas, allow_split, (force_bn && N >= force_bn) ? force_bn : 0, call_mh, batch == 1 && !bf16, &p->bn, &p->mh,
                     &p->dp_tiles);
     p->tiles_m = (M + p->mh * BM - 1) / (p->mh * BM);
     p->tiles_n = (N + p->bn - 1) / p->bn;

@@ -54,6 +54,12 @@ int sm_count() {
 struct Scratch { void *p = nullptr; size_t cap = 0; };
 static Scratch g_scratch[64][SCR_SLOTS];
 static std::mutex g_scratch_mu;
+static std::atomic<unsigned long long> g_scratch_gen[64];
+
+unsigned long long scratch_generation() {
+    const int d = current_device();
+    return (d < 0 || d >= 64) ? 0ULL : g_scratch_gen[d].load(std::memory_order_relaxed);
+}
 
 void *device_scratch(ScratchSlot slot, size_t bytes) {
     const int d = current_device();
@@ -61,8 +67,10 @@ void *device_scratch(ScratchSlot slot, size_t bytes) {
     std::lock_guard<std::mutex> lk(g_scratch_mu);
     Scratch &s = g_scratch[d][slot];
     if (s.cap >= bytes && s.p) return s.p;
-    // Growing: earlier work on this device may still read the old block.
+    // Growing: earlier work on this device may still read the old block.  Anything that has
+    // remembered the old address (a captured CUDA graph) learns of the move from the generation count.
     if (s.p) { cudaDeviceSynchronize(); cudaFree(s.p); s.p = nullptr; s.cap = 0; }
+    g_scratch_gen[d].fetch_add(1, std::memory_order_relaxed);
     size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, want);

@@ -80,3 +80,73 @@ int status_word(int **dev_ptr, volatile int **host_ptr) {
 
 }  // namespace tc
 }  // namespace bmb
+
+// ---- the status word through the C ABI, and a self-test of the give-up path --------------------
+namespace bmb {
+namespace {
+// One CTA waits, with the caller's cycle limit, on an mbarrier that nothing ever arrives on: the
+// same bounded wait the GEMM and attention kernels use.  The wait runs out, the role raises the
+// CTA's give-up flag and the kernel reports through the status word and returns by itself -- no
+// trap, no fault, nothing left in flight (it issues no copy and holds no tensor memory).
+__global__ void wait_expiry_selftest_k(long long limit_cycles, int *status, long long *waited_out) {
+    __shared__ uint64_t bar;
+    __shared__ int giveup;
+    if (threadIdx.x == 0) {
+        giveup = 0;
+        tc::mbar_init(tc::smem_u32(&bar), 1);
+        tc::mbar_init_fence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        const bool ok = tc::mbar_wait_limit(tc::smem_u32(&bar), 0, &giveup, limit_cycles);
+        if (waited_out) *waited_out = clock64() - t0;
+        if (!ok) {
+            *reinterpret_cast<volatile int *>(status) = 9;
+            __threadfence_system();
+        }
+    }
+}
+}  // namespace
+}  // namespace bmb
+
+extern "C" {
+
+int bmb_kernel_status(int *status_out) {
+    int *dev = nullptr;
+    volatile int *host = nullptr;
+    BMB_TRY(bmb::tc::status_word(&dev, &host));
+    if (status_out) *status_out = *host;
+    return BMB_OK;
+}
+
+int bmb_kernel_status_clear(void) {
+    int *dev = nullptr;
+    volatile int *host = nullptr;
+    BMB_TRY(bmb::tc::status_word(&dev, &host));
+    BMB_CUDA(cudaDeviceSynchronize());        // no kernel that could still raise it is running
+    *host = 0;
+    return BMB_OK;
+}
+
+int bmb_selftest_wait_expiry(long long limit_cycles, long long *host_waited_cycles) {
+    if (limit_cycles < 1 || limit_cycles > 100000000LL)
+        return bmb::fail(BMB_E_ARG, "selftest_wait_expiry: limit must be 1..1e8 cycles");
+    int *dev = nullptr;
+    volatile int *host = nullptr;
+    BMB_TRY(bmb::tc::status_word(&dev, &host));
+    long long *d_waited = nullptr;
+    BMB_CUDA(cudaMalloc(&d_waited, sizeof(long long)));
+    bmb::wait_expiry_selftest_k<<<1, 32, 0, bmb::cur_stream()>>>(limit_cycles, dev, d_waited);
+    bmb::count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(bmb::cur_stream());
+    long long waited = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&waited, d_waited, sizeof(long long), cudaMemcpyDeviceToHost);
+    cudaFree(d_waited);
+    if (e != cudaSuccess) return bmb::fail(BMB_E_CUDA, "selftest_wait_expiry -> %s", cudaGetErrorString(e));
+    if (host_waited_cycles) *host_waited_cycles = waited;
+    return BMB_OK;
+}
+
+}  // extern "C"

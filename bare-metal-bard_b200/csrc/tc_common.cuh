@@ -33,7 +33,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false when the limit ran out or another role of the CTA gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *giveup) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int *giveup, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -41,8 +41,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*giveup) return false;
-        if (clock64() - t0 > WAIT_CYCLES) { *giveup = 1; return false; }
+        if (clock64() - t0 > limit) { *giveup = 1; return false; }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *giveup) {
+    return mbar_wait_limit(bar, parity, giveup, WAIT_CYCLES);
 }
 // Wait (bounded) without raising the flag: used while draining copies in flight.
 __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {

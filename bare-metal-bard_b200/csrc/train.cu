@@ -64,6 +64,7 @@ struct bmb_trainer {
     int eager_passes = 0;                 // the first pass runs eagerly (it sizes the library's scratch)
     cudaGraphExec_t graph_exec = nullptr;
     long long graph_launches = 0;
+    unsigned long long graph_scratch_gen = 0;   // the device's scratch generation the graph was captured under
     // profiling
     bool prof = false;
     std::vector<cudaEvent_t> ev;
@@ -288,6 +289,14 @@ int forward_backward_step(bmb_trainer *t) {
         BMB_TRY(forward(t));
         return backward(t);
     }
+    // The captured launches carry the addresses of the library's per-device scratch.  If another
+    // caller on this device has made that scratch grow since (the old block was freed), the graph
+    // is dropped and built again: one eager pass to size the scratch, then a new capture.
+    if (t->graph_exec && t->graph_scratch_gen != scratch_generation()) {
+        cudaGraphExecDestroy(t->graph_exec);
+        t->graph_exec = nullptr;
+        t->eager_passes = 0;
+    }
     if (!t->graph_exec) {
         if (t->eager_passes < 1) {
             t->eager_passes++;
@@ -295,6 +304,7 @@ int forward_backward_step(bmb_trainer *t) {
             return backward(t);
         }
         const long long before = launches_total();
+        const unsigned long long gen_before = scratch_generation();
         cudaGraph_t graph = nullptr;
         if (cudaStreamBeginCapture(t->st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
             cudaGetLastError();
@@ -305,7 +315,7 @@ int forward_backward_step(bmb_trainer *t) {
         int rc = forward(t);
         if (rc == BMB_OK) rc = backward(t);
         const cudaError_t e = cudaStreamEndCapture(t->st, &graph);
-        if (rc != BMB_OK || e != cudaSuccess || !graph ||
+        if (rc != BMB_OK || e != cudaSuccess || !graph || gen_before != scratch_generation() ||
             cudaGraphInstantiate(&t->graph_exec, graph, 0) != cudaSuccess) {
             // nothing ran during the capture: fall back to eager launches for good and run this pass now
             cudaGetLastError();
@@ -316,6 +326,7 @@ int forward_backward_step(bmb_trainer *t) {
             return backward(t);
         }
         cudaGraphDestroy(graph);
+        t->graph_scratch_gen = gen_before;
         t->graph_launches = launches_total() - before;
         count_launch((int)-t->graph_launches);        // counted again at every replay, this first one included
     }
@@ -340,6 +351,8 @@ int refresh_shadow(bmb_trainer *t) {
     return bmb_round_tf32(t->shadow, t->params, t->num_params, t->st);
 }
 
+int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed);
+
 }  // namespace
 
 extern "C" {
@@ -357,6 +370,20 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
         return fail(BMB_E_UNSUPPORTED, "trainer_create: fused attention needs head size 32, 64 or 128 (got %d)", hs);
 
     bmb_trainer *t = new bmb_trainer();
+    const int rc = trainer_build(t, c, seed);
+    if (rc != BMB_OK) {
+        // a failed allocation part-way (a busy device) must not strand the gigabytes already taken
+        bmb_trainer_destroy(t);
+        return rc;
+    }
+    *out = t;
+    return BMB_OK;
+}
+
+}  // extern "C"
+
+namespace {
+int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     t->c = c;
     if (const char *g = getenv("BMB_TRAINER_GRAPH")) t->use_graph = atoi(g) != 0;
     BMB_CUDA(cudaGetDevice(&t->dev));
@@ -451,14 +478,16 @@ int bmb_trainer_create(bmb_trainer **out, const bmb_train_config *cfg, unsigned 
         BMB_TRY(refresh_shadow(t));
         BMB_CUDA(cudaStreamSynchronize(t->st));
     }
-    *out = t;
     return BMB_OK;
 }
+}  // namespace
+
+extern "C" {
 
 int bmb_trainer_destroy(bmb_trainer *t) {
     if (!t) return BMB_OK;
     cudaSetDevice(t->dev);
-    cudaStreamSynchronize(t->st);
+    if (t->st) cudaStreamSynchronize(t->st);
     for (cudaEvent_t e : t->ev) cudaEventDestroy(e);
     if (t->graph_exec) cudaGraphExecDestroy(t->graph_exec);
     cudaFree(t->params); cudaFree(t->grads); cudaFree(t->m); cudaFree(t->v);
@@ -466,7 +495,7 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
     cudaFree(t->d_loss); cudaFree(t->d_sumsq); cudaFree(t->d_token);
     dp_fused_destroy(t->dp);
-    cudaStreamDestroy(t->st);
+    if (t->st) cudaStreamDestroy(t->st);
     delete t;
     return BMB_OK;
 }
@@ -531,8 +560,9 @@ int bmb_trainer_upload(bmb_trainer *t, const int *host_tokens, const int *host_t
     if (!t || !host_tokens || !host_targets) return fail(BMB_E_ARG, "trainer_upload: null argument");
     Scope sc(t);
     const size_t n = (size_t)t->c.B * t->c.T * sizeof(int);
-    BMB_CUDA(cudaMemcpyAsync(t->d_tokens, host_tokens, n, cudaMemcpyHostToDevice, t->st));
-    BMB_CUDA(cudaMemcpyAsync(t->d_targets, host_targets, n, cudaMemcpyHostToDevice, t->st));
+    // cudaMemcpyDefault: the source may also be a batch already staged in device memory
+    BMB_CUDA(cudaMemcpyAsync(t->d_tokens, host_tokens, n, cudaMemcpyDefault, t->st));
+    BMB_CUDA(cudaMemcpyAsync(t->d_targets, host_targets, n, cudaMemcpyDefault, t->st));
     return BMB_OK;
 }
 

@@ -42,6 +42,21 @@ int bmb_gemm_schedule_check(int math, int flags, int batch, int M, int N, int K,
  * graph included).  No counterpart in the reference; bench.py reports it. */
 long long bmb_launch_count(void);
 
+/* ---- device-side waits that ran out ------------------------------------ */
+/* No counterparts in the reference.  Every wait inside the tensor-core kernels (on a copy, on the
+ * tensor core, on another role of the CTA) is bounded; when one runs out the kernel drains what it
+ * has in flight, returns, and leaves a nonzero word per device that makes every later tensor-core
+ * call on that device return BMB_E_TIMEOUT.  bmb_kernel_status reads the word of the current device
+ * (0 = nothing happened).  bmb_kernel_status_clear waits for the device to go idle and resets it,
+ * so that a process can carry on after it has dealt with the failed step.
+ * bmb_selftest_wait_expiry exercises that path without any fault: one CTA waits at most
+ * limit_cycles (1..1e8 SM clocks) on a barrier that nothing arrives on, gives up, raises the word
+ * and returns; the call blocks until then and reports the cycles the wait took.  Afterwards the
+ * status is set, exactly as after a real expiry, until bmb_kernel_status_clear. */
+int bmb_kernel_status(int *status_out);
+int bmb_kernel_status_clear(void);
+int bmb_selftest_wait_expiry(long long limit_cycles, long long *host_waited_cycles);
+
 /* ---- per-thread launch context ---------------------------------------- */
 /* Stream used by every entry point without a `stream` parameter.  Thread
  * local: rank threads of one process do not disturb one another. */
@@ -92,6 +107,8 @@ int bmb_gemm(int transA, int transB, int M, int N, int K, float alpha,
 #define BMB_GEMM_B_ROUNDED 2 /* B already holds TF32-representable values */
 #define BMB_GEMM_C_ROUNDED 4 /* store C rounded to TF32 (it feeds another tensor-core kernel) */
 #define BMB_GEMM_NO_SPLIT 8  /* never split K across CTAs (keeps the summation order fixed) */
+#define BMB_GEMM_TILE_M128 16 /* TF32 tensor-core path: 128-row tiles whatever the cost model says */
+#define BMB_GEMM_TILE_M256 32 /* TF32 tensor-core path: 256-row tiles where the shape allows (M >= 256, N >= 256) */
 int bmb_gemm_ex(int math, int flags, int transA, int transB, int M, int N,
                 int K, float alpha, const float *A, const float *B, float beta,
                 float *C, void *stream);
@@ -301,7 +318,8 @@ size_t bmb_trainer_num_params(const bmb_trainer *t);
 int bmb_trainer_get_params(bmb_trainer *t, float *host_out);
 int bmb_trainer_set_params(bmb_trainer *t, const float *host_in);
 int bmb_trainer_get_grads(bmb_trainer *t, float *host_out);
-/* Upload host tokens/targets (B*T ints each, pinned or pageable). Async. */
+/* Make tokens/targets (B*T ints each) the resident batch: an asynchronous copy on the trainer's
+ * stream from host memory (pinned or pageable) or from device memory where a batch was staged. */
 int bmb_trainer_upload(bmb_trainer *t, const int *host_tokens,
                        const int *host_targets);
 /* One optimiser step on the resident batch: forward, backward, gradient

@@ -1,0 +1,237 @@
+"""GPU parity at the configurations the benchmark numbers are quoted on, through the C ABI,
+against the reference's own kernels (oracle/_ref/libbmbref.so) on the same seeded inputs:
+
+  * the GPT-2-small-shaped training step (12 layers, d_model 768, 12 heads, context 1024,
+    vocab 50304, batch 8): 20 optimiser steps in fp32 and in the fused TF32 mode against
+    the reference's gpt_forward / gpt_backward / adamw_update (src/train_gpt.cu:442-451),
+    and the first step's gradient (tools/test_grad.cu:58-75);
+  * fused causal attention forward and backward on the tensor cores at B=8, H=12, T=1024,
+    head size 64 against the reference's fp32 flash kernels (tools/test_flash.cu:142-346);
+  * the tensor-core GEMM with both tile heights forced on the shapes the training step spends
+    its time in, against a float64 product on the device;
+  * the attention-shaped batched GEMM, batch 96, against the reference's batched_gemm.
+
+The CPU oracle cannot finish these sizes in seconds, which is why the checker here is the
+reference compiled for the same GPU.
+"""
+import numpy as np
+import pytest
+
+from helpers import _np, normwise
+
+pytestmark = pytest.mark.gpu
+
+GPT124M = dict(max_seq_len=1024, vocab_size=50304, padded_vocab=50304, n_layer=12, n_head=12, n_embd=768, B=8, T=1024)
+HP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, grad_clip=1.0)
+STEPS = 20
+
+
+def batches():
+    rng = np.random.default_rng(4242)
+    c = GPT124M
+    toks = rng.integers(0, c["vocab_size"], (STEPS, c["B"], c["T"]), dtype=np.int32)
+    tgts = rng.integers(0, c["vocab_size"], (STEPS, c["B"], c["T"]), dtype=np.int32)
+    return toks, tgts
+
+
+@pytest.fixture(scope="module")
+def reference_run(ref, cuda):
+    """The reference trainer on the 124M configuration: initial parameters, the gradient of the
+    first batch, and the loss of each of 20 optimiser steps."""
+    c = GPT124M
+    h = ref.ref_trainer_create(c["max_seq_len"], c["vocab_size"], c["padded_vocab"], c["n_layer"], c["n_head"],
+                               c["n_embd"], c["B"], c["T"], 1, 1337, 1, HP["beta1"], HP["beta2"], HP["eps"],
+                               HP["weight_decay"], HP["grad_clip"])
+    n = ref.ref_trainer_num_params(h)
+    params0, grads0 = np.empty(n, np.float32), np.empty(n, np.float32)
+    ref.ref_trainer_get_params(h, _np(params0))
+    toks, tgts = batches()
+    ref.ref_trainer_forward_backward(h, _np(toks[0]), _np(tgts[0]))
+    ref.ref_trainer_get_grads(h, _np(grads0))
+    losses = [ref.ref_trainer_step(h, _np(toks[s]), _np(tgts[s]), HP["lr"], s + 1) for s in range(STEPS)]
+    ref.ref_trainer_destroy(h)
+    cuda.cuda.set_device(0)
+    cuda.cuda.empty_cache()
+    return dict(n=n, params0=params0, grads0=grads0, losses=np.array(losses, np.float64))
+
+
+# (mode, fused, per-step loss bar, normwise bar on the first gradient).  The gradient bars: fp32 differs
+# from the reference by summation order only; TF32 rounds every GEMM and attention operand to 10 mantissa
+# bits (measured on this configuration: see the printed value).
+MODES = [("fp32", 0, 2e-3, 1e-4), ("tf32", 1, 2e-2, 2e-2)]
+
+
+@pytest.mark.parametrize("mode,fused,loss_bar,grad_bar", MODES)
+def test_gpt124m_20_steps_vs_reference_trainer(bmb, cuda, reference_run, capsys, mode, fused, loss_bar, grad_bar):
+    math = bmb.MATH_FP32 if mode == "fp32" else bmb.MATH_TF32
+    tr = bmb.Trainer(seed=1337, use_flash=1, math=math, fused=fused, beta1=HP["beta1"], beta2=HP["beta2"],
+                     eps=HP["eps"], weight_decay=HP["weight_decay"], grad_clip=HP["grad_clip"], **GPT124M)
+    n = tr.num_params
+    assert n == reference_run["n"] == 124475904
+    p = np.empty(n, np.float32)
+    tr.get_params(p)
+    assert np.array_equal(p, reference_run["params0"])        # identical initialisation, bit for bit
+    toks, tgts = batches()
+    tr.upload(toks[0], tgts[0])
+    tr.forward_backward()
+    g = np.empty(n, np.float32)
+    tr.get_grads(g)
+    want = reference_run["grads0"]
+    e_max = normwise(g, want)
+    e_l2 = float(np.linalg.norm(g.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64)))
+    losses = []
+    for s in range(STEPS):
+        tr.upload(toks[s], tgts[s])
+        tr.step(HP["lr"], s + 1)
+        losses.append(tr.loss())
+    tr.close()
+    gap = np.abs(np.array(losses, np.float64) - reference_run["losses"])
+    with capsys.disabled():
+        print("\n[gpt124m %s] first-step gradient vs reference: max-norm %.3e, l2 %.3e; loss gap over %d steps: max %.3e "
+              "(loss %.4f -> %.4f, reference %.4f -> %.4f)" % (mode, e_max, e_l2, STEPS, gap.max(), losses[0], losses[-1],
+                                                           reference_run["losses"][0], reference_run["losses"][-1]))
+    assert np.all(np.isfinite(losses))
+    assert e_max < grad_bar, e_max
+    assert gap.max() < loss_bar, gap
+
+
+def test_tensorcore_flash_at_benchmark_shape_vs_reference_kernels(bmb, ref, cuda, capsys):
+    """B=8, H=12, T=1024, head size 64: the tcgen05 forward and backward (96 (batch, head) pairs dispatched
+    longest first, dQ and dK/dV sharing one grid) against the reference's fp32 flash kernels.  Outputs start as
+    NaN so that every element must be written.  Bars: out and lse 2e-3, dq / dk / dv 5e-3 normwise."""
+    B, T, C, NH = 8, 1024, 768, 12
+    g = cuda.Generator(device="cuda").manual_seed(2024)
+    qkv = cuda.randn(B * T * 3 * C, device="cuda", generator=g)
+    dout = cuda.randn(B * T * C, device="cuda", generator=g)
+    nan = lambda n: cuda.full((n,), float("nan"), device="cuda")
+    o_ref, l_ref, d_ref, s_ref = nan(B * T * C), nan(B * NH * T), nan(B * T * 3 * C), nan(B * NH * T)
+    ref.ref_flash_attention_forward(o_ref.data_ptr(), l_ref.data_ptr(), qkv.data_ptr(), B, T, C, NH)
+    ref.ref_flash_attention_backward(d_ref.data_ptr(), s_ref.data_ptr(), dout.data_ptr(), qkv.data_ptr(), o_ref.data_ptr(),
+                                     l_ref.data_ptr(), B, T, C, NH)
+    cuda.cuda.synchronize()
+    o, l, d, s = nan(B * T * C), nan(B * NH * T), nan(B * T * 3 * C), nan(B * NH * T)
+    bmb.call("bmb_flash_attention_forward_cfg", 2, o, l, qkv, B, T, C, NH)
+    # the backward takes the forward's own out / lse, as in the training step
+    bmb.call("bmb_flash_attention_backward_cfg", 2, d, s, dout, qkv, o, l, B, T, C, NH)
+    cuda.cuda.synchronize()
+
+    def nw(a, b):
+        assert bool(cuda.isfinite(a).all())
+        return float((a.double() - b.double()).abs().max() / b.double().abs().max())
+
+    e_o, e_l = nw(o, o_ref), nw(l, l_ref)
+    dv, rv = d.view(B * T, 3, C), d_ref.view(B * T, 3, C)
+    e_d = [nw(dv[:, i], rv[:, i]) for i in range(3)]
+    with capsys.disabled():
+        print("\n[flash tc B8 H12 T1024 hs64] vs reference fp32 kernels: out %.2e lse %.2e dq %.2e dk %.2e dv %.2e" %
+              (e_o, e_l, e_d[0], e_d[1], e_d[2]))
+    assert e_o < 2e-3 and e_l < 2e-3, (e_o, e_l)
+    assert max(e_d) < 5e-3, e_d
+
+
+@pytest.mark.parametrize("ta,tb,M,N,K,beta", [
+    (0, 1, 8192, 2304, 768, 0.0),       # qkv projection
+    (0, 1, 8192, 50304, 768, 0.0),      # logits
+    (0, 0, 8192, 768, 50304, 0.0),      # gradient of the final layernorm output
+    (1, 0, 50304, 768, 8192, 1.0),      # token-embedding weight gradient, accumulated
+    (0, 0, 8192, 8192, 8192, 0.0),      # the sweep's largest square
+])
+@pytest.mark.parametrize("height", [128, 256])
+def test_tensorcore_gemm_forced_tile_heights(bmb, cuda, ta, tb, M, N, K, beta, height):
+    """Both tile heights of the TF32 kernel, forced per call, on the products the training step (and the
+    square sweep) spend most of their time in: pre-rounded operands against the float64 product computed on
+    the device in row blocks, 2e-5 normwise -- only the accumulation order may use that up."""
+    lib = bmb.lib()
+    flag = bmb.GEMM_TILE_M256 if height == 256 else bmb.GEMM_TILE_M128
+    import ctypes as C
+    tm, tn = C.c_int(), C.c_int()
+    assert lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flag, 1, M, N, K, 148, C.byref(tm), C.byref(tn), None, None) == 0
+    assert tm.value == height                      # the flag decides, not the cost model
+    g = cuda.Generator(device="cuda").manual_seed(11)
+    A = cuda.rand(M * K, device="cuda", generator=g) * 2 - 1
+    B = cuda.rand(K * N, device="cuda", generator=g) * 2 - 1
+    C0 = cuda.rand(M * N, device="cuda", generator=g) if beta else None
+    bmb.call("bmb_round_tf32", A, A, M * K, None)
+    bmb.call("bmb_round_tf32", B, B, K * N, None)
+    Cm = C0.clone() if beta else cuda.full((M * N,), float("nan"), device="cuda")
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED | flag, ta, tb, M, N, K, 1.0, A, B, beta,
+             Cm, None)
+    cuda.cuda.synchronize()
+    Am = A.view(K, M).t() if ta else A.view(M, K)
+    Bm = (B.view(N, K).t() if tb else B.view(K, N)).double()
+    num = den = 0.0
+    step = 1024 if K * N > (1 << 28) else 4096
+    for r0 in range(0, M, step):                   # float64 product a block of rows at a time
+        r1 = min(M, r0 + step)
+        want = Am[r0:r1].double() @ Bm
+        if beta:
+            want += beta * C0.view(M, N)[r0:r1].double()
+        diff = Cm.view(M, N)[r0:r1].double() - want
+        num += float((diff * diff).sum())
+        den += float((want * want).sum())
+    err = (num / den) ** 0.5
+    assert err < 2e-5, err
+
+
+@pytest.mark.parametrize("name,ta,tb,M,N,K", [("QK^T", 0, 1, 1024, 1024, 64), ("PV", 0, 0, 1024, 64, 1024)])
+def test_attention_shaped_batched_gemm_at_full_size_vs_reference(bmb, ref, cuda, name, ta, tb, M, N, K):
+    """batch 96 (8 sequences x 12 heads), normal(0,1) inputs: batched_gemm in fp32 against the reference's
+    batched_gemm at 1e-6 normwise, and in TF32 mode at 5e-4."""
+    batch = 96
+    g = cuda.Generator(device="cuda").manual_seed(33)
+    A = cuda.randn(batch * M * K, device="cuda", generator=g)
+    B = cuda.randn(batch * K * N, device="cuda", generator=g)
+    want = cuda.full((batch * M * N,), float("nan"), device="cuda")
+    ref.ref_batched_gemm(ta, tb, batch, M, N, K, 1.0, A.data_ptr(), M * K, B.data_ptr(), K * N, 0.0, want.data_ptr(), M * N)
+    cuda.cuda.synchronize()
+    lib = bmb.lib()
+    prev = lib.bmb_get_math_mode()
+    try:
+        for math, bar in ((bmb.MATH_FP32, 1e-6), (bmb.MATH_TF32, 5e-4)):
+            lib.bmb_set_math_mode(math)
+            got = cuda.full((batch * M * N,), float("nan"), device="cuda")
+            bmb.call("bmb_batched_gemm", ta, tb, batch, M, N, K, 1.0, A, M * K, B, K * N, 0.0, got, M * N, None)
+            cuda.cuda.synchronize()
+            assert bool(cuda.isfinite(got).all())
+            err = float((got - want).abs().max() / want.abs().max())
+            assert err < bar, (name, math, err)
+    finally:
+        lib.bmb_set_math_mode(prev)
+
+
+def test_scratch_growth_does_not_break_the_captured_step(bmb, cuda, monkeypatch):
+    """The trainer replays its forward + backward from a CUDA graph that carries the addresses of the
+    library's per-device scratch.  A larger scratch request from another caller on the same device moves
+    that scratch; the next steps must notice and still give the losses of a trainer that launches kernel by
+    kernel."""
+    cfg = dict(max_seq_len=64, vocab_size=300, padded_vocab=384, n_layer=2, n_head=4, n_embd=256, B=4, T=64)
+    rng = np.random.default_rng(3)
+    toks = rng.integers(0, 300, (6, 4, 64), dtype=np.int32)
+    tgts = rng.integers(0, 300, (6, 4, 64), dtype=np.int32)
+    runs = []
+    for graph in ("1", "0"):
+        monkeypatch.setenv("BMB_TRAINER_GRAPH", graph)
+        tr = bmb.Trainer(seed=1337, use_flash=1, math=bmb.MATH_TF32, fused=0, **cfg)   # unfused: the GEMMs round into scratch
+        losses = []
+        for s in range(6):
+            if s == 3:
+                # un-rounded operands far larger than anything the trainer staged, and a wide layernorm backward
+                n = 3072
+                a = cuda.rand(n * n, device="cuda")
+                c = cuda.zeros(n * n, device="cuda")
+                bmb.call("bmb_sgemm_tf32", n, n, n, 1.0, a, a, 0.0, c)
+                N, Cw = 65536, 1024
+                x = cuda.rand(N * Cw, device="cuda")
+                m, r = cuda.zeros(N, device="cuda"), cuda.ones(N, device="cuda")
+                w = cuda.ones(Cw, device="cuda")
+                dw, db = cuda.zeros(Cw, device="cuda"), cuda.zeros(Cw, device="cuda")
+                dx = cuda.zeros(N * Cw, device="cuda")
+                bmb.call("bmb_layernorm_backward", dx, dw, db, x, x, w, m, r, N, Cw)
+                cuda.cuda.synchronize()
+            tr.upload(toks[s], tgts[s])
+            tr.step(3e-4, s + 1)
+            losses.append(tr.loss())
+        tr.close()
+        runs.append(losses)
+    assert np.all(np.isfinite(runs[0]))
+    assert max(abs(a - b) for a, b in zip(*runs)) <= 1e-3, runs

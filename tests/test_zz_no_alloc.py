@@ -1,13 +1,14 @@
 """bmb_layernorm_backward_noalloc: the layernorm backward for callers that cannot allocate
 (a training loop whose device memory is fully handed out at start-up, where a lazy
 cudaMalloc inside a step could fail or stall the device).  Its scratch is a fixed array in
-the library image, so the check is simply that it gives what bmb_layernorm_backward gives --
-on two calls in a row, because the array keeps the previous call's contents -- and that it
-refuses rows wider than the array was sized for.  Collected last on purpose."""
+the library image, so the check is that it gives what bmb_layernorm_backward gives and what
+the CPU oracle (src/nn.cu:85-113 restated) gives -- on two calls in a row, because the array
+keeps the previous call's contents -- and that it refuses rows wider than the array was sized
+for.  Collected last on purpose."""
 import numpy as np
 import pytest
 
-from helpers import normal, normwise
+from helpers import _np, normal, normwise
 
 pytestmark = pytest.mark.gpu
 
@@ -24,7 +25,7 @@ def run(bmb, torch, name, args_np, N, C):
 
 
 @pytest.mark.parametrize("N,C", [(8192, 768), (100, 64), (33, 1024)])
-def test_noalloc_layernorm_backward_matches_the_allocating_entry_point(bmb, cuda, N, C):
+def test_noalloc_layernorm_backward_matches_the_allocating_entry_point(bmb, orc, cuda, N, C):
     for call in range(2):                     # second call meets the first call's leftovers in the array
         x, w, dy = normal((N, C), 10 + call), normal(C, 20 + call), normal((N, C), 30 + call)
         b = np.zeros(C, np.float32)
@@ -38,6 +39,13 @@ def test_noalloc_layernorm_backward_matches_the_allocating_entry_point(bmb, cuda
         got = run(bmb, cuda, "bmb_layernorm_backward_noalloc", args, N, C)
         for g, wnt in zip(got, want):
             assert normwise(g, wnt) < 1e-5     # the bar of the other layernorm tests
+        # and against the CPU oracle, started from the same dinp / dweight / dbias (all three accumulate)
+        odx, odw, odb = args[5].copy(), args[6].copy(), args[7].copy()
+        orc.orc_layernorm_backward(_np(odx), _np(odw), _np(odb), _np(dy), _np(x), _np(w), _np(args[3]), _np(args[4]), N, C)
+        # the oracle sums the N rows one after another in fp32: its own rounding grows with N
+        bar = 1e-5 if N <= 1024 else 1e-4
+        for g, wnt in zip(got, (odx, odw, odb)):
+            assert normwise(g, wnt) < bar
 
 
 def test_noalloc_layernorm_backward_rejects_rows_beyond_its_array(bmb, cuda):
