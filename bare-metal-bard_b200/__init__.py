@@ -128,6 +128,14 @@ SIGNATURES = {
     "bmb_trainer_loss": (_i, [_p, C.POINTER(_f)]),
     "bmb_trainer_loss_async": (_i, [_p, _p]),
     "bmb_trainer_sync": (_i, [_p]),
+    "bmb_trainer_memory": (_i, [_p, C.POINTER(_z), C.POINTER(_z), C.POINTER(_z)]),
+    "bmb_trainer_grad_norm": (_i, [_p, C.POINTER(_f)]),
+    "bmb_trainer_forward_loss": (_i, [_p, C.POINTER(_f)]),
+    "bmb_trainer_save": (_i, [_p, C.c_char_p, C.c_char_p, _i, _i, _i]),
+    "bmb_checkpoint_header": (_i, [C.c_char_p, C.POINTER(TrainConfig), C.POINTER(_i), C.c_char_p, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "bmb_trainer_load": (_i, [_p, C.c_char_p, _i, C.POINTER(_i)]),
+    "bmb_trainer_next_token_probs": (_i, [_p, _p, _i, _p]),
+    "bmb_trainer_generate": (_i, [_p, _i, _i, _u, _f, _p]),
     "bmb_trainer_stream": (_p, [_p]),
     "bmb_trainer_profile": (_i, [_p, _i]),
     "bmb_trainer_profile_read": (_i, [_p, C.POINTER(_d), C.POINTER(_d), C.POINTER(_ll), C.POINTER(_ll)]),
@@ -249,6 +257,30 @@ class Trainer:
         check(lib().bmb_trainer_profile_read(self.h, C.byref(fl), C.byref(ms), C.byref(calls), C.byref(launches)),
               "bmb_trainer_profile_read")
         return dict(gemm_flop=fl.value, gemm_ms=ms.value, gemm_calls=calls.value, launches=launches.value)
+
+    def save(self, path, itos=b"", with_optimizer_state=False, step=0):
+        check(lib().bmb_trainer_save(self.h, str(path).encode(), bytes(itos), len(itos), 1 if with_optimizer_state else 0, step),
+              "bmb_trainer_save")
+
+    def load(self, path, optimizer_state=False):
+        step = _i(0)
+        check(lib().bmb_trainer_load(self.h, str(path).encode(), 1 if optimizer_state else 0, C.byref(step)), "bmb_trainer_load")
+        return step.value
+
+    def forward_loss(self):
+        v = _f()
+        check(lib().bmb_trainer_forward_loss(self.h, C.byref(v)), "bmb_trainer_forward_loss")
+        return v.value
+
+    def grad_norm(self):
+        v = _f()
+        check(lib().bmb_trainer_grad_norm(self.h, C.byref(v)), "bmb_trainer_grad_norm")
+        return v.value
+
+    def generate(self, start_token, steps, seed, temperature=1.0):
+        out = (C.c_int * max(steps, 1))()
+        check(lib().bmb_trainer_generate(self.h, start_token, steps, seed, temperature, out), "bmb_trainer_generate")
+        return list(out[:steps])
 
     def close(self):
         if self.h:

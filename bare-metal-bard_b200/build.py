@@ -1,4 +1,5 @@
-"""Build libbmb.so (the CUDA kernels and the C ABI) for sm_100a with nvcc.
+"""Build libbmb.so (the CUDA kernels and the C ABI) for sm_100a with nvcc, and the
+bmb_train_gpt driver that links against it.
 
 Run as a script (``python bare-metal-bard_b200/build.py``) or call
 ``build_library()``.  Objects go to ``build/`` at the repository root and the
@@ -66,7 +67,23 @@ def build_library(verbose=False, force=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    build_cli()
     return LIB
+
+
+def build_cli():
+    """bmb_train_gpt, the training driver over the C ABI (host C++ only), next to the library."""
+    src = os.path.join(HERE, "cli", "bmb_train_gpt.cpp")
+    exe = os.path.join(HERE, "bmb_train_gpt")
+    newest = max(os.path.getmtime(src), os.path.getmtime(LIB), os.path.getmtime(os.path.join(ROOT, "include", "bmb.h")))
+    if os.path.exists(exe) and os.path.getmtime(exe) > newest:
+        return exe
+    cmd = ["nvcc", "-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"), src, "-o", exe, "-L", HERE, "-lbmb",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building bmb_train_gpt failed:\n%s\n%s" % (r.stdout, r.stderr))
+    return exe
 
 
 if __name__ == "__main__":

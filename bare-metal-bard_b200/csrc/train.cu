@@ -9,7 +9,9 @@
 // order (src/gpt.cu:32-51), so raw parameter dumps are interchangeable.
 #include "common.cuh"
 #include <cmath>
+#include <cstring>
 #include <random>
+#include <string>
 #include <vector>
 
 namespace bmb {
@@ -65,6 +67,7 @@ struct bmb_trainer {
     cudaGraphExec_t graph_exec = nullptr;
     long long graph_launches = 0;
     unsigned long long graph_scratch_gen = 0;   // the device's scratch generation the graph was captured under
+    float *gen_probs = nullptr;   // one row of next-token probabilities, allocated by the first sampling call
     // profiling
     bool prof = false;
     std::vector<cudaEvent_t> ev;
@@ -140,7 +143,7 @@ int mm(bmb_trainer *t, int flags, int ta, int tb, int M, int N, int K, const flo
     return BMB_OK;
 }
 
-int forward(bmb_trainer *t) {
+int forward(bmb_trainer *t, bool with_loss = true) {
     const bmb_train_config &c = t->c;
     const int B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head;
     const int Vp = c.padded_vocab, V = c.vocab_size, N = B * T;
@@ -211,6 +214,7 @@ int forward(bmb_trainer *t) {
         residual = res3;
     }
     BMB_TRY(mm(t, wflag, 0, 1, N, Vp, C, t->lnf, W + t->poff[P_WTE], 0.0f, t->logits));
+    if (!with_loss) return BMB_OK;        // sampling reads the logits only
     // Loss and its gradient with respect to the logits in one sweep (mean loss: dloss = 1/N).
     BMB_TRY(bmb_softmax_crossentropy_fused(t->dlogits, t->losses, t->logits, t->d_targets, N, V, Vp, 1.0f / N));
     BMB_TRY(bmb_reduce_mean_device(t->losses, N, t->d_loss));
@@ -494,6 +498,7 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     if (t->shadow) cudaFree(t->shadow);
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
     cudaFree(t->d_loss); cudaFree(t->d_sumsq); cudaFree(t->d_token);
+    if (t->gen_probs) cudaFree(t->gen_probs);
     dp_fused_destroy(t->dp);
     if (t->st) cudaStreamDestroy(t->st);
     delete t;
@@ -643,6 +648,201 @@ int bmb_trainer_profile_read(bmb_trainer *t, double *gemm_flop, double *gemm_ms,
     if (gemm_ms) *gemm_ms = t->prof_ms;
     if (gemm_calls) *gemm_calls = t->prof_calls;
     if (kernel_launches) *kernel_launches = launches_total() - t->launches0;
+    return BMB_OK;
+}
+
+
+// ---- memory report, gradient norm, forward-only loss -------------------------------------------
+int bmb_trainer_memory(const bmb_trainer *t, size_t *param_floats, size_t *activation_floats, size_t *scratch_floats) {
+    if (!t) return fail(BMB_E_ARG, "trainer_memory: null handle");
+    if (param_floats) *param_floats = t->num_params;
+    if (activation_floats) *activation_floats = t->num_acts;
+    if (scratch_floats) *scratch_floats = t->num_bacts;
+    return BMB_OK;
+}
+
+int bmb_trainer_grad_norm(bmb_trainer *t, float *host_norm) {
+    if (!t || !host_norm) return fail(BMB_E_ARG, "trainer_grad_norm: null argument");
+    Scope sc(t);
+    double ss = 0.0;
+    BMB_CUDA(cudaMemcpyAsync(&ss, t->d_sumsq, sizeof(double), cudaMemcpyDeviceToHost, t->st));
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    *host_norm = (float)(sqrt(ss) / (double)t->nranks);
+    return BMB_OK;
+}
+
+int bmb_trainer_forward_loss(bmb_trainer *t, float *host_loss) {
+    if (!t || !host_loss) return fail(BMB_E_ARG, "trainer_forward_loss: null argument");
+    Scope sc(t);
+    BMB_TRY(forward(t));
+    BMB_CUDA(cudaMemcpyAsync(host_loss, t->d_loss, sizeof(float), cudaMemcpyDeviceToHost, t->st));
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    return check_kernel_status();
+}
+
+// ---- GPT1 checkpoints (src/train_gpt.cu:175-227) -------------------------------------------------
+// Layout, all little-endian as the reference writes it with fwrite:
+//   int32 magic 0x47505431 ("GPT1") | GPTConfig as six int32 (max_seq_len, vocab_size, padded_vocab,
+//   n_layer, n_head, n_embd; src/gpt.h:10-17) | int32 nvocab | nvocab bytes (token id -> character) |
+//   num_params fp32 in the tensor order of src/gpt.cu:32-51.
+// The reference's reader stops there.  Optionally this library appends the optimiser state, which
+// the reference does not keep:  int32 magic 0x4F424D42 ("BMBO") | int32 step | m | v (fp32 each).
+namespace {
+constexpr int GPT1_MAGIC = 0x47505431, OPT_MAGIC = 0x4F424D42;
+struct Gpt1Header { int cfg[6]; int nvocab; std::string itos; long params_at; };
+
+int read_gpt1_header(FILE *f, const char *path, Gpt1Header *h) {
+    int magic = 0;
+    if (fread(&magic, sizeof(int), 1, f) != 1 || magic != GPT1_MAGIC) return fail(BMB_E_ARG, "%s is not a GPT1 checkpoint", path);
+    if (fread(h->cfg, sizeof(int), 6, f) != 6 || fread(&h->nvocab, sizeof(int), 1, f) != 1 || h->nvocab < 0 || h->nvocab > (1 << 24))
+        return fail(BMB_E_ARG, "%s: truncated or corrupt header", path);
+    h->itos.resize((size_t)h->nvocab);
+    if (h->nvocab && fread(&h->itos[0], 1, (size_t)h->nvocab, f) != (size_t)h->nvocab) return fail(BMB_E_ARG, "%s: truncated vocabulary", path);
+    h->params_at = ftell(f);
+    return BMB_OK;
+}
+}  // namespace
+
+int bmb_trainer_save(bmb_trainer *t, const char *path, const char *itos, int nvocab, int with_optimizer_state, int step) {
+    if (!t || !path || nvocab < 0 || (nvocab && !itos)) return fail(BMB_E_ARG, "trainer_save: bad argument");
+    Scope sc(t);
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    std::vector<float> h(t->num_params);
+    FILE *f = fopen(path, "wb");
+    if (!f) return fail(BMB_E_ARG, "trainer_save: cannot write %s", path);
+    const int cfg[6] = {t->c.max_seq_len, t->c.vocab_size, t->c.padded_vocab, t->c.n_layer, t->c.n_head, t->c.n_embd};
+    bool ok = fwrite(&GPT1_MAGIC, sizeof(int), 1, f) == 1 && fwrite(cfg, sizeof(int), 6, f) == 6 &&
+              fwrite(&nvocab, sizeof(int), 1, f) == 1 && (nvocab == 0 || fwrite(itos, 1, (size_t)nvocab, f) == (size_t)nvocab);
+    auto dump = [&](const float *dev) {
+        if (!ok) return;
+        ok = cudaMemcpy(h.data(), dev, t->num_params * sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess &&
+             fwrite(h.data(), sizeof(float), t->num_params, f) == t->num_params;
+    };
+    dump(t->params);
+    if (with_optimizer_state) {
+        ok = ok && fwrite(&OPT_MAGIC, sizeof(int), 1, f) == 1 && fwrite(&step, sizeof(int), 1, f) == 1;
+        dump(t->m);
+        dump(t->v);
+    }
+    ok = (fclose(f) == 0) && ok;
+    return ok ? BMB_OK : fail(BMB_E_CUDA, "trainer_save: writing %s failed", path);
+}
+
+int bmb_checkpoint_header(const char *path, bmb_train_config *cfg_out, int *nvocab_out, char *itos_out, int itos_cap,
+                          int *has_optimizer_state, int *step_out) {
+    if (!path) return fail(BMB_E_ARG, "checkpoint_header: null path");
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(BMB_E_ARG, "cannot open %s", path);
+    Gpt1Header h;
+    int rc = read_gpt1_header(f, path, &h);
+    if (rc == BMB_OK) {
+        if (cfg_out) {
+            cfg_out->max_seq_len = h.cfg[0]; cfg_out->vocab_size = h.cfg[1]; cfg_out->padded_vocab = h.cfg[2];
+            cfg_out->n_layer = h.cfg[3]; cfg_out->n_head = h.cfg[4]; cfg_out->n_embd = h.cfg[5];
+        }
+        if (nvocab_out) *nvocab_out = h.nvocab;
+        if (itos_out) memcpy(itos_out, h.itos.data(), (size_t)(h.nvocab < itos_cap ? h.nvocab : (itos_cap > 0 ? itos_cap : 0)));
+        bmb_train_config c{};
+        c.max_seq_len = h.cfg[0]; c.vocab_size = h.cfg[1]; c.padded_vocab = h.cfg[2]; c.n_layer = h.cfg[3]; c.n_head = h.cfg[4]; c.n_embd = h.cfg[5];
+        int opt = 0, step = 0;
+        if (c.n_layer > 0 && c.n_embd > 0 && c.padded_vocab > 0 && c.max_seq_len > 0) {
+            size_t ps[NPT], n = 0;
+            param_sizes(ps, c);
+            for (int i = 0; i < NPT; ++i) n += ps[i];
+            int magic = 0;
+            if (fseek(f, h.params_at + (long)(n * sizeof(float)), SEEK_SET) == 0 && fread(&magic, sizeof(int), 1, f) == 1 &&
+                magic == OPT_MAGIC && fread(&step, sizeof(int), 1, f) == 1)
+                opt = 1;
+        }
+        if (has_optimizer_state) *has_optimizer_state = opt;
+        if (step_out) *step_out = opt ? step : 0;
+    }
+    fclose(f);
+    return rc;
+}
+
+int bmb_trainer_load(bmb_trainer *t, const char *path, int load_optimizer_state, int *step_out) {
+    if (!t || !path) return fail(BMB_E_ARG, "trainer_load: null argument");
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(BMB_E_ARG, "cannot open %s", path);
+    Gpt1Header h;
+    int rc = read_gpt1_header(f, path, &h);
+    const int mine[6] = {t->c.max_seq_len, t->c.vocab_size, t->c.padded_vocab, t->c.n_layer, t->c.n_head, t->c.n_embd};
+    // the context length only sizes the position table: a trainer may run shorter sequences than the file's
+    if (rc == BMB_OK && memcmp(h.cfg, mine, sizeof(mine)) != 0)
+        rc = fail(BMB_E_ARG, "%s holds a %d-layer %d-head %d-wide model (ctx %d, vocab %d/%d); this trainer is %d/%d/%d (ctx %d, vocab %d/%d)",
+                  path, h.cfg[3], h.cfg[4], h.cfg[5], h.cfg[0], h.cfg[1], h.cfg[2], mine[3], mine[4], mine[5], mine[0], mine[1], mine[2]);
+    std::vector<float> buf(rc == BMB_OK ? t->num_params : 0);
+    Scope sc(t);
+    auto slurp = [&](float *dev, const char *what) {
+        if (rc != BMB_OK) return;
+        if (fread(buf.data(), sizeof(float), t->num_params, f) != t->num_params) { rc = fail(BMB_E_ARG, "%s: %s truncated", path, what); return; }
+        if (cudaMemcpy(dev, buf.data(), t->num_params * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+            rc = fail(BMB_E_CUDA, "trainer_load: copy of %s failed", what);
+    };
+    if (rc == BMB_OK) cudaStreamSynchronize(t->st);
+    slurp(t->params, "parameters");
+    int step = 0;
+    if (rc == BMB_OK && load_optimizer_state) {
+        int magic = 0;
+        if (fread(&magic, sizeof(int), 1, f) != 1 || magic != OPT_MAGIC || fread(&step, sizeof(int), 1, f) != 1)
+            rc = fail(BMB_E_ARG, "%s carries no optimiser state", path);
+        slurp(t->m, "first moments");
+        slurp(t->v, "second moments");
+    }
+    fclose(f);
+    if (rc != BMB_OK) return rc;
+    if (step_out) *step_out = step;
+    BMB_TRY(refresh_shadow(t));
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    return BMB_OK;
+}
+
+// ---- sampling (src/train_gpt.cu:46-102) ------------------------------------------------------------
+int bmb_trainer_next_token_probs(bmb_trainer *t, const int *host_tokens, int pos, float *host_probs) {
+    if (!t || !host_tokens || !host_probs || pos < 0 || pos >= t->c.B * t->c.T) return fail(BMB_E_ARG, "next_token_probs: bad argument");
+    Scope sc(t);
+    const int Vp = t->c.padded_vocab, V = t->c.vocab_size;
+    if (!t->gen_probs) BMB_CUDA(cudaMalloc(&t->gen_probs, ((size_t)Vp + 1) * sizeof(float)));
+    BMB_CUDA(cudaMemcpyAsync(t->d_tokens, host_tokens, (size_t)t->c.B * t->c.T * sizeof(int), cudaMemcpyDefault, t->st));
+    BMB_TRY(forward(t, false));
+    set_emit_rounded(false);
+    // the softmax of the reference's loss kernel over that one row (src/nn.cu:197-237); its target only picks which
+    // loss is written, so row `pos` of the resident targets serves
+    BMB_TRY(bmb_softmax_crossentropy_forward(t->gen_probs, t->gen_probs + Vp, t->logits + (size_t)pos * Vp, t->d_targets + pos, 1, V, Vp));
+    BMB_CUDA(cudaMemcpyAsync(host_probs, t->gen_probs, (size_t)Vp * sizeof(float), cudaMemcpyDeviceToHost, t->st));
+    BMB_CUDA(cudaStreamSynchronize(t->st));
+    return check_kernel_status();
+}
+
+int bmb_trainer_generate(bmb_trainer *t, int start_token, int steps, unsigned seed, float temperature, int *host_tokens_out) {
+    if (!t || steps < 0 || (steps && !host_tokens_out) || start_token < 0 || start_token >= t->c.vocab_size || !(temperature > 0.0f))
+        return fail(BMB_E_ARG, "trainer_generate: bad argument");
+    const int T = t->c.T, Vp = t->c.padded_vocab, V = t->c.vocab_size;
+    std::vector<int> ctx((size_t)t->c.B * T, 0);
+    std::vector<float> row((size_t)Vp);
+    std::mt19937 rng(seed);
+    std::uniform_real_distribution<float> uni(0.0f, 1.0f);
+    int cur_len = 1;
+    ctx[0] = start_token;
+    for (int s = 0; s < steps; ++s) {
+        BMB_TRY(bmb_trainer_next_token_probs(t, ctx.data(), cur_len - 1, row.data()));
+        if (temperature != 1.0f) {
+            float sum = 0.0f;
+            for (int i = 0; i < V; ++i) { row[i] = powf(row[i], 1.0f / temperature); sum += row[i]; }
+            for (int i = 0; i < V; ++i) row[i] /= sum;
+        }
+        const float coin = uni(rng);
+        float cdf = 0.0f;
+        int tok = V - 1;
+        for (int i = 0; i < V; ++i) { cdf += row[i]; if (coin < cdf) { tok = i; break; } }
+        host_tokens_out[s] = tok;
+        if (cur_len < T) ctx[cur_len++] = tok;
+        else {                               // context full: slide the window left by one
+            for (int i = 0; i < T - 1; ++i) ctx[i] = ctx[i + 1];
+            ctx[T - 1] = tok;
+        }
+    }
     return BMB_OK;
 }
 

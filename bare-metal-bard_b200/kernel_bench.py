@@ -2,6 +2,13 @@
 
     python bare-metal-bard_b200/kernel_bench.py [gemm] [bgemm] [flash] [nn] [--small]
     python bare-metal-bard_b200/kernel_bench.py one:tf32:nt:8192x3072x768:rounded      (a single GEMM case)
+    python bare-metal-bard_b200/kernel_bench.py registry --csv runs/a.csv [-s 1024,2048]   (the registry sweep as CSV)
+
+`registry --csv` appends one row per (registry entry, size) in the columns the reference harness writes
+(src/bench.cu:238-245, 293-299): kernel_id,kernel,size,gflops_best,gflops_median,cublas_gflops_best,
+pct_of_cublas -- so that tools/merge_runs.py and tools/plot_results.py of the reference read the
+new numbers unchanged.  The cuBLAS column is torch.matmul in true fp32 on the same operands, the
+harness's baseline column; it is not part of the library.
 
 Timing follows the reference harness (src/bench.cu:75-105): 5 warm-up calls,
 then 20 calls bracketed by CUDA events one at a time; best and median are
@@ -170,6 +177,50 @@ def bench_nn(bmb, small):
              gbs_best=round(nbytes / best / 1e6, 1), gbs_median=round(nbytes / med / 1e6, 1))
 
 
+CSV_FIELDS = ["kernel_id", "kernel", "size", "gflops_best", "gflops_median", "cublas_gflops_best", "pct_of_cublas"]
+
+
+def append_csv(path, rows):
+    """Append rows (dicts keyed by CSV_FIELDS) in the reference harness's format: header only when the
+    file is new, two decimals (src/bench.cu:244, 297-298)."""
+    new = not os.path.exists(path)
+    with open(path, "a") as f:
+        if new:
+            f.write(",".join(CSV_FIELDS) + "\n")
+        for r in rows:
+            f.write("%d,%s,%d,%.2f,%.2f,%.2f,%.2f\n" % (r["kernel_id"], r["kernel"], r["size"], r["gflops_best"],
+                                                       r["gflops_median"], r["cublas_gflops_best"], r["pct_of_cublas"]))
+
+
+def bench_registry(bmb, csv_path, sizes):
+    """Every registry entry over square sizes, 5 warm-ups + 20 timed calls each, with the table the
+    reference harness prints and, when asked, its CSV."""
+    lib = bmb.lib()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    table = lib.bmb_kernel_table()
+    print("%-4s %-20s %6s %11s %11s %11s %8s" % ("id", "kernel", "size", "best GF/s", "med GF/s", "cuBLAS GF/s", "%cuBLAS"))
+    rows = []
+    for k in range(lib.bmb_num_kernels()):
+        e = table[k]
+        fn = getattr(lib, {1: "bmb_sgemm_simt", 2: "bmb_sgemm_tf32", 3: "bmb_sgemm_bf16"}[e.id])
+        for n in sizes:
+            A = torch.rand(n, n, device="cuda") * 2 - 1
+            B = torch.rand(n, n, device="cuda") * 2 - 1
+            Cm = torch.zeros(n, n, device="cuda")
+            best, med = timed(lambda: bmb.check(fn(n, n, n, 1.0, A.data_ptr(), B.data_ptr(), 0.0, Cm.data_ptr())))
+            cb, _ = timed(lambda: torch.matmul(A, B, out=Cm))
+            gf, gfm, gfb = (2.0 * n ** 3 / (t * 1e-3) / 1e9 for t in (best, med, cb))
+            row = dict(kernel_id=e.id, kernel=e.name.decode(), size=n, gflops_best=gf, gflops_median=gfm,
+                       cublas_gflops_best=gfb, pct_of_cublas=100.0 * gf / gfb)
+            rows.append(row)
+            print("%-4d %-20s %6d %11.1f %11.1f %11.1f %7.1f%%" % (e.id, row["kernel"], n, gf, gfm, gfb, row["pct_of_cublas"]))
+            del A, B, Cm
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    if csv_path:
+        append_csv(csv_path, rows)
+
+
 def bench_one(bmb, spec):
     """One GEMM case, for a profiler capture or a quick comparison:
         one:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][:nosplit]
@@ -197,11 +248,27 @@ def bench_one(bmb, spec):
 
 
 def main():
-    args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    small = "--small" in sys.argv
+    argv = sys.argv[1:]
+    csv_path, sizes = None, [1024, 1536, 2048, 4096, 6144, 8192]
+    for flag in ("--csv", "-s"):
+        if flag in argv:
+            i = argv.index(flag)
+            value = argv[i + 1]
+            del argv[i:i + 2]
+            if flag == "--csv":
+                csv_path = value
+            else:
+                sizes = [int(x) for x in value.split(",")]
+    args = [a for a in argv if not a.startswith("--")]
+    small = "--small" in argv
     which = args or ["gemm", "bgemm", "flash", "nn"]
     bmb = load_package()
     torch.cuda.set_device(0)
+    if "registry" in which:
+        bench_registry(bmb, csv_path, sizes)
+        which = [x for x in which if x != "registry"]
+        if not which:
+            return
     for w in [x for x in which if x.startswith("one:")]:
         bench_one(bmb, w)
     which = [x for x in which if not x.startswith("one:")]

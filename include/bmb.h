@@ -336,6 +336,41 @@ int bmb_trainer_loss(bmb_trainer *t, float *host_loss);
  * training loop read every step's loss one step late instead of draining the GPU every step. */
 int bmb_trainer_loss_async(bmb_trainer *t, float *pinned_host_loss);
 int bmb_trainer_sync(bmb_trainer *t);
+/* Floats held by one replica: parameters (x4 with gradients and the two AdamW moments), forward
+ * activations, backward scratch -- the figures the reference prints before training and under
+ * --alloc-only (src/train_gpt.cu:339-355). */
+int bmb_trainer_memory(const bmb_trainer *t, size_t *param_floats, size_t *activation_floats,
+                       size_t *scratch_floats);
+/* Blocks: the gradient norm the last bmb_trainer_step clipped against, ||sum over ranks of g|| / ranks
+ * (src/train_gpt.cu:442-446). */
+int bmb_trainer_grad_norm(bmb_trainer *t, float *host_norm);
+/* Blocks: forward pass only on the resident batch, mean loss returned (the evaluate() of
+ * src/train_gpt.cu:163-173 calls gpt_forward this way).  Parameters and gradients are untouched. */
+int bmb_trainer_forward_loss(bmb_trainer *t, float *host_loss);
+
+/* ---- GPT1 checkpoints and sampling (src/train_gpt.cu:175-227, 46-102) ---- */
+/* Write the parameters in the reference's GPT1 layout: int32 magic 0x47505431, the six int32 of GPTConfig,
+ * int32 nvocab, nvocab bytes mapping token id -> character, then num_params fp32 in the reference's tensor
+ * order.  A file written here loads in the reference's `train_gpt --load` and the other way round.
+ * with_optimizer_state != 0 appends what the reference does not keep -- int32 magic 0x4F424D42, int32 step,
+ * the AdamW first and second moments -- after the point where the reference's reader stops. */
+int bmb_trainer_save(bmb_trainer *t, const char *path, const char *itos, int nvocab,
+                     int with_optimizer_state, int step);
+/* Read a GPT1 file's header: fills the six model fields of *cfg_out (the others are left alone), the
+ * vocabulary (at most itos_cap bytes of it), whether the optimiser-state section is present and its step. */
+int bmb_checkpoint_header(const char *path, bmb_train_config *cfg_out, int *nvocab_out, char *itos_out,
+                          int itos_cap, int *has_optimizer_state, int *step_out);
+/* Load parameters (and, if asked, the optimiser state and *step_out) into a trainer whose six model fields
+ * equal the file's; BMB_E_ARG otherwise, or when the state is asked for and absent. */
+int bmb_trainer_load(bmb_trainer *t, const char *path, int load_optimizer_state, int *step_out);
+/* Forward pass on host_tokens (B*T ints) and the softmax of row `pos` (0 <= pos < B*T) of the logits:
+ * host_probs receives padded_vocab floats, zeros on the padding (what src/train_gpt.cu:73-78 reads). Blocks. */
+int bmb_trainer_next_token_probs(bmb_trainer *t, const int *host_tokens, int pos, float *host_probs);
+/* The reference's generate(): starts from start_token, draws `steps` tokens with mt19937(seed) and a
+ * uniform float per token, probabilities raised to 1/temperature and renormalised when temperature != 1,
+ * the window sliding once the context is full.  host_tokens_out receives the drawn token ids. Blocks. */
+int bmb_trainer_generate(bmb_trainer *t, int start_token, int steps, unsigned seed, float temperature,
+                         int *host_tokens_out);
 /* The CUDA stream every step of this trainer is enqueued on (for events). */
 void *bmb_trainer_stream(bmb_trainer *t);
 /* Per-call event timing of the GEMMs inside steps (on = 1 / off = 0); the

@@ -117,3 +117,66 @@ def test_tensorcore_gemm_schedule_covers_every_slice_once(bmb):
     assert shared > 20                      # the sweep does exercise shared tiles
     st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 96, 1024, 64, 1024, 148, None, None, None, None)   # batched
     assert st == 0, lib.bmb_last_error()
+
+
+def test_checkpoint_header_reads_the_gpt1_layout(bmb, tmp_path):
+    """bmb_checkpoint_header on a file laid out by hand as src/train_gpt.cu:175-193 writes it (magic,
+    GPTConfig, nvocab, vocabulary, parameters), without and with the appended optimiser section."""
+    import struct
+    import numpy as np
+    cfg = (32, 5, 128, 1, 2, 8)                       # max_seq_len, vocab, padded vocab, layers, heads, width
+    L, Cw, Vp, maxT = cfg[3], cfg[5], cfg[2], cfg[0]
+    nparams = Vp * Cw + maxT * Cw + L * (2 * Cw + 3 * Cw * Cw + 3 * Cw + Cw * Cw + Cw + 2 * Cw + 4 * Cw * Cw + 4 * Cw + 4 * Cw * Cw + Cw) + 2 * Cw
+    itos = b"\nabcd"
+    params = np.arange(nparams, dtype=np.float32)
+    plain, full = tmp_path / "plain.bin", tmp_path / "full.bin"
+    head = struct.pack("<i6ii", 0x47505431, *cfg, len(itos)) + itos
+    plain.write_bytes(head + params.tobytes())
+    full.write_bytes(head + params.tobytes() + struct.pack("<2i", 0x4F424D42, 77) + params.tobytes() * 2)
+    lib = bmb.lib()
+    for path, want_opt, want_step in ((plain, 0, 0), (full, 1, 77)):
+        hc, nv, opt, step = bmb.TrainConfig(), C.c_int(), C.c_int(-1), C.c_int(-1)
+        buf = C.create_string_buffer(16)
+        assert lib.bmb_checkpoint_header(str(path).encode(), C.byref(hc), C.byref(nv), buf, 16, C.byref(opt), C.byref(step)) == 0
+        assert (hc.max_seq_len, hc.vocab_size, hc.padded_vocab, hc.n_layer, hc.n_head, hc.n_embd) == cfg
+        assert nv.value == len(itos) and buf.raw[:len(itos)] == itos
+        assert (opt.value, step.value) == (want_opt, want_step)
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(b"\0" * 64)
+    assert lib.bmb_checkpoint_header(str(bad).encode(), None, None, None, 0, None, None) != 0
+    assert b"not a GPT1 checkpoint" in lib.bmb_last_error()
+
+
+def test_registry_csv_feeds_the_reference_merge_tool(tmp_path):
+    """kernel_bench.py's CSV writer, given made-up numbers, produces files the reference's
+    tools/merge_runs.py merges (it keys on kernel_id, kernel, size and reads the four float columns)."""
+    import importlib.util
+    import json
+    import sys
+    spec = importlib.util.spec_from_file_location("kernel_bench", os.path.join(ROOT, "bare-metal-bard_b200", "kernel_bench.py"))
+    kb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(kb)
+    runs = []
+    for i in range(3):
+        p = tmp_path / ("run%d.csv" % i)
+        rows = [dict(kernel_id=k, kernel=n, size=s, gflops_best=1000.0 * k + s + i, gflops_median=900.0 * k + s,
+                     cublas_gflops_best=50000.0, pct_of_cublas=(1000.0 * k + s + i) / 500.0)
+                for k, n in ((1, "simt_fp32"), (2, "tcgen05_tf32")) for s in (1024, 2048)]
+        kb.append_csv(str(p), rows[:2])
+        kb.append_csv(str(p), rows[2:])          # appending must not repeat the header
+        runs.append(str(p))
+    text = open(runs[0]).read().splitlines()
+    assert text[0] == "kernel_id,kernel,size,gflops_best,gflops_median,cublas_gflops_best,pct_of_cublas" and len(text) == 5
+    assert text[1] == "1,simt_fp32,1024,2024.00,1924.00,50000.00,4.05"
+    try:
+        ref = json.load(open(os.path.join(ROOT, "BASELINE.json"))).get("reference_path")
+    except Exception:
+        ref = None
+    tool = os.path.join(ref or "", "tools", "merge_runs.py")
+    if not (ref and os.path.exists(tool)):
+        pytest.skip("reference checkout absent: merge_runs.py not run")
+    out = tmp_path / "merged.csv"
+    r = subprocess.run([sys.executable, tool, str(out)] + runs, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    merged = out.read_text().splitlines()
+    assert merged[0] == text[0] and len(merged) == 5 and merged[1].startswith("1,simt_fp32,1024,2025.00")
