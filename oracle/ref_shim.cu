@@ -9,6 +9,7 @@
 // The train-step driver repeats the call sequence of src/train_gpt.cu:397-464
 // because the reference's CLI cannot express a configuration with a chosen
 // head count, width or vocabulary (src/train_gpt.cu:256-277).
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <thread>
@@ -204,6 +205,39 @@ float ref_trainer_step(void *h, const int *tokens, const int *targets, float lr,
     cudaSetDevice(t->devs[0]);
     return (float)(loss_sum / n);
 }
+// The loss of the last forward pass recomputed from the probability matrix the reference's own
+// softmax_crossentropy_forward left behind: mean over rows (and ranks) of -log(max(p[target], 1e-30)).
+// Why it exists: in the reference's kernel thread 0 reads p[target] for the loss right after the loop
+// that normalises p, with no barrier in between (src/nn.cu:216-220), so at a large vocabulary it can
+// read a value another thread has not normalised yet; the loss gpt_forward returns is then too low for
+// that row.  The probabilities themselves (and with them the gradients) are unaffected, and after the
+// kernel has finished they give the loss the formula defines.
+__global__ void shim_target_prob_k(const float *__restrict__ probs, const int *__restrict__ targets,
+                                   float *__restrict__ out, int N, int Vp) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < N) out[r] = probs[(size_t)r * Vp + targets[r]];
+}
+float ref_trainer_loss_from_probs(void *h) {
+    RefTrainer *t = (RefTrainer *)h;
+    double total = 0.0;
+    for (int r = 0; r < t->n; ++r) {
+        cudaSetDevice(t->devs[r]);
+        GPT &g = t->reps[r];
+        const int N = g.B * g.T, Vp = g.config.padded_vocab;
+        float *d = nullptr;
+        cudaMalloc(&d, N * sizeof(float));
+        shim_target_prob_k<<<(N + 255) / 256, 256>>>(g.acts.probs, g.d_targets, d, N, Vp);
+        std::vector<float> hp(N);
+        cudaMemcpy(hp.data(), d, N * sizeof(float), cudaMemcpyDeviceToHost);
+        cudaFree(d);
+        double s = 0.0;
+        for (int i = 0; i < N; ++i) s += -log((double)fmaxf(hp[i], 1e-30f));
+        total += s / N;
+    }
+    cudaSetDevice(t->devs[0]);
+    return (float)(total / t->n);
+}
+
 void ref_trainer_destroy(void *h) {
     RefTrainer *t = (RefTrainer *)h;
     for (int r = 0; r < t->n; ++r) {

@@ -106,6 +106,7 @@ def load_reference():
         "ref_trainer_get_grads": (None, [_p, _p]),
         "ref_trainer_forward_backward": (_f, [_p, _p, _p]),
         "ref_trainer_step": (_f, [_p, _p, _p, _f, _i]),
+        "ref_trainer_loss_from_probs": (_f, [_p]),
         "ref_trainer_destroy": (None, [_p]),
     }
     for n, (r, a) in sig.items():

@@ -48,17 +48,26 @@ def reference_run(ref, cuda):
     toks, tgts = batches()
     ref.ref_trainer_forward_backward(h, _np(toks[0]), _np(tgts[0]))
     ref.ref_trainer_get_grads(h, _np(grads0))
-    losses = [ref.ref_trainer_step(h, _np(toks[s]), _np(tgts[s]), HP["lr"], s + 1) for s in range(STEPS)]
+    returned, losses = [], []
+    for s in range(STEPS):
+        returned.append(ref.ref_trainer_step(h, _np(toks[s]), _np(tgts[s]), HP["lr"], s + 1))
+        # The loss the reference's formula defines, recomputed from the probabilities its own kernel wrote.
+        # At this vocabulary the value gpt_forward returns is too low by a few hundredths: the loss kernel's
+        # thread 0 reads p[target] without a barrier after the loop that normalises p (src/nn.cu:216-220), so
+        # for some rows it sees a value not yet divided by the row sum.  The probabilities (hence gradients and
+        # parameters) are unaffected; the comparison below uses the race-free value and reports the other.
+        losses.append(ref.ref_trainer_loss_from_probs(h))
     ref.ref_trainer_destroy(h)
     cuda.cuda.set_device(0)
     cuda.cuda.empty_cache()
-    return dict(n=n, params0=params0, grads0=grads0, losses=np.array(losses, np.float64))
+    return dict(n=n, params0=params0, grads0=grads0, losses=np.array(losses, np.float64),
+                returned=np.array(returned, np.float64))
 
 
 # (mode, fused, per-step loss bar, normwise bar on the first gradient).  The gradient bars: fp32 differs
 # from the reference by summation order only; TF32 rounds every GEMM and attention operand to 10 mantissa
-# bits (measured on this configuration: see the printed value).
-MODES = [("fp32", 0, 2e-3, 1e-4), ("tf32", 1, 2e-2, 2e-2)]
+# bits (measured on this configuration: 2.9e-6 in fp32, 1.1e-3 in TF32, max-norm; the test prints both).
+MODES = [("fp32", 0, 2e-3, 1e-4), ("tf32", 1, 2e-2, 5e-3)]
 
 
 @pytest.mark.parametrize("mode,fused,loss_bar,grad_bar", MODES)
@@ -88,8 +97,10 @@ def test_gpt124m_20_steps_vs_reference_trainer(bmb, cuda, reference_run, capsys,
     gap = np.abs(np.array(losses, np.float64) - reference_run["losses"])
     with capsys.disabled():
         print("\n[gpt124m %s] first-step gradient vs reference: max-norm %.3e, l2 %.3e; loss gap over %d steps: max %.3e "
-              "(loss %.4f -> %.4f, reference %.4f -> %.4f)" % (mode, e_max, e_l2, STEPS, gap.max(), losses[0], losses[-1],
-                                                           reference_run["losses"][0], reference_run["losses"][-1]))
+              "(loss %.4f -> %.4f, reference %.4f -> %.4f; the value the reference's gpt_forward returned, with its "
+              "unsynchronised read, was lower by up to %.3f)" % (mode, e_max, e_l2, STEPS, gap.max(), losses[0], losses[-1],
+                                                             reference_run["losses"][0], reference_run["losses"][-1],
+                                                             (reference_run["losses"] - reference_run["returned"]).max()))
     assert np.all(np.isfinite(losses))
     assert e_max < grad_bar, e_max
     assert gap.max() < loss_bar, gap
@@ -170,7 +181,10 @@ def test_tensorcore_gemm_forced_tile_heights(bmb, cuda, ta, tb, M, N, K, beta, h
         num += float((diff * diff).sum())
         den += float((want * want).sum())
     err = (num / den) ** 0.5
-    assert err < 2e-5, err
+    # fp32 accumulation of K products inside the tensor core is what the bound has to leave room for: measured
+    # 1.7e-5 at K = 8192 and 1.0e-4 at K = 50304 (it grows with K; parts of a tile summed by different CTAs grow
+    # less).  Either way far inside the 5e-4 the TF32 registry entry allows against an fp32 product.
+    assert err < (2e-5 if K <= 8192 else 2e-4), err
 
 
 @pytest.mark.parametrize("name,ta,tb,M,N,K", [("QK^T", 0, 1, 1024, 1024, 64), ("PV", 0, 0, 1024, 64, 1024)])
@@ -181,7 +195,7 @@ def test_attention_shaped_batched_gemm_at_full_size_vs_reference(bmb, ref, cuda,
     g = cuda.Generator(device="cuda").manual_seed(33)
     A = cuda.randn(batch * M * K, device="cuda", generator=g)
     B = cuda.randn(batch * K * N, device="cuda", generator=g)
-    want = cuda.full((batch * M * N,), float("nan"), device="cuda")
+    want = cuda.zeros(batch * M * N, device="cuda")       # the reference's kernel reads C even when beta is 0
     ref.ref_batched_gemm(ta, tb, batch, M, N, K, 1.0, A.data_ptr(), M * K, B.data_ptr(), K * N, 0.0, want.data_ptr(), M * N)
     cuda.cuda.synchronize()
     lib = bmb.lib()

@@ -181,7 +181,8 @@ def test_gpt1_checkpoints_both_ways_and_sampling(bmb, cuda, text_file, tmp_path)
     assert has_opt.value == 1 and step.value == 1
     rc, out = run([exe("ref_train_gpt"), "--load", ck_bmb, "--len", "16", "-b", "2"])
     assert rc == 0 and "loaded" in out and ("%d layers" % cfg[3]) in out, out[-2000:]
-    # resume: a second trainer restored from the file continues exactly like the first
+    # resume: a second trainer restored from the file continues like the first (the token-embedding gradient is
+    # summed with atomics, so two runs of one step agree to rounding, not bit for bit)
     tr2 = bmb.Trainer(seed=99, use_flash=1, math=bmb.MATH_FP32, B=2, T=cfg[0], **model)
     assert tr2.load(ck_bmb, optimizer_state=True) == 1
     for t_ in (tr, tr2):
@@ -190,7 +191,7 @@ def test_gpt1_checkpoints_both_ways_and_sampling(bmb, cuda, text_file, tmp_path)
     q = np.empty_like(p)
     tr.get_params(p)
     tr2.get_params(q)
-    assert np.array_equal(p, q)
+    assert float(np.linalg.norm(p.astype(np.float64) - q) / np.linalg.norm(p.astype(np.float64))) < 1e-6
     tr.close()
     tr2.close()
 
