@@ -5,8 +5,8 @@
 // The (T x T) score matrix never leaves tensor memory and registers (src/flash.h:1-34).
 //
 // One CTA owns 256 consecutive queries of one (batch, head) as two tiles of
-// 128 and walks the keys up to the diagonal: shared-memory stages and S
-// products cover 128 keys, softmax steps 64.  384 threads:
+// 128 and walks the keys up to the diagonal: shared-memory stages cover 128
+// keys, S products and softmax steps 64.  384 threads:
 //   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: a thread reads 64 scores
 //                    of its row from TMEM (tcgen05.ld), masks the diagonal,
 //                    updates the running max and sum (the scale rides in the
@@ -17,10 +17,11 @@
 //                    o = o * exp2(m_old - m_new) + PV;
 //   warp 8           producer: TMA loads of the two Q tiles, then K blocks into
 //                    a 2-deep ring and V blocks into a 3-deep ring;
-//   warp 9           issuer of S_t = Q_t K_j^T (N = 128: one instruction costs
-//                    the tensor pipe its 64 cycles, whereas a thread cannot
-//                    issue N = 64 instructions as fast as the pipe retires
-//                    them), as soon as the group has taken S_t(j-1) out of TMEM;
+//   warp 9           issuer of S_t = Q_t K_j^T, 64 keys (one half of the tile's
+//                    128-column S buffer) at a time, each half as soon as the
+//                    group has taken that half of the previous block out of
+//                    TMEM -- the next block's first scores are multiplied while
+//                    the group still works on this block's second half;
 //   warps 10, 11     issuers of PV_t = P_t V for tile 0 / tile 1 (A operand read from
 //                    tensor memory, 64 keys per step) as soon as P_t is written.
 // Three issuing threads keep the next block's scores from queueing behind a wait
@@ -85,8 +86,9 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
     // barrier indices
+    // S_FULL / S_EMPTY: one pair per query tile and per 64-key half of the S buffer (index 2 * tile + half)
     enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + K_STAGES, V_FULL = K_EMPTY + K_STAGES, V_EMPTY = V_FULL + V_STAGES,
-           S_FULL = V_EMPTY + V_STAGES, S_EMPTY = S_FULL + NQ, P_FULL = S_EMPTY + NQ, PV_FULL = P_FULL + NQ, NBARS = PV_FULL + NQ };
+           S_FULL = V_EMPTY + V_STAGES, S_EMPTY = S_FULL + 2 * NQ, P_FULL = S_EMPTY + 2 * NQ, PV_FULL = P_FULL + NQ, NBARS = PV_FULL + NQ };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -115,7 +117,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
         for (int s = 0; s < V_STAGES; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), NQ); }   // one release per P V issuer
         for (int t = 0; t < NQ; ++t) {
-            mbar_init(bar(S_FULL + t), 1); mbar_init(bar(S_EMPTY + t), 4);
+            for (int hf = 0; hf < 2; ++hf) { mbar_init(bar(S_FULL + 2 * t + hf), 1); mbar_init(bar(S_EMPTY + 2 * t + hf), 4); }
             mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_FULL + t), 1);
         }
         *giveup = 0;
@@ -174,7 +176,12 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     } else if (warp == 9) {
         // ----------------------------------------------------- issuer of S = Q K^T
         if (lane == 0) {
-            const uint32_t idesc_s = make_idesc(2, 0, 0, KBLK, QT);    // Q (K-major) x K (K-major), 128 keys at a time
+            // Q (K-major) x K (K-major), 64 keys at a time: each half of the 128-column S buffer is refilled as
+            // soon as the softmax group has taken that half out of tensor memory, so the scores of the next
+            // block's first 64 keys are being multiplied while the group still works on this block's last 64.
+            // (An N = 64 instruction occupies the pipe longer than its 32 cycles of arithmetic; that is the
+            // price of not leaving the pipe idle while a whole 128-key buffer drains.)
+            const uint32_t idesc_s = make_idesc(2, 0, 0, KB, QT);
 #ifdef BMB_FLASH_TRACE
             // issuer phases of CTA (0, 0): 9 wait K, 10 wait S_EMPTY, 11 issue S
             const bool tr = (blockIdx.x == 0 && blockIdx.y == 0);
@@ -188,22 +195,25 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                 if (!mbar_wait(bar(K_FULL + st), (uint32_t)((j / K_STAGES) & 1), giveup)) { ok = false; break; }
                 TRI(9);
                 const uint32_t ka = base + OFF_K + st * KV_TILE_BYTES;
-                for (int t = 0; t < NQ; ++t) {
-                    if (j >= nblk[t]) continue;
-                    // the group has taken block j-1's scores out of tensor memory
-                    if (j > 0 && !mbar_wait(bar(S_EMPTY + t), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
-                    fence_after();
-                    TRI(10);
-                    const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES;
-                    const uint32_t d = tmem_base + (uint32_t)(t * TILE_COLS);
+                for (int hf = 0; ok && hf < 2; ++hf) {
+                    for (int t = 0; t < NQ; ++t) {
+                        if (2 * j + hf >= nstep[t]) continue;
+                        // the group has taken this half of block j-1's scores out of tensor memory
+                        if (j > 0 && !mbar_wait(bar(S_EMPTY + 2 * t + hf), (uint32_t)((j - 1) & 1), giveup)) { ok = false; break; }
+                        fence_after();
+                        TRI(10);
+                        const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES;
+                        const uint32_t d = tmem_base + (uint32_t)(t * TILE_COLS + hf * KB);
+                        const uint32_t kh = ka + (uint32_t)(hf * (KB * 128));          // key rows 64 hf .. 64 hf + 63 of the block
 #pragma unroll
-                    for (int ks = 0; ks < HS / 8; ++ks) {
-                        const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-                        mma_tf32(d, smem_desc_kmajor(qa + half * (QT * 128) + off),
-                                 smem_desc_kmajor(ka + half * (KBLK * 128) + off), idesc_s, ks ? 1u : 0u);
+                        for (int ks = 0; ks < HS / 8; ++ks) {
+                            const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+                            mma_tf32(d, smem_desc_kmajor(qa + half * (QT * 128) + off),
+                                     smem_desc_kmajor(kh + half * (KBLK * 128) + off), idesc_s, ks ? 1u : 0u);
+                        }
+                        commit(bar(S_FULL + 2 * t + hf));
+                        TRI(11);
                     }
-                    commit(bar(S_FULL + t));
-                    TRI(11);
                 }
                 if (!ok) break;
                 commit(bar(K_EMPTY + st));      // every product that reads this K block has been issued
@@ -267,20 +277,16 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
 #endif
             for (int j = 0; j < nb; ++j) {
                 TR(0);
-                // one S product covers two steps: wait for it on the even step, release it on the odd (or last) one
-                if (!(j & 1)) {
-                    if (!mbar_wait(bar(S_FULL + t), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
-                    fence_after();
-                }
+                // every step has its own half of the S buffer: wait for its product, take it, hand the half back
+                if (!mbar_wait(bar(S_FULL + 2 * t + (j & 1)), (uint32_t)((j >> 1) & 1), giveup)) { ok = false; break; }
+                fence_after();
                 TR(1);
                 float s[KB];
                 tmem_ld64(s_addr + (uint32_t)((j & 1) * KB), s);
                 TR(2);
-                if ((j & 1) || j + 1 == nb) {
-                    fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(S_EMPTY + t));       // S_t may be overwritten
-                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(S_EMPTY + 2 * t + (j & 1)));       // this half may be overwritten
 
                 // m is the running maximum of the raw scores (the scale is positive, so the order is
                 // the same); the scale rides in the exponent's multiply-add.

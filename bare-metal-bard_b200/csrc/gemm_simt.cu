@@ -241,6 +241,9 @@ __global__ void scale_c_k(float *C, long long n, float beta) {
 
 }  // namespace
 
+int gemm_simt_tma(int transA, int transB, int batch, int M, int N, int K, float alpha, const float *A, long long sA,
+                  const float *B, long long sB, float beta, float *C, long long sC, cudaStream_t st);
+
 int gemm_simt(int transA, int transB, int batch, int M, int N, int K, float alpha, const float *A,
               long long sA, const float *B, long long sB, float beta, float *C, long long sC,
               cudaStream_t st) {
@@ -255,6 +258,11 @@ int gemm_simt(int transA, int transB, int batch, int M, int N, int K, float alph
         }
         BMB_LAUNCH_CHECK();
         return BMB_OK;
+    }
+    // NN and TN on aligned shapes: the kernel fed by the copy engine (gemm_simt_tma.cu)
+    {
+        const int rc = gemm_simt_tma(transA, transB, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st);
+        if (rc != BMB_E_UNSUPPORTED) return rc;
     }
     if (!transA && !transB) return launch_simt<false, false>(batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st);
     if (!transA && transB)  return launch_simt<false, true >(batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st);

@@ -76,6 +76,21 @@ __host__ __device__ constexpr int stages_for(int mh) { return mh == 2 ? 3 : STAG
 constexpr int smem_bytes(int bn, int mh = 1) { return stages_for(mh) * (mh * A_BYTES + bn * KBYTES) + 1024 /*align*/ + 256 /*barriers*/ + EPI_BYTES; }
 constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 128 bytes of M/N
 
+#ifdef BMB_GEMM_TRACE
+// Developer timeline (compiled in only with -DBMB_GEMM_TRACE): per CTA, nanosecond stamps of kernel entry,
+// set-up done, first copy issued, first slice landed, last product issued, first accumulator ready,
+// last tile stored, stores landed, exit.
+__device__ unsigned long long g_gemm_trace[256][10];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define GTR(i) do { g_gemm_trace[blockIdx.x & 255][(i)] = gtime(); } while (0)
+#else
+#define GTR(i)
+#endif
+
 struct TileSched {
     int tiles_m, tiles_n, num_tiles;
     __host__ __device__ __forceinline__ void coords(int tile, int &tm, int &tn) const {
@@ -216,6 +231,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     int tile, kb0, kb1;
 
     if (threadIdx.x == 0) {
+        GTR(0);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); armed[s] = -1; }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, EPI_WARPS); }
         *giveup = 0;
@@ -226,6 +242,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) GTR(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -233,6 +250,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+#ifdef BMB_GEMM_TRACE
+            bool first_copy = true;
+#endif
             while (ok && wi.next(tile, kb0, kb1)) {
                 int tm, tn;
                 const int bi = tile / tiles_per_problem;
@@ -261,6 +281,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     } else {
                         tma_load_2d(sb, &mapB, k0, b_row0 + tn * BN, fb);
                     }
+#ifdef BMB_GEMM_TRACE
+                    if (first_copy) { GTR(2); first_copy = false; }
+#endif
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
@@ -279,6 +302,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0, acc = 0;
             uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
+#ifdef BMB_GEMM_TRACE
+            bool first_slice = true;
+#endif
             while (ok && wi.next(tile, kb0, kb1)) {
                 if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
                 fence_after();
@@ -286,6 +312,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
                     fence_after();
+#ifdef BMB_GEMM_TRACE
+                    if (first_slice) { GTR(3); first_slice = false; }
+#endif
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + MH * A_BYTES;
 #pragma unroll
                     for (int k = 0; k < KBYTES / 32; ++k) {
@@ -303,6 +332,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 }
                 if (!ok) break;
                 commit(tfull0 + 8 * acc);               // accumulator complete
+                GTR(4);
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
         }
@@ -324,6 +354,9 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             const bool whole = (kb0 == 0 && kb1 == kblocks);
             if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
             fence_after();
+#ifdef BMB_GEMM_TRACE
+            if (warp == 2 && lane == 0 && g_gemm_trace[blockIdx.x & 255][9] == 0) { GTR(5); g_gemm_trace[blockIdx.x & 255][9] = 1; }
+#endif
             // The accumulator leaves TMEM one row per thread; the rows are parked in shared memory and
             // written out four rows per instruction, each row segment a contiguous 128 bytes, so that
             // the global stores (loads of C, atomics) are fully coalesced.  A whole tile is stored; a
@@ -414,8 +447,14 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
             if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+#ifdef BMB_GEMM_TRACE
+            if (warp == 2 && lane == 0) GTR(6);
+#endif
         }
         if (c_mode && lane == 0) tma_store_wait_all();   // every block this warp handed to the copy engine has landed
+#ifdef BMB_GEMM_TRACE
+        if (warp == 2 && lane == 0) GTR(7);
+#endif
     }
 
     fence_before();
@@ -429,6 +468,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         *reinterpret_cast<volatile int *>(status) = 1;
         __threadfence_system();
     }
+    if (threadIdx.x == 0) GTR(8);
 }
 
 // ---- operand prepass --------------------------------------------------------
@@ -779,3 +819,13 @@ extern "C" int bmb_gemm_schedule_check(int math, int flags, int batch, int M, in
         if (!seen[i]) return fail(BMB_E_LIMIT, "schedule_check: tile %zu slice %zu never computed", i / p.kblocks, i % p.kblocks);
     return BMB_OK;
 }
+
+#ifdef BMB_GEMM_TRACE
+// Developer entry point: copy out (and clear) the per-CTA timeline of the last tensor-core GEMM launch.
+extern "C" int bmb_dbg_gemm_trace(unsigned long long *host_256x10) {
+    cudaError_t e = cudaMemcpyFromSymbol(host_256x10, bmb::g_gemm_trace, sizeof(unsigned long long) * 2560);
+    if (e != cudaSuccess) return (int)e;
+    static unsigned long long zeros[2560];
+    return (int)cudaMemcpyToSymbol(bmb::g_gemm_trace, zeros, sizeof(zeros));
+}
+#endif

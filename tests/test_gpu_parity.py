@@ -67,6 +67,26 @@ def test_sgemm_1024_seed0_config(bmb, orc, cuda):
     assert e.name == b"simt_fp32" and err < e.tol
 
 
+@pytest.mark.parametrize("ta", [0, 1])
+def test_gemm_fp32_tma_fed_kernel_is_bit_identical_to_the_register_staged_one(bmb, orc, cuda, monkeypatch, ta):
+    """NN and TN on aligned shapes run on the SIMT kernel whose operand slices arrive by TMA.  Same k order,
+    same fused multiply-add: against the CPU oracle's sequential fmaf chain (orc_gemm) the result is exact
+    for alpha 1, beta 0, and a long K (many trips round the 3-slot ring) with beta != 0 stays within 1e-6."""
+    M, N, K = 256, 384, 2048
+    A, B, C0 = uniform(M * K, 21), uniform(K * N, 22), uniform(M * N, 23)
+    want = np.zeros(M * N, np.float32)
+    orc.orc_gemm(ta, 0, M, N, K, 1.0, _np(A), _np(B), 0.0, _np(want))
+    dA, dB = dev(cuda, A), dev(cuda, B)
+    dC = cuda.full((M * N,), float("nan"), device="cuda")
+    bmb.call("bmb_gemm_ex", bmb.MATH_FP32, 0, ta, 0, M, N, K, 1.0, dA, dB, 0.0, dC, None)
+    assert np.array_equal(host(cuda, dC), want)
+    want2 = C0.copy()
+    orc.orc_gemm(ta, 0, M, N, K, 0.75, _np(A), _np(B), 1.25, _np(want2))
+    dC = dev(cuda, C0)
+    bmb.call("bmb_gemm_ex", bmb.MATH_FP32, 0, ta, 0, M, N, K, 0.75, dA, dB, 1.25, dC, None)
+    assert normwise(host(cuda, dC), want2) < 1e-6
+
+
 def test_gemm_beta_zero_ignores_garbage_and_k0(bmb, cuda):
     dA, dB = dev(cuda, uniform(128 * 16, 1)), dev(cuda, uniform(16 * 128, 2))
     dC = cuda.full((128 * 128,), float("nan"), device="cuda")
@@ -79,7 +99,8 @@ def test_gemm_beta_zero_ignores_garbage_and_k0(bmb, cuda):
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
-@pytest.mark.parametrize("batch,M,N,K", [(24, 64, 64, 32), (8, 100, 48, 33), (12, 256, 256, 64), (12, 256, 64, 256)])
+@pytest.mark.parametrize("batch,M,N,K", [(24, 64, 64, 32), (8, 100, 48, 33), (12, 256, 256, 64), (12, 256, 64, 256),
+                                         (3, 128, 256, 96)])   # the last: aligned, NN / TN go to the kernel fed by TMA
 def test_batched_gemm_vs_oracle(bmb, orc, cuda, ta, tb, batch, M, N, K):
     A, B, C0 = normal(batch * M * K, 1), normal(batch * K * N, 2), normal(batch * M * N, 3)
     want = C0.copy()
