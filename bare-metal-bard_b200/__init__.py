@@ -18,6 +18,8 @@ LIB_PATH = os.path.join(HERE, "libbmb.so")
 MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2
 GEMM_A_ROUNDED, GEMM_B_ROUNDED, GEMM_C_ROUNDED, GEMM_NO_SPLIT = 1, 2, 4, 8
 GEMM_TILE_M128, GEMM_TILE_M256 = 16, 32
+GEMM_PAIR, GEMM_NO_PAIR = 64, 128
+GEMM_HALF_SMS = 256
 FLASH_OPERANDS_ROUNDED = 1
 E_UNSUPPORTED = 3
 E_TIMEOUT = 4

@@ -471,6 +471,257 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     if (threadIdx.x == 0) GTR(8);
 }
 
+// ---- the same GEMM on CTA pairs ----------------------------------------------------------------
+// TF32 only.  Two CTAs (a cluster of 2, on neighbouring SMs) share one 256 x BN output tile: each loads
+// its own 128 rows of A and HALF of the B slice, one thread of the leader CTA issues
+// tcgen05.mma.cta_group::2 (M = 256) for both, and each CTA ends up with its 128 x BN block of the
+// accumulator in its own tensor memory.  Against one CTA per 128 x 256 tile this halves the B bytes every
+// SM has to land in and feed from shared memory (with fp32 operands it is shared-memory bandwidth that
+// bounds a 128 x 256 tile at about two thirds of the tensor pipe's rate), and unlike the two-block tile
+// of one CTA the accumulators stay double-buffered, so the epilogue of a tile still hides behind the
+// next tile's products.
+//   producer (warp 0, both CTAs)   waits for its own slot to be free, the leader arms its "full" barrier
+//                                  with the bytes of BOTH CTAs, and each CTA's copies complete on the
+//                                  leader's barrier (TMA without any multicast);
+//   issuer (warp 1, leader only)   as in gemm_tc_k; when a slot's products retire it releases the slot in
+//                                  both CTAs, and hands a finished accumulator to both CTAs' epilogues;
+//   epilogue (warps 2..9, both)    as in gemm_tc_k, on the CTA's own 128 rows; the accumulator is handed
+//                                  back by arriving on the leader's barrier.
+// Work items are per pair.  Waits are bounded as everywhere; a pair leaves together (cluster barrier).
+constexpr int PAIR_STAGES = 5;
+constexpr int pair_smem_bytes(int bn) { return PAIR_STAGES * (A_BYTES + (bn / 2) * KBYTES) + 1024 + 256 + EPI_BYTES; }
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
+gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+               const __grid_constant__ CUtensorMap mapC, int c_mode, int M, int N, int kblocks, int kelems_per_block,
+               int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C, int vec_ok, int dp_tiles, int g_sk,
+               const float *__restrict__ bias, int round_c, int *__restrict__ status) {
+    constexpr int STAGES = PAIR_STAGES, BMT = 2 * BM, BH = BN / 2;
+    constexpr int B_BYTES = BH * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t ACC_COLS = BN > 128 ? 256 : 128;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(gen + STAGES * STAGE_BYTES + EPI_BYTES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+
+    TileSched sch;
+    sch.tiles_m = (M + BMT - 1) / BMT;
+    sch.tiles_n = (N + BN - 1) / BN;
+    sch.num_tiles = sch.tiles_m * sch.tiles_n;
+    WorkIter wi;
+    wi.init((int)(blockIdx.x >> 1), (int)(gridDim.x >> 1), dp_tiles, sch.num_tiles - dp_tiles, kblocks, g_sk);
+    int tile, kb0, kb1;
+
+    if (threadIdx.x == 0) {
+        // full: the leader's own arrival (with the byte count of both CTAs); empty, tmem_full: one arrival
+        // from the leader's issuer per use; tmem_empty (used in the leader only): the epilogue warps of both CTAs
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 2 * EPI_WARPS); }
+        *giveup = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    cluster_sync_all();                                // both CTAs' barriers exist before anyone signals across
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // Each CTA asked its own SM for all the columns it will ever use, so both got the same address; the
+    // pair instruction writes the same columns on both SMs and relies on that.
+    if (threadIdx.x == 0 && rank == 0 && ld_shared_cluster_u32(map_to_cta(smem_u32(tmem_slot), 1)) != tmem_base) *giveup = 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (each CTA for its own tiles)
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            int armed_par[STAGES];
+            for (int i = 0; i < STAGES; ++i) armed_par[i] = -1;
+            while (ok && wi.next(tile, kb0, kb1)) {
+                int tm, tn;
+                sch.coords(tile, tm, tn);
+                const int a_x0 = tm * BMT + (int)rank * BM, b_x0 = tn * BN + (int)rank * BH;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; }
+                    const uint32_t fb_local = full0 + 8 * s;
+                    if (rank == 0) { mbar_arrive_expect_tx(fb_local, 2 * STAGE_BYTES); armed_par[s] = (int)ph; }
+                    const uint32_t fb = map_to_cta(fb_local, 0);
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+                    const int k0 = kb * kelems_per_block;
+                    if (a_mn == 2) tma_load_3d_pair(sa, &mapA, 0, k0, a_x0 / 32, fb);
+                    else tma_load_2d_pair(sa, &mapA, k0, a_x0, fb);
+                    if (b_mn == 2) tma_load_3d_pair(sb, &mapB, 0, k0, b_x0 / 32, fb);
+                    else tma_load_2d_pair(sb, &mapB, k0, b_x0, fb);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+            // Do not leave while the issuer's releases of the last slots may still be on their way to this
+            // CTA's barriers: wait until every slot has been handed back.
+            for (int i = 0; ok && i < STAGES; ++i) {
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) ok = false;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+            if (!ok && rank == 0) {
+                // the leader's barriers count the bytes of both CTAs: once they have completed, no copy of
+                // the pair is in flight any more (the peer stays until the cluster barrier at the end)
+                for (int i = 0; i < STAGES; ++i)
+                    if (armed_par[i] >= 0) mbar_drain(full0 + 8 * i, (uint32_t)armed_par[i]);
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc(2u, a_mn ? 1u : 0u, b_mn ? 1u : 0u, BN, BMT);
+            const uint32_t a_step = a_mn ? 1024u : 32u, b_step = b_mn ? 1024u : 32u;
+            const uint32_t peer_empty0 = map_to_cta(empty0, 1), peer_tfull0 = map_to_cta(tfull0, 1);
+            int s = 0, acc = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            bool ok = true;
+            while (ok && wi.next(tile, kb0, kb1)) {
+                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
+                fence_after();
+                const uint32_t d = tmem_base + (uint32_t)acc * ACC_COLS;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
+                    fence_after();
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < KBYTES / 32; ++k) {
+                        const uint64_t db = b_mn ? smem_desc_mnmajor32(sb + k * b_step, CHUNK_BYTES) : smem_desc_kmajor(sb + k * b_step);
+                        const uint64_t da = a_mn ? smem_desc_mnmajor32(sa + k * a_step, CHUNK_BYTES) : smem_desc_kmajor(sa + k * a_step);
+                        mma_tf32_pair(d, da, db, idesc, ((kb - kb0) | k) ? 1u : 0u);
+                    }
+                    commit_pair(empty0 + 8 * s);                 // the slot is reusable, here ...
+                    commit_pair(peer_empty0 + 8 * s);            // ... and in the peer CTA
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                commit_pair(tfull0 + 8 * acc);
+                commit_pair(peer_tfull0 + 8 * acc);
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (each CTA for its own 128 rows)
+        const int q = warp & 3;
+        const int wgroup = (warp - 2) >> 2;
+        const uint32_t leader_tempty0 = map_to_cta(tempty0, 0);
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        while (ok && wi.next(tile, kb0, kb1)) {
+            int tm, tn;
+            sch.coords(tile, tm, tn);
+            const bool whole = (kb0 == 0 && kb1 == kblocks);
+            if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
+            fence_after();
+            const int row_base = tm * BMT + (int)rank * BM + q * 32;
+            const uint32_t trow = tmem_base + (uint32_t)acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+            float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES) + (warp - 2) * (32 * 32);
+            const int sub_r = lane >> 3, sub_u = lane & 7, sub_c = sub_u * 4;
+            const float *part_bias = (kb0 == 0) ? bias : nullptr;
+#pragma unroll 1
+            for (int c = wgroup; c < BN / 32; c += 2) {
+                const int n0 = tn * BN + c * 32;
+                if (n0 >= N) break;
+                if (whole && c_mode == 3) {
+                    float lo[16], hi[16];
+                    tmem_ld_16x256b_x4_nowait(trow + (uint32_t)(c * 32), lo);
+                    tmem_ld_16x256b_x4_nowait(trow + (uint32_t)(c * 32) + (16u << 16), hi);
+                    tmem_wait_ld();
+                    const int r0 = row_base + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int n = n0 + 8 * j + cq;
+                        if (n >= N) continue;
+                        float2 bb = make_float2(0.f, 0.f);
+                        if (bias) bb = *reinterpret_cast<const float2 *>(bias + n);
+                        float2 o[4] = {make_float2(lo[4 * j], lo[4 * j + 1]), make_float2(lo[4 * j + 2], lo[4 * j + 3]),
+                                       make_float2(hi[4 * j], hi[4 * j + 1]), make_float2(hi[4 * j + 2], hi[4 * j + 3])};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int m = r0 + 8 * k;
+                            float2 x = make_float2(fmaf(alpha, o[k].x, bb.x), fmaf(alpha, o[k].y, bb.y));
+                            if (round_c) x = make_float2(round_tf32(x.x), round_tf32(x.y));
+                            if (m < M) *reinterpret_cast<float2 *>(C + (size_t)m * N + n) = x;
+                        }
+                    }
+                    continue;
+                }
+                float v[32];
+                tmem_ld32(trow + (uint32_t)(c * 32), v);
+                if (c_mode) {
+                    if (row_base >= M) continue;
+                    const float *bsrc = whole ? bias : part_bias;
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        float4 o = make_float4(alpha * v[4 * u], alpha * v[4 * u + 1], alpha * v[4 * u + 2], alpha * v[4 * u + 3]);
+                        if (bsrc && n0 + 4 * u < N) {
+                            const float4 bb = *reinterpret_cast<const float4 *>(bsrc + n0 + 4 * u);
+                            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                        }
+                        if (round_c) o = make_float4(round_tf32(o.x), round_tf32(o.y), round_tf32(o.z), round_tf32(o.w));
+                        *reinterpret_cast<float4 *>(stg + lane * 32 + ((u ^ (lane & 7)) << 2)) = o;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (whole && c_mode == 1) tma_store_2d(&mapC, smem_u32(stg), n0, row_base);
+                        else tma_reduce_add_2d(&mapC, smem_u32(stg), n0, row_base);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    *reinterpret_cast<float4 *>(stg + lane * 32 + ((u ^ (lane & 7)) << 2)) =
+                        make_float4(alpha * v[4 * u], alpha * v[4 * u + 1], alpha * v[4 * u + 2], alpha * v[4 * u + 3]);
+                __syncwarp();
+                const int n = n0 + sub_c;
+                const bool vec = vec_ok && (n + 4 <= N);
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int row = rr * 4 + sub_r;
+                    const float4 o = *reinterpret_cast<const float4 *>(stg + row * 32 + ((sub_u ^ (row & 7)) << 2));
+                    if (whole) store_result(o, C, M, N, row_base + row, n, vec, beta, bias, round_c);
+                    else add_result(o, C, M, N, row_base + row, n, vec, part_bias);
+                }
+                __syncwarp();
+            }
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * acc);      // the issuer counts both CTAs' warps
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+        if (c_mode && lane == 0) tma_store_wait_all();
+    }
+
+    fence_before();
+    __syncthreads();
+    cluster_sync_all();          // neither CTA leaves (or frees tensor memory) while the other may still signal it
+    if (warp == 1) {
+        __syncwarp();
+        fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *giveup) {
+        *reinterpret_cast<volatile int *>(status) = 4;
+        __threadfence_system();
+    }
+}
+
 // ---- operand prepass --------------------------------------------------------
 template <typename OUT>
 __device__ __forceinline__ OUT cvt_out(float x);
@@ -664,11 +915,55 @@ void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int 
 }
 
 // Everything the launch decides about how the tiles are handed out.
-struct Plan { int bn, mh, kblocks, tiles_m, tiles_n, tiles, dp_tiles, sk_tiles, g_sk, grid; };
+struct Plan { int bn, mh, kblocks, tiles_m, tiles_n, tiles, dp_tiles, sk_tiles, g_sk, grid; bool pair; };
+
+// CTA pairs this device can keep resident at once for the pair kernel (one CTA per SM, clusters of 2).
+int pair_clusters();
+
+// Whether a problem goes to the pair kernel: TF32, one problem, at least one 256 x 256 tile, and operands
+// the pair kernel's loads take (an M- or N-contiguous operand needs its extent to be a multiple of 32).
+// BMB_GEMM_PAIR / BMB_GEMM_NO_PAIR in the flags decide for a call; the environment variable
+// BMB_GEMM_PAIR=0 turns the default off.
+bool wants_pair(bool bf16, int flags, int transA, int transB, int batch, int M, int N) {
+    static const bool env_on = [] { const char *e = getenv("BMB_GEMM_PAIR"); return !(e && atoi(e) == 0); }();
+    if (bf16 || batch != 1 || M < 2 * BM || N < 256) return false;
+    if ((transA && M % 32) || (!transB && N % 32)) return false;
+    if (flags & BMB_GEMM_NO_PAIR) return false;
+    if (flags & (BMB_GEMM_TILE_M128 | BMB_GEMM_TILE_M256)) return (flags & BMB_GEMM_PAIR) != 0;
+    return (flags & BMB_GEMM_PAIR) ? true : env_on;
+}
+
+// The pair kernel's plan: 256 x 256 tiles handed to `clusters` CTA pairs; what does not fill a wave of
+// pairs is shared along K like in the one-CTA kernel.
+void plan_pair(Plan *p, int flags, int M, int N, int clusters) {
+    p->pair = true;
+    p->bn = 256;
+    p->mh = 2;
+    p->tiles_m = (M + 2 * BM - 1) / (2 * BM);
+    p->tiles_n = (N + 255) / 256;
+    p->tiles = p->tiles_m * p->tiles_n;
+    const bool allow_split = !(flags & (BMB_GEMM_NO_SPLIT | BMB_GEMM_C_ROUNDED));
+    const int full = p->tiles / clusters, rem = p->tiles % clusters;
+    p->dp_tiles = p->tiles;
+    if (allow_split && rem && p->kblocks >= 8) {
+        const double whole = (double)(full + 1) * (p->kblocks + 4.0);
+        const double shared = (double)full * (p->kblocks + 4.0) + (double)(((long long)rem * p->kblocks + clusters - 1) / clusters) + 10.0;
+        if (shared < whole) p->dp_tiles = p->tiles - rem;
+    }
+    p->sk_tiles = p->tiles - p->dp_tiles;
+    p->g_sk = 1;
+    if (p->sk_tiles > 0) {
+        const long long runs = (long long)p->sk_tiles * p->kblocks / 4;
+        p->g_sk = (int)(runs < 1 ? 1 : (runs > clusters ? clusters : runs));
+    }
+    p->grid = p->sk_tiles > 0 ? (p->dp_tiles >= clusters ? clusters : (p->dp_tiles > p->g_sk ? p->dp_tiles : p->g_sk))
+                              : (p->tiles < clusters ? p->tiles : clusters);          // in pairs
+}
 
 int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int ctas) {
     const int kper = KBYTES / (bf16 ? 2 : 4);
     p->kblocks = (K + kper - 1) / kper;
+    p->pair = false;
     // Sharing tiles between CTAs adds parts into C in whatever order they finish, so the last bits of
     // such a result vary from run to run, and a rounded result would need another pass: both
     // BMB_GEMM_NO_SPLIT and BMB_GEMM_C_ROUNDED keep every tile on one CTA; so do batched problems.
@@ -720,6 +1015,48 @@ int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensor
     return BMB_OK;
 }
 
+template <int BN>
+int launch_pair(int pairs, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, int c_mode,
+                int M, int N, int kblocks, int kper, int amn, int bmn, float alpha, float beta, float *C, int vec_ok, int dp_tiles,
+                int g_sk, const float *bias, int round_c, int *status_dev) {
+    static bool attr_set[64];
+    {
+        std::lock_guard<std::mutex> lk(g_attr_mu);
+        const int d = current_device();
+        if (d >= 0 && d < 64 && !attr_set[d]) {
+            BMB_CUDA(cudaFuncSetAttribute(gemm_tc_pair_k<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(BN)));
+            attr_set[d] = true;
+        }
+    }
+    gemm_tc_pair_k<BN><<<2 * pairs, NTHREADS, pair_smem_bytes(BN), st>>>(mapA, mapB, mapC, c_mode, M, N, kblocks, kper, amn, bmn, alpha, beta,
+                                                                       C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev);
+    return BMB_OK;
+}
+
+int pair_clusters() {
+    static int cache[64];
+    const int d = current_device();
+    if (d < 0 || d >= 64) return 1;
+    std::lock_guard<std::mutex> lk(g_attr_mu);
+    if (cache[d] == 0) {
+        int n = 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
+        cfg.blockDim = dim3(NTHREADS);
+        cfg.dynamicSmemBytes = pair_smem_bytes(256);
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        cudaFuncSetAttribute(gemm_tc_pair_k<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(256));
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_k<256>, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = sm_count() / 2; }
+        if (n > sm_count() / 2) n = sm_count() / 2;
+        cache[d] = n;
+    }
+    return cache[d];
+}
+
 }  // namespace
 
 int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N, int K, float alpha,
@@ -733,13 +1070,17 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     const bool bf16 = (math == BMB_MATH_BF16);
     const int esize = bf16 ? 2 : 4;
     const int kper = KBYTES / esize;
-    const int ctas = sm_count();
+    // BMB_GEMM_HALF_SMS: plan for half of the SMs, so that two such launches on two streams run side by side
+    const int ctas = (flags & BMB_GEMM_HALF_SMS) ? (sm_count() + 1) / 2 : sm_count();
     Plan plan;
     BMB_TRY(plan_gemm(&plan, bf16, flags, batch, M, N, K, ctas));
+    if (wants_pair(bf16, flags, transA, transB, batch, M, N))
+        plan_pair(&plan, flags, M, N, (flags & BMB_GEMM_HALF_SMS) ? (pair_clusters() + 1) / 2 : pair_clusters());
     const int kblocks = plan.kblocks, bn = plan.bn, dp_tiles = plan.dp_tiles;
     Operand a, b;
-    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, plan.mh * BM, st, batch));
-    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, bn, st, batch));
+    // per CTA: the pair kernel loads 128 rows of A and half of the B tile
+    BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, plan.pair ? BM : plan.mh * BM, st, batch));
+    BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, plan.pair ? bn / 2 : bn, st, batch));
     CUtensorMap mapA, mapB;
     if (a.map3d) BMB_TRY(make_map_mn3d(&mapA, a.ptr, a.rows, a.cols, a.pitch_bytes, a.tile_chunks));
     else BMB_TRY(make_map_2d(&mapA, a.ptr, esize, a.rows, a.cols, a.pitch_bytes, a.box_rows, a.mn_major));
@@ -764,6 +1105,15 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     int c_mode = (!no_tma_store && vec_ok && (beta == 0.0f || beta == 1.0f)) ? (beta == 0.0f ? (no_direct ? 1 : 3) : 2) : 0;
     if (batch > 1 && c_mode != 3) c_mode = 0;        // the tensor map over C describes one problem only
     if (c_mode) BMB_TRY(make_map_2d(&mapC, C, 4, M, N, (long long)N * 4, 32, false));
+    if (plan.pair) {
+        // (a K-major operand may have gone the padded-copy route; an MN-major one is 3-d by wants_pair's rule)
+        if ((a.mn_major && !a.map3d) || (b.mn_major && !b.map3d)) return fail(BMB_E_UNSUPPORTED, "gemm_tc: operand layout not served by the pair kernel");
+        BMB_TRY((launch_pair<256>(grid, st, mapA, mapB, mapC, c_mode, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias,
+                                  round_c, status_dev)));
+        count_launch();
+        BMB_LAUNCH_CHECK();
+        return BMB_OK;
+    }
 #define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
     if (bf16) {
         if (plan.mh == 2) BMB_TRY((launch_tc<1, 256, 2>(BMB_TC_ARGS)));
@@ -795,6 +1145,9 @@ extern "C" int bmb_gemm_schedule_check(int math, int flags, int batch, int M, in
     if (M < 1 || N < 1 || K < 1 || batch < 1 || ctas < 1) return fail(BMB_E_ARG, "schedule_check: bad argument");
     Plan p;
     BMB_TRY(plan_gemm(&p, math == BMB_MATH_BF16, flags, batch, M, N, K, ctas));
+    // the pair kernel's plan is replayed only when the call asks for it by flag (no device is consulted here):
+    // `ctas` then counts CTA pairs
+    if ((flags & BMB_GEMM_PAIR) && wants_pair(math == BMB_MATH_BF16, flags, 0, 1, batch, M, N)) plan_pair(&p, flags, M, N, ctas);
     if (bm_out) *bm_out = p.mh * BM;
     if (bn_out) *bn_out = p.bn;
     if (dp_tiles_out) *dp_tiles_out = p.dp_tiles;

@@ -68,6 +68,12 @@ struct bmb_trainer {
     long long graph_launches = 0;
     unsigned long long graph_scratch_gen = 0;   // the device's scratch generation the graph was captured under
     float *gen_probs = nullptr;   // one row of next-token probabilities, allocated by the first sampling call
+    // The two products of a linear layer's backward (dX = dY W and dW = dY^T X: the same FLOP count, both waiting only
+    // for dY) run side by side, each on half of the SMs: dX on the main stream, dW on this one, forked and joined
+    // by events -- one launch gap, one ramp and one tail per pair instead of two.
+    cudaStream_t st_dw = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool side_by_side = true;
     // profiling
     bool prof = false;
     std::vector<cudaEvent_t> ev;
@@ -122,7 +128,8 @@ int collect_profile(bmb_trainer *t) {
 
 // One matmul of the model, optionally bracketed by events.
 int mm(bmb_trainer *t, int flags, int ta, int tb, int M, int N, int K, const float *A, const float *B,
-       float beta, float *C, const float *bias = nullptr) {
+       float beta, float *C, const float *bias = nullptr, cudaStream_t on = nullptr) {
+    if (on) return gemm_any_bias(t->c.math, flags, ta, tb, 1, M, N, K, 1.0f, A, 0, B, 0, beta, C, 0, bias, on);
     if (t->prof) {
         if (t->ev_used + 2 > t->ev.size()) {
             for (int i = 0; i < 64; ++i) {
@@ -241,6 +248,26 @@ int backward(bmb_trainer *t) {
         return mm(t, flags, 0, 0, M_, N_, K_, dY, W + t->poff[id] + woff, 0.0f, dX);
     };
 
+    // dX and dW of one linear layer.  Side by side (fused TF32 mode, not while GEMMs are being timed one by one):
+    // the weight gradient goes to the second stream, both planned for half of the SMs.
+    // (only where both read their operands in place: a product that first rounds an operand into the per-device
+    // staging scratch must not share it with another in flight)
+    const bool sbs = t->side_by_side && fz && !t->prof && t->st_dw;
+    auto pair = [&](int xflags, int Mx, int Nx, int Kx, const float *dY, int id, size_t woff, float *dX,
+                    int Mw, int Nw, const float *act, float *dW) -> int {
+        if (!sbs) {
+            BMB_TRY(dx(xflags, Mx, Nx, Kx, dY, id, woff, dX));
+            return mm(t, gflag, 1, 0, Mw, Nw, Mx, dY, act, 1.0f, dW);
+        }
+        BMB_CUDA(cudaEventRecord(t->ev_fork, t->st));
+        BMB_CUDA(cudaStreamWaitEvent(t->st_dw, t->ev_fork, 0));
+        BMB_TRY(mm(t, gflag | BMB_GEMM_HALF_SMS, 1, 0, Mw, Nw, Mx, dY, act, 1.0f, dW, nullptr, t->st_dw));
+        BMB_TRY(dx(xflags | BMB_GEMM_HALF_SMS, Mx, Nx, Kx, dY, id, woff, dX));
+        BMB_CUDA(cudaEventRecord(t->ev_join, t->st_dw));
+        BMB_CUDA(cudaStreamWaitEvent(t->st, t->ev_join, 0));
+        return BMB_OK;
+    };
+
     BMB_CUDA(cudaMemsetAsync(G, 0, t->num_params * sizeof(float), t->st));
     BMB_TRY(dx(wflag, N, C, Vp, t->dlogits, P_WTE, 0, t->dlnf));
     BMB_TRY(mm(t, gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
@@ -258,16 +285,16 @@ int backward(bmb_trainer *t) {
         float *fch = t->fch + l * BT4C, *fchg = t->fch_gelu + l * BT4C;
         const size_t lC = (size_t)l * C;
 
-        BMB_TRY(dx(wflag, N, 4 * C, C, t->dres, P_FPW, (size_t)l * C * 4 * C, t->dfch_gelu));
-        BMB_TRY(mm(t, gflag, 1, 0, C, 4 * C, N, t->dres, fchg, 1.0f, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
+        BMB_TRY(pair(wflag, N, 4 * C, C, t->dres, P_FPW, (size_t)l * C * 4 * C, t->dfch_gelu,
+                     C, 4 * C, fchg, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
         BMB_TRY(bmb_gelu_backward_colsum(t->dfch, G + t->poff[P_FCB] + 4 * lC, fch, t->dfch_gelu, N, 4 * C));
-        BMB_TRY(dx(wflag, N, C, 4 * C, t->dfch, P_FCW, (size_t)l * 4 * C * C, t->dln2));
-        BMB_TRY(mm(t, gflag, 1, 0, 4 * C, C, N, t->dfch, ln2, 1.0f, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
+        BMB_TRY(pair(wflag, N, C, 4 * C, t->dfch, P_FCW, (size_t)l * 4 * C * C, t->dln2,
+                     4 * C, C, ln2, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
         BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC,
                                               G + t->poff[P_APB] + lC, t->dln2, res2,
                                               P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
-        BMB_TRY(dx(wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), N, C, C, t->dres, P_APW, (size_t)l * C * C, t->datty));
-        BMB_TRY(mm(t, gflag, 1, 0, C, C, N, t->dres, atty, 1.0f, G + t->poff[P_APW] + (size_t)l * C * C));
+        BMB_TRY(pair(wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), N, C, C, t->dres, P_APW, (size_t)l * C * C, t->datty,
+                     C, C, atty, G + t->poff[P_APW] + (size_t)l * C * C));
         if (c.use_flash && fz && attn_cfg(c) == 2)
             BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH, true, t->st));
         else if (c.use_flash)
@@ -275,8 +302,8 @@ int backward(bmb_trainer *t) {
         else
             BMB_TRY(bmb_attention_backward(t->dqkv, t->dqkvr, t->datt, t->datt, t->datty, t->qkvr + l * qkvr_sz,
                                            t->att + l * att_sz, B, T, C, NH));
-        BMB_TRY(dx(wflag, N, C, 3 * C, t->dqkv, P_QKVW, (size_t)l * 3 * C * C, t->dln1));
-        BMB_TRY(mm(t, gflag, 1, 0, 3 * C, C, N, t->dqkv, ln1, 1.0f, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
+        BMB_TRY(pair(wflag, N, C, 3 * C, t->dqkv, P_QKVW, (size_t)l * 3 * C * C, t->dln1,
+                     3 * C, C, ln1, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
         BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
         BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC,
                                               l > 0 ? G + t->poff[P_FPB] + lC - C : nullptr, t->dln1, residual,
@@ -392,6 +419,10 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     if (const char *g = getenv("BMB_TRAINER_GRAPH")) t->use_graph = atoi(g) != 0;
     BMB_CUDA(cudaGetDevice(&t->dev));
     BMB_CUDA(cudaStreamCreateWithFlags(&t->st, cudaStreamNonBlocking));
+    BMB_CUDA(cudaStreamCreateWithFlags(&t->st_dw, cudaStreamNonBlocking));
+    BMB_CUDA(cudaEventCreateWithFlags(&t->ev_fork, cudaEventDisableTiming));
+    BMB_CUDA(cudaEventCreateWithFlags(&t->ev_join, cudaEventDisableTiming));
+    if (const char *e = getenv("BMB_TRAINER_SIDE_BY_SIDE")) t->side_by_side = atoi(e) != 0;
     param_sizes(t->psize, c);
     t->num_params = 0;
     for (int i = 0; i < NPT; ++i) { t->poff[i] = t->num_params; t->num_params += t->psize[i]; }
@@ -500,6 +531,9 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     cudaFree(t->d_loss); cudaFree(t->d_sumsq); cudaFree(t->d_token);
     if (t->gen_probs) cudaFree(t->gen_probs);
     dp_fused_destroy(t->dp);
+    if (t->ev_fork) cudaEventDestroy(t->ev_fork);
+    if (t->ev_join) cudaEventDestroy(t->ev_join);
+    if (t->st_dw) cudaStreamDestroy(t->st_dw);
     if (t->st) cudaStreamDestroy(t->st);
     delete t;
     return BMB_OK;

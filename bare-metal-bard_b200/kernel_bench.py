@@ -3,6 +3,7 @@
     python bare-metal-bard_b200/kernel_bench.py [gemm] [bgemm] [flash] [nn] [--small]
     python bare-metal-bard_b200/kernel_bench.py one:tf32:nt:8192x3072x768:rounded      (a single GEMM case)
     python bare-metal-bard_b200/kernel_bench.py registry --csv runs/a.csv [-s 1024,2048]   (the registry sweep as CSV)
+    python bare-metal-bard_b200/kernel_bench.py timeline:tf32:nt:8192x3072x768:rounded     (per-CTA timeline, timer build)
 
 `registry --csv` appends one row per (registry entry, size) in the columns the reference harness writes
 (src/bench.cu:238-245, 293-299): kernel_id,kernel,size,gflops_best,gflops_median,cublas_gflops_best,
@@ -223,9 +224,11 @@ def bench_registry(bmb, csv_path, sizes):
 
 def bench_one(bmb, spec):
     """One GEMM case, for a profiler capture or a quick comparison:
-        one:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][:nosplit]
+        one:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][:nosplit][:pair|:nopair][:m128|:m256][:beta1]
     math = fp32 | tf32 | bf16; ta/tb = n or t; `rounded` feeds operands already rounded to TF32
-    (what the training step does), `nosplit` keeps every tile on one CTA."""
+    (what the training step does), `nosplit` keeps every tile on one CTA, `pair` / `nopair` force or forbid
+    CTA pairs, `m128` / `m256` force the tile height of single CTAs, `beta1` accumulates into C.  Timed as
+    20 back-to-back launches between one pair of events (what a kernel costs inside a stream of kernels)."""
     parts = spec.split(":")
     math = {"fp32": bmb.MATH_FP32, "tf32": bmb.MATH_TF32, "bf16": bmb.MATH_BF16}[parts[1]]
     ta, tb = (1 if ch == "t" else 0 for ch in parts[2])
@@ -241,10 +244,83 @@ def bench_one(bmb, spec):
         flags |= bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED
     if "nosplit" in opts:
         flags |= bmb.GEMM_NO_SPLIT
-    best, med = timed(lambda: bmb.call("bmb_gemm_ex", math, flags, ta, tb, M, N, K, 1.0, A, B, 0.0, Cm, None),
-                      warmup=3, iters=5)
+    if "pair" in opts:
+        flags |= bmb.GEMM_PAIR
+    if "nopair" in opts:
+        flags |= bmb.GEMM_NO_PAIR
+    if "m128" in opts:
+        flags |= bmb.GEMM_TILE_M128
+    if "m256" in opts:
+        flags |= bmb.GEMM_TILE_M256
+    beta = 1.0 if "beta1" in opts else 0.0
+    call = lambda: bmb.call("bmb_gemm_ex", math, flags, ta, tb, M, N, K, 1.0, A, B, beta, Cm, None)
+    best, med = timed(call, warmup=3, iters=5)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        call()
+    e1.record()
+    e1.synchronize()
+    b2b = e0.elapsed_time(e1) / 20
     emit(kernel="gemm_ex", spec=spec, best_ms=round(best, 4), median_ms=round(med, 4),
-         tflops_best=round(2.0 * M * N * K / best / 1e9, 2))
+         tflops_best=round(2.0 * M * N * K / best / 1e9, 2), back_to_back_ms=round(b2b, 4),
+         tflops_back_to_back=round(2.0 * M * N * K / b2b / 1e9, 2))
+
+
+def bench_timeline(bmb, spec):
+    """timeline:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][...]  -- where one tensor-core GEMM launch spends its time.
+    Needs a library built with the developer timers (`BMB_NVCC_FLAGS=-DBMB_GEMM_TRACE python
+    bare-metal-bard_b200/build.py -f`): every CTA then stamps, in nanoseconds of the global timer, its entry,
+    set-up done, first copy issued, first K slice landed, last product issued, first accumulator ready, last tile
+    stored, stores landed, exit.  Printed: min / median / max over CTAs of each stamp, in microseconds after the
+    first CTA's entry, next to the event-timed cost of the launch alone and inside 20 back-to-back launches."""
+    import ctypes as C
+    lib = bmb.lib()
+    try:
+        dbg = C.CDLL(bmb.LIB_PATH).bmb_dbg_gemm_trace
+    except AttributeError:
+        raise SystemExit("this libbmb.so has no timers: rebuild with BMB_NVCC_FLAGS=-DBMB_GEMM_TRACE")
+    dbg.argtypes = [C.c_void_p]
+    parts = spec.split(":")
+    math = {"fp32": bmb.MATH_FP32, "tf32": bmb.MATH_TF32, "bf16": bmb.MATH_BF16}[parts[1]]
+    ta, tb = (1 if ch == "t" else 0 for ch in parts[2])
+    M, N, K = (int(x) for x in parts[3].split("x"))
+    opts = parts[4:]
+    A = torch.rand(M * K, device="cuda") * 2 - 1
+    B = torch.rand(K * N, device="cuda") * 2 - 1
+    Cm = torch.zeros(M * N, device="cuda")
+    flags = 0
+    if "rounded" in opts:
+        bmb.call("bmb_round_tf32", A, A, M * K, None)
+        bmb.call("bmb_round_tf32", B, B, K * N, None)
+        flags |= bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED
+    for name, bit in (("nosplit", bmb.GEMM_NO_SPLIT), ("pair", bmb.GEMM_PAIR), ("nopair", bmb.GEMM_NO_PAIR),
+                      ("m128", bmb.GEMM_TILE_M128), ("m256", bmb.GEMM_TILE_M256)):
+        if name in opts:
+            flags |= bit
+    beta = 1.0 if "beta1" in opts else 0.0
+    call = lambda: bmb.call("bmb_gemm_ex", math, flags, ta, tb, M, N, K, 1.0, A, B, beta, Cm, None)
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    buf = np.zeros((256, 10), np.uint64)
+    dbg(buf.ctypes.data)                       # clears the device-side stamps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); call(); e1.record(); e1.synchronize()
+    single = e0.elapsed_time(e1) * 1e3
+    dbg(buf.ctypes.data)
+    t = buf[:, :9].astype(np.float64)
+    t = t[t[:, 0] > 0]
+    rel = (t - t[:, 0].min()) / 1e3
+    names = ["entry", "setup", "copy1", "slice1", "lastmma", "acc1", "laststore", "landed", "exit"]
+    e0.record()
+    for _ in range(20):
+        call()
+    e1.record(); e1.synchronize()
+    emit(kernel="gemm_timeline", spec=spec, ctas=int(t.shape[0]), single_us=round(single, 1),
+         back_to_back_us=round(e0.elapsed_time(e1) * 1e3 / 20, 1),
+         us_min_median_max={n: [round(float(rel[:, i].min()), 1), round(float(np.median(rel[:, i])), 1), round(float(rel[:, i].max()), 1)]
+                            for i, n in enumerate(names)})
 
 
 def main():
@@ -271,7 +347,9 @@ def main():
             return
     for w in [x for x in which if x.startswith("one:")]:
         bench_one(bmb, w)
-    which = [x for x in which if not x.startswith("one:")]
+    for w in [x for x in which if x.startswith("timeline:")]:
+        bench_timeline(bmb, w)
+    which = [x for x in which if not x.startswith(("one:", "timeline:"))]
     for w in which:
         {"gemm": bench_gemm, "bgemm": bench_bgemm, "flash": bench_flash, "nn": bench_nn}[w](bmb, small)
 

@@ -147,17 +147,19 @@ def test_tensorcore_flash_at_benchmark_shape_vs_reference_kernels(bmb, ref, cuda
     (1, 0, 50304, 768, 8192, 1.0),      # token-embedding weight gradient, accumulated
     (0, 0, 8192, 8192, 8192, 0.0),      # the sweep's largest square
 ])
-@pytest.mark.parametrize("height", [128, 256])
+@pytest.mark.parametrize("height", [128, 256, "pair"])
 def test_tensorcore_gemm_forced_tile_heights(bmb, cuda, ta, tb, M, N, K, beta, height):
-    """Both tile heights of the TF32 kernel, forced per call, on the products the training step (and the
-    square sweep) spend most of their time in: pre-rounded operands against the float64 product computed on
-    the device in row blocks, 2e-5 normwise -- only the accumulation order may use that up."""
+    """The three forms of the TF32 kernel -- 128-row tiles, 256-row tiles of one CTA, 256 x 256 tiles of a CTA
+    pair (tcgen05 cta_group::2) -- each forced per call, on the products the training step (and the square
+    sweep) spend most of their time in: pre-rounded operands against the float64 product computed on the
+    device in row blocks, 2e-5 normwise -- only the accumulation order may use that up."""
     lib = bmb.lib()
-    flag = bmb.GEMM_TILE_M256 if height == 256 else bmb.GEMM_TILE_M128
+    flag = {128: bmb.GEMM_TILE_M128 | bmb.GEMM_NO_PAIR, 256: bmb.GEMM_TILE_M256 | bmb.GEMM_NO_PAIR, "pair": bmb.GEMM_PAIR}[height]
     import ctypes as C
     tm, tn = C.c_int(), C.c_int()
-    assert lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flag, 1, M, N, K, 148, C.byref(tm), C.byref(tn), None, None) == 0
-    assert tm.value == height                      # the flag decides, not the cost model
+    units = 74 if height == "pair" else 148         # CTA pairs, or CTAs
+    assert lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flag, 1, M, N, K, units, C.byref(tm), C.byref(tn), None, None) == 0
+    assert tm.value == (256 if height == "pair" else height)      # the flag decides, not the cost model
     g = cuda.Generator(device="cuda").manual_seed(11)
     A = cuda.rand(M * K, device="cuda", generator=g) * 2 - 1
     B = cuda.rand(K * N, device="cuda", generator=g) * 2 - 1

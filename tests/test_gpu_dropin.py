@@ -181,17 +181,25 @@ def test_gpt1_checkpoints_both_ways_and_sampling(bmb, cuda, text_file, tmp_path)
     assert has_opt.value == 1 and step.value == 1
     rc, out = run([exe("ref_train_gpt"), "--load", ck_bmb, "--len", "16", "-b", "2"])
     assert rc == 0 and "loaded" in out and ("%d layers" % cfg[3]) in out, out[-2000:]
-    # resume: a second trainer restored from the file continues like the first (the token-embedding gradient is
-    # summed with atomics, so two runs of one step agree to rounding, not bit for bit)
+    # resume: a second trainer restored from the file holds exactly the saved state (writing it out again gives the
+    # same bytes: parameters, both AdamW moments, the step) and continues like the first.  The token-embedding
+    # gradient is summed with atomics, so the two continuations agree to rounding, not bit for bit -- and AdamW
+    # turns a rounding-sized gradient difference into a step-sized parameter difference where the second moment is
+    # tiny, so what is compared after the step is the loss, and the parameters to within one learning-rate step.
     tr2 = bmb.Trainer(seed=99, use_flash=1, math=bmb.MATH_FP32, B=2, T=cfg[0], **model)
     assert tr2.load(ck_bmb, optimizer_state=True) == 1
+    ck_again = str(tmp_path / "again.bin")
+    tr2.save(ck_again, itos, with_optimizer_state=True, step=1)
+    assert open(ck_again, "rb").read() == open(ck_bmb, "rb").read()
+    losses = []
     for t_ in (tr, tr2):
         t_.upload(tok, tok)
         t_.step(1e-3, 2)
+        losses.append(t_.loss())
     q = np.empty_like(p)
     tr.get_params(p)
     tr2.get_params(q)
-    assert float(np.linalg.norm(p.astype(np.float64) - q) / np.linalg.norm(p.astype(np.float64))) < 1e-6
+    assert abs(losses[0] - losses[1]) < 1e-5 and float(np.abs(p - q).max()) <= 2.5e-3
     tr.close()
     tr2.close()
 

@@ -351,7 +351,7 @@ def test_softmax_xent_vs_oracle(bmb, orc, cuda, N, V, Vp):
     # the one-sweep variant the training step uses gives the same losses and the same gradient
     fl, fd = (cuda.full((n,), float("nan"), device="cuda") for n in (N, N * Vp))
     bmb.call("bmb_softmax_crossentropy_fused", fd, fl, dev(cuda, logits), tt, N, V, Vp, 1.0 / N)
-    assert np.array_equal(host(cuda, fl), host(cuda, tl))
+    assert normwise(host(cuda, fl), host(cuda, tl)) < 1e-6   # its row sum is accumulated in a different order
     assert normwise(host(cuda, fd), d) < 1e-5
     assert np.all(host(cuda, fd).reshape(N, Vp)[:, V:] == 0)
 

@@ -58,6 +58,30 @@ def test_tensorcore_gemm_vs_oracle(bmb, orc, cuda, kind, ta, tb, M, N, K):
     assert normwise(got, want32) < (5e-4 if kind == "tf32" else 8e-3)
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 32), (512, 768, 256), (300, 515, 77), (1024, 320, 1024), (2304, 768, 512), (288, 288, 40)])
+@pytest.mark.parametrize("split", [0, 1])
+def test_pair_kernel_vs_oracle(bmb, orc, cuda, ta, tb, M, N, K, split):
+    """The CTA-pair form (one tcgen05.mma.cta_group::2 per 256 rows, each CTA loading half of B) forced by flag:
+    all four transposes, ragged edges (a peer CTA whose rows or columns lie outside the matrix), tiles shared
+    along K or not, alpha and beta, against the float64 product of the rounded operands (2e-5).  Shapes whose
+    M- or N-contiguous operand is not a multiple of 32 wide fall back to single CTAs, which must agree too."""
+    A, B, C0 = uniform(M * K, 1), uniform(K * N, 2), uniform(M * N, 3)
+    Ar, Br = rounded(orc, A, "tf32"), rounded(orc, B, "tf32")
+    want_r = C0.copy()
+    orc.orc_gemm_f64(ta, tb, M, N, K, 0.75, _np(Ar), _np(Br), 1.25, _np(want_r))
+    dA, dB, dC = dev(cuda, A), dev(cuda, B), dev(cuda, C0)
+    flags = bmb.GEMM_PAIR | (0 if split else bmb.GEMM_NO_SPLIT)
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, flags, ta, tb, M, N, K, 0.75, dA, dB, 1.25, dC, None)
+    assert normwise(host(cuda, dC), want_r) < 2e-5
+    # beta = 0 on a poisoned C: every element must be written exactly once
+    dP = cuda.full((M * N,), float("nan"), device="cuda")
+    want0 = np.zeros(M * N, np.float32)
+    orc.orc_gemm_f64(ta, tb, M, N, K, 1.0, _np(Ar), _np(Br), 0.0, _np(want0))
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, flags, ta, tb, M, N, K, 1.0, dA, dB, 0.0, dP, None)
+    assert normwise(host(cuda, dP), want0) < 2e-5
+
+
 @pytest.mark.parametrize("ta,tb,M,N,K,beta", [
     (0, 1, 8192, 3072, 768, 0.0),      # 192-column tiles, whole tiles stored from registers
     (0, 1, 8192, 768, 3072, 0.0),      # last wave shared between CTAs along K
@@ -81,14 +105,16 @@ def test_training_step_shapes_at_full_size(bmb, cuda, ta, tb, M, N, K, beta):
     Bm = B.view(N, K).t() if tb else B.view(K, N)
     want = (Am.double() @ Bm.double() + beta * C0.view(M, N).double())
     outs = []
-    for extra in (0, bmb.GEMM_NO_SPLIT):
+    # every tile on one CTA / tiles shared along K, on single CTAs and on CTA pairs
+    for extra in (bmb.GEMM_NO_PAIR, bmb.GEMM_NO_PAIR | bmb.GEMM_NO_SPLIT, bmb.GEMM_PAIR, bmb.GEMM_PAIR | bmb.GEMM_NO_SPLIT):
         Cm = C0.clone()
         bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED | extra, ta, tb, M, N, K, 1.0, A, B, beta, Cm, None)
         cuda.cuda.synchronize()
         err = ((Cm.view(M, N).double() - want).norm() / want.norm()).item()
         assert err < 2e-5, (extra, err)
         outs.append(Cm)
-    assert ((outs[0] - outs[1]).double().norm() / want.norm()).item() < 2e-5
+    for o in outs[1:]:
+        assert ((outs[0] - o).double().norm() / want.norm()).item() < 2e-5
 
 
 @pytest.mark.parametrize("ta,tb,batch,M,N,K", [
@@ -297,3 +323,25 @@ def test_graph_replay_equals_eager_launches(bmb, cuda, monkeypatch):
             runs.append(losses)
         assert max(abs(a - b) for a, b in zip(*runs)) <= tol, runs
 
+
+
+def test_side_by_side_backward_products_equal_one_after_the_other(bmb, cuda, monkeypatch):
+    """In the fused TF32 mode the trainer runs the two products of a linear layer's backward (dX and dW) side by
+    side, each on half of the SMs, the weight gradient on a second stream forked and joined by events (also
+    inside the captured graph).  BMB_TRAINER_SIDE_BY_SIDE=0 runs them one after the other on all SMs: same
+    losses up to the run-to-run wobble of the sums that use atomics (1e-3, as for graph replay)."""
+    rng = np.random.default_rng(11)
+    toks = rng.integers(0, TINY["vocab_size"], (6, TINY["B"], TINY["T"]), dtype=np.int32)
+    tgts = rng.integers(0, TINY["vocab_size"], (6, TINY["B"], TINY["T"]), dtype=np.int32)
+    runs = []
+    for mode in ("1", "0"):
+        monkeypatch.setenv("BMB_TRAINER_SIDE_BY_SIDE", mode)
+        tr = bmb.Trainer(seed=1337, use_flash=1, math=bmb.MATH_TF32, fused=1, **TINY)
+        losses = []
+        for s in range(6):
+            tr.upload(toks[s], tgts[s])
+            tr.step(3e-4, s + 1)
+            losses.append(tr.loss())
+        tr.close()
+        runs.append(losses)
+    assert np.all(np.isfinite(runs[0])) and max(abs(a - b) for a, b in zip(*runs)) <= 1e-3, runs
