@@ -13,7 +13,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libbmb.so")
+# BMB_LIB points at another build of the library (e.g. one compiled with the developer timers)
+LIB_PATH = os.environ.get("BMB_LIB") or os.path.join(HERE, "libbmb.so")
 
 MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2
 GEMM_A_ROUNDED, GEMM_B_ROUNDED, GEMM_C_ROUNDED, GEMM_NO_SPLIT = 1, 2, 4, 8

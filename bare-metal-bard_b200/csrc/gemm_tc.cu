@@ -80,15 +80,26 @@ constexpr int CHUNK_BYTES = 32 * KBYTES;   // one MN-major chunk: 32 K rows x 12
 // Developer timeline (compiled in only with -DBMB_GEMM_TRACE): per CTA, nanosecond stamps of kernel entry,
 // set-up done, first copy issued, first slice landed, last product issued, first accumulator ready,
 // last tile stored, stores landed, exit.
-__device__ unsigned long long g_gemm_trace[256][10];
+__device__ unsigned long long g_gemm_trace[256][16];
 __device__ __forceinline__ unsigned long long gtime() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
 #define GTR(i) do { g_gemm_trace[blockIdx.x & 255][(i)] = gtime(); } while (0)
+// cycles a role spent inside a wait: 10 issuer on full, 11 issuer on tmem-empty, 12 producer on empty, 13 epilogue warp 2 on tmem-full,
+// 14 epilogue warp 2 working, 15 issuer total
+// (summed in a register of the waiting thread, written once when its role ends)
+#define GWAIT_DECL(v) long long v = 0
+#define GWAIT_BEGIN() const long long gw0_ = clock64()
+#define GWAIT_END(v) v += clock64() - gw0_
+#define GWAIT_FLUSH(i, v) g_gemm_trace[blockIdx.x & 255][(i)] = (unsigned long long)(v)
 #else
 #define GTR(i)
+#define GWAIT_DECL(v)
+#define GWAIT_BEGIN()
+#define GWAIT_END(v)
+#define GWAIT_FLUSH(i, v)
 #endif
 
 struct TileSched {
@@ -250,6 +261,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            GWAIT_DECL(gw_empty);
 #ifdef BMB_GEMM_TRACE
             bool first_copy = true;
 #endif
@@ -259,7 +271,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 sch.coords(tile - bi * tiles_per_problem, tm, tn);
                 const int a_row0 = bi * M, b_row0 = bi * N, k_row0 = bi * (kblocks * kelems_per_block);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; }
+                    { GWAIT_BEGIN(); if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; } GWAIT_END(gw_empty); }
                     const uint32_t fb = full0 + 8 * s;
                     mbar_arrive_expect_tx(fb, STAGE_BYTES);
                     armed[s] = (int)ph;
@@ -287,6 +299,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
+            GWAIT_FLUSH(12, gw_empty);
             if (!ok) {
                 // Leave no copy in flight behind us: every armed slice must land.
                 for (int i = 0; i < STAGES; ++i)
@@ -302,15 +315,17 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             int s = 0, acc = 0;
             uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
+            GWAIT_DECL(gw_full);
+            GWAIT_DECL(gw_tempty);
 #ifdef BMB_GEMM_TRACE
             bool first_slice = true;
 #endif
             while (ok && wi.next(tile, kb0, kb1)) {
-                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
+                { GWAIT_BEGIN(); if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; } GWAIT_END(gw_tempty); }
                 fence_after();
                 const uint32_t d = tmem_base + (uint32_t)acc * ACC_COLS;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
+                    { GWAIT_BEGIN(); if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; } GWAIT_END(gw_full); }
                     fence_after();
 #ifdef BMB_GEMM_TRACE
                     if (first_slice) { GTR(3); first_slice = false; }
@@ -335,6 +350,8 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 GTR(4);
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
+            GWAIT_FLUSH(10, gw_full);
+            GWAIT_FLUSH(11, gw_tempty);
         }
     } else {
         // ------------------------------------------------------------ epilogue
@@ -345,6 +362,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
+        GWAIT_DECL(gw_tfull);
         float *const C0 = C;
         while (ok && wi.next(tile, kb0, kb1)) {
             int tm, tn;
@@ -352,7 +370,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             sch.coords(tile - bi * tiles_per_problem, tm, tn);
             float *C = C0 + (size_t)bi * M * N;          // this problem's result
             const bool whole = (kb0 == 0 && kb1 == kblocks);
-            if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
+            { GWAIT_BEGIN(); if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; } GWAIT_END(gw_tfull); }
             fence_after();
 #ifdef BMB_GEMM_TRACE
             if (warp == 2 && lane == 0 && g_gemm_trace[blockIdx.x & 255][9] == 0) { GTR(5); g_gemm_trace[blockIdx.x & 255][9] = 1; }
@@ -451,6 +469,7 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             if (warp == 2 && lane == 0) GTR(6);
 #endif
         }
+        if (warp == 2 && lane == 0) GWAIT_FLUSH(13, gw_tfull);
         if (c_mode && lane == 0) tma_store_wait_all();   // every block this warp handed to the copy engine has landed
 #ifdef BMB_GEMM_TRACE
         if (warp == 2 && lane == 0) GTR(7);
@@ -522,6 +541,7 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     int tile, kb0, kb1;
 
     if (threadIdx.x == 0) {
+        GTR(0);
         // full: the leader's own arrival (with the byte count of both CTAs); empty, tmem_full: one arrival
         // from the leader's issuer per use; tmem_empty (used in the leader only): the epilogue warps of both CTAs
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -545,6 +565,7 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            GWAIT_DECL(gw_empty);
             int armed_par[STAGES];
             for (int i = 0; i < STAGES; ++i) armed_par[i] = -1;
             while (ok && wi.next(tile, kb0, kb1)) {
@@ -552,7 +573,7 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 sch.coords(tile, tm, tn);
                 const int a_x0 = tm * BMT + (int)rank * BM, b_x0 = tn * BN + (int)rank * BH;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; }
+                    { GWAIT_BEGIN(); if (!mbar_wait(empty0 + 8 * s, ph ^ 1, giveup)) { ok = false; break; } GWAIT_END(gw_empty); }
                     const uint32_t fb_local = full0 + 8 * s;
                     if (rank == 0) { mbar_arrive_expect_tx(fb_local, 2 * STAGE_BYTES); armed_par[s] = (int)ph; }
                     const uint32_t fb = map_to_cta(fb_local, 0);
@@ -565,6 +586,7 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
+            GWAIT_FLUSH(12, gw_empty);
             // Do not leave while the issuer's releases of the last slots may still be on their way to this
             // CTA's barriers: wait until every slot has been handed back.
             for (int i = 0; ok && i < STAGES; ++i) {
@@ -587,12 +609,14 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             int s = 0, acc = 0;
             uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
+            GWAIT_DECL(gw_full);
+            GWAIT_DECL(gw_tempty);
             while (ok && wi.next(tile, kb0, kb1)) {
-                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; }
+                { GWAIT_BEGIN(); if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, giveup)) { ok = false; break; } GWAIT_END(gw_tempty); }
                 fence_after();
                 const uint32_t d = tmem_base + (uint32_t)acc * ACC_COLS;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; }
+                    { GWAIT_BEGIN(); if (!mbar_wait(full0 + 8 * s, ph, giveup)) { ok = false; break; } GWAIT_END(gw_full); }
                     fence_after();
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
 #pragma unroll
@@ -608,8 +632,11 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 commit_pair(tfull0 + 8 * acc);
                 commit_pair(peer_tfull0 + 8 * acc);
+                GTR(4);
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
+            GWAIT_FLUSH(10, gw_full);
+            GWAIT_FLUSH(11, gw_tempty);
         }
     } else {
         // ------------------------------------------------------------ epilogue (each CTA for its own 128 rows)
@@ -619,11 +646,12 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
+        GWAIT_DECL(gw_tfull);
         while (ok && wi.next(tile, kb0, kb1)) {
             int tm, tn;
             sch.coords(tile, tm, tn);
             const bool whole = (kb0 == 0 && kb1 == kblocks);
-            if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; }
+            { GWAIT_BEGIN(); if (!mbar_wait(tfull0 + 8 * acc, acc_ph, giveup)) { ok = false; break; } GWAIT_END(gw_tfull); }
             fence_after();
             const int row_base = tm * BMT + (int)rank * BM + q * 32;
             const uint32_t trow = tmem_base + (uint32_t)acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
@@ -705,6 +733,7 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * acc);      // the issuer counts both CTAs' warps
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+        if (warp == 2 && lane == 0) GWAIT_FLUSH(13, gw_tfull);
         if (c_mode && lane == 0) tma_store_wait_all();
     }
 
@@ -720,6 +749,7 @@ gemm_tc_pair_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         *reinterpret_cast<volatile int *>(status) = 4;
         __threadfence_system();
     }
+    if (threadIdx.x == 0) GTR(8);
 }
 
 // ---- operand prepass --------------------------------------------------------
@@ -923,9 +953,12 @@ int pair_clusters();
 // Whether a problem goes to the pair kernel: TF32, one problem, at least one 256 x 256 tile, and operands
 // the pair kernel's loads take (an M- or N-contiguous operand needs its extent to be a multiple of 32).
 // BMB_GEMM_PAIR / BMB_GEMM_NO_PAIR in the flags decide for a call; the environment variable
-// BMB_GEMM_PAIR=0 turns the default off.
+// BMB_GEMM_PAIR=1 makes pairs the default where the shape allows.
 bool wants_pair(bool bf16, int flags, int transA, int transB, int batch, int M, int N) {
-    static const bool env_on = [] { const char *e = getenv("BMB_GEMM_PAIR"); return !(e && atoi(e) == 0); }();
+    // Measured on the step's shapes the pair form runs within +-6 % of single CTAs (both sit at the same
+    // shared-memory bandwidth bound: a CTA of a pair still feeds its half of B to both tensor cores), so it
+    // is opt-in.
+    static const bool env_on = [] { const char *e = getenv("BMB_GEMM_PAIR"); return e && atoi(e) != 0; }();
     if (bf16 || batch != 1 || M < 2 * BM || N < 256) return false;
     if ((transA && M % 32) || (!transB && N % 32)) return false;
     if (flags & BMB_GEMM_NO_PAIR) return false;
@@ -1175,10 +1208,10 @@ extern "C" int bmb_gemm_schedule_check(int math, int flags, int batch, int M, in
 
 #ifdef BMB_GEMM_TRACE
 // Developer entry point: copy out (and clear) the per-CTA timeline of the last tensor-core GEMM launch.
-extern "C" int bmb_dbg_gemm_trace(unsigned long long *host_256x10) {
-    cudaError_t e = cudaMemcpyFromSymbol(host_256x10, bmb::g_gemm_trace, sizeof(unsigned long long) * 2560);
+extern "C" int bmb_dbg_gemm_trace(unsigned long long *host_256x16) {
+    cudaError_t e = cudaMemcpyFromSymbol(host_256x16, bmb::g_gemm_trace, sizeof(unsigned long long) * 4096);
     if (e != cudaSuccess) return (int)e;
-    static unsigned long long zeros[2560];
+    static unsigned long long zeros[4096];
     return (int)cudaMemcpyToSymbol(bmb::g_gemm_trace, zeros, sizeof(zeros));
 }
 #endif

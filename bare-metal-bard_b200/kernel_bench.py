@@ -227,7 +227,8 @@ def bench_one(bmb, spec):
         one:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][:nosplit][:pair|:nopair][:m128|:m256][:beta1]
     math = fp32 | tf32 | bf16; ta/tb = n or t; `rounded` feeds operands already rounded to TF32
     (what the training step does), `nosplit` keeps every tile on one CTA, `pair` / `nopair` force or forbid
-    CTA pairs, `m128` / `m256` force the tile height of single CTAs, `beta1` accumulates into C.  Timed as
+    CTA pairs, `m128` / `m256` force the tile height of single CTAs, `half` plans for half of the SMs, `beta1`
+    accumulates into C.  Timed as
     20 back-to-back launches between one pair of events (what a kernel costs inside a stream of kernels)."""
     parts = spec.split(":")
     math = {"fp32": bmb.MATH_FP32, "tf32": bmb.MATH_TF32, "bf16": bmb.MATH_BF16}[parts[1]]
@@ -252,6 +253,8 @@ def bench_one(bmb, spec):
         flags |= bmb.GEMM_TILE_M128
     if "m256" in opts:
         flags |= bmb.GEMM_TILE_M256
+    if "half" in opts:
+        flags |= bmb.GEMM_HALF_SMS
     beta = 1.0 if "beta1" in opts else 0.0
     call = lambda: bmb.call("bmb_gemm_ex", math, flags, ta, tb, M, N, K, 1.0, A, B, beta, Cm, None)
     best, med = timed(call, warmup=3, iters=5)
@@ -272,8 +275,10 @@ def bench_timeline(bmb, spec):
     Needs a library built with the developer timers (`BMB_NVCC_FLAGS=-DBMB_GEMM_TRACE python
     bare-metal-bard_b200/build.py -f`): every CTA then stamps, in nanoseconds of the global timer, its entry,
     set-up done, first copy issued, first K slice landed, last product issued, first accumulator ready, last tile
-    stored, stores landed, exit.  Printed: min / median / max over CTAs of each stamp, in microseconds after the
-    first CTA's entry, next to the event-timed cost of the launch alone and inside 20 back-to-back launches."""
+    stored, stores landed, exit -- and adds up the cycles its issuing thread waited for operand slices and for a free
+    accumulator, its producer for a free slot, and one epilogue warp for a finished accumulator.  Printed: min /
+    median / max over CTAs of each stamp, in microseconds after the first CTA's entry, the waits (median, max), and
+    the event-timed cost of the launch alone and inside 20 back-to-back launches."""
     import ctypes as C
     lib = bmb.lib()
     try:
@@ -295,7 +300,7 @@ def bench_timeline(bmb, spec):
         bmb.call("bmb_round_tf32", B, B, K * N, None)
         flags |= bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED
     for name, bit in (("nosplit", bmb.GEMM_NO_SPLIT), ("pair", bmb.GEMM_PAIR), ("nopair", bmb.GEMM_NO_PAIR),
-                      ("m128", bmb.GEMM_TILE_M128), ("m256", bmb.GEMM_TILE_M256)):
+                      ("m128", bmb.GEMM_TILE_M128), ("m256", bmb.GEMM_TILE_M256), ("half", bmb.GEMM_HALF_SMS)):
         if name in opts:
             flags |= bit
     beta = 1.0 if "beta1" in opts else 0.0
@@ -303,7 +308,7 @@ def bench_timeline(bmb, spec):
     for _ in range(3):
         call()
     torch.cuda.synchronize()
-    buf = np.zeros((256, 10), np.uint64)
+    buf = np.zeros((256, 16), np.uint64)
     dbg(buf.ctypes.data)                       # clears the device-side stamps
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(); call(); e1.record(); e1.synchronize()
@@ -317,7 +322,10 @@ def bench_timeline(bmb, spec):
     for _ in range(20):
         call()
     e1.record(); e1.synchronize()
-    emit(kernel="gemm_timeline", spec=spec, ctas=int(t.shape[0]), single_us=round(single, 1),
+    live = buf[:, 0] > 0
+    waits = {n: [int(np.median(buf[live, 10 + i])), int(buf[live, 10 + i].max())] for i, n in
+             enumerate(["issuer_on_full", "issuer_on_tmem_empty", "producer_on_empty", "epilogue_on_tmem_full"])}
+    emit(kernel="gemm_timeline", spec=spec, ctas=int(t.shape[0]), single_us=round(single, 1), wait_cycles_median_max=waits,
          back_to_back_us=round(e0.elapsed_time(e1) * 1e3 / 20, 1),
          us_min_median_max={n: [round(float(rel[:, i].min()), 1), round(float(np.median(rel[:, i])), 1), round(float(rel[:, i].max()), 1)]
                             for i, n in enumerate(names)})

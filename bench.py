@@ -52,11 +52,12 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 GPT124M = dict(max_seq_len=1024, vocab_size=50304, padded_vocab=50304, n_layer=12, n_head=12, n_embd=768)
 B_PER_GPU, T = 8, 1024
-# DRAM bytes per tensor-core GEMM launch of one TF32 training step (mean over its 147 launches), from
-# an earlier profiler capture, and the algorithmic bytes of the same launches (each operand and result
-# once, C twice where beta = 1).  Stored constants: this run does not measure DRAM traffic.
-GEMM_DRAM_BYTES_PER_LAUNCH = 170.5e6
-GEMM_ALGO_BYTES_PER_LAUNCH = 145.6e6
+# DRAM bytes per tensor-core GEMM launch of one TF32 training step: each of the step's 15 GEMM shapes
+# captured alone under a profiler (one launch, DRAM read + write counters), weighted by its launches per
+# step (147 in all); and the algorithmic bytes of the same launches (each operand and result once, C
+# twice where beta = 1).  Stored constants: this run does not measure DRAM traffic.
+GEMM_DRAM_BYTES_PER_LAUNCH = 176.0e6
+GEMM_ALGO_BYTES_PER_LAUNCH = 146.2e6
 HP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, grad_clip=1.0)
 LOSSES_HEAD = 20
 WORKLOAD = ("GPT-2-small-shaped train step: 12 layers, d_model 768, 12 heads, ctx 1024, vocab 50304, "
@@ -396,6 +397,13 @@ def cpu_baseline():
                        "tokens, one optimiser step in %.1f s, loss %.4f; the reference has no CPU path" % (Tc, dt, loss))
 
 
+def note(msg):
+    """Progress line on stderr when BMB_BENCH_VERBOSE is set (rank and wall clock in front)."""
+    if os.environ.get("BMB_BENCH_VERBOSE"):
+        sys.stderr.write("[bench rank %s %.1f] %s\n" % (os.environ.get("RANK", "0"), time.time() % 1000, msg))
+        sys.stderr.flush()
+
+
 def make_trainer(bmb, math, fused):
     return bmb.Trainer(seed=1337, B=B_PER_GPU, T=T, use_flash=1, math=math, fused=fused, beta1=HP["beta1"], beta2=HP["beta2"],
                        eps=HP["eps"], weight_decay=HP["weight_decay"], grad_clip=HP["grad_clip"], **GPT124M)
@@ -482,7 +490,7 @@ def dp_selfcheck(bmb, torch, dist_mod, comm, rank, world):
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     gap = dist_mod.max_over_ranks(float(np.abs(l0 - l1).max()))
-    return {"small_model_loss_gap_fused_vs_nccl": gap, "small_model_params_equal_across_ranks": bool(torch.equal(lo, hi))}
+    return {"small_model_loss_gap_fused_vs_nccl": float(gap), "small_model_params_equal_across_ranks": bool(torch.equal(lo, hi))}
 
 
 def run_bmb(args):
@@ -502,6 +510,7 @@ def run_bmb(args):
     peaks = measured_peaks()
 
     tr = make_trainer(bmb, math, 0 if args.unfused else 1)
+    note("trainer created")
     comm = None
     if world > 1:
         ident = (C.c_ubyte * 128)()
@@ -557,6 +566,7 @@ def run_bmb(args):
         tr.sync()
     torch.cuda.synchronize()
     dist_mod.barrier()
+    note("warm-up done")
 
     # ---- timed region 1: kernel throughput, every batch already resident in HBM (forward + backward
     # replayed as a CUDA graph).  One step streams ~10 GB of activations through the 126 MB L2, so nothing
@@ -576,6 +586,7 @@ def run_bmb(args):
     dist_mod.barrier()
     ms_dev = dist_mod.max_over_ranks(e0.elapsed_time(e1))
     launches_timed = lib.bmb_launch_count() - launches_before
+    note("resident-batch region timed: %.2f ms/step" % (ms_dev / args.steps))
 
     # ---- timed region 2: end to end.  Every step uploads its batch from pinned memory and its loss is
     # copied back to pinned memory; the host reads the loss of step i-1 while step i runs (the way a
@@ -605,6 +616,7 @@ def run_bmb(args):
     dist_mod.barrier()
     ms_e2e = dist_mod.max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
     step_clocks = clocks.window(t_mark, time.time()) if clocks else None
+    note("end-to-end region timed")
 
     # ---- GEMM breakdown: a few more steps launched one kernel at a time with an event pair around
     # every GEMM (not part of either timed region)
@@ -617,6 +629,7 @@ def run_bmb(args):
     prof["launches"] = launches_timed
     tr.sync()
 
+    note("GEMM breakdown done")
     # losses of the first optimiser steps, averaged over ranks (each rank's loss is its shard's mean)
     head = all_losses[:min(LOSSES_HEAD, nsteps)].clone().double()
     params_equal = None
@@ -637,13 +650,22 @@ def run_bmb(args):
         if not args.nccl_dp and not args.no_dp_check:
             dp_check = dp_selfcheck(bmb, torch, dist_mod, comm, rank, world)
 
+    note("cross-rank checks done: params_equal=%s dp_check=%s" % (params_equal, dp_check))
     tokens_per_step = B_PER_GPU * T * world
     ms_step = ms_dev / args.steps
     value = tokens_per_step / (ms_step * 1e-3)
     e2e_value = tokens_per_step / (ms_e2e / args.steps * 1e-3)
     num_params = tr.num_params
-    if rank != 0:
+
+    def finish():
+        # every rank leaves together and without a communicator still alive at interpreter exit
         tr.close()
+        if comm is not None:
+            dist_mod.barrier()
+            lib.bmb_comm_destroy(comm)
+
+    if rank != 0:
+        finish()
         return
     achieved = prof["gemm_flop"] / (prof["gemm_ms"] * 1e-3) / 1e12 if prof["gemm_ms"] > 0 else 0.0
     if math == bmb.MATH_FP32:
@@ -675,8 +697,8 @@ def run_bmb(args):
                      "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
                      "frac": round(achieved / peak, 3) if peak else None,
                      "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if stored_traffic else None,
-                     "traffic_source": ("stored constant from an earlier profiler capture of one step's GEMM launches "
-                                        "(mean per launch), not measured in this run") if stored_traffic else None,
+                     "traffic_source": ("stored constant: each GEMM shape of the step captured alone under a profiler, "
+                                        "weighted by launches per step; not measured in this run") if stored_traffic else None,
                      "algorithmic_bytes_per_launch": GEMM_ALGO_BYTES_PER_LAUNCH,
                      "gemm_ms_per_step": round(prof["gemm_ms"] / prof["steps"], 3), "peak_note": peak_note,
                      "bound_detail": bound},
@@ -686,8 +708,7 @@ def run_bmb(args):
         line["params_equal_across_ranks"] = params_equal
         if dp_check:
             line["dp_check"] = dp_check
-    tr.close()
-    del tr
+    finish()
     torch.cuda.empty_cache()
     if world == 1:
         if not args.no_sweep:
@@ -705,7 +726,8 @@ def run_bmb(args):
             line["cpu_matmul"] = cpu_matmul()
     if clocks:
         clocks.stop()
-    print(json.dumps(line))
+    note("printing the line")
+    print(json.dumps(line), flush=True)
 
 
 def run_reference(args):
@@ -795,7 +817,7 @@ def run_reference(args):
     if n == 1 and not args.no_sweep:
         line.update(reference_kernels(ref, torch, clocks))
     clocks.stop()
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
 
 
 def reference_kernels(ref, torch, clocks):

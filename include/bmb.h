@@ -109,7 +109,8 @@ int bmb_gemm(int transA, int transB, int M, int N, int K, float alpha,
 #define BMB_GEMM_NO_SPLIT 8  /* never split K across CTAs (keeps the summation order fixed) */
 #define BMB_GEMM_TILE_M128 16 /* TF32 tensor-core path: 128-row tiles whatever the cost model says */
 #define BMB_GEMM_TILE_M256 32 /* TF32 tensor-core path: 256-row tiles where the shape allows (M >= 256, N >= 256) */
-#define BMB_GEMM_PAIR 64      /* TF32: run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles) where the shape allows */
+#define BMB_GEMM_PAIR 64      /* TF32: run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles) where the shape allows
+                                 (M >= 256, N >= 256, an M- or N-contiguous operand a multiple of 32 wide); opt-in */
 #define BMB_GEMM_NO_PAIR 128  /* TF32: never use CTA pairs for this call */
 #define BMB_GEMM_HALF_SMS 256 /* tensor-core path: occupy only half of the SMs (one CTA each), so that two products
                                  launched on two streams share the GPU side by side instead of one after the other */
