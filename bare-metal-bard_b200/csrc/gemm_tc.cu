@@ -384,20 +384,19 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             float *stg = reinterpret_cast<float *>(gen + STAGES * STAGE_BYTES) + (warp - 2) * (32 * 32);
             const int sub_r = lane >> 3, sub_u = lane & 7, sub_c = sub_u * 4;
             const float *part_bias = (kb0 == 0) ? bias : nullptr;
-#pragma unroll 1
-            for (int c = chunk_first; c < BN / 32; c += chunk_step) {
-                const int n0 = tn * BN + c * 32;
-                if (n0 >= N) break;                      // warp-uniform
-                if (whole && c_mode == 3) {
-                    // Direct path (beta 0, aligned C): the accumulator leaves TMEM in the 16x256b shape,
-                    // where four neighbouring lanes hold 32 contiguous bytes of a row, so the registers
-                    // go straight to global memory in whole sectors -- no trip through shared memory,
-                    // whose bandwidth the main loop needs.
-                    float lo[16], hi[16];
+            if (whole && c_mode == 3) {
+                // Direct path (beta 0, aligned C): the accumulator leaves TMEM in the 16x256b shape, where four
+                // neighbouring lanes hold 32 contiguous bytes of a row, so the registers go straight to global
+                // memory in whole sectors -- no trip through shared memory, whose bandwidth the main loop needs.
+                // Two register sets: the tensor-memory load of the next 32-column chunk is in flight while this
+                // chunk's stores are issued (the epilogue of a 256-row tile is not hidden behind a main loop).
+                const int r0 = row_base + (lane >> 2), cq = 2 * (lane & 3);
+                auto fetch = [&](int c, float (&lo)[16], float (&hi)[16]) {
                     tmem_ld_16x256b_x4_nowait(trow + (uint32_t)(c * 32), lo);                       // rows 0..15 of this quadrant
                     tmem_ld_16x256b_x4_nowait(trow + (uint32_t)(c * 32) + (16u << 16), hi);         // rows 16..31
-                    tmem_wait_ld();
-                    const int r0 = row_base + (lane >> 2), cq = 2 * (lane & 3);
+                };
+                auto put = [&](int c, const float (&lo)[16], const float (&hi)[16]) {
+                    const int n0 = tn * BN + c * 32;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int n = n0 + 8 * j + cq;
@@ -414,8 +413,28 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                             if (m < M) *reinterpret_cast<float2 *>(C + (size_t)m * N + n) = x;
                         }
                     }
-                    continue;
+                };
+                auto live = [&](int c) { return c < BN / 32 && tn * BN + c * 32 < N; };     // warp-uniform
+                float la[16], ha[16], lb[16], hb[16];
+                int c = chunk_first;
+                if (live(c)) fetch(c, la, ha);
+#pragma unroll 1
+                while (live(c)) {
+                    tmem_wait_ld();
+                    const int c2 = c + chunk_step;
+                    if (live(c2)) fetch(c2, lb, hb);
+                    put(c, la, ha);
+                    if (!live(c2)) break;
+                    tmem_wait_ld();
+                    c = c2 + chunk_step;
+                    if (live(c)) fetch(c, la, ha);
+                    put(c2, lb, hb);
                 }
+            } else
+#pragma unroll 1
+            for (int c = chunk_first; c < BN / 32; c += chunk_step) {
+                const int n0 = tn * BN + c * 32;
+                if (n0 >= N) break;                      // warp-uniform
                 float v[32];
                 tmem_ld32(trow + (uint32_t)(c * 32), v);
                 if (c_mode) {

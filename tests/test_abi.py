@@ -117,6 +117,22 @@ def test_tensorcore_gemm_schedule_covers_every_slice_once(bmb):
     assert shared > 20                      # the sweep does exercise shared tiles
     st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 96, 1024, 64, 1024, 148, None, None, None, None)   # batched
     assert st == 0, lib.bmb_last_error()
+    # the CTA-pair form (256 x 256 tiles handed to pairs), the half-GPU plans of the side-by-side backward
+    # products, and the forced tile heights
+    for units in (74, 37, 66, 1):
+        for (M, N, K) in shapes:
+            if M < 256 or N < 256:
+                continue
+            for flags in (bmb.GEMM_PAIR, bmb.GEMM_PAIR | bmb.GEMM_NO_SPLIT):
+                bm, bn, dp, grid = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+                st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flags, 1, M, N, K, units, C.byref(bm), C.byref(bn), C.byref(dp), C.byref(grid))
+                assert st == 0, (M, N, K, units, flags, lib.bmb_last_error())
+                assert (bm.value, bn.value) == (256, 256) and 1 <= grid.value <= units
+    for (M, N, K) in shapes[:10]:
+        for flags, want in ((bmb.GEMM_TILE_M128 | bmb.GEMM_NO_PAIR, 128), (bmb.GEMM_TILE_M256 | bmb.GEMM_NO_PAIR, 256)):
+            bm = C.c_int()
+            assert lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flags, 1, M, N, K, 148, C.byref(bm), None, None, None) == 0
+            assert bm.value == want
 
 
 def test_checkpoint_header_reads_the_gpt1_layout(bmb, tmp_path):
