@@ -382,10 +382,10 @@ struct FwdCfg { int kc; const char *name; };
 struct BwdCfg { int kc; const char *name; };
 // Forward config 2 is the tensor-core kernel (flash_tc.cu), head size 64 only.
 const FwdCfg FWD[] = {{16, "simt-fp32 rowgroup keys16"}, {8, "simt-fp32 rowgroup keys8"},
-                      {0, "tcgen05-tf32 q2x128 k64"}};
+                      {0, "tcgen05-tf32 q2x128 k64 (head size 64 only)"}};
 // Backward config 2 is the tensor-core kernel pair (flash_tc_bwd.cu), head size 64 only.
 const BwdCfg BWD[] = {{4, "simt-fp32 rowgroup keys4"}, {8, "simt-fp32 rowgroup keys8"},
-                      {0, "tcgen05-tf32 dq128x128 dkv128x128"}};
+                      {0, "tcgen05-tf32 dq128x128 dkv128x128 (head size 64 only)"}};
 constexpr int NFWD = 3, NBWD = 3, FWD_TC = 2, BWD_TC = 2;
 
 bool shape_ok(const float *a, const float *b, int C, int NH) {

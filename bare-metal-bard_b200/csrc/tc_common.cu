@@ -59,6 +59,23 @@ int make_map_mn3d(CUtensorMap *map, const void *ptr, long long rows_k, long long
     return BMB_OK;
 }
 
+// An fp32 array [batches][rows][cols] (cols % 32 == 0, contiguous) for tile stores of box_rows x 32 columns with the
+// 128-byte swizzle: rows past the end of a batch are clipped instead of running into the next batch.
+int make_map_rows3d(CUtensorMap *map, const void *ptr, long long cols, long long rows, long long batches, int box_rows) {
+    EncodeFn enc = encode_fn();
+    if (!enc) return fail(BMB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batches};
+    const cuuint64_t strides[2] = {(cuuint64_t)(cols * 4), (cuuint64_t)(rows * cols * 4)};
+    const cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(BMB_E_CUDA, "cuTensorMapEncodeTiled (3-d rows) failed (%d) for %lld x %lld x %lld", (int)r, batches, rows, cols);
+    return BMB_OK;
+}
+
 struct Status { int *dev = nullptr; int *host = nullptr; };
 static Status g_status[64];
 static std::mutex g_status_mu;

@@ -325,6 +325,7 @@ EncodeFn encode_fn();
 // box = 128 bytes of columns x box_rows rows, zero fill outside the matrix; atom32 = false: SWIZZLE_128B,
 // atom32 = true: SWIZZLE_128B_ATOM_32B (for MN-major tiles of 32-bit elements).
 int make_map_mn3d(CUtensorMap *map, const void *ptr, long long rows_k, long long cols_x, long long pitch_bytes, int box_chunks);
+int make_map_rows3d(CUtensorMap *map, const void *ptr, long long cols, long long rows, long long batches, int box_rows);
 int make_map_2d(CUtensorMap *map, const void *ptr, int esize, long long rows, long long cols, long long pitch_bytes,
                 int box_rows, bool atom32 = false);
 
