@@ -121,6 +121,7 @@ SIGNATURES = {
     "bmb_trainer_attach_comm": (_i, [_p, _p, _i]),
     "bmb_trainer_ipc_export": (_i, [_p, _p]),
     "bmb_trainer_attach_peers": (_i, [_p, _i, _i, _p]),
+    "bmb_trainer_step_plan": (_i, [_p, _i, _p, _p, _p, _p]),
     "bmb_trainer_num_params": (_z, [_p]),
     "bmb_trainer_get_params": (_i, [_p, _p]),
     "bmb_trainer_set_params": (_i, [_p, _p]),

@@ -45,6 +45,14 @@ cudaStream_t cur_stream();
 bool emit_rounded();
 void set_emit_rounded(bool on);
 
+// ---- data-parallel exchange: a list of ranges of a flat float buffer ------
+// (offsets and lengths in floats, each a multiple of 4)
+constexpr int DP_MAX_RANGES = 16;
+struct DpRangeList {
+    unsigned long long off[DP_MAX_RANGES], len[DP_MAX_RANGES];
+    int n;
+};
+
 // ---- per-device scratch ---------------------------------------------------
 // The reference keeps process-wide static device scratch (src/nn.cu:347, 362)
 // that every rank thread shares regardless of device.  Here each device owns

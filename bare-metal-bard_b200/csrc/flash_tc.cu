@@ -81,7 +81,7 @@ __device__ __forceinline__ unsigned long long ftime() {
 #define FW_BEGIN() const long long fw_t0 = clock64()
 #define FW_END(acc) acc += clock64() - fw_t0
 // knock-out switches for timing experiments (results are then wrong): 1 no exponentials, 2 no P V load / fold,
-// 4 no maximum, 8 no store of P
+// 4 no maximum, 8 no store of P, 16 no score products, 32 no P V products
 __device__ int g_flash_ko;
 #define KO_DECL() const int ko = g_flash_ko
 #define KO(bit) (ko & (bit))
@@ -233,6 +233,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             const uint32_t s_tmem = tmem_base + (uint32_t)(t * TILE_COLS);
             const uint32_t pa = s_tmem + COL_P, pvd = s_tmem + COL_PV;
             bool ok = true;
+            KO_DECL();
             int kc = 0, vc = 0, pc = 0;                   // key blocks, value blocks, P tiles consumed so far (all items)
             int sn0 = 0, sn1 = 0;                         // score products issued so far into each half of the S buffer
             for (int r = 0; ok && fwd_item(r, T, BH, nqblk, it); ++r) {
@@ -254,6 +255,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                             const uint32_t kh = base + OFF_K + st * KV_TILE_BYTES + (uint32_t)(hf * (KB * 128));   // key rows 64 hf .. 64 hf + 63 of the block
 #pragma unroll
                             for (int ks = 0; ks < HS / 8; ++ks) {
+                                if (KO(16)) break;
                                 const uint32_t half = ks >> 2, off = (ks & 3) * 32;
                                 mma_tf32(d, smem_desc_kmajor(qa + half * (QT * 128) + off),
                                          smem_desc_kmajor(kh + half * (KBLK * 128) + off), idesc_s, ks ? 1u : 0u);
@@ -275,7 +277,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                             const uint32_t va = base + OFF_V + st * KV_TILE_BYTES + (uint32_t)((i & 1) * (KB * 128));
 #pragma unroll
                             for (int ks = 0; ks < KB / 8; ++ks)
-                                mma_tf32_ts(pvd, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, ks ? 1u : 0u);
+                                if (!KO(32)) mma_tf32_ts(pvd, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, ks ? 1u : 0u);
                             commit(bar(PV_FULL + t));
                             ++pc;
                         }

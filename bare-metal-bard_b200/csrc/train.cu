@@ -29,9 +29,11 @@ int dp_fused_export(const float *grads, const float *params, const float *shadow
 int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads, float *params, float *shadow,
                     const void *all_handles);
 void dp_fused_destroy(DpFused *d);
-int dp_fused_reduce(DpFused *d, size_t n, float *grads, double *d_sumsq_slice, cudaStream_t st);
-int dp_fused_update(DpFused *d, size_t n, const float *grads, float *m, float *v, float lr, float beta1, float beta2,
-                    float eps, float wd, int step, const double *d_sumsq_total, float clip, cudaStream_t st);
+int dp_fused_reduce_ranges(DpFused *d, const DpRangeList &rl, float *grads, int slot, cudaStream_t st);
+int dp_fused_sumsq(DpFused *d, double *d_sumsq_pieces, cudaStream_t st);
+int dp_fused_update_ranges(DpFused *d, const DpRangeList &rl, const float *grads, float *m, float *v, float lr, float beta1,
+                           float beta2, float eps, float wd, int step, const double *d_sumsq_total, float clip, cudaStream_t st);
+int dp_round_ranges(const DpRangeList &rl, float *shadow, const float *params, cudaStream_t st);
 }
 using namespace bmb;
 
@@ -62,11 +64,31 @@ struct bmb_trainer {
     float *dres, *dln1, *dln2, *datty, *dqkv, *dqkvr, *datt, *dsum, *dfch, *dfch_gelu, *dlogits, *dlnf;
     // The forward and backward pass of a step, captured once into a CUDA graph and replayed: the
     // ~370 launches of a step then follow one another without a host round trip each.
+    // The step is a list of pieces (runs of units: embedding, layers, head, and their backward counterparts), one
+    // graph each: a single piece without the fused exchange, five with it (see plan_pieces).
     bool use_graph = true, graph_failed = false;
     int eager_passes = 0;                 // the first pass runs eagerly (it sizes the library's scratch)
-    cudaGraphExec_t graph_exec = nullptr;
-    long long graph_launches = 0;
-    unsigned long long graph_scratch_gen = 0;   // the device's scratch generation the graph was captured under
+    struct Piece {
+        int u0 = 0, u1 = 0;               // units [u0, u1)
+        int needs = -1;                   // chunk whose new parameters must have arrived before the piece starts
+        int reduces = -1;                 // chunk whose gradients are final when the piece ends
+        cudaGraphExec_t exec = nullptr;
+        long long launches = 0;
+    };
+    std::vector<Piece> pieces;
+    unsigned long long graph_scratch_gen = 0;   // the device's scratch generation the graphs were captured under
+    // Fused exchange, overlapped: the parameter space is cut into three chunks -- A: embeddings + layer 0,
+    // B: layers 1 .. c2-1, C: layers c2 .. L-1 + final layernorm.  Backward finishes C, then B, then A, and each
+    // chunk's reduce runs on the exchange stream while backward goes on; the next forward needs A, then B, then
+    // C, and each chunk's update + broadcast is awaited only by the first piece that reads it.
+    static constexpr int NCHUNK = 3;
+    DpRangeList chunk[NCHUNK];
+    int chunk_split = 0;                  // c2
+    bool overlap = true;                  // BMB_TRAINER_OVERLAP=0: one chunk, exchanged after backward
+    cudaStream_t st_x = nullptr;          // exchange stream
+    cudaEvent_t ev_seg[NCHUNK] = {nullptr, nullptr, nullptr};   // main stream: the chunk's gradients are final
+    cudaEvent_t ev_upd[NCHUNK] = {nullptr, nullptr, nullptr};   // exchange stream: the chunk's new parameters are in place
+    bool upd_pending[NCHUNK] = {false, false, false};
     float *gen_probs = nullptr;   // one row of next-token probabilities, allocated by the first sampling call
     // The two products of a linear layer's backward (dX = dY W and dW = dY^T X: the same FLOP count, both waiting only
     // for dY) run side by side, each on half of the SMs: dX on the main stream, dW on this one, forked and joined
@@ -92,14 +114,19 @@ void param_sizes(size_t *s, const bmb_train_config &c) {
 }
 enum { P_WTE, P_WPE, P_LN1W, P_LN1B, P_QKVW, P_QKVB, P_APW, P_APB, P_LN2W, P_LN2B, P_FCW, P_FCB, P_FPW, P_FPB, P_LNFW, P_LNFB };
 
+// Entry points run on the trainer's device and stream.  Unless told otherwise they first make the main stream
+// wait for what the last step left running on the exchange stream (parameter chunks still being updated).
 struct Scope {
     int prev_dev = 0;
     void *prev_stream;
-    explicit Scope(bmb_trainer *t) {
+    explicit Scope(bmb_trainer *t, bool join = true) {
         cudaGetDevice(&prev_dev);
         cudaSetDevice(t->dev);
         prev_stream = bmb_get_stream();
         bmb_set_stream(t->st);
+        if (join)
+            for (int c = 0; c < bmb_trainer::NCHUNK; ++c)
+                if (t->upd_pending[c]) { cudaStreamWaitEvent(t->st, t->ev_upd[c], 0); t->upd_pending[c] = false; }
     }
     ~Scope() { set_emit_rounded(false); bmb_set_stream(prev_stream); cudaSetDevice(prev_dev); }
 };
@@ -150,220 +177,338 @@ int mm(bmb_trainer *t, int flags, int ta, int tb, int M, int N, int K, const flo
     return BMB_OK;
 }
 
-int forward(bmb_trainer *t, bool with_loss = true) {
+// Shapes and operand conventions shared by the units of a pass.
+struct Dims {
+    int B, T, C, L, NH, Vp, V, N;
+    size_t BTC, BT, BT3C, BT4C, qkvr_sz, att_sz, lse_sz;
+    const float *W, *P;      // weights as the GEMMs read them (the pre-rounded shadow copy in the tensor-core modes), and as stored
+    float *G;
+    bool fz;
+    int wflag;               // products with a weight: A = an activation or gradient (rounded by its producer when fused), B = the weight
+    int gflag;               // weight-gradient products: both operands are activations / gradients
+};
+Dims dims_of(bmb_trainer *t) {
     const bmb_train_config &c = t->c;
-    const int B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head;
-    const int Vp = c.padded_vocab, V = c.vocab_size, N = B * T;
-    const size_t BTC = (size_t)N * C, BT = N, BT3C = 3 * BTC, BT4C = 4 * BTC;
-    const size_t qkvr_sz = 4 * BTC, att_sz = (size_t)B * NH * T * T, lse_sz = (size_t)B * NH * T;
-    // Weights: the tensor-core modes read the pre-rounded shadow copy.
-    const float *W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
-    const bool fz = fused_tf32(c);
-    // forward GEMMs: A = an activation (rounded by its producer when fused), B = a weight (rounded shadow)
-    const int wflag = ((W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0) | (fz ? BMB_GEMM_A_ROUNDED : 0);
-    const float *P = t->params;
-    set_emit_rounded(fz);
+    Dims d;
+    d.B = c.B; d.T = c.T; d.C = c.n_embd; d.L = c.n_layer; d.NH = c.n_head; d.Vp = c.padded_vocab; d.V = c.vocab_size;
+    d.N = d.B * d.T;
+    d.BTC = (size_t)d.N * d.C; d.BT = d.N; d.BT3C = 3 * d.BTC; d.BT4C = 4 * d.BTC;
+    d.qkvr_sz = 4 * d.BTC; d.att_sz = (size_t)d.B * d.NH * d.T * d.T; d.lse_sz = (size_t)d.B * d.NH * d.T;
+    d.W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
+    d.P = t->params;
+    d.G = t->grads;
+    d.fz = fused_tf32(c);
+    d.wflag = ((d.W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0) | (d.fz ? BMB_GEMM_A_ROUNDED : 0);
+    d.gflag = d.fz ? (BMB_GEMM_A_ROUNDED | BMB_GEMM_B_ROUNDED) : 0;
+    return d;
+}
 
-    BMB_TRY(bmb_encoder_forward(t->encoded, t->d_tokens, P + t->poff[P_WTE], P + t->poff[P_WPE], B, T, C));
-    float *residual = t->encoded;
+int fwd_embed(bmb_trainer *t, const Dims &d) {
+    BMB_TRY(bmb_encoder_forward(t->encoded, t->d_tokens, d.P + t->poff[P_WTE], d.P + t->poff[P_WPE], d.B, d.T, d.C));
     // The first layernorm stands alone; every later one (and the final one) rides with the
     // residual add that produces its input.
-    BMB_TRY(bmb_layernorm_forward(t->ln1, t->ln1_mean, t->ln1_rstd, residual, P + t->poff[P_LN1W], P + t->poff[P_LN1B], N, C));
-    for (int l = 0; l < L; ++l) {
-        float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * BT3C, *atty = t->atty + l * BTC;
-        float *attproj = t->attproj + l * BTC, *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
-        float *fch = t->fch + l * BT4C, *fchg = t->fch_gelu + l * BT4C, *fcproj = t->fcproj + l * BTC;
-        float *res3 = t->residual3 + l * BTC;
-        if (fz) {
-            BMB_TRY(mm(t, wflag | BMB_GEMM_C_ROUNDED, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv,
-                       P + t->poff[P_QKVB] + (size_t)l * 3 * C));
-        } else {
-            BMB_TRY(mm(t, wflag, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv));
-            BMB_TRY(bmb_bias_forward(qkv, P + t->poff[P_QKVB] + (size_t)l * 3 * C, N, 3 * C));
-        }
-        if (c.use_flash && fz && attn_cfg(c) == 2)
-            BMB_TRY(flash_forward_tc(atty, t->lse + l * lse_sz, qkv, B, T, C, NH, true, t->st));
-        else if (c.use_flash)
-            BMB_TRY(bmb_flash_attention_forward_cfg(attn_cfg(c), atty, t->lse + l * lse_sz, qkv, B, T, C, NH));
-        else
-            BMB_TRY(bmb_attention_forward(atty, t->qkvr + l * qkvr_sz, t->att + l * att_sz, qkv, B, T, C, NH));
-        if (fz) {
-            BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj,
-                       P + t->poff[P_APB] + (size_t)l * C));
-        } else {
-            BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
-            BMB_TRY(bmb_bias_forward(attproj, P + t->poff[P_APB] + (size_t)l * C, N, C));
-        }
-        BMB_TRY(bmb_residual_layernorm_forward(res2, ln2, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, residual, attproj,
-                                               P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
-        if (fz) {
-            BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch,
-                       P + t->poff[P_FCB] + (size_t)l * 4 * C));
-        } else {
-            BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch));
-            BMB_TRY(bmb_bias_forward(fch, P + t->poff[P_FCB] + (size_t)l * 4 * C, N, 4 * C));
-        }
-        BMB_TRY(bmb_gelu_forward(fchg, fch, (int)BT4C));
-        if (fz) {
-            BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj,
-                       P + t->poff[P_FPB] + (size_t)l * C));
-        } else {
-            BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj));
-            BMB_TRY(bmb_bias_forward(fcproj, P + t->poff[P_FPB] + (size_t)l * C, N, C));
-        }
-        if (l + 1 < L)
-            BMB_TRY(bmb_residual_layernorm_forward(res3, t->ln1 + (l + 1) * BTC, t->ln1_mean + (l + 1) * BT, t->ln1_rstd + (l + 1) * BT,
-                                                   res2, fcproj, P + t->poff[P_LN1W] + (size_t)(l + 1) * C,
-                                                   P + t->poff[P_LN1B] + (size_t)(l + 1) * C, N, C));
-        else
-            BMB_TRY(bmb_residual_layernorm_forward(res3, t->lnf, t->lnf_mean, t->lnf_rstd, res2, fcproj, P + t->poff[P_LNFW],
-                                                   P + t->poff[P_LNFB], N, C));
-        residual = res3;
+    return bmb_layernorm_forward(t->ln1, t->ln1_mean, t->ln1_rstd, t->encoded, d.P + t->poff[P_LN1W], d.P + t->poff[P_LN1B], d.N, d.C);
+}
+
+int fwd_layer(bmb_trainer *t, const Dims &d, int l) {
+    const bmb_train_config &c = t->c;
+    const int N = d.N, C = d.C, L = d.L, NH = d.NH, B = d.B, T = d.T;
+    const size_t BTC = d.BTC, BT = d.BT;
+    const float *W = d.W, *P = d.P;
+    const int wflag = d.wflag;
+    const bool fz = d.fz;
+    float *residual = (l == 0) ? t->encoded : t->residual3 + (size_t)(l - 1) * BTC;
+    float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * d.BT3C, *atty = t->atty + l * BTC;
+    float *attproj = t->attproj + l * BTC, *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
+    float *fch = t->fch + l * d.BT4C, *fchg = t->fch_gelu + l * d.BT4C, *fcproj = t->fcproj + l * BTC;
+    float *res3 = t->residual3 + l * BTC;
+    if (fz) {
+        BMB_TRY(mm(t, wflag | BMB_GEMM_C_ROUNDED, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv,
+                   P + t->poff[P_QKVB] + (size_t)l * 3 * C));
+    } else {
+        BMB_TRY(mm(t, wflag, 0, 1, N, 3 * C, C, ln1, W + t->poff[P_QKVW] + (size_t)l * 3 * C * C, 0.0f, qkv));
+        BMB_TRY(bmb_bias_forward(qkv, P + t->poff[P_QKVB] + (size_t)l * 3 * C, N, 3 * C));
     }
-    BMB_TRY(mm(t, wflag, 0, 1, N, Vp, C, t->lnf, W + t->poff[P_WTE], 0.0f, t->logits));
+    if (c.use_flash && fz && attn_cfg(c) == 2)
+        BMB_TRY(flash_forward_tc(atty, t->lse + l * d.lse_sz, qkv, B, T, C, NH, true, t->st));
+    else if (c.use_flash)
+        BMB_TRY(bmb_flash_attention_forward_cfg(attn_cfg(c), atty, t->lse + l * d.lse_sz, qkv, B, T, C, NH));
+    else
+        BMB_TRY(bmb_attention_forward(atty, t->qkvr + l * d.qkvr_sz, t->att + l * d.att_sz, qkv, B, T, C, NH));
+    if (fz) {
+        BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj,
+                   P + t->poff[P_APB] + (size_t)l * C));
+    } else {
+        BMB_TRY(mm(t, wflag, 0, 1, N, C, C, atty, W + t->poff[P_APW] + (size_t)l * C * C, 0.0f, attproj));
+        BMB_TRY(bmb_bias_forward(attproj, P + t->poff[P_APB] + (size_t)l * C, N, C));
+    }
+    BMB_TRY(bmb_residual_layernorm_forward(res2, ln2, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, residual, attproj,
+                                           P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
+    if (fz) {
+        BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch,
+                   P + t->poff[P_FCB] + (size_t)l * 4 * C));
+    } else {
+        BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch));
+        BMB_TRY(bmb_bias_forward(fch, P + t->poff[P_FCB] + (size_t)l * 4 * C, N, 4 * C));
+    }
+    BMB_TRY(bmb_gelu_forward(fchg, fch, (int)d.BT4C));
+    if (fz) {
+        BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj,
+                   P + t->poff[P_FPB] + (size_t)l * C));
+    } else {
+        BMB_TRY(mm(t, wflag, 0, 1, N, C, 4 * C, fchg, W + t->poff[P_FPW] + (size_t)l * C * 4 * C, 0.0f, fcproj));
+        BMB_TRY(bmb_bias_forward(fcproj, P + t->poff[P_FPB] + (size_t)l * C, N, C));
+    }
+    if (l + 1 < L)
+        return bmb_residual_layernorm_forward(res3, t->ln1 + (l + 1) * BTC, t->ln1_mean + (l + 1) * BT, t->ln1_rstd + (l + 1) * BT,
+                                              res2, fcproj, P + t->poff[P_LN1W] + (size_t)(l + 1) * C,
+                                              P + t->poff[P_LN1B] + (size_t)(l + 1) * C, N, C);
+    return bmb_residual_layernorm_forward(res3, t->lnf, t->lnf_mean, t->lnf_rstd, res2, fcproj, P + t->poff[P_LNFW],
+                                          P + t->poff[P_LNFB], N, C);
+}
+
+int fwd_head(bmb_trainer *t, const Dims &d, bool with_loss) {
+    BMB_TRY(mm(t, d.wflag, 0, 1, d.N, d.Vp, d.C, t->lnf, d.W + t->poff[P_WTE], 0.0f, t->logits));
     if (!with_loss) return BMB_OK;        // sampling reads the logits only
     // Loss and its gradient with respect to the logits in one sweep (mean loss: dloss = 1/N).
-    BMB_TRY(bmb_softmax_crossentropy_fused(t->dlogits, t->losses, t->logits, t->d_targets, N, V, Vp, 1.0f / N));
-    BMB_TRY(bmb_reduce_mean_device(t->losses, N, t->d_loss));
+    BMB_TRY(bmb_softmax_crossentropy_fused(t->dlogits, t->losses, t->logits, t->d_targets, d.N, d.V, d.Vp, 1.0f / d.N));
+    return bmb_reduce_mean_device(t->losses, d.N, t->d_loss);
+}
+
+// dX = dY * W with W stored [out, in]: W is the MN-major operand of this product.
+int dx(bmb_trainer *t, const Dims &d, int flags, int M_, int N_, int K_, const float *dY, int id, size_t woff, float *dX) {
+    return mm(t, flags, 0, 0, M_, N_, K_, dY, d.W + t->poff[id] + woff, 0.0f, dX);
+}
+
+// dX and dW of one linear layer.  Side by side (fused TF32 mode, not while GEMMs are being timed one by one):
+// the weight gradient goes to the second stream, both planned for half of the SMs.
+// (only where both read their operands in place: a product that first rounds an operand into the per-device
+// staging scratch must not share it with another in flight)
+int dx_dw(bmb_trainer *t, const Dims &d, int xflags, int Mx, int Nx, int Kx, const float *dY, int id, size_t woff, float *dX,
+          int Mw, int Nw, const float *act, float *dW) {
+    const bool sbs = t->side_by_side && d.fz && !t->prof && t->st_dw;
+    if (!sbs) {
+        BMB_TRY(dx(t, d, xflags, Mx, Nx, Kx, dY, id, woff, dX));
+        return mm(t, d.gflag, 1, 0, Mw, Nw, Mx, dY, act, 1.0f, dW);
+    }
+    BMB_CUDA(cudaEventRecord(t->ev_fork, t->st));
+    BMB_CUDA(cudaStreamWaitEvent(t->st_dw, t->ev_fork, 0));
+    BMB_TRY(mm(t, d.gflag | BMB_GEMM_HALF_SMS, 1, 0, Mw, Nw, Mx, dY, act, 1.0f, dW, nullptr, t->st_dw));
+    BMB_TRY(dx(t, d, xflags | BMB_GEMM_HALF_SMS, Mx, Nx, Kx, dY, id, woff, dX));
+    BMB_CUDA(cudaEventRecord(t->ev_join, t->st_dw));
+    BMB_CUDA(cudaStreamWaitEvent(t->st, t->ev_join, 0));
     return BMB_OK;
 }
 
-int backward(bmb_trainer *t) {
-    const bmb_train_config &c = t->c;
-    const int B = c.B, T = c.T, C = c.n_embd, L = c.n_layer, NH = c.n_head;
-    const int Vp = c.padded_vocab, V = c.vocab_size, N = B * T;
-    const size_t BTC = (size_t)N * C, BT = N, BT3C = 3 * BTC, BT4C = 4 * BTC;
-    const size_t qkvr_sz = 4 * BTC, att_sz = (size_t)B * NH * T * T, lse_sz = (size_t)B * NH * T;
-    const float *W = (c.math == BMB_MATH_FP32 || !t->shadow) ? t->params : t->shadow;
-    const bool fz = fused_tf32(c);
-    // dX GEMMs: A = a gradient (rounded by its producer when fused), B = a weight (rounded shadow);
-    // dW GEMMs: both operands are activations / gradients.
-    const int wflag = ((W == t->shadow) ? BMB_GEMM_B_ROUNDED : 0) | (fz ? BMB_GEMM_A_ROUNDED : 0);
-    const int gflag = fz ? (BMB_GEMM_A_ROUNDED | BMB_GEMM_B_ROUNDED) : 0;
-    const float *P = t->params;
-    float *G = t->grads;
-    set_emit_rounded(fz);
-    // dX = dY * W with W stored [out, in]: W is the MN-major operand of this product.
-    auto dx = [&](int flags, int M_, int N_, int K_, const float *dY, int id, size_t woff, float *dX) -> int {
-        return mm(t, flags, 0, 0, M_, N_, K_, dY, W + t->poff[id] + woff, 0.0f, dX);
-    };
-
-    // dX and dW of one linear layer.  Side by side (fused TF32 mode, not while GEMMs are being timed one by one):
-    // the weight gradient goes to the second stream, both planned for half of the SMs.
-    // (only where both read their operands in place: a product that first rounds an operand into the per-device
-    // staging scratch must not share it with another in flight)
-    const bool sbs = t->side_by_side && fz && !t->prof && t->st_dw;
-    auto pair = [&](int xflags, int Mx, int Nx, int Kx, const float *dY, int id, size_t woff, float *dX,
-                    int Mw, int Nw, const float *act, float *dW) -> int {
-        if (!sbs) {
-            BMB_TRY(dx(xflags, Mx, Nx, Kx, dY, id, woff, dX));
-            return mm(t, gflag, 1, 0, Mw, Nw, Mx, dY, act, 1.0f, dW);
-        }
-        BMB_CUDA(cudaEventRecord(t->ev_fork, t->st));
-        BMB_CUDA(cudaStreamWaitEvent(t->st_dw, t->ev_fork, 0));
-        BMB_TRY(mm(t, gflag | BMB_GEMM_HALF_SMS, 1, 0, Mw, Nw, Mx, dY, act, 1.0f, dW, nullptr, t->st_dw));
-        BMB_TRY(dx(xflags | BMB_GEMM_HALF_SMS, Mx, Nx, Kx, dY, id, woff, dX));
-        BMB_CUDA(cudaEventRecord(t->ev_join, t->st_dw));
-        BMB_CUDA(cudaStreamWaitEvent(t->st, t->ev_join, 0));
-        return BMB_OK;
-    };
-
+int bwd_head(bmb_trainer *t, const Dims &d) {
+    const int N = d.N, C = d.C, L = d.L, Vp = d.Vp;
+    float *G = d.G;
     BMB_CUDA(cudaMemsetAsync(G, 0, t->num_params * sizeof(float), t->st));
-    BMB_TRY(dx(wflag, N, C, Vp, t->dlogits, P_WTE, 0, t->dlnf));
-    BMB_TRY(mm(t, gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
-    float *last_res = t->residual3 + (size_t)(L - 1) * BTC;
-    BMB_CUDA(cudaMemsetAsync(t->dres, 0, BTC * sizeof(float), t->st));
+    BMB_TRY(dx(t, d, d.wflag, N, C, Vp, t->dlogits, P_WTE, 0, t->dlnf));
+    BMB_TRY(mm(t, d.gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
+    float *last_res = t->residual3 + (size_t)(L - 1) * d.BTC;
+    BMB_CUDA(cudaMemsetAsync(t->dres, 0, d.BTC * sizeof(float), t->st));
     // Each layernorm backward also sums the columns of the residual-stream gradient it leaves behind:
     // that is the bias gradient of the projection feeding that point of the stream.
-    BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LNFW], G + t->poff[P_LNFB],
-                                          G + t->poff[P_FPB] + (size_t)(L - 1) * C, t->dlnf, last_res,
-                                          P + t->poff[P_LNFW], t->lnf_mean, t->lnf_rstd, N, C));
-    for (int l = L - 1; l >= 0; --l) {
-        float *residual = (l == 0) ? t->encoded : t->residual3 + (size_t)(l - 1) * BTC;
-        float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * BT3C, *atty = t->atty + l * BTC;
-        float *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
-        float *fch = t->fch + l * BT4C, *fchg = t->fch_gelu + l * BT4C;
-        const size_t lC = (size_t)l * C;
-
-        BMB_TRY(pair(wflag, N, 4 * C, C, t->dres, P_FPW, (size_t)l * C * 4 * C, t->dfch_gelu,
-                     C, 4 * C, fchg, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
-        BMB_TRY(bmb_gelu_backward_colsum(t->dfch, G + t->poff[P_FCB] + 4 * lC, fch, t->dfch_gelu, N, 4 * C));
-        BMB_TRY(pair(wflag, N, C, 4 * C, t->dfch, P_FCW, (size_t)l * 4 * C * C, t->dln2,
-                     4 * C, C, ln2, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
-        BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC,
-                                              G + t->poff[P_APB] + lC, t->dln2, res2,
-                                              P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
-        BMB_TRY(pair(wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), N, C, C, t->dres, P_APW, (size_t)l * C * C, t->datty,
-                     C, C, atty, G + t->poff[P_APW] + (size_t)l * C * C));
-        if (c.use_flash && fz && attn_cfg(c) == 2)
-            BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH, true, t->st));
-        else if (c.use_flash)
-            BMB_TRY(bmb_flash_attention_backward_cfg(attn_cfg(c), t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * lse_sz, B, T, C, NH));
-        else
-            BMB_TRY(bmb_attention_backward(t->dqkv, t->dqkvr, t->datt, t->datt, t->datty, t->qkvr + l * qkvr_sz,
-                                           t->att + l * att_sz, B, T, C, NH));
-        BMB_TRY(pair(wflag, N, C, 3 * C, t->dqkv, P_QKVW, (size_t)l * 3 * C * C, t->dln1,
-                     3 * C, C, ln1, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
-        BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
-        BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC,
-                                              l > 0 ? G + t->poff[P_FPB] + lC - C : nullptr, t->dln1, residual,
-                                              P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C));
-    }
-    BMB_TRY(bmb_encoder_backward(G + t->poff[P_WTE], G + t->poff[P_WPE], t->dres, t->d_tokens, B, T, C));
-    return BMB_OK;
+    return bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LNFW], G + t->poff[P_LNFB],
+                                         G + t->poff[P_FPB] + (size_t)(L - 1) * C, t->dlnf, last_res,
+                                         d.P + t->poff[P_LNFW], t->lnf_mean, t->lnf_rstd, N, C);
 }
 
-// forward + backward of one step on t->st: replay of the captured graph, or eager launches while
-// there is no graph (first pass, GEMM event profiling on, graphs switched off, or capture failed).
-int forward_backward_step(bmb_trainer *t) {
-    if (!t->use_graph || t->graph_failed || t->prof) {
-        BMB_TRY(forward(t));
-        return backward(t);
+int bwd_layer(bmb_trainer *t, const Dims &d, int l) {
+    const bmb_train_config &c = t->c;
+    const int N = d.N, C = d.C, NH = d.NH, B = d.B, T = d.T;
+    const size_t BTC = d.BTC, BT = d.BT;
+    const float *P = d.P;
+    float *G = d.G;
+    const int wflag = d.wflag;
+    const bool fz = d.fz;
+    float *residual = (l == 0) ? t->encoded : t->residual3 + (size_t)(l - 1) * BTC;
+    float *ln1 = t->ln1 + l * BTC, *qkv = t->qkv + l * d.BT3C, *atty = t->atty + l * BTC;
+    float *res2 = t->residual2 + l * BTC, *ln2 = t->ln2 + l * BTC;
+    float *fch = t->fch + l * d.BT4C, *fchg = t->fch_gelu + l * d.BT4C;
+    const size_t lC = (size_t)l * C;
+
+    BMB_TRY(dx_dw(t, d, wflag, N, 4 * C, C, t->dres, P_FPW, (size_t)l * C * 4 * C, t->dfch_gelu,
+                  C, 4 * C, fchg, G + t->poff[P_FPW] + (size_t)l * C * 4 * C));
+    BMB_TRY(bmb_gelu_backward_colsum(t->dfch, G + t->poff[P_FCB] + 4 * lC, fch, t->dfch_gelu, N, 4 * C));
+    BMB_TRY(dx_dw(t, d, wflag, N, C, 4 * C, t->dfch, P_FCW, (size_t)l * 4 * C * C, t->dln2,
+                  4 * C, C, ln2, G + t->poff[P_FCW] + (size_t)l * 4 * C * C));
+    BMB_TRY(bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN2W] + lC, G + t->poff[P_LN2B] + lC,
+                                          G + t->poff[P_APB] + lC, t->dln2, res2,
+                                          P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
+    BMB_TRY(dx_dw(t, d, wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), N, C, C, t->dres, P_APW, (size_t)l * C * C, t->datty,
+                  C, C, atty, G + t->poff[P_APW] + (size_t)l * C * C));
+    if (c.use_flash && fz && attn_cfg(c) == 2)
+        BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * d.lse_sz, B, T, C, NH, true, t->st));
+    else if (c.use_flash)
+        BMB_TRY(bmb_flash_attention_backward_cfg(attn_cfg(c), t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * d.lse_sz, B, T, C, NH));
+    else
+        BMB_TRY(bmb_attention_backward(t->dqkv, t->dqkvr, t->datt, t->datt, t->datty, t->qkvr + l * d.qkvr_sz,
+                                       t->att + l * d.att_sz, B, T, C, NH));
+    BMB_TRY(dx_dw(t, d, wflag, N, C, 3 * C, t->dqkv, P_QKVW, (size_t)l * 3 * C * C, t->dln1,
+                  3 * C, C, ln1, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
+    BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
+    return bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC,
+                                         l > 0 ? G + t->poff[P_FPB] + lC - C : nullptr, t->dln1, residual,
+                                         P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C);
+}
+
+int bwd_embed(bmb_trainer *t, const Dims &d) {
+    return bmb_encoder_backward(d.G + t->poff[P_WTE], d.G + t->poff[P_WPE], t->dres, t->d_tokens, d.B, d.T, d.C);
+}
+
+// The units of a pass, in execution order: 0 embedding; 1 .. L the layers; L+1 the head with the loss;
+// L+2 the head's backward; L+3 .. 2L+2 the layers' backward (last layer first); 2L+3 the embedding's backward.
+int num_units(const bmb_trainer *t) { return 2 * t->c.n_layer + 4; }
+int run_units(bmb_trainer *t, int u0, int u1, bool with_loss = true) {
+    const Dims d = dims_of(t);
+    const int L = d.L;
+    set_emit_rounded(d.fz);
+    for (int u = u0; u < u1; ++u) {
+        if (u == 0) BMB_TRY(fwd_embed(t, d));
+        else if (u <= L) BMB_TRY(fwd_layer(t, d, u - 1));
+        else if (u == L + 1) BMB_TRY(fwd_head(t, d, with_loss));
+        else if (u == L + 2) BMB_TRY(bwd_head(t, d));
+        else if (u <= 2 * L + 2) BMB_TRY(bwd_layer(t, d, 2 * L + 2 - u));
+        else BMB_TRY(bwd_embed(t, d));
     }
-    // The captured launches carry the addresses of the library's per-device scratch.  If another
-    // caller on this device has made that scratch grow since (the old block was freed), the graph
-    // is dropped and built again: one eager pass to size the scratch, then a new capture.
-    if (t->graph_exec && t->graph_scratch_gen != scratch_generation()) {
-        cudaGraphExecDestroy(t->graph_exec);
-        t->graph_exec = nullptr;
-        t->eager_passes = 0;
+    return BMB_OK;
+}
+int forward(bmb_trainer *t, bool with_loss = true) { return run_units(t, 0, t->c.n_layer + 2, with_loss); }
+int backward(bmb_trainer *t) { return run_units(t, t->c.n_layer + 2, num_units(t)); }
+
+void drop_graphs(bmb_trainer *t) {
+    for (auto &pc : t->pieces) {
+        if (pc.exec) cudaGraphExecDestroy(pc.exec);
+        pc.exec = nullptr;
+        pc.launches = 0;
     }
-    if (!t->graph_exec) {
-        if (t->eager_passes < 1) {
-            t->eager_passes++;
-            BMB_TRY(forward(t));
-            return backward(t);
-        }
+}
+
+// The chunks of the parameter space (see bmb_trainer) as range lists, and the pieces of a step.
+// Without the fused exchange the step is one piece.  With it:
+//   [embedding, layer 0] needs A | [layers 1 .. c2-1] needs B | [layers c2 .. L-1, head, head backward,
+//   backward of layers L-1 .. c2] needs C, finishes C | [backward of layers c2-1 .. 1] finishes B |
+//   [backward of layer 0, embedding backward] finishes A.
+// Every gradient of a layer is written during that layer's backward or the unit before it (the bias of its
+// second MLP projection comes out of the following layernorm's backward), so a chunk is final when the last of
+// its layers is done.
+struct StepPlan {
+    DpRangeList chunk[bmb_trainer::NCHUNK];
+    int split = 0;
+    int npieces = 0;
+    struct { int u0, u1, needs, reduces; } piece[5];
+};
+void make_plan(const bmb_train_config &c, bool chunks, StepPlan &pl) {
+    size_t psize[NPT], poff[NPT], total = 0;
+    param_sizes(psize, c);
+    for (int i = 0; i < NPT; ++i) { poff[i] = total; total += psize[i]; }
+    const int L = c.n_layer, U = 2 * L + 4;
+    for (int k = 0; k < bmb_trainer::NCHUNK; ++k) pl.chunk[k].n = 0;
+    pl.npieces = 0;
+    auto add = [&](int k, size_t off, size_t len) {
+        if (!len) return;
+        DpRangeList &rl = pl.chunk[k];
+        rl.off[rl.n] = off; rl.len[rl.n] = len; ++rl.n;
+    };
+    auto piece = [&](int u0, int u1, int needs, int reduces) {
+        if (u0 >= u1) return;
+        pl.piece[pl.npieces].u0 = u0; pl.piece[pl.npieces].u1 = u1;
+        pl.piece[pl.npieces].needs = needs; pl.piece[pl.npieces].reduces = reduces;
+        ++pl.npieces;
+    };
+    if (!chunks || L < 2) {               // (a single layer also applies the final layernorm: nothing to split)
+        add(0, 0, total);
+        piece(0, U, 0, 0);                 // (needs / reduces are read by the fused exchange only)
+        pl.split = L;
+        return;
+    }
+    const int c2 = 1 + (L - 1) / 2;
+    pl.split = c2;
+    add(0, poff[P_WTE], psize[P_WTE]);
+    add(0, poff[P_WPE], psize[P_WPE]);
+    for (int id = P_LN1W; id <= P_FPB; ++id) {                 // the twelve tensors stacked over the layers
+        const size_t per = psize[id] / L;
+        add(0, poff[id], per);
+        add(1, poff[id] + per, per * (size_t)(c2 - 1));
+        add(2, poff[id] + per * (size_t)c2, per * (size_t)(L - c2));
+    }
+    add(2, poff[P_LNFW], psize[P_LNFW]);
+    add(2, poff[P_LNFB], psize[P_LNFB]);
+    // forward units: 0 embedding, 1 + l layer l, L + 1 head; backward: L + 2 head, 2L + 2 - l layer l, 2L + 3 embedding
+    piece(0, 2, 0, -1);
+    piece(2, 1 + c2, 1, -1);
+    piece(1 + c2, 2 * L + 3 - c2, 2, 2);
+    piece(2 * L + 3 - c2, 2 * L + 2, -1, 1);
+    piece(2 * L + 2, U, -1, 0);
+}
+
+void plan_pieces(bmb_trainer *t) {
+    drop_graphs(t);
+    t->pieces.clear();
+    StepPlan pl;
+    make_plan(t->c, t->dp && t->overlap, pl);
+    for (int k = 0; k < bmb_trainer::NCHUNK; ++k) t->chunk[k] = pl.chunk[k];
+    t->chunk_split = pl.split;
+    for (int i = 0; i < pl.npieces; ++i) {
+        bmb_trainer::Piece pc;
+        pc.u0 = pl.piece[i].u0; pc.u1 = pl.piece[i].u1; pc.needs = pl.piece[i].needs; pc.reduces = pl.piece[i].reduces;
+        t->pieces.push_back(pc);
+    }
+}
+
+// One piece on t->st: replay of its captured graph, or eager launches (`eager`: first pass, GEMM event
+// profiling on, graphs switched off, or a capture failed).
+int run_piece(bmb_trainer *t, bmb_trainer::Piece &pc, bool eager) {
+    if (eager || t->graph_failed) return run_units(t, pc.u0, pc.u1);
+    if (!pc.exec) {
         const long long before = launches_total();
         const unsigned long long gen_before = scratch_generation();
         cudaGraph_t graph = nullptr;
         if (cudaStreamBeginCapture(t->st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
             cudaGetLastError();
             t->graph_failed = true;
-            BMB_TRY(forward(t));
-            return backward(t);
+            return run_units(t, pc.u0, pc.u1);
         }
-        int rc = forward(t);
-        if (rc == BMB_OK) rc = backward(t);
+        const int rc = run_units(t, pc.u0, pc.u1);
         const cudaError_t e = cudaStreamEndCapture(t->st, &graph);
         if (rc != BMB_OK || e != cudaSuccess || !graph || gen_before != scratch_generation() ||
-            cudaGraphInstantiate(&t->graph_exec, graph, 0) != cudaSuccess) {
-            // nothing ran during the capture: fall back to eager launches for good and run this pass now
+            cudaGraphInstantiate(&pc.exec, graph, 0) != cudaSuccess) {
+            // nothing ran during the capture: fall back to eager launches for good and run this piece now
             cudaGetLastError();
             if (graph) cudaGraphDestroy(graph);
-            t->graph_exec = nullptr;
+            pc.exec = nullptr;
             t->graph_failed = true;
-            BMB_TRY(forward(t));
-            return backward(t);
+            return run_units(t, pc.u0, pc.u1);
         }
         cudaGraphDestroy(graph);
         t->graph_scratch_gen = gen_before;
-        t->graph_launches = launches_total() - before;
-        count_launch((int)-t->graph_launches);        // counted again at every replay, this first one included
+        pc.launches = launches_total() - before;
+        count_launch((int)-pc.launches);        // counted again at every replay, this first one included
     }
-    BMB_CUDA(cudaGraphLaunch(t->graph_exec, t->st));
-    count_launch((int)t->graph_launches);
+    BMB_CUDA(cudaGraphLaunch(pc.exec, t->st));
+    count_launch((int)pc.launches);
     return BMB_OK;
+}
+
+// Whether this step's pieces run eagerly.  The captured launches carry the addresses of the library's
+// per-device scratch: if another caller on this device has made that scratch grow since (the old block was
+// freed), the graphs are dropped and built again -- one eager pass to size the scratch, then new captures.
+bool step_is_eager(bmb_trainer *t) {
+    if (!t->use_graph || t->graph_failed || t->prof) return true;
+    bool any = false;
+    for (auto &pc : t->pieces) any = any || pc.exec;
+    if (any && t->graph_scratch_gen != scratch_generation()) {
+        drop_graphs(t);
+        t->eager_passes = 0;
+        any = false;
+    }
+    if (!any && t->eager_passes < 1) {
+        t->eager_passes++;
+        return true;
+    }
+    return false;
 }
 
 // The tensor-core kernels report a bounded wait that ran out through a host-mapped word; the eager
@@ -423,6 +568,12 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     BMB_CUDA(cudaEventCreateWithFlags(&t->ev_fork, cudaEventDisableTiming));
     BMB_CUDA(cudaEventCreateWithFlags(&t->ev_join, cudaEventDisableTiming));
     if (const char *e = getenv("BMB_TRAINER_SIDE_BY_SIDE")) t->side_by_side = atoi(e) != 0;
+    if (const char *e = getenv("BMB_TRAINER_OVERLAP")) t->overlap = atoi(e) != 0;
+    BMB_CUDA(cudaStreamCreateWithFlags(&t->st_x, cudaStreamNonBlocking));
+    for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {
+        BMB_CUDA(cudaEventCreateWithFlags(&t->ev_seg[c], cudaEventDisableTiming));
+        BMB_CUDA(cudaEventCreateWithFlags(&t->ev_upd[c], cudaEventDisableTiming));
+    }
     param_sizes(t->psize, c);
     t->num_params = 0;
     for (int i = 0; i < NPT; ++i) { t->poff[i] = t->num_params; t->num_params += t->psize[i]; }
@@ -523,8 +674,14 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     if (!t) return BMB_OK;
     cudaSetDevice(t->dev);
     if (t->st) cudaStreamSynchronize(t->st);
+    if (t->st_x) cudaStreamSynchronize(t->st_x);
     for (cudaEvent_t e : t->ev) cudaEventDestroy(e);
-    if (t->graph_exec) cudaGraphExecDestroy(t->graph_exec);
+    drop_graphs(t);
+    for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {
+        if (t->ev_seg[c]) cudaEventDestroy(t->ev_seg[c]);
+        if (t->ev_upd[c]) cudaEventDestroy(t->ev_upd[c]);
+    }
+    if (t->st_x) cudaStreamDestroy(t->st_x);
     cudaFree(t->params); cudaFree(t->grads); cudaFree(t->m); cudaFree(t->v);
     if (t->shadow) cudaFree(t->shadow);
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
@@ -554,19 +711,38 @@ int bmb_trainer_ipc_export(bmb_trainer *t, void *record192) {
 
 int bmb_trainer_attach_peers(bmb_trainer *t, int rank, int nranks, const void *records) {
     if (!t) return fail(BMB_E_ARG, "trainer_attach_peers: null handle");
-    if (!records) {                       // detach: back to the communicator's all-reduce
-        Scope sc(t);
-        BMB_CUDA(cudaStreamSynchronize(t->st));
-        dp_fused_destroy(t->dp);
-        t->dp = nullptr;
-        return BMB_OK;
-    }
-    if (!t->comm || t->nranks != nranks) return fail(BMB_E_ARG, "trainer_attach_peers: attach the communicator of %d ranks first", nranks);
+    if (records && (!t->comm || t->nranks != nranks))
+        return fail(BMB_E_ARG, "trainer_attach_peers: attach the communicator of %d ranks first", nranks);
     Scope sc(t);
     BMB_CUDA(cudaStreamSynchronize(t->st));
+    BMB_CUDA(cudaStreamSynchronize(t->st_x));
     dp_fused_destroy(t->dp);
     t->dp = nullptr;
-    return dp_fused_create(&t->dp, rank, nranks, t->num_params, t->grads, t->params, t->shadow, records);
+    int rc = BMB_OK;
+    if (records)                          // (null: detach, back to the communicator's all-reduce)
+        rc = dp_fused_create(&t->dp, rank, nranks, t->num_params, t->grads, t->params, t->shadow, records);
+    plan_pieces(t);                       // the step's pieces follow the exchange
+    return rc;
+}
+
+int bmb_trainer_step_plan(const bmb_train_config *cfg, int overlapped, unsigned long long *ranges, int *nranges, int *pieces,
+                          int *npieces) {
+    if (!cfg || !ranges || !nranges || !pieces || !npieces || cfg->n_layer < 1) return fail(BMB_E_ARG, "trainer_step_plan: bad argument");
+    StepPlan pl;
+    make_plan(*cfg, overlapped != 0, pl);
+    for (int k = 0; k < bmb_trainer::NCHUNK; ++k) {
+        nranges[k] = pl.chunk[k].n;
+        for (int q = 0; q < DP_MAX_RANGES; ++q) {
+            ranges[(k * DP_MAX_RANGES + q) * 2 + 0] = q < pl.chunk[k].n ? pl.chunk[k].off[q] : 0;
+            ranges[(k * DP_MAX_RANGES + q) * 2 + 1] = q < pl.chunk[k].n ? pl.chunk[k].len[q] : 0;
+        }
+    }
+    *npieces = pl.npieces;
+    for (int i = 0; i < pl.npieces; ++i) {
+        pieces[4 * i + 0] = pl.piece[i].u0; pieces[4 * i + 1] = pl.piece[i].u1;
+        pieces[4 * i + 2] = pl.piece[i].needs; pieces[4 * i + 3] = pl.piece[i].reduces;
+    }
+    return BMB_OK;
 }
 
 size_t bmb_trainer_num_params(const bmb_trainer *t) { return t ? t->num_params : 0; }
@@ -597,7 +773,7 @@ int bmb_trainer_get_grads(bmb_trainer *t, float *host_out) {
 
 int bmb_trainer_upload(bmb_trainer *t, const int *host_tokens, const int *host_targets) {
     if (!t || !host_tokens || !host_targets) return fail(BMB_E_ARG, "trainer_upload: null argument");
-    Scope sc(t);
+    Scope sc(t, /*join=*/false);          // token buffers only: nothing the exchange stream touches
     const size_t n = (size_t)t->c.B * t->c.T * sizeof(int);
     // cudaMemcpyDefault: the source may also be a batch already staged in device memory
     BMB_CUDA(cudaMemcpyAsync(t->d_tokens, host_tokens, n, cudaMemcpyDefault, t->st));
@@ -608,45 +784,64 @@ int bmb_trainer_upload(bmb_trainer *t, const int *host_tokens, const int *host_t
 int bmb_trainer_forward_backward(bmb_trainer *t) {
     if (!t) return fail(BMB_E_ARG, "trainer: null handle");
     Scope sc(t);
-    BMB_TRY(forward(t));
-    BMB_TRY(backward(t));
-    return BMB_OK;
+    return run_units(t, 0, num_units(t));
 }
 
 int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
     if (!t || step < 1) return fail(BMB_E_ARG, "trainer_step: bad argument");
-    Scope sc(t);
-    BMB_TRY(forward_backward_step(t));
-    if (t->dp) {
-        // Collectives on this stream order the phases across ranks: no rank's reduce starts before
-        // every rank's backward is done, no update before every slice is summed, and the next
-        // forward not before every rank has received every slice of the new parameters.
-        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st));
-        BMB_TRY(dp_fused_reduce(t->dp, t->num_params, t->grads, t->d_sumsq, t->st));
-        BMB_TRY(bmb_comm_allreduce_f64(t->comm, t->d_sumsq, 1, t->st));
-        BMB_TRY(dp_fused_update(t->dp, t->num_params, t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
-                                t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, t->st));
-        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st));
-        return refresh_shadow(t);         // every slice of the new parameters has arrived
+    Scope sc(t, /*join=*/false);
+    if (t->pieces.empty()) plan_pieces(t);
+    const bool eager = step_is_eager(t);
+    if (!t->dp) {
+        for (auto &pc : t->pieces) BMB_TRY(run_piece(t, pc, eager));
+        if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
+        BMB_TRY(bmb_grad_sumsq_device(t->grads, t->num_params, t->d_sumsq));
+        BMB_TRY(bmb_adamw_update_clipped(t->params, t->grads, t->m, t->v, t->num_params, lr, t->c.beta1, t->c.beta2,
+                                         t->c.eps, t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip,
+                                         (float)t->nranks, t->shadow));
+        return BMB_OK;
     }
-    if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
-    BMB_TRY(bmb_grad_sumsq_device(t->grads, t->num_params, t->d_sumsq));
-    BMB_TRY(bmb_adamw_update_clipped(t->params, t->grads, t->m, t->v, t->num_params, lr, t->c.beta1, t->c.beta2,
-                                     t->c.eps, t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip,
-                                     (float)t->nranks, t->shadow));
+    // Fused exchange.  Everything that crosses GPUs runs on the exchange stream, ordered across ranks by small
+    // collectives on that stream: no rank reads a chunk's gradients before every rank has finished them, none
+    // updates before every piece of the gradient is summed (the norm), and none reads a chunk's new parameters
+    // before every rank has stored its pieces of them.  The main stream only waits where it needs a result.
+    for (auto &pc : t->pieces) {
+        if (pc.needs >= 0 && t->upd_pending[pc.needs]) {
+            BMB_CUDA(cudaStreamWaitEvent(t->st, t->ev_upd[pc.needs], 0));
+            t->upd_pending[pc.needs] = false;
+        }
+        BMB_TRY(run_piece(t, pc, eager));
+        const int c = pc.reduces;
+        if (c < 0 || t->chunk[c].n == 0) continue;
+        BMB_CUDA(cudaEventRecord(t->ev_seg[c], t->st));
+        BMB_CUDA(cudaStreamWaitEvent(t->st_x, t->ev_seg[c], 0));
+        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st_x));
+        BMB_TRY(dp_fused_reduce_ranges(t->dp, t->chunk[c], t->grads, c, t->st_x));
+    }
+    BMB_TRY(dp_fused_sumsq(t->dp, t->d_sumsq, t->st_x));
+    BMB_TRY(bmb_comm_allreduce_f64(t->comm, t->d_sumsq, 1, t->st_x));
+    for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {           // in the order the next forward needs them
+        if (t->chunk[c].n == 0) continue;
+        BMB_TRY(dp_fused_update_ranges(t->dp, t->chunk[c], t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
+                                       t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, t->st_x));
+        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st_x));
+        if (t->shadow) BMB_TRY(dp_round_ranges(t->chunk[c], t->shadow, t->params, t->st_x));
+        BMB_CUDA(cudaEventRecord(t->ev_upd[c], t->st_x));
+        t->upd_pending[c] = true;
+    }
     return BMB_OK;
 }
 
 int bmb_trainer_loss_async(bmb_trainer *t, float *pinned_host_loss) {
     if (!t || !pinned_host_loss) return fail(BMB_E_ARG, "trainer_loss_async: null argument");
-    Scope sc(t);
+    Scope sc(t, /*join=*/false);
     BMB_CUDA(cudaMemcpyAsync(pinned_host_loss, t->d_loss, sizeof(float), cudaMemcpyDeviceToHost, t->st));
     return BMB_OK;
 }
 
 int bmb_trainer_loss(bmb_trainer *t, float *host_loss) {
     if (!t || !host_loss) return fail(BMB_E_ARG, "trainer_loss: null argument");
-    Scope sc(t);
+    Scope sc(t, /*join=*/false);
     BMB_CUDA(cudaMemcpyAsync(host_loss, t->d_loss, sizeof(float), cudaMemcpyDeviceToHost, t->st));
     BMB_CUDA(cudaStreamSynchronize(t->st));
     return check_kernel_status();

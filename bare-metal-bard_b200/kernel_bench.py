@@ -4,6 +4,7 @@
     python bare-metal-bard_b200/kernel_bench.py one:tf32:nt:8192x3072x768:rounded      (a single GEMM case)
     python bare-metal-bard_b200/kernel_bench.py registry --csv runs/a.csv [-s 1024,2048]   (the registry sweep as CSV)
     python bare-metal-bard_b200/kernel_bench.py timeline:tf32:nt:8192x3072x768:rounded     (per-CTA timeline, timer build)
+    python bare-metal-bard_b200/kernel_bench.py flash_timeline                             (attention forward: work-item stamps and knock-out timings, timer build)
 
 `registry --csv` appends one row per (registry entry, size) in the columns the reference harness writes
 (src/bench.cu:238-245, 293-299): kernel_id,kernel,size,gflops_best,gflops_median,cublas_gflops_best,
@@ -270,6 +271,65 @@ def bench_one(bmb, spec):
          tflops_back_to_back=round(2.0 * M * N * K / b2b / 1e9, 2))
 
 
+def bench_flash_timeline(bmb, small):
+    """flash_timeline -- where the tensor-core attention forward spends its time (B = 8 or, with --small, 2; 12 heads,
+    T = 1024, head size 64, operands pre-rounded).  Needs a library built with the developer timers
+    (`BMB_NVCC_FLAGS=-DBMB_FLASH_TRACE python bare-metal-bard_b200/build.py -f`).  Printed: per CTA (a sample) the
+    nanosecond stamps of its work items (first scores ready, last block folded, output stored) after the first
+    CTA's entry; then the back-to-back cost of a launch with parts of the kernel switched off (the results are
+    then wrong, only the time means something): 1 no exponentials, 2 no P V load / fold, 4 no maximum, 8 no store
+    of P, 16 no score products, 32 no P V products."""
+    import ctypes as C
+    import numpy as np
+    try:
+        dbg = C.CDLL(bmb.LIB_PATH)
+        dbg.bmb_dbg_flash_trace.argtypes = [C.c_void_p]
+        dbg.bmb_dbg_flash_ko.argtypes = [C.c_int]
+    except AttributeError:
+        raise SystemExit("this libbmb.so has no timers: rebuild with BMB_NVCC_FLAGS=-DBMB_FLASH_TRACE")
+    B, NH, T, hs = (2 if small else 8), 12, 1024, 64
+    Cd = NH * hs
+    qkv = torch.randn(B * T * 3 * Cd, device="cuda")
+    out = torch.empty(B * T * Cd, device="cuda")
+    lse = torch.empty(B * NH * T, device="cuda")
+    bmb.call("bmb_round_tf32", qkv, qkv, qkv.numel(), None)
+    run = lambda: bmb.call("bmb_flash_attention_forward_ex", 2, bmb.FLASH_OPERANDS_ROUNDED, out, lse, qkv, B, T, Cd, NH)
+    for _ in range(5):
+        run()
+    torch.cuda.synchronize()
+    dbg.bmb_dbg_flash_trace_clear()
+    run()
+    torch.cuda.synchronize()
+    buf = np.zeros((160, 24), dtype=np.uint64)
+    dbg.bmb_dbg_flash_trace(buf.ctypes.data)
+    t = buf[:148].astype(np.int64)
+    t = t[t[:, 0] > 0]
+    t0 = t[:, 0].min()
+    us = lambda a: round(float(a - t0) / 1000.0, 1)
+    rows = []
+    for c in sorted(set([0, 8, len(t) // 2, len(t) - 1])):
+        items = [[us(t[c][2 + 4 * r]), us(t[c][3 + 4 * r]), us(t[c][4 + 4 * r])] for r in range(5) if t[c][2 + 4 * r]]
+        rows.append({"cta": int(c), "items_first_scores_last_fold_stored_us": items, "exit_us": us(t[c][1]),
+                     "wait_scores_cycles": int(t[c][22]), "wait_pv_cycles": int(t[c][23])})
+    emit(kernel="flash_fwd_timeline", B=B, ctas=int(len(t)), last_exit_us=us(t[:, 1].max()), median_exit_us=us(np.median(t[:, 1])), sample=rows)
+    for ko in (0, 1, 2, 15, 16, 32, 48, 63, 0):
+        dbg.bmb_dbg_flash_ko(ko)
+        for _ in range(5):
+            run()
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / 20 * 1000)
+        emit(kernel="flash_fwd_knockout", B=B, switched_off=ko, back_to_back_us=round(best, 1))
+    dbg.bmb_dbg_flash_ko(0)
+
+
 def bench_timeline(bmb, spec):
     """timeline:<math>:<ta><tb>:<M>x<N>x<K>[:rounded][...]  -- where one tensor-core GEMM launch spends its time.
     Needs a library built with the developer timers (`BMB_NVCC_FLAGS=-DBMB_GEMM_TRACE python
@@ -357,7 +417,9 @@ def main():
         bench_one(bmb, w)
     for w in [x for x in which if x.startswith("timeline:")]:
         bench_timeline(bmb, w)
-    which = [x for x in which if not x.startswith(("one:", "timeline:"))]
+    if "flash_timeline" in which:
+        bench_flash_timeline(bmb, small)
+    which = [x for x in which if not x.startswith(("one:", "timeline:")) and x != "flash_timeline"]
     for w in which:
         {"gemm": bench_gemm, "bgemm": bench_bgemm, "flash": bench_flash, "nn": bench_nn}[w](bmb, small)
 

@@ -309,16 +309,30 @@ int bmb_trainer_destroy(bmb_trainer *t);
 int bmb_trainer_attach_comm(bmb_trainer *t, bmb_comm *c, int nranks);
 /* Fused gradient exchange + optimiser over peer memory (one process per GPU, 2..8 ranks; replaces
  * ddp_allreduce + grad norm + adamw_update of src/train_gpt.cu:431-451 inside bmb_trainer_step):
- * every rank sums its slice of all ranks' gradients by reading the peers' buffers, the ranks add
- * their squared norms, every rank updates its slice and stores the new parameters into all
- * ranks' buffers.  bmb_trainer_ipc_export writes this rank's 192-byte handle record; the launcher
+ * rank r owns the r-th of n equal pieces of every tensor (of every layer group of a stacked tensor); it
+ * sums its pieces of all ranks' gradients by reading the peers' buffers, the ranks add their squared
+ * norms, every rank updates its pieces and stores the new parameters into all ranks' buffers.  The
+ * parameter space is exchanged in three chunks (embeddings + layer 0 | the first half of the other
+ * layers | the second half + final layernorm): a chunk's gradients are summed on a second stream as soon
+ * as backward has finished them, and the next step's forward waits only for the chunk it is about to
+ * read, so bmb_trainer_step returns with the tail of the exchange still running; every other entry point
+ * waits for it first.  BMB_TRAINER_OVERLAP=0: one chunk, exchanged after backward.
+ * bmb_trainer_ipc_export writes this rank's 192-byte handle record; the launcher
  * gathers the records of all ranks in rank order and hands them to bmb_trainer_attach_peers
  * (after bmb_trainer_attach_comm, whose communicator carries the small collectives that order
  * the phases).  records = NULL detaches (back to the communicator's all-reduce); all ranks must
  * attach or none.  After a fused step bmb_trainer_get_grads returns summed values only inside
- * this rank's slice. */
+ * this rank's pieces. */
 int bmb_trainer_ipc_export(bmb_trainer *t, void *record192);
 int bmb_trainer_attach_peers(bmb_trainer *t, int rank, int nranks, const void *records);
+/* The step's plan for a configuration (host only, no GPU needed; no counterpart in the reference): the chunks
+ * as ranges of the flat parameter space -- ranges[(chunk * 16 + i) * 2 + {0, 1}] = offset, length in floats,
+ * nranges[chunk] of them, 3 chunks -- and the pieces the step is captured in: pieces[4 * i + {0..3}] = first
+ * unit, end unit, chunk whose update the piece waits for (-1: none), chunk whose gradients are final when it ends
+ * (-1: none); units are 0 embedding, 1 + l layer l, L + 1 head and loss, L + 2 head backward, 2L + 2 - l layer
+ * l backward, 2L + 3 embedding backward.  overlapped = 0 gives the single-chunk, single-piece plan. */
+int bmb_trainer_step_plan(const bmb_train_config *cfg, int overlapped, unsigned long long *ranges /* [3][16][2] */,
+                          int *nranges /* [3] */, int *pieces /* [5][4] */, int *npieces);
 size_t bmb_trainer_num_params(const bmb_trainer *t);
 int bmb_trainer_get_params(bmb_trainer *t, float *host_out);
 int bmb_trainer_set_params(bmb_trainer *t, const float *host_in);

@@ -1,7 +1,8 @@
 """Run under torchrun with 2..8 ranks (one per GPU): trains a small model for a few steps twice --
 gradients summed by NCCL and every rank running the whole optimiser, then the fused exchange over
-peer memory -- from the same seed on the same batches, and checks that the losses agree, that
-every rank ends with the same parameters, and that the two ways end with the same parameters up
+peer memory, once in one chunk after backward and once in three chunks overlapped with backward and
+the next forward -- from the same seed on the same batches, and checks that the losses agree, that
+every rank ends with the same parameters, and that the ways end with the same parameters up
 to the reassociation of the gradient sum.  Exit status 0 = ok.  Used by test_gpu_parity.py."""
 import ctypes as C
 import os
@@ -23,13 +24,14 @@ def main():
     torch.cuda.set_device(local)
     dist_mod.init_process_group("gloo")
     lib = bmb.lib()
-    cfg = dict(max_seq_len=128, vocab_size=512, padded_vocab=512, n_layer=2, n_head=2, n_embd=128, B=4, T=128)
-    steps = 5
+    cfg = dict(max_seq_len=128, vocab_size=512, padded_vocab=512, n_layer=4, n_head=2, n_embd=128, B=4, T=128)   # four layers: all three chunks of the overlapped exchange hold something
+    steps = 6
     rng = np.random.default_rng(99)
     toks = rng.integers(0, 512, (steps, 4 * world, 128), dtype=np.int32)
     tgts = rng.integers(0, 512, (steps, 4 * world, 128), dtype=np.int32)
 
-    def run(fused):
+    def run(fused, overlap=True):
+        os.environ["BMB_TRAINER_OVERLAP"] = "1" if overlap else "0"       # read when the trainer is created
         tr = bmb.Trainer(seed=1337, use_flash=1, math=bmb.MATH_TF32, fused=1, **cfg)
         ident = (C.c_ubyte * 128)()
         if rank == 0:
@@ -56,24 +58,26 @@ def main():
     l0, p0 = run(False)
     l0b, p0b = run(False)
     l1, p1 = run(True)
+    l2, p2 = run(True, overlap=False)
     ok = True
-    if np.abs(l0 - l1).max() > 1e-4:
-        print("rank %d: losses differ %s %s" % (rank, l0, l1)); ok = False
+    if np.abs(l0 - l1).max() > 1e-4 or np.abs(l0 - l2).max() > 1e-4:
+        print("rank %d: losses differ %s %s %s" % (rank, l0, l1, l2)); ok = False
     # Sums that use atomics (token-embedding gradient, GEMM tiles shared between CTAs) wobble from run to
     # run, and AdamW's g / sqrt(v) magnifies that where v is tiny: the bar is the gap between two runs
     # of the SAME way.
     norm = np.linalg.norm(p0.astype(np.float64))
     wobble = np.linalg.norm(p0.astype(np.float64) - p0b) / norm
-    rel = np.linalg.norm(p0.astype(np.float64) - p1) / norm
+    rel = max(np.linalg.norm(p0.astype(np.float64) - p1) / norm, np.linalg.norm(p0.astype(np.float64) - p2) / norm)
     if rel > 5 * wobble + 1e-6:
         print("rank %d: parameters differ between the two ways: %.3e (run-to-run wobble %.3e)" % (rank, rel, wobble)); ok = False
     # every rank must hold the same parameters after the fused steps
     import torch.distributed as dist
-    t = torch.from_numpy(p1.copy())
-    ref = t.clone()
-    dist.broadcast(ref, src=0)
-    if not torch.equal(t, ref):
-        print("rank %d: parameters differ from rank 0 after the fused steps" % rank); ok = False
+    for name, p in (("overlapped", p1), ("one chunk", p2)):
+        t = torch.from_numpy(p.copy())
+        ref = t.clone()
+        dist.broadcast(ref, src=0)
+        if not torch.equal(t, ref):
+            print("rank %d: parameters differ from rank 0 after the fused steps (%s)" % (rank, name)); ok = False
     flag = torch.tensor([0 if ok else 1])
     dist.all_reduce(flag)
     if rank == 0:

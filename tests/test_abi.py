@@ -2,6 +2,7 @@
 function include/bmb.h declares (and the reference's C++ names), and the
 host-only entry points behave."""
 import ctypes as C
+C_ull = C.c_ulonglong
 import os
 import re
 import subprocess
@@ -196,3 +197,59 @@ def test_registry_csv_feeds_the_reference_merge_tool(tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     merged = out.read_text().splitlines()
     assert merged[0] == text[0] and len(merged) == 5 and merged[1].startswith("1,simt_fp32,1024,2025.00")
+
+
+@pytest.mark.parametrize("L,E,V,maxT", [(12, 768, 50304, 1024), (1, 32, 96, 16), (2, 64, 128, 32), (3, 32, 96, 16), (5, 64, 256, 64)])
+def test_step_plan_chunks_partition_the_parameters_and_pieces_cover_the_step(bmb, L, E, V, maxT):
+    """The overlapped exchange's plan (host logic, no GPU): the three chunks are disjoint ranges that
+    together cover every parameter exactly once and hold the layers they are named for; the pieces run
+    every unit once, in order; a chunk's update is awaited by the first piece that reads its layers and
+    its reduce follows the piece that writes the last of its gradients."""
+    import numpy as np
+    cfg = bmb.TrainConfig(maxT, V, V, L, 2, E, 2, maxT, 1, 1, 1, 0.9, 0.95, 1e-8, 0.0, 1.0)
+    ranges = (C_ull * (3 * 16 * 2))()
+    nranges, pieces, npieces = (C.c_int * 3)(), (C.c_int * 20)(), C.c_int(0)
+    lib = bmb.lib()
+    total = V * E + maxT * E + L * (2 * E + 3 * E * E + 3 * E + E * E + E + 2 * E + 4 * E * E + 4 * E + 4 * E * E + E) + 2 * E
+    for overlapped in (0, 1):
+        assert lib.bmb_trainer_step_plan(C.byref(cfg), overlapped, ranges, nranges, pieces, C.byref(npieces)) == 0
+        cover = np.zeros(total, dtype=np.int8)
+        owner = np.full(total, -1, dtype=np.int8)
+        for k in range(3):
+            for q in range(nranges[k]):
+                off, ln = ranges[(k * 16 + q) * 2], ranges[(k * 16 + q) * 2 + 1]
+                assert off % 4 == 0 and ln % 4 == 0 and ln > 0 and off + ln <= total
+                cover[off:off + ln] += 1
+                owner[off:off + ln] = k
+        assert cover.min() == 1 and cover.max() == 1
+        ps = [tuple(pieces[4 * i:4 * i + 4]) for i in range(npieces.value)]
+        U = 2 * L + 4
+        assert ps[0][0] == 0 and ps[-1][1] == U and all(a[1] == b[0] for a, b in zip(ps, ps[1:]))
+        if not overlapped or L < 2:
+            assert len(ps) == 1 and nranges[0] == 1 and ranges[0] == 0 and ranges[1] == total
+            continue
+        # the chunk every layer's first tensor (ln1w, right after wte and wpe) lives in
+        ln1w = V * E + maxT * E
+        layer_chunk = [int(owner[ln1w + l * E]) for l in range(L)]
+        assert layer_chunk[0] == 0 and layer_chunk == sorted(layer_chunk)
+        assert owner[0] == 0 and owner[V * E] == 0 and owner[total - 1] == 2          # embeddings in A, final layernorm in C
+        first_use, last_write = {}, {}
+        for i, (u0, u1, needs, reduces) in enumerate(ps):
+            for u in range(u0, u1):
+                if u == 0 or u == L + 1: ks = [0]                       # embedding; head (tied weights)
+                elif 1 <= u <= L: ks = [layer_chunk[u - 1]] + ([2] if u == L else [])   # the last layer also applies the final layernorm
+                elif u == L + 2: ks = [0, 2, layer_chunk[L - 1]]      # head backward: dwte, final layernorm, last layer's second bias
+                elif u <= 2 * L + 2:
+                    l = 2 * L + 2 - u
+                    ks = [layer_chunk[l]] + ([layer_chunk[l - 1]] if l > 0 else [])
+                else: ks = [0]
+                for k in ks:
+                    first_use.setdefault(k, i)
+                    if u >= L + 2: last_write[k] = i
+        for k in (0, 1, 2):
+            if nranges[k] == 0:
+                continue
+            waits = [i for i, pc in enumerate(ps) if pc[2] == k]
+            reds = [i for i, pc in enumerate(ps) if pc[3] == k]
+            assert waits and waits[0] <= first_use[k], (k, ps)
+            assert len(reds) == 1 and reds[0] >= last_write[k], (k, ps)
