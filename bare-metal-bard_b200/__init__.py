@@ -21,6 +21,7 @@ GEMM_A_ROUNDED, GEMM_B_ROUNDED, GEMM_C_ROUNDED, GEMM_NO_SPLIT = 1, 2, 4, 8
 GEMM_TILE_M128, GEMM_TILE_M256 = 16, 32
 GEMM_PAIR, GEMM_NO_PAIR = 64, 128
 GEMM_HALF_SMS = 256
+GEMM_AUX_ROUNDED = 512
 FLASH_OPERANDS_ROUNDED = 1
 E_UNSUPPORTED = 3
 E_TIMEOUT = 4
@@ -64,6 +65,7 @@ SIGNATURES = {
     "bmb_sgemm_bf16": (_i, [_i, _i, _i, _f, _p, _p, _f, _p]),
     "bmb_gemm": (_i, [_i, _i, _i, _i, _i, _f, _p, _p, _f, _p, _p]),
     "bmb_gemm_ex": (_i, [_i, _i, _i, _i, _i, _i, _i, _f, _p, _p, _f, _p, _p]),
+    "bmb_gemm_bias_gelu": (_i, [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "bmb_batched_gemm": (_i, [_i, _i, _i, _i, _i, _i, _f, _p, _ll, _p, _ll, _f, _p, _ll, _p]),
     "bmb_round_tf32": (_i, [_p, _p, _z, _p]),
     "bmb_flash_attention_forward": (_i, [_p, _p, _p, _i, _i, _i, _i]),

@@ -80,7 +80,9 @@ int gemm_any(int math, int flags, int ta, int tb, int batch, int M, int N, int K
 // Same with a bias row added to every output row (null = none).
 int gemm_any_bias(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
                   const float *A, long long sA, const float *B, long long sB, float beta, float *C,
-                  long long sC, const float *bias, cudaStream_t st);
+                  long long sC, const float *bias, cudaStream_t st, float *aux_gelu = nullptr);
+// (aux_gelu: a second output of the same shape, GELU of the result -- in the product's epilogue where the
+//  tensor-core kernel can, by a pass of its own otherwise)
 
 }  // namespace bmb
 
@@ -116,6 +118,11 @@ __device__ __forceinline__ float block_reduce(float v, float *red) {
     v = (lane < nw) ? red[lane] : (IS_MAX ? -3.402823466e38f : 0.0f);
     v = IS_MAX ? warp_max(v) : warp_sum(v);
     return v;
+}
+// tanh-approximation GELU with the accurate tanhf (src/nn.cu:118-127).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float s = 0.7978845608028654f;
+    return 0.5f * x * (1.0f + tanhf(s * (x + 0.044715f * x * x * x)));
 }
 // Round to nearest TF32 (ties away), result as an fp32 bit pattern whose low
 // 13 mantissa bits are zero.

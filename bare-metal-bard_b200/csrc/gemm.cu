@@ -11,7 +11,7 @@ int gemm_simt(int transA, int transB, int batch, int M, int N, int K, float alph
 // not take; the caller then falls back to the SIMT kernel (still on the GPU).
 int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N, int K,
             float alpha, const float *A, long long sA, const float *B, long long sB, float beta,
-            float *C, long long sC, const float *bias, cudaStream_t st);
+            float *C, long long sC, const float *bias, cudaStream_t st, float *aux_gelu = nullptr);
 bool gemm_tc_accepts(int math, int transA, int transB, int batch, int M, int N, int K,
                      const float *A, long long sA, const float *B, long long sB, const float *C,
                      long long sC);
@@ -19,19 +19,36 @@ bool gemm_tc_accepts(int math, int transA, int transB, int batch, int M, int N, 
 // C = alpha*op(A)op(B) + bias (broadcast over rows, may be null) + beta*C.
 int gemm_any_bias(int math, int flags, int ta, int tb, int batch, int M, int N, int K, float alpha,
                   const float *A, long long sA, const float *B, long long sB, float beta, float *C,
-                  long long sC, const float *bias, cudaStream_t st) {
-    if (math != BMB_MATH_FP32 && M > 0 && N > 0 && K > 0 && batch > 0 &&
-        gemm_tc_accepts(math, ta, tb, batch, M, N, K, A, sA, B, sB, C, sC))
-        return gemm_tc(math, flags, ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, bias, st);
-    BMB_TRY(gemm_simt(ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st));
-    // SIMT route: the bias and the optional rounding are separate passes on the same stream.
-    void *prev = bmb_get_stream();
-    bmb_set_stream((void *)st);
+                  long long sC, const float *bias, cudaStream_t st, float *aux_gelu) {
     int rc = BMB_OK;
-    if (bias && batch == 1) rc = bmb_bias_forward(C, bias, M, N);
-    if (rc == BMB_OK && (flags & BMB_GEMM_C_ROUNDED) && batch == 1)
-        rc = bmb_round_tf32(C, C, (size_t)M * N, (void *)st);
-    bmb_set_stream(prev);
+    bool aux_done = false;
+    if (math != BMB_MATH_FP32 && M > 0 && N > 0 && K > 0 && batch > 0 &&
+        gemm_tc_accepts(math, ta, tb, batch, M, N, K, A, sA, B, sB, C, sC)) {
+        rc = BMB_E_UNSUPPORTED;
+        if (aux_gelu) {
+            rc = gemm_tc(math, flags, ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, bias, st, aux_gelu);
+            aux_done = (rc == BMB_OK);
+        }
+        if (rc == BMB_E_UNSUPPORTED) rc = gemm_tc(math, flags, ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, bias, st);
+        if (rc != BMB_OK) return rc;
+    } else {
+        BMB_TRY(gemm_simt(ta, tb, batch, M, N, K, alpha, A, sA, B, sB, beta, C, sC, st));
+        // SIMT route: the bias and the optional rounding are separate passes on the same stream.
+        void *prev = bmb_get_stream();
+        bmb_set_stream((void *)st);
+        if (bias && batch == 1) rc = bmb_bias_forward(C, bias, M, N);
+        if (rc == BMB_OK && (flags & BMB_GEMM_C_ROUNDED) && batch == 1)
+            rc = bmb_round_tf32(C, C, (size_t)M * N, (void *)st);
+        bmb_set_stream(prev);
+        if (rc != BMB_OK) return rc;
+    }
+    if (aux_gelu && !aux_done) {
+        if (batch != 1) return fail(BMB_E_ARG, "gemm: the activation output serves single products only");
+        void *prev = bmb_get_stream();
+        bmb_set_stream((void *)st);
+        rc = bmb_gelu_forward(aux_gelu, C, M * N);
+        bmb_set_stream(prev);
+    }
     return rc;
 }
 
@@ -57,6 +74,18 @@ int bmb_gemm_ex(int math, int flags, int transA, int transB, int M, int N, int K
     if (math < BMB_MATH_FP32 || math > BMB_MATH_BF16) return fail(BMB_E_ARG, "gemm_ex: math %d", math);
     return gemm_any(math, flags, transA, transB, 1, M, N, K, alpha, A, 0, B, 0, beta, C, 0,
                     (cudaStream_t)stream);
+}
+
+int bmb_gemm_bias_gelu(int math, int flags, int M, int N, int K, const float *A, const float *W, const float *bias,
+                       float *C, float *C_gelu, void *stream) {
+    if (math < BMB_MATH_FP32 || math > BMB_MATH_BF16) return fail(BMB_E_ARG, "gemm_bias_gelu: math %d", math);
+    if (!A || !W || !C || !C_gelu || M < 1 || N < 1 || K < 1) return fail(BMB_E_ARG, "gemm_bias_gelu: bad argument");
+    const bool was = emit_rounded();
+    set_emit_rounded((flags & BMB_GEMM_AUX_ROUNDED) != 0);
+    const int rc = gemm_any_bias(math, flags & ~BMB_GEMM_AUX_ROUNDED, 0, 1, 1, M, N, K, 1.0f, A, 0, W, 0, 0.0f, C, 0, bias,
+                                 (cudaStream_t)stream, C_gelu);
+    set_emit_rounded(was);
+    return rc;
 }
 
 int bmb_batched_gemm(int transA, int transB, int batch, int M, int N, int K, float alpha,

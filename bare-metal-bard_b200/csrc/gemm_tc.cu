@@ -204,12 +204,13 @@ __device__ __forceinline__ void add_result(float4 o, float *__restrict__ C, int 
 // KIND 0 = tf32 (fp32 operands), 1 = f16 (bf16 operands, always K-major).
 // a_mn / b_mn: the operand's tile is MN-major (TF32 only); 2 = its tensor map is the 3-d one that
 // brings all chunks of a slice in one copy.
-template <int KIND, int BN, int MH>
+template <int KIND, int BN, int MH, int AUX>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
           const __grid_constant__ CUtensorMap mapC, int c_mode, int batch, int M, int N,
           int kblocks, int kelems_per_block, int a_mn, int b_mn, float alpha, float beta, float *__restrict__ C,
-          int vec_ok, int dp_tiles, int g_sk, const float *__restrict__ bias, int round_c, int *__restrict__ status) {
+          int vec_ok, int dp_tiles, int g_sk, const float *__restrict__ bias, int round_c, int *__restrict__ status,
+          float *__restrict__ aux, int round_aux) {
     static_assert(MH == 1 || (MH == 2 && BN == 256), "two-block tiles are 256 columns wide");
     constexpr int STAGES = stages_for(MH), BMT = BM * MH;
     constexpr int B_BYTES = BN * KBYTES, STAGE_BYTES = MH * A_BYTES + B_BYTES;
@@ -411,6 +412,11 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                             float2 x = make_float2(fmaf(alpha, o[k].x, bb.x), fmaf(alpha, o[k].y, bb.y));
                             if (round_c) x = make_float2(round_tf32(x.x), round_tf32(x.y));
                             if (m < M) *reinterpret_cast<float2 *>(C + (size_t)m * N + n) = x;
+                            if (AUX && m < M) {                      // second output: GELU of the first
+                                float2 g = make_float2(gelu_tanh(x.x), gelu_tanh(x.y));
+                                if (round_aux) g = make_float2(round_tf32(g.x), round_tf32(g.y));
+                                *reinterpret_cast<float2 *>(aux + (size_t)m * N + n) = g;
+                            }
                         }
                     }
                 };
@@ -1048,22 +1054,22 @@ int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int
     return BMB_OK;
 }
 
-template <int KIND, int BN, int MH>
+template <int KIND, int BN, int MH, int AUX = 0>
 int launch_tc(int grid, cudaStream_t st, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, int c_mode,
               int batch, int M, int N, int kblocks, int kper,
               int amn, int bmn, float alpha, float beta, float *C, int vec_ok, int dp_tiles, int g_sk, const float *bias,
-              int round_c, int *status_dev) {
+              int round_c, int *status_dev, float *aux, int round_aux) {
     static bool attr_set[64];
     {
         std::lock_guard<std::mutex> lk(g_attr_mu);
         const int d = current_device();
         if (d >= 0 && d < 64 && !attr_set[d]) {
-            BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<KIND, BN, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN, MH)));
+            BMB_CUDA(cudaFuncSetAttribute(gemm_tc_k<KIND, BN, MH, AUX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN, MH)));
             attr_set[d] = true;
         }
     }
-    gemm_tc_k<KIND, BN, MH><<<grid, NTHREADS, smem_bytes(BN, MH), st>>>(mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
-                                                                dp_tiles, g_sk, bias, round_c, status_dev);
+    gemm_tc_k<KIND, BN, MH, AUX><<<grid, NTHREADS, smem_bytes(BN, MH), st>>>(mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok,
+                                                                dp_tiles, g_sk, bias, round_c, status_dev, aux, round_aux);
     return BMB_OK;
 }
 
@@ -1111,9 +1117,15 @@ int pair_clusters() {
 
 }  // namespace
 
+// aux_gelu (optional): a second output, GELU (tanh form, src/nn.cu:118-127) of the result, rounded to TF32 when the
+// library is emitting rounded operands -- the MLP's activation rides in the epilogue of the product before it.
+// Served where every tile is stored by one CTA straight from registers (beta 0, aligned C, no tile shared
+// along K, which costs a problem of many tiles about 1 %); otherwise the caller gets BMB_E_UNSUPPORTED with C
+// untouched and applies the activation itself.
 int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N, int K, float alpha,
             const float *A, long long, const float *B, long long, float beta, float *C, long long,
-            const float *bias, cudaStream_t st) {
+            const float *bias, cudaStream_t st, float *aux_gelu) {
+    if (aux_gelu) flags |= BMB_GEMM_NO_SPLIT | BMB_GEMM_NO_PAIR | BMB_GEMM_TILE_M128;
     int *status_dev = nullptr;
     volatile int *status_host = nullptr;
     BMB_TRY(tc::status_word(&status_dev, &status_host));
@@ -1156,6 +1168,10 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     // 3 = whole tiles stored straight from registers (beta 0), parts of shared tiles added by the copy engine
     int c_mode = (!no_tma_store && vec_ok && (beta == 0.0f || beta == 1.0f)) ? (beta == 0.0f ? (no_direct ? 1 : 3) : 2) : 0;
     if (batch > 1 && c_mode != 3) c_mode = 0;        // the tensor map over C describes one problem only
+    float *aux = aux_gelu;
+    const int round_aux = emit_rounded() ? 1 : 0;
+    if (aux && (c_mode != 3 || plan.pair || plan.sk_tiles > 0 || batch != 1 || ((uintptr_t)aux & 15) || bf16 || plan.mh != 1 || bn < 128))
+        return fail(BMB_E_UNSUPPORTED, "gemm_tc: the fused activation needs beta 0, an aligned C and whole tiles");
     if (c_mode) BMB_TRY(make_map_2d(&mapC, C, 4, M, N, (long long)N * 4, 32, false));
     if (plan.pair) {
         // (a K-major operand may have gone the padded-copy route; an MN-major one is 3-d by wants_pair's rule)
@@ -1166,8 +1182,14 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
         BMB_LAUNCH_CHECK();
         return BMB_OK;
     }
-#define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev
-    if (bf16) {
+#define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev, aux, round_aux
+    if (aux) {
+        // the second output is compiled into three instances only (the plain kernels stay as lean as they were:
+        // the activation's code in every epilogue cost all products 13 %)
+        if (bn == 256) BMB_TRY((launch_tc<0, 256, 1, 1>(BMB_TC_ARGS)));
+        else if (bn == 192) BMB_TRY((launch_tc<0, 192, 1, 1>(BMB_TC_ARGS)));
+        else BMB_TRY((launch_tc<0, 128, 1, 1>(BMB_TC_ARGS)));
+    } else if (bf16) {
         if (plan.mh == 2) BMB_TRY((launch_tc<1, 256, 2>(BMB_TC_ARGS)));
         else if (bn == 256) BMB_TRY((launch_tc<1, 256, 1>(BMB_TC_ARGS)));
         else if (bn == 192) BMB_TRY((launch_tc<1, 192, 1>(BMB_TC_ARGS)));

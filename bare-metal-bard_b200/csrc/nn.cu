@@ -326,10 +326,7 @@ column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
 
 // --------------------------------------------------------------------- gelu
 // tanh-approximation GELU with the accurate tanhf (src/nn.cu:118-150).
-__device__ __forceinline__ float gelu1(float x) {
-    const float s = 0.7978845608028654f;
-    return 0.5f * x * (1.0f + tanhf(s * (x + 0.044715f * x * x * x)));
-}
+__device__ __forceinline__ float gelu1(float x) { return gelu_tanh(x); }
 __device__ __forceinline__ float dgelu1(float x, float g) {
     const float s = 0.7978845608028654f;
     const float inner = s * (x + 0.044715f * x * x * x);
@@ -355,6 +352,21 @@ __global__ void gelu_bwd_k(float *__restrict__ dinp, const float *__restrict__ i
         float4 d;
         d.x = dgelu1(x.x, g.x); d.y = dgelu1(x.y, g.y); d.z = dgelu1(x.z, g.z); d.w = dgelu1(x.w, g.w);
         ST4(dinp + i * 4) = rnd4(d, rnd);
+    }
+}
+
+// element-wise forms for operands that are not 16-byte aligned or whose count is not a multiple of 4
+__global__ void gelu_fwd_scalar_k(float *__restrict__ out, const float *__restrict__ inp, long long n, int rnd) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float g = gelu1(inp[i]);
+        out[i] = rnd ? round_tf32(g) : g;
+    }
+}
+__global__ void gelu_bwd_scalar_k(float *__restrict__ dinp, const float *__restrict__ inp, const float *__restrict__ dout,
+                                  long long n, int rnd) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float d = dgelu1(inp[i], dout[i]);
+        dinp[i] = rnd ? round_tf32(d) : d;
     }
 }
 
@@ -764,6 +776,7 @@ extern "C" {
 int bmb_encoder_forward(float *out, const int *tokens, const float *wte, const float *wpe, int B,
                         int T, int C) {
     if (C % 4) return fail(BMB_E_ARG, "encoder_forward: C=%d must be a multiple of 4", C);
+    if (!aligned16(out) || !aligned16(wte) || !aligned16(wpe)) return fail(BMB_E_ARG, "encoder_forward: out, wte and wpe must be 16-byte aligned");
     const long long n4 = (long long)B * T * C / 4;
     if (n4 == 0) return BMB_OK;
     encoder_fwd_k<<<grid_for(n4, 256, 8), 256, 0, cur_stream()>>>(out, tokens, wte, wpe, T, C, n4);
@@ -775,6 +788,7 @@ int bmb_encoder_forward(float *out, const int *tokens, const float *wte, const f
 int bmb_encoder_backward(float *dwte, float *dwpe, const float *dout, const int *tokens, int B,
                          int T, int C) {
     if (C % 4) return fail(BMB_E_ARG, "encoder_backward: C=%d must be a multiple of 4", C);
+    if (!aligned16(dwte) || !aligned16(dwpe) || !aligned16(dout)) return fail(BMB_E_ARG, "encoder_backward: dwte, dwpe and dout must be 16-byte aligned");
     const long long n4 = (long long)B * T * C / 4;
     if (n4 == 0) return BMB_OK;
     cudaStream_t st = cur_stream();
@@ -924,17 +938,21 @@ int bmb_layernorm_backward_noalloc(float *dinp, float *dweight, float *dbias, co
 }
 
 int bmb_gelu_forward(float *out, const float *inp, int n) {
-    if (n % 4) return fail(BMB_E_ARG, "gelu_forward: n=%d must be a multiple of 4", n);
-    if (n == 0) return BMB_OK;
-    gelu_fwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(out, inp, n / 4, emit_rounded() ? 1 : 0);
+    if (n <= 0) return BMB_OK;
+    if (n % 4 || !aligned16(out) || !aligned16(inp))
+        gelu_fwd_scalar_k<<<grid_for(n, 256, 8), 256, 0, cur_stream()>>>(out, inp, n, emit_rounded() ? 1 : 0);
+    else
+        gelu_fwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(out, inp, n / 4, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
 }
 int bmb_gelu_backward(float *dinp, const float *inp, const float *dout, int n) {
-    if (n % 4) return fail(BMB_E_ARG, "gelu_backward: n=%d must be a multiple of 4", n);
-    if (n == 0) return BMB_OK;
-    gelu_bwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(dinp, inp, dout, n / 4, emit_rounded() ? 1 : 0);
+    if (n <= 0) return BMB_OK;
+    if (n % 4 || !aligned16(dinp) || !aligned16(inp) || !aligned16(dout))
+        gelu_bwd_scalar_k<<<grid_for(n, 256, 8), 256, 0, cur_stream()>>>(dinp, inp, dout, n, emit_rounded() ? 1 : 0);
+    else
+        gelu_bwd_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(dinp, inp, dout, n / 4, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -943,7 +961,6 @@ int bmb_gelu_backward_colsum(float *dinp, float *dcolsum, const float *inp, cons
     if (N <= 0 || C <= 0) return BMB_OK;
     cudaStream_t st = cur_stream();
     if (C % 4 != 0 || !aligned16(dinp) || !aligned16(inp) || !aligned16(dout) || !dcolsum) {
-        if ((long long)N * C % 4) return fail(BMB_E_ARG, "gelu_backward_colsum: N*C must be a multiple of 4");
         BMB_TRY(bmb_gelu_backward(dinp, inp, dout, N * C));
         return dcolsum ? bmb_bias_backward(dcolsum, dinp, N, C) : BMB_OK;
     }
@@ -960,6 +977,7 @@ int bmb_gelu_backward_colsum(float *dinp, float *dcolsum, const float *inp, cons
 }
 int bmb_residual_forward(float *out, const float *a, const float *b, int n) {
     if (n % 4) return fail(BMB_E_ARG, "residual_forward: n=%d must be a multiple of 4", n);
+    if (!aligned16(out) || !aligned16(a) || !aligned16(b)) return fail(BMB_E_ARG, "residual_forward: the operands must be 16-byte aligned");
     if (n == 0) return BMB_OK;
     add3_k<<<grid_for(n / 4, 256, 8), 256, 0, cur_stream()>>>(out, a, b, n / 4);
     count_launch();
@@ -971,6 +989,7 @@ int bmb_add_inplace(float *dst, const float *src, int n) {
 }
 int bmb_bias_forward(float *out, const float *bias, int N, int C) {
     if (C % 4) return fail(BMB_E_ARG, "bias_forward: C=%d must be a multiple of 4", C);
+    if (!aligned16(out) || !aligned16(bias)) return fail(BMB_E_ARG, "bias_forward: out and bias must be 16-byte aligned");
     const long long n4 = (long long)N * C / 4;
     if (n4 == 0) return BMB_OK;
     bias_fwd_k<<<grid_for(n4, 256, 8), 256, 0, cur_stream()>>>(out, bias, C, n4, emit_rounded() ? 1 : 0);

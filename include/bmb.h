@@ -117,6 +117,15 @@ int bmb_gemm(int transA, int transB, int M, int N, int K, float alpha,
 int bmb_gemm_ex(int math, int flags, int transA, int transB, int M, int N,
                 int K, float alpha, const float *A, const float *B, float beta,
                 float *C, void *stream);
+/* The MLP's first half in one call (no counterpart in the reference; equals gemm + bias_forward + gelu_forward of
+ * src/gpt.cu:268-272): C = A W^T + bias (A [M,K], W [N,K], bias [N] or NULL, all row-major) and
+ * C_gelu = GELU(C), bit-identical to bmb_gelu_forward on C.  On the tensor-core paths both leave the
+ * accumulator in the product's epilogue when C and C_gelu are 16-byte aligned and N % 4 == 0 (no tile is then
+ * split along K); otherwise, and for BMB_MATH_FP32, the activation is a pass of its own.
+ * BMB_GEMM_AUX_ROUNDED: C_gelu is stored rounded to TF32 (it feeds another tensor-core product). */
+#define BMB_GEMM_AUX_ROUNDED 512
+int bmb_gemm_bias_gelu(int math, int flags, int M, int N, int K, const float *A, const float *W, const float *bias,
+                       float *C, float *C_gelu, void *stream);
 int bmb_batched_gemm(int transA, int transB, int batch, int M, int N, int K,
                      float alpha, const float *A, long long strideA,
                      const float *B, long long strideB, float beta, float *C,

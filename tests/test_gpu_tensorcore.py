@@ -345,3 +345,33 @@ def test_side_by_side_backward_products_equal_one_after_the_other(bmb, cuda, mon
         tr.close()
         runs.append(losses)
     assert np.all(np.isfinite(runs[0])) and max(abs(a - b) for a, b in zip(*runs)) <= 1e-3, runs
+
+
+@pytest.mark.parametrize("M,N,K,pad,with_bias", [(512, 768, 256, 0, True), (8192, 3072, 768, 0, True), (300, 516, 77, 0, True),
+                                                  (256, 132, 64, 1, False)])
+def test_gemm_bias_gelu_equals_the_three_calls(bmb, orc, cuda, M, N, K, pad, with_bias):
+    """bmb_gemm_bias_gelu (the activation in the product's epilogue on aligned outputs, a pass of its own otherwise)
+    against gemm + bias_forward + gelu_forward on the same operands: C agrees to the last bits that a different
+    tile plan may move (no tile is split along K in the fused form), C_gelu is bit-identical to gelu_forward
+    applied to the C the fused call returned, and both agree with the oracle's GELU."""
+    A, W, bias = rounded(orc, uniform(M * K, 21), "tf32"), rounded(orc, uniform(N * K, 22), "tf32"), uniform(N, 23)
+    dA, dW, db = dev(cuda, A), dev(cuda, W), (dev(cuda, bias) if with_bias else None)
+    flags = bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED
+    # pad = 1: outputs that start 4 bytes off a 16-byte boundary (the activation then runs as its own element-wise pass)
+    c_f = cuda.full((M * N + 4,), float("nan"), device="cuda")[pad:pad + M * N]
+    g_f = cuda.full((M * N + 4,), float("nan"), device="cuda")[pad:pad + M * N]
+    bmb.call("bmb_gemm_bias_gelu", bmb.MATH_TF32, flags | bmb.GEMM_AUX_ROUNDED, M, N, K, dA, dW, db, c_f, g_f, None)
+    c_s, g_s = cuda.zeros(M * N, device="cuda"), cuda.zeros(M * N, device="cuda")
+    bmb.call("bmb_gemm_ex", bmb.MATH_TF32, flags | bmb.GEMM_NO_SPLIT, 0, 1, M, N, K, 1.0, dA, dW, 0.0, c_s, None)
+    if with_bias:
+        bmb.call("bmb_bias_forward", c_s, db, M, N)
+    cf, cs = host(cuda, c_f), host(cuda, c_s)
+    assert np.all(np.isfinite(cf)) and normwise(cf, cs) <= 2e-6
+    # the activation of exactly what the fused call stored, by the stand-alone kernel, then rounded
+    bmb.call("bmb_gelu_forward", g_s, c_f.clone(), M * N)
+    bmb.call("bmb_round_tf32", g_s, g_s, M * N, None)
+    gf = host(cuda, g_f)
+    assert np.array_equal(gf, host(cuda, g_s))
+    want = np.empty_like(cf)
+    orc.orc_gelu_forward(_np(want), _np(cf), cf.size)
+    assert normwise(gf, want) <= 5e-4                            # TF32 rounding of the activation
