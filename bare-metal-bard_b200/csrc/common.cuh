@@ -60,6 +60,10 @@ struct DpRangeList {
 // Returns nullptr (and records an error) on failure.
 enum ScratchSlot { SCR_REDUCE = 0, SCR_GEMM_A = 1, SCR_GEMM_B = 2, SCR_MISC = 3, SCR_SLOTS = 4 };
 void *device_scratch(ScratchSlot slot, size_t bytes);
+// Order the users of a scratch slot across streams of one device: acquire before the first launch that writes
+// the slot, release after the last launch that reads it (both on the stream those launches go to).
+int scratch_acquire(ScratchSlot slot, cudaStream_t st);
+int scratch_release(ScratchSlot slot, cudaStream_t st);
 // Counts the times any scratch block of the current device was (re)allocated.  A caller that keeps
 // scratch addresses beyond one call (the trainer's captured graph) compares it before reusing them.
 unsigned long long scratch_generation();

@@ -479,6 +479,7 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
         const long long n = (long long)B * T * 3 * C;
         float *scr = (float *)device_scratch(SCR_GEMM_A, (size_t)n * sizeof(float));
         if (!scr) return BMB_E_CUDA;
+        BMB_TRY(scratch_acquire(SCR_GEMM_A, st));         // another stream's product may still read the staging slot
         long long blocks = (n / 4 + 255) / 256, cap = 8LL * sm_count();
         round_copy_k<<<(int)(blocks > cap ? cap : blocks), 256, 0, st>>>(scr, qkv, n / 4);
         count_launch();
@@ -507,6 +508,7 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
                                                         emit_rounded() ? 1 : 0, status_dev);
     count_launch();
     BMB_LAUNCH_CHECK();
+    if (!qkv_rounded) BMB_TRY(scratch_release(SCR_GEMM_A, st));
     return BMB_OK;
 }
 

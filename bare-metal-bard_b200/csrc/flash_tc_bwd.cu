@@ -752,6 +752,8 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
         float *sq = (float *)device_scratch(SCR_GEMM_A, (size_t)nq * sizeof(float));
         float *sg = (float *)device_scratch(SCR_GEMM_B, (size_t)ng * sizeof(float));
         if (!sq || !sg) return BMB_E_CUDA;
+        BMB_TRY(scratch_acquire(SCR_GEMM_A, st));         // another stream's product may still read the staging slots
+        BMB_TRY(scratch_acquire(SCR_GEMM_B, st));
         const long long cap = 8LL * sm_count();
         long long b1 = (nq / 4 + 255) / 256, b2 = (ng / 4 + 255) / 256;
         round_copy2_k<<<(int)(b1 > cap ? cap : b1), 256, 0, st>>>(sq, qkv, nq / 4);
@@ -782,6 +784,10 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
     flash_bwd_tc_k<<<grid, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     count_launch();
     BMB_LAUNCH_CHECK();
+    if (!rounded) {
+        BMB_TRY(scratch_release(SCR_GEMM_A, st));
+        BMB_TRY(scratch_release(SCR_GEMM_B, st));
+    }
     return BMB_OK;
 }
 

@@ -825,6 +825,17 @@ struct Operand {
     int box_rows;
     bool map3d;           // MN-major with the extent a multiple of 32: one 3-d copy per slice
     int tile_chunks;      // 32-wide chunks per tile (3-d map only)
+    bool staged = false;  // ptr is a converted copy in the per-device staging scratch
+};
+// Marks the staging slots this call wrote as used by its stream when the call returns (its last launch reads
+// them): the next caller on another stream of the device waits for that launch before overwriting them.
+struct StagingRelease {
+    const Operand &a, &b;
+    cudaStream_t st;
+    ~StagingRelease() {
+        if (a.staged) scratch_release(SCR_GEMM_A, st);
+        if (b.staged) scratch_release(SCR_GEMM_B, st);
+    }
 };
 
 inline int blocks_for(long long items) {
@@ -845,6 +856,8 @@ int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int 
             if (!rounded) {
                 float *scr = (float *)device_scratch(slot, (size_t)batch * X * K * sizeof(float));
                 if (!scr) return BMB_E_CUDA;
+                BMB_TRY(scratch_acquire(slot, st));
+                op->staged = true;
                 const long long n4 = (long long)batch * X * (long long)K / 4;
                 prep_round_vec4_k<<<blocks_for(n4), 256, 0, st>>>(scr, src, n4);
                 count_launch();
@@ -865,6 +878,8 @@ int stage_operand(Operand *op, const float *src, bool kcontig, long long X, int 
     const int Kp = (K + kalign - 1) / kalign * kalign;
     void *scr = device_scratch(slot, (size_t)X * Kp * esize);
     if (!scr) return BMB_E_CUDA;
+    BMB_TRY(scratch_acquire(slot, st));
+    op->staged = true;
     if (kcontig) {
         if (bf16) prep_rows_k<__nv_bfloat16><<<blocks_for(X * (long long)Kp), 256, 0, st>>>((__nv_bfloat16 *)scr, src, X, K, Kp);
         else prep_rows_k<float><<<blocks_for(X * (long long)Kp), 256, 0, st>>>((float *)scr, src, X, K, Kp);
@@ -1142,6 +1157,7 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
         plan_pair(&plan, flags, M, N, (flags & BMB_GEMM_HALF_SMS) ? (pair_clusters() + 1) / 2 : pair_clusters());
     const int kblocks = plan.kblocks, bn = plan.bn, dp_tiles = plan.dp_tiles;
     Operand a, b;
+    StagingRelease release_on_return{a, b, st};
     // per CTA: the pair kernel loads 128 rows of A and half of the B tile
     BMB_TRY(stage_operand(&a, A, !transA, M, K, bf16, (flags & BMB_GEMM_A_ROUNDED) != 0, SCR_GEMM_A, plan.pair ? BM : plan.mh * BM, st, batch));
     BMB_TRY(stage_operand(&b, B, transB != 0, N, K, bf16, (flags & BMB_GEMM_B_ROUNDED) != 0, SCR_GEMM_B, plan.pair ? bn / 2 : bn, st, batch));

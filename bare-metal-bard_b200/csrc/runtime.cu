@@ -79,6 +79,40 @@ void *device_scratch(ScratchSlot slot, size_t bytes) {
     return p;
 }
 
+// Who used a scratch slot last.  A caller about to overwrite a slot from another stream than its last user first
+// makes its stream wait for that user's last kernel, so that two streams of one device take turns instead of racing.
+// (Not while a stream is being captured: the captured launches carry their own order, and an event recorded inside a
+// capture cannot be waited for outside it.)
+struct SlotUse { cudaStream_t stream = nullptr; cudaEvent_t done = nullptr; bool valid = false; };
+static SlotUse g_slot_use[64][SCR_SLOTS];
+
+static bool capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) { cudaGetLastError(); return false; }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+int scratch_acquire(ScratchSlot slot, cudaStream_t st) {
+    const int d = current_device();
+    if (d < 0 || d >= 64 || capturing(st)) return BMB_OK;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    SlotUse &u = g_slot_use[d][slot];
+    if (u.valid && u.stream != st) BMB_CUDA(cudaStreamWaitEvent(st, u.done, 0));
+    return BMB_OK;
+}
+
+int scratch_release(ScratchSlot slot, cudaStream_t st) {
+    const int d = current_device();
+    if (d < 0 || d >= 64 || capturing(st)) return BMB_OK;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    SlotUse &u = g_slot_use[d][slot];
+    if (!u.done) BMB_CUDA(cudaEventCreateWithFlags(&u.done, cudaEventDisableTiming));
+    BMB_CUDA(cudaEventRecord(u.done, st));
+    u.stream = st;
+    u.valid = true;
+    return BMB_OK;
+}
+
 }  // namespace bmb
 
 extern "C" {

@@ -832,9 +832,25 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
         BMB_TRY(dp_fused_update_ranges(t->dp, t->chunk[c], t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
                                        t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, t->st_x));
         BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st_x));
-        if (t->shadow) BMB_TRY(dp_round_ranges(t->chunk[c], t->shadow, t->params, t->st_x));
+        // The rounded copy of the token embedding is read by the head's product only, at the end of the forward
+        // pass (the embedding look-up reads the fp32 rows): in the chunked plan it is rounded after chunk A's event,
+        // still ahead of chunk C's, which the piece holding the head waits for.
+        const bool wte_later = t->shadow && c == 0 && t->pieces.size() > 1 && t->chunk[0].n > 1 && t->chunk[0].off[0] == t->poff[P_WTE];
+        if (t->shadow) {
+            DpRangeList first = t->chunk[c];
+            if (wte_later) {
+                for (int q = 1; q < first.n; ++q) { first.off[q - 1] = first.off[q]; first.len[q - 1] = first.len[q]; }
+                --first.n;
+            }
+            BMB_TRY(dp_round_ranges(first, t->shadow, t->params, t->st_x));
+        }
         BMB_CUDA(cudaEventRecord(t->ev_upd[c], t->st_x));
         t->upd_pending[c] = true;
+        if (wte_later) {
+            DpRangeList wte;
+            wte.n = 1; wte.off[0] = t->chunk[0].off[0]; wte.len[0] = t->chunk[0].len[0];
+            BMB_TRY(dp_round_ranges(wte, t->shadow, t->params, t->st_x));
+        }
     }
     return BMB_OK;
 }

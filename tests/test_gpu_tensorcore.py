@@ -375,3 +375,29 @@ def test_gemm_bias_gelu_equals_the_three_calls(bmb, orc, cuda, M, N, K, pad, wit
     want = np.empty_like(cf)
     orc.orc_gelu_forward(_np(want), _np(cf), cf.size)
     assert normwise(gf, want) <= 5e-4                            # TF32 rounding of the activation
+
+
+def test_two_streams_take_turns_on_the_staging_scratch(bmb, cuda):
+    """Tensor-core products whose operands are not flagged as rounded first round them into one per-device staging
+    block.  Two streams of one device issuing such products at the same time must take turns on it (the library
+    orders a slot's users with an event) instead of overwriting each other's operands: every result equals the
+    one the same call gives when it runs alone."""
+    import ctypes as C
+    M, N, K = 1024, 768, 512
+    ops = [(cuda.rand(M * K, device="cuda") * 2 - 1, cuda.rand(N * K, device="cuda") * 2 - 1) for _ in range(2)]
+    alone = []
+    for A, B in ops:
+        c = cuda.zeros(M * N, device="cuda")
+        bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_NO_SPLIT, 0, 1, M, N, K, 1.0, A, B, 0.0, c, None)
+        alone.append(host(cuda, c))
+    streams = [cuda.cuda.Stream(), cuda.cuda.Stream()]
+    outs = [[cuda.zeros(M * N, device="cuda") for _ in range(8)] for _ in range(2)]
+    cuda.cuda.synchronize()
+    for it in range(8):
+        for i, (A, B) in enumerate(ops):
+            bmb.call("bmb_gemm_ex", bmb.MATH_TF32, bmb.GEMM_NO_SPLIT, 0, 1, M, N, K, 1.0, A, B, 0.0, outs[i][it],
+                     C.c_void_p(streams[i].cuda_stream))
+    cuda.cuda.synchronize()
+    for i in range(2):
+        for it in range(8):
+            assert np.array_equal(host(cuda, outs[i][it]), alone[i]), (i, it)
