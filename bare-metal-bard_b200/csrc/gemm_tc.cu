@@ -126,14 +126,31 @@ struct WorkIter {
     long long R;            // K slices in the stream-K region
     long long it, hi;       // what is left of this CTA's run
     int dp_next;
+    // Chunk-major form (g_sk < 0: -g_sk chunks; every tile is shared): the K range is cut into chunks and the items
+    // (chunk, tile) are dealt round-robin in chunk-major order, so that at any time all CTAs work at about the same
+    // depth of K -- CTAs that share an operand panel read the same slices at the same time, and panels too large for
+    // L2 come from DRAM once instead of once per tile sharing them.
+    int kchunks, ntiles;
+    long long q;
     __host__ __device__ __forceinline__ long long run_start(int c) const { return ((long long)c * R) / g_sk; }
     __host__ __device__ __forceinline__ void init(int cta, int grid_, int dp_tiles_, int sk_tiles, int kblocks_, int g_sk_) {
         dp_tiles = dp_tiles_; kblocks = kblocks_; g_sk = g_sk_; grid = grid_;
+        kchunks = 0; ntiles = sk_tiles; q = cta;
+        if (g_sk_ < 0) { kchunks = -g_sk_; it = hi = 0; R = 0; dp_next = dp_tiles_; return; }
         R = (long long)sk_tiles * kblocks_;
         if (cta < g_sk_) { it = run_start(cta); hi = run_start(cta + 1); } else { it = hi = 0; }
         dp_next = cta;
     }
     __host__ __device__ __forceinline__ bool next(int &tile, int &kb0, int &kb1) {
+        if (kchunks) {
+            if (q >= (long long)ntiles * kchunks) return false;
+            const int chunk = (int)(q / ntiles);
+            tile = dp_tiles + (int)(q - (long long)chunk * ntiles);
+            kb0 = (int)(((long long)chunk * kblocks) / kchunks);
+            kb1 = (int)(((long long)(chunk + 1) * kblocks) / kchunks);
+            q += grid;
+            return true;
+        }
         if (it < hi) {
             const long long t = it / kblocks;
             kb0 = (int)(it - t * kblocks);
@@ -1066,6 +1083,24 @@ int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int
     }
     p->grid = p->sk_tiles > 0 ? (p->dp_tiles >= ctas ? ctas : (p->dp_tiles > p->g_sk ? p->dp_tiles : p->g_sk))
                               : (p->tiles < ctas ? p->tiles : ctas);
+    // A problem shared as a whole (fewer tiles than would fill two waves, a long K) whose operands do not fit L2:
+    // with end-to-end runs every CTA is at a different depth of K, and an operand panel shared by several tiles is
+    // fetched from DRAM once per tile (measured at 8192 x 768 x 50304: 6.2 GB for 1.8 GB of operands, the launch
+    // DRAM-bound).  The chunk-major order keeps all CTAs at about the same depth.  Chunks: the smallest count from 4
+    // that fills the last round of items to 99 % (else the best up to 40), at least 16 K slices per item.
+    static const bool no_chunks = getenv("BMB_GEMM_NO_KCHUNKS") != nullptr;
+    const double operand_bytes = ((double)M + (double)N) * (double)K * (bf16 ? 2.0 : 4.0);
+    if (!no_chunks && p->sk_tiles == p->tiles && p->dp_tiles == 0 && p->grid == ctas && p->g_sk == ctas && operand_bytes > 96.0e6) {
+        int best = 0;
+        double best_eff = 0.0;
+        for (int s = 4; s <= 40 && p->kblocks / s >= 16; ++s) {
+            const long long items = (long long)p->tiles * s;
+            const double eff = (double)items / (double)(((items + ctas - 1) / ctas) * ctas);
+            if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+            if (eff >= 0.99) { best = s; best_eff = eff; break; }
+        }
+        if (best && best_eff >= 0.97) p->g_sk = -best;
+    }
     return BMB_OK;
 }
 

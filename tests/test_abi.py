@@ -100,7 +100,9 @@ def test_tensorcore_gemm_schedule_covers_every_slice_once(bmb):
     rng = random.Random(11)
     shapes = [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072), (8192, 50304, 768),
               (8192, 768, 50304), (3072, 768, 8192), (768, 768, 8192), (50304, 768, 8192), (8192, 8192, 8192),
-              (128, 64, 32), (129, 65, 33), (1000, 1000, 1000), (4096, 160, 512)]
+              (128, 64, 32), (129, 65, 33), (1000, 1000, 1000), (4096, 160, 512),
+              # long K, few tiles, operands beyond L2: shared as a whole, in chunk-major order
+              (4096, 512, 100000), (2048, 768, 65536), (8192, 256, 40000), (1024, 1024, 30011)]
     shapes += [(rng.randrange(128, 5000), rng.randrange(64, 5000), rng.randrange(32, 5000)) for _ in range(60)]
     shared = 0
     for ctas in (148, 132, 7, 1):
