@@ -22,6 +22,7 @@
 // no kernel spins on another GPU.
 #include "common.cuh"
 #include <cmath>
+#include <mutex>
 
 namespace bmb {
 namespace {
@@ -45,25 +46,37 @@ __device__ __forceinline__ void my_piece(size_t len4, int rank, int nranks, size
 
 // For every range of the list, over this rank's piece of it: out[e] = sum over ranks (in rank order) of
 // grads_r[e]; partial[blockIdx.x] = this block's share of sum(out^2).
+// NR = 2, 4 or 8 bounds the rank count; a thread keeps NR * U = 8 sixteen-byte loads in flight, so that one block
+// per SM (the grid used while the main stream's kernels own the SMs) still covers the NVLink round trip.
+template <int NR, int U>
 __global__ void __launch_bounds__(256)
 dp_reduce_ranges_k(PeerBufs pb, int nranks, int rank, float *__restrict__ out, DpRangeList rl, float *__restrict__ partial) {
     __shared__ float red[32];
     float acc2 = 0.0f;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (int q = 0; q < rl.n; ++q) {
         size_t lo, hi;
         my_piece(rl.len[q] >> 2, rank, nranks, lo, hi);
-        for (size_t i = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
-            const size_t e = rl.off[q] + i * 4;
-            float4 v[MAX_RANKS];
+        for (size_t i0 = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i0 < hi; i0 += stride * U) {
+            float4 v[U][NR];
 #pragma unroll
-            for (int r = 0; r < MAX_RANKS; ++r)
-                if (r < nranks) v[r] = ld4(pb.grads[r] + e);          // all loads in flight before the adds
-            float4 s = v[0];
+            for (int u = 0; u < U; ++u) {
+                const size_t i = i0 + (size_t)u * stride;
 #pragma unroll
-            for (int r = 1; r < MAX_RANKS; ++r)
-                if (r < nranks) { s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w; }
-            st4(out + e, s);
-            acc2 += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
+                for (int r = 0; r < NR; ++r)
+                    if (r < nranks && i < hi) v[u][r] = ld4(pb.grads[r] + rl.off[q] + i * 4);   // all loads in flight before the adds
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t i = i0 + (size_t)u * stride;
+                if (i >= hi) continue;
+                float4 s = v[u][0];
+#pragma unroll
+                for (int r = 1; r < NR; ++r)
+                    if (r < nranks) { s.x += v[u][r].x; s.y += v[u][r].y; s.z += v[u][r].z; s.w += v[u][r].w; }
+                st4(out + rl.off[q] + i * 4, s);
+                acc2 += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
+            }
         }
     }
     const float t = block_reduce<false>(acc2, red);
@@ -145,7 +158,7 @@ struct DpFused {
     void *opened[3 * MAX_RANKS] = {nullptr};
     int nopened = 0;
     float *partial = nullptr;   // per-block sums of squares, DP_SLOTS reduce launches per step side by side
-    int blocks = 0;             // grid of the exchange kernels
+    int blocks = 0;             // largest grid of the exchange kernels (a slot of the partials holds this many)
 };
 
 int dp_fused_export(const float *grads, const float *params, const float *shadow, void *out192) {
@@ -215,10 +228,18 @@ int check_ranges(const DpRangeList &rl) {
 
 // Phase 1 on `st`: reduce this rank's pieces of the listed ranges; their sum of squares goes to slot `slot`
 // (0 .. DP_SLOTS-1) of the partials.  Slots not used in a step must be cleared with dp_fused_clear_slot.
-int dp_fused_reduce_ranges(DpFused *d, const DpRangeList &rl, float *grads, int slot, cudaStream_t st) {
+// `alone`: nothing else is running on the GPU (the main stream is waiting for this), so the kernel may fill it; otherwise
+// one block per SM, which leaves room for a GPU-filling kernel of the main stream beside it (four blocks per SM of
+// these kernels take the whole register file, and the two streams then only take turns).
+int dp_fused_reduce_ranges(DpFused *d, const DpRangeList &rl, float *grads, int slot, bool alone, cudaStream_t st) {
     BMB_TRY(check_ranges(rl));
     if (slot < 0 || slot >= DP_SLOTS) return fail(BMB_E_ARG, "fused data-parallel step: slot %d", slot);
-    dp_reduce_ranges_k<<<d->blocks, 256, 0, st>>>(d->pb, d->nranks, d->rank, grads, rl, d->partial + (size_t)slot * d->blocks);
+    const int grid = alone ? d->blocks : sm_count();
+    float *partial = d->partial + (size_t)slot * d->blocks;
+    if (grid < d->blocks) BMB_CUDA(cudaMemsetAsync(partial + grid, 0, (size_t)(d->blocks - grid) * sizeof(float), st));
+    if (d->nranks <= 2) dp_reduce_ranges_k<2, 4><<<grid, 256, 0, st>>>(d->pb, d->nranks, d->rank, grads, rl, partial);
+    else if (d->nranks <= 4) dp_reduce_ranges_k<4, 2><<<grid, 256, 0, st>>>(d->pb, d->nranks, d->rank, grads, rl, partial);
+    else dp_reduce_ranges_k<8, 1><<<grid, 256, 0, st>>>(d->pb, d->nranks, d->rank, grads, rl, partial);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;
@@ -238,10 +259,11 @@ int dp_fused_sumsq(DpFused *d, double *d_sumsq_pieces, cudaStream_t st) {
 
 // Phase 3 on `st`: *d_sumsq_total holds the squared norm of the whole summed gradient.
 int dp_fused_update_ranges(DpFused *d, const DpRangeList &rl, const float *grads, float *m, float *v, float lr, float beta1,
-                           float beta2, float eps, float wd, int step, const double *d_sumsq_total, float clip, cudaStream_t st) {
+                           float beta2, float eps, float wd, int step, const double *d_sumsq_total, float clip, bool alone,
+                           cudaStream_t st) {
     BMB_TRY(check_ranges(rl));
     const float bc1 = 1.0f - powf(beta1, (float)step), bc2 = 1.0f - powf(beta2, (float)step);
-    dp_adamw_broadcast_ranges_k<<<d->blocks, 256, 0, st>>>(d->pb, d->nranks, d->rank, grads, m, v, rl, lr, beta1, beta2, eps,
+    dp_adamw_broadcast_ranges_k<<<alone ? d->blocks : sm_count(), 256, 0, st>>>(d->pb, d->nranks, d->rank, grads, m, v, rl, lr, beta1, beta2, eps,
                                                           wd, bc1, bc2, d_sumsq_total, clip, (float)d->nranks);
     count_launch();
     BMB_LAUNCH_CHECK();
@@ -249,9 +271,9 @@ int dp_fused_update_ranges(DpFused *d, const DpRangeList &rl, const float *grads
 }
 
 // shadow = TF32-rounded params over the listed ranges, on `st`.
-int dp_round_ranges(const DpRangeList &rl, float *shadow, const float *params, cudaStream_t st) {
+int dp_round_ranges(const DpRangeList &rl, float *shadow, const float *params, bool alone, cudaStream_t st) {
     BMB_TRY(check_ranges(rl));
-    dp_round_ranges_k<<<4 * sm_count(), 256, 0, st>>>(rl, shadow, params);
+    dp_round_ranges_k<<<(alone ? 4 : 1) * sm_count(), 256, 0, st>>>(rl, shadow, params);
     count_launch();
     BMB_LAUNCH_CHECK();
     return BMB_OK;

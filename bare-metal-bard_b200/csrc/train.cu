@@ -29,11 +29,12 @@ int dp_fused_export(const float *grads, const float *params, const float *shadow
 int dp_fused_create(DpFused **out, int rank, int nranks, size_t n, float *grads, float *params, float *shadow,
                     const void *all_handles);
 void dp_fused_destroy(DpFused *d);
-int dp_fused_reduce_ranges(DpFused *d, const DpRangeList &rl, float *grads, int slot, cudaStream_t st);
+int dp_fused_reduce_ranges(DpFused *d, const DpRangeList &rl, float *grads, int slot, bool alone, cudaStream_t st);
 int dp_fused_sumsq(DpFused *d, double *d_sumsq_pieces, cudaStream_t st);
 int dp_fused_update_ranges(DpFused *d, const DpRangeList &rl, const float *grads, float *m, float *v, float lr, float beta1,
-                           float beta2, float eps, float wd, int step, const double *d_sumsq_total, float clip, cudaStream_t st);
-int dp_round_ranges(const DpRangeList &rl, float *shadow, const float *params, cudaStream_t st);
+                           float beta2, float eps, float wd, int step, const double *d_sumsq_total, float clip, bool alone,
+                           cudaStream_t st);
+int dp_round_ranges(const DpRangeList &rl, float *shadow, const float *params, bool alone, cudaStream_t st);
 }
 using namespace bmb;
 
@@ -77,18 +78,27 @@ struct bmb_trainer {
     };
     std::vector<Piece> pieces;
     unsigned long long graph_scratch_gen = 0;   // the device's scratch generation the graphs were captured under
-    // Fused exchange, overlapped: the parameter space is cut into three chunks -- A: embeddings + layer 0,
+    // Fused exchange, overlapped forms: the parameter space is cut into three chunks -- A: embeddings + layer 0,
     // B: layers 1 .. c2-1, C: layers c2 .. L-1 + final layernorm.  Backward finishes C, then B, then A, and each
     // chunk's reduce runs on the exchange stream while backward goes on; the next forward needs A, then B, then
     // C, and each chunk's update + broadcast is awaited only by the first piece that reads it.
     static constexpr int NCHUNK = 3;
     DpRangeList chunk[NCHUNK];
     int chunk_split = 0;                  // c2
-    bool overlap = true;                  // BMB_TRAINER_OVERLAP=0: one chunk, exchanged after backward
+    // BMB_TRAINER_OVERLAP: 0 (default) one chunk, exchanged after backward; 1 three chunks, each reduced while backward
+    // goes on, all updated after the last reduce; 2 also the updates overlapped, with the next step's forward.
+    // Measured at 2 and 4 GPUs (per-step timelines, BMB_TRAINER_TIMELINE): what the overlapped forms hide they give
+    // back -- the kernels of the main stream run slower beside the exchange's memory traffic by about the time the
+    // exchange takes -- so 0 is never worse there: 17.52 / 17.73 / 17.85 ms per step at 2 GPUs for 0 / 1 / 2.
+    int overlap = 0;
     cudaStream_t st_x = nullptr;          // exchange stream
     cudaEvent_t ev_seg[NCHUNK] = {nullptr, nullptr, nullptr};   // main stream: the chunk's gradients are final
     cudaEvent_t ev_upd[NCHUNK] = {nullptr, nullptr, nullptr};   // exchange stream: the chunk's new parameters are in place
     bool upd_pending[NCHUNK] = {false, false, false};
+    // Developer timeline (BMB_TRAINER_TIMELINE=<step>): timed events at the ends of the pieces and of the exchange's
+    // phases in that step and the next, printed to stderr once both have drained.
+    int tl_step = 0;
+    std::vector<std::pair<std::string, cudaEvent_t>> tl;
     float *gen_probs = nullptr;   // one row of next-token probabilities, allocated by the first sampling call
     // The two products of a linear layer's backward (dX = dY W and dW = dY^T X: the same FLOP count, both waiting only
     // for dY) run side by side, each on half of the SMs: dX on the main stream, dW on this one, forked and joined
@@ -393,10 +403,11 @@ void drop_graphs(bmb_trainer *t) {
 }
 
 // The chunks of the parameter space (see bmb_trainer) as range lists, and the pieces of a step.
-// Without the fused exchange the step is one piece.  With it:
+// Without the fused exchange the step is one piece.  With it (overlap 2):
 //   [embedding, layer 0] needs A | [layers 1 .. c2-1] needs B | [layers c2 .. L-1, head, head backward,
 //   backward of layers L-1 .. c2] needs C, finishes C | [backward of layers c2-1 .. 1] finishes B |
-//   [backward of layer 0, embedding backward] finishes A.
+//   [backward of layer 0, embedding backward] finishes A;
+// with overlap 1 the first three are one piece that needs all chunks.
 // Every gradient of a layer is written during that layer's backward or the unit before it (the bias of its
 // second MLP projection comes out of the following layernorm's backward), so a chunk is final when the last of
 // its layers is done.
@@ -406,7 +417,8 @@ struct StepPlan {
     int npieces = 0;
     struct { int u0, u1, needs, reduces; } piece[5];
 };
-void make_plan(const bmb_train_config &c, bool chunks, StepPlan &pl) {
+void make_plan(const bmb_train_config &c, int overlap, StepPlan &pl) {
+    const bool chunks = overlap > 0;
     size_t psize[NPT], poff[NPT], total = 0;
     param_sizes(psize, c);
     for (int i = 0; i < NPT; ++i) { poff[i] = total; total += psize[i]; }
@@ -443,9 +455,13 @@ void make_plan(const bmb_train_config &c, bool chunks, StepPlan &pl) {
     add(2, poff[P_LNFW], psize[P_LNFW]);
     add(2, poff[P_LNFB], psize[P_LNFB]);
     // forward units: 0 embedding, 1 + l layer l, L + 1 head; backward: L + 2 head, 2L + 2 - l layer l, 2L + 3 embedding
-    piece(0, 2, 0, -1);
-    piece(2, 1 + c2, 1, -1);
-    piece(1 + c2, 2 * L + 3 - c2, 2, 2);
+    if (overlap >= 2) {
+        piece(0, 2, 0, -1);
+        piece(2, 1 + c2, 1, -1);
+        piece(1 + c2, 2 * L + 3 - c2, 2, 2);
+    } else {
+        piece(0, 2 * L + 3 - c2, 2, 2);    // waits for the last chunk's update, i.e. for all of them (one stream)
+    }
     piece(2 * L + 3 - c2, 2 * L + 2, -1, 1);
     piece(2 * L + 2, U, -1, 0);
 }
@@ -454,7 +470,7 @@ void plan_pieces(bmb_trainer *t) {
     drop_graphs(t);
     t->pieces.clear();
     StepPlan pl;
-    make_plan(t->c, t->dp && t->overlap, pl);
+    make_plan(t->c, t->dp ? t->overlap : 0, pl);
     for (int k = 0; k < bmb_trainer::NCHUNK; ++k) t->chunk[k] = pl.chunk[k];
     t->chunk_split = pl.split;
     for (int i = 0; i < pl.npieces; ++i) {
@@ -574,9 +590,17 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     BMB_CUDA(cudaEventCreateWithFlags(&t->ev_fork, cudaEventDisableTiming));
     BMB_CUDA(cudaEventCreateWithFlags(&t->ev_join, cudaEventDisableTiming));
     if (const char *e = getenv("BMB_TRAINER_SIDE_BY_SIDE")) t->side_by_side = atoi(e) != 0;
-    if (const char *e = getenv("BMB_TRAINER_OVERLAP")) t->overlap = atoi(e) != 0;
+    if (const char *e = getenv("BMB_TRAINER_OVERLAP")) { const int v = atoi(e); t->overlap = v < 0 ? 0 : (v > 2 ? 2 : v); }
     if (const char *e = getenv("BMB_TRAINER_FUSE_GELU")) t->fuse_gelu = atoi(e) != 0;
-    BMB_CUDA(cudaStreamCreateWithFlags(&t->st_x, cudaStreamNonBlocking));
+    if (const char *e = getenv("BMB_TRAINER_TIMELINE")) t->tl_step = atoi(e);
+    {
+        // The exchange stream outranks the main stream: its small kernels (barrier collectives, piece-wise reduce
+        // and update) must get the SMs that free up between two of the main stream's GPU-filling kernels, or they
+        // queue behind a whole piece of the step and nothing overlaps.
+        int lo = 0, hi = 0;
+        BMB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        BMB_CUDA(cudaStreamCreateWithPriority(&t->st_x, cudaStreamNonBlocking, hi));
+    }
     for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {
         BMB_CUDA(cudaEventCreateWithFlags(&t->ev_seg[c], cudaEventDisableTiming));
         BMB_CUDA(cudaEventCreateWithFlags(&t->ev_upd[c], cudaEventDisableTiming));
@@ -736,7 +760,7 @@ int bmb_trainer_step_plan(const bmb_train_config *cfg, int overlapped, unsigned 
                           int *npieces) {
     if (!cfg || !ranges || !nranges || !pieces || !npieces || cfg->n_layer < 1) return fail(BMB_E_ARG, "trainer_step_plan: bad argument");
     StepPlan pl;
-    make_plan(*cfg, overlapped != 0, pl);
+    make_plan(*cfg, overlapped < 0 ? 0 : (overlapped > 2 ? 2 : overlapped), pl);
     for (int k = 0; k < bmb_trainer::NCHUNK; ++k) {
         nranges[k] = pl.chunk[k].n;
         for (int q = 0; q < DP_MAX_RANGES; ++q) {
@@ -794,11 +818,37 @@ int bmb_trainer_forward_backward(bmb_trainer *t) {
     return run_units(t, 0, num_units(t));
 }
 
+namespace {
+void tl_mark(bmb_trainer *t, int step, cudaStream_t st, const char *what, int idx = -1) {
+    if (!t->tl_step || (step != t->tl_step && step != t->tl_step + 1)) return;
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    cudaEventRecord(e, st);
+    char name[64];
+    if (idx >= 0) snprintf(name, sizeof name, "step %d %s %d", step, what, idx);
+    else snprintf(name, sizeof name, "step %d %s", step, what);
+    t->tl.emplace_back(name, e);
+}
+void tl_flush(bmb_trainer *t, int step) {
+    if (!t->tl_step || step != t->tl_step + 2 || t->tl.empty()) return;
+    cudaDeviceSynchronize();
+    for (auto &m : t->tl) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, t->tl.front().second, m.second);
+        fprintf(stderr, "[timeline dev %d] %8.3f ms  %s\n", t->dev, ms, m.first.c_str());
+    }
+    for (auto &m : t->tl) cudaEventDestroy(m.second);
+    t->tl.clear();
+}
+}  // namespace
+
 int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
     if (!t || step < 1) return fail(BMB_E_ARG, "trainer_step: bad argument");
     Scope sc(t, /*join=*/false);
     if (t->pieces.empty()) plan_pieces(t);
+    tl_flush(t, step);
     const bool eager = step_is_eager(t);
+    tl_mark(t, step, t->st, "start (main)");
     if (!t->dp) {
         for (auto &pc : t->pieces) BMB_TRY(run_piece(t, pc, eager));
         if (t->comm && t->nranks > 1) BMB_TRY(bmb_comm_allreduce(t->comm, t->grads, t->num_params, t->st));
@@ -817,39 +867,69 @@ int bmb_trainer_step(bmb_trainer *t, float lr, int step) {
             BMB_CUDA(cudaStreamWaitEvent(t->st, t->ev_upd[pc.needs], 0));
             t->upd_pending[pc.needs] = false;
         }
+        tl_mark(t, step, t->st, "piece waits done, starts (main), first unit", pc.u0);
         BMB_TRY(run_piece(t, pc, eager));
+        tl_mark(t, step, t->st, "piece ends (main), end unit", pc.u1);
         const int c = pc.reduces;
         if (c < 0 || t->chunk[c].n == 0) continue;
         BMB_CUDA(cudaEventRecord(t->ev_seg[c], t->st));
         BMB_CUDA(cudaStreamWaitEvent(t->st_x, t->ev_seg[c], 0));
         BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st_x));
-        BMB_TRY(dp_fused_reduce_ranges(t->dp, t->chunk[c], t->grads, c, t->st_x));
+        tl_mark(t, step, t->st_x, "barrier before reduce done (exchange), chunk", c);
+        // the last piece's chunk is reduced with the main stream waiting; the others while backward goes on
+        BMB_TRY(dp_fused_reduce_ranges(t->dp, t->chunk[c], t->grads, c, /*alone=*/&pc == &t->pieces.back(), t->st_x));
+        tl_mark(t, step, t->st_x, "reduce done (exchange), chunk", c);
     }
     BMB_TRY(dp_fused_sumsq(t->dp, t->d_sumsq, t->st_x));
     BMB_TRY(bmb_comm_allreduce_f64(t->comm, t->d_sumsq, 1, t->st_x));
+    tl_mark(t, step, t->st_x, "norm done (exchange)");
+    if (t->overlap < 2) {
+        // All chunks updated with the main stream waiting: every update may fill the GPU, one barrier for all, then
+        // the rounded copies; the next step's first piece waits for the last event.
+        for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {
+            if (t->chunk[c].n == 0) continue;
+            BMB_TRY(dp_fused_update_ranges(t->dp, t->chunk[c], t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
+                                           t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, /*alone=*/true, t->st_x));
+        }
+        tl_mark(t, step, t->st_x, "updates + broadcasts done (exchange)");
+        BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st_x));
+        for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {
+            if (t->chunk[c].n == 0) continue;
+            if (t->shadow) BMB_TRY(dp_round_ranges(t->chunk[c], t->shadow, t->params, /*alone=*/true, t->st_x));
+            BMB_CUDA(cudaEventRecord(t->ev_upd[c], t->st_x));
+            t->upd_pending[c] = true;
+        }
+        tl_mark(t, step, t->st_x, "rounded copies done (exchange)");
+        return BMB_OK;
+    }
     for (int c = 0; c < bmb_trainer::NCHUNK; ++c) {           // in the order the next forward needs them
         if (t->chunk[c].n == 0) continue;
+        // the first chunk is updated with the main stream waiting for it; the others while the next forward has begun
+        const bool alone = (c == 0);
         BMB_TRY(dp_fused_update_ranges(t->dp, t->chunk[c], t->grads, t->m, t->v, lr, t->c.beta1, t->c.beta2, t->c.eps,
-                                       t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, t->st_x));
+                                       t->c.weight_decay, step, t->d_sumsq, t->c.grad_clip, alone, t->st_x));
+        tl_mark(t, step, t->st_x, "update + broadcast done (exchange), chunk", c);
         BMB_TRY(bmb_comm_allreduce(t->comm, t->d_token, 1, t->st_x));
+        tl_mark(t, step, t->st_x, "barrier after update done (exchange), chunk", c);
         // The rounded copy of the token embedding is read by the head's product only, at the end of the forward
-        // pass (the embedding look-up reads the fp32 rows): in the chunked plan it is rounded after chunk A's event,
+        // pass (the embedding look-up reads the fp32 rows): it is rounded after chunk A's event,
         // still ahead of chunk C's, which the piece holding the head waits for.
-        const bool wte_later = t->shadow && c == 0 && t->pieces.size() > 1 && t->chunk[0].n > 1 && t->chunk[0].off[0] == t->poff[P_WTE];
+        const bool wte_later = t->shadow && c == 0 && t->chunk[0].n > 1 && t->chunk[0].off[0] == t->poff[P_WTE];
         if (t->shadow) {
             DpRangeList first = t->chunk[c];
             if (wte_later) {
                 for (int q = 1; q < first.n; ++q) { first.off[q - 1] = first.off[q]; first.len[q - 1] = first.len[q]; }
                 --first.n;
             }
-            BMB_TRY(dp_round_ranges(first, t->shadow, t->params, t->st_x));
+            BMB_TRY(dp_round_ranges(first, t->shadow, t->params, alone, t->st_x));
         }
         BMB_CUDA(cudaEventRecord(t->ev_upd[c], t->st_x));
         t->upd_pending[c] = true;
+        tl_mark(t, step, t->st_x, "rounded copy done (exchange), chunk", c);
         if (wte_later) {
             DpRangeList wte;
             wte.n = 1; wte.off[0] = t->chunk[0].off[0]; wte.len[0] = t->chunk[0].len[0];
-            BMB_TRY(dp_round_ranges(wte, t->shadow, t->params, t->st_x));
+            BMB_TRY(dp_round_ranges(wte, t->shadow, t->params, /*alone=*/false, t->st_x));
         }
     }
     return BMB_OK;

@@ -684,8 +684,8 @@ def run_bmb(args):
         "config": config_dict(world, num_params),
         "notes": {"gradient_exchange": ("none" if world == 1 else "NCCL all-reduce, full optimiser per rank" if args.nccl_dp
                                         else ("fused over peer memory: piece-wise reduce, AdamW on the pieces, parameter broadcast; "
-                                              + ("one chunk after backward" if os.environ.get("BMB_TRAINER_OVERLAP") == "0" else
-                                                 "three chunks on a second stream, under backward and the next forward"))),
+                                              + {"1": "three chunks, reduced under backward", "2": "three chunks, under backward and the next forward"}.get(
+                                                  os.environ.get("BMB_TRAINER_OVERLAP", "0"), "one chunk after backward"))),
                   "l2": "per-step working set (~10 GB of activations) exceeds the 126 MB L2",
                   "arithmetic": "TF32 tensor-core GEMMs and attention, fp32 everywhere else" if math == bmb.MATH_TF32 else
                                 ("fp32 SIMT" if math == bmb.MATH_FP32 else "BF16 tensor-core GEMMs")},

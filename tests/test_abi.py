@@ -203,7 +203,8 @@ def test_registry_csv_feeds_the_reference_merge_tool(tmp_path):
 
 @pytest.mark.parametrize("L,E,V,maxT", [(12, 768, 50304, 1024), (1, 32, 96, 16), (2, 64, 128, 32), (3, 32, 96, 16), (5, 64, 256, 64)])
 def test_step_plan_chunks_partition_the_parameters_and_pieces_cover_the_step(bmb, L, E, V, maxT):
-    """The overlapped exchange's plan (host logic, no GPU): the three chunks are disjoint ranges that
+    """The overlapped exchange's plans (host logic, no GPU; 1 = reduces under backward, 2 = also updates under the
+    next forward): the three chunks are disjoint ranges that
     together cover every parameter exactly once and hold the layers they are named for; the pieces run
     every unit once, in order; a chunk's update is awaited by the first piece that reads its layers and
     its reduce follows the piece that writes the last of its gradients."""
@@ -213,7 +214,7 @@ def test_step_plan_chunks_partition_the_parameters_and_pieces_cover_the_step(bmb
     nranges, pieces, npieces = (C.c_int * 3)(), (C.c_int * 20)(), C.c_int(0)
     lib = bmb.lib()
     total = V * E + maxT * E + L * (2 * E + 3 * E * E + 3 * E + E * E + E + 2 * E + 4 * E * E + 4 * E + 4 * E * E + E) + 2 * E
-    for overlapped in (0, 1):
+    for overlapped in (0, 1, 2):
         assert lib.bmb_trainer_step_plan(C.byref(cfg), overlapped, ranges, nranges, pieces, C.byref(npieces)) == 0
         cover = np.zeros(total, dtype=np.int8)
         owner = np.full(total, -1, dtype=np.int8)
@@ -251,7 +252,9 @@ def test_step_plan_chunks_partition_the_parameters_and_pieces_cover_the_step(bmb
         for k in (0, 1, 2):
             if nranges[k] == 0:
                 continue
-            waits = [i for i, pc in enumerate(ps) if pc[2] == k]
+            # (mode 1: only the reduces are overlapped; the first piece waits for the last chunk's update, which the
+            #  exchange stream finishes after all the others)
+            waits = [i for i, pc in enumerate(ps) if pc[2] == k or (overlapped == 1 and pc[2] == 2)]
             reds = [i for i, pc in enumerate(ps) if pc[3] == k]
             assert waits and waits[0] <= first_use[k], (k, ps)
             assert len(reds) == 1 and reds[0] >= last_write[k], (k, ps)
