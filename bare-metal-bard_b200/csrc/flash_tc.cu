@@ -13,21 +13,22 @@
 //                    of its row from TMEM (tcgen05.ld), masks the diagonal,
 //                    updates the running max and sum (the scale rides in the
 //                    exponent's multiply-add), writes P = exp2(.) rounded to
-//                    TF32 back into tensor memory (tcgen05.st) and, after
-//                    handing P to the tensor core, folds the previous step's
-//                    P V into its output registers:
-//                    o = o * exp2(m_old - m_new) + PV;
+//                    TF32 back into tensor memory over the scores it took
+//                    (tcgen05.st) and hands it to the tensor core, which
+//                    accumulates O += P V in tensor memory.  The exponentials
+//                    are taken against a maximum that follows the running one
+//                    only in jumps of more than 2^8: O and the row sum are
+//                    rescaled (a tensor-memory round trip) only then, so most
+//                    steps never touch O;
 //                    the finished tile goes to shared memory and from there to global memory by TMA store
 //                    (a row per thread written straight to global memory costs one memory transaction per
 //                    row and instruction: 3 us per item);
 //   warp 8           producer: TMA loads of the two Q tiles, K blocks and V blocks into 2-deep rings;
-//   warps 9, 10      issuer of tile 0 / tile 1: S_t = Q_t K^T 64 keys (one half of the tile's 128-column S
-//                    buffer) at a time, each half as soon as the group has taken that half of the previous
-//                    block out of TMEM, two steps ahead of PV_t = P_t V (A operand read from tensor memory)
-//                    -- the order in which the group releases S halves and hands over P tiles, so an issuer
-//                    never waits behind an event that comes later, and the two tiles never wait for one
-//                    another (one issuer for both made them run in lockstep: each tile's next scores queued
-//                    behind the other tile's release).
+//   warps 9, 10      issuer of tile 0 / tile 1: O_t += P_t V of step e - 2 (A operand read from tensor memory),
+//                    then S_t = Q_t K^T of step e into the half of the tile's 128-column S buffer that P was
+//                    just read from (products of one thread retire in order).  It waits for P only, so the two
+//                    tiles never wait for one another (one issuer for both made them run in lockstep: each
+//                    tile's next scores queued behind the other tile's release).
 // V is the B operand of P V with the head dimension contiguous, i.e. MN-major:
 // its TMA map uses the 128-byte swizzle with 32-byte atoms.  K and Q are
 // K-major.  Keys beyond the end of a sequence are never seen unmasked: a key
@@ -48,8 +49,9 @@ using namespace tc;
 constexpr int HS = 64, QT = 128, NQ = 2, KB = 64, KBLK = 128, K_STAGES = 2, V_STAGES = 2;
 constexpr int Q_TILE_BYTES = QT * HS * 4;          // 32 KB: two halves of 128 rows x 128 B
 constexpr int KV_TILE_BYTES = KBLK * HS * 4;       // 32 KB: two halves / chunks of 128 rows x 128 B
-constexpr int TILE_COLS = 256;                     // TMEM columns per query tile: S (128) | P (64) | P V (64)
-constexpr int COL_P = 128, COL_PV = 192;
+constexpr int TILE_COLS = 256;                     // TMEM columns per query tile: S / P halves (2 x 64) | O (64) | unused (64)
+constexpr int COL_O = 128;
+constexpr float RESCALE_LOG2 = 8.0f;               // O and the row sum are rescaled only when the running maximum has grown by more than 2^8
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + NQ * Q_TILE_BYTES;
 constexpr int OFF_V = OFF_K + K_STAGES * KV_TILE_BYTES;
@@ -139,9 +141,11 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
-    // S_FULL / S_EMPTY: one pair per query tile and per 64-key half of the S buffer (index 2 * tile + half)
+    // S_FULL: one per query tile and per 64-key half of the S buffer (index 2 * tile + half); P_FULL: the group has
+    // written P over the half it took the scores from; PV_DONE: a P V product has retired (O is readable, the half
+    // may be overwritten); O_FREE: the group has taken the finished item's O out of tensor memory
     enum { Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = K_FULL + K_STAGES, V_FULL = K_EMPTY + K_STAGES, V_EMPTY = V_FULL + V_STAGES,
-           S_FULL = V_EMPTY + V_STAGES, S_EMPTY = S_FULL + 2 * NQ, P_FULL = S_EMPTY + 2 * NQ, PV_FULL = P_FULL + NQ, NBARS = PV_FULL + NQ };
+           S_FULL = V_EMPTY + V_STAGES, P_FULL = S_FULL + 2 * NQ, PV_DONE = P_FULL + NQ, O_FREE = PV_DONE + NQ, NBARS = O_FREE + NQ };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -157,8 +161,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), NQ); }
         for (int s = 0; s < V_STAGES; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), NQ); }
         for (int t = 0; t < NQ; ++t) {
-            for (int hf = 0; hf < 2; ++hf) { mbar_init(bar(S_FULL + 2 * t + hf), 1); mbar_init(bar(S_EMPTY + 2 * t + hf), 4); }
-            mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_FULL + t), 1);
+            for (int hf = 0; hf < 2; ++hf) mbar_init(bar(S_FULL + 2 * t + hf), 1);
+            mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_DONE + t), 1); mbar_init(bar(O_FREE + t), 4);
         }
         *giveup = 0;
         mbar_init_fence();
@@ -227,30 +231,47 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         // ------------------------------------- issuer of one query tile: S = Q K^T and O += P V
         if (lane == 0) {
             const int t = warp - 9;
-            // Q (K-major) x K (K-major), 64 keys at a time; P (tensor memory) x V (MN-major)
+            // Q (K-major) x K (K-major), 64 keys at a time; P (tensor memory) x V (MN-major), accumulated into O
             const uint32_t idesc_s = make_idesc(2, 0, 0, KB, QT), idesc_pv = make_idesc(2, 0, 1, HS, QT);
             const uint32_t qa = base + OFF_Q + t * Q_TILE_BYTES;
             const uint32_t s_tmem = tmem_base + (uint32_t)(t * TILE_COLS);
-            const uint32_t pa = s_tmem + COL_P, pvd = s_tmem + COL_PV;
+            const uint32_t od = s_tmem + COL_O;
             bool ok = true;
             KO_DECL();
             int kc = 0, vc = 0, pc = 0;                   // key blocks, value blocks, P tiles consumed so far (all items)
-            int sn0 = 0, sn1 = 0;                         // score products issued so far into each half of the S buffer
+            int items = 0;                                // items in which this tile had rows (all so far)
             for (int r = 0; ok && fwd_item(r, T, BH, nqblk, it); ++r) {
                 const int mine = t ? it.nstep[1] : it.nstep[0];
                 if (!mbar_wait(bar(Q_FULL), (uint32_t)(r & 1), giveup)) { ok = false; break; }
-                // Step e's scores are issued two steps ahead of step e - 2's P V.  Blocks past this tile's diagonal
-                // (the other tile still needs them) are only waited for and released, which keeps both issuers'
-                // releases of a ring slot in the same phase.
+                // P V of step e - 2, then the scores of step e: the scores go to the half that P of step e - 2 was read
+                // from, and products issued by one thread retire in order, so they land after that read.  Blocks past
+                // this tile's diagonal (the other tile still needs them) are only waited for and released, which keeps
+                // both issuers' releases of a ring slot in the same phase.
                 for (int e = 0; ok && e < it.maxstep + 2; ++e) {
+                    const int i = e - 2;
+                    if (i >= 0) {
+                        const int st = vc % V_STAGES;
+                        if (!(i & 1) && !mbar_wait(bar(V_FULL + st), (uint32_t)((vc / V_STAGES) & 1), giveup)) { ok = false; break; }
+                        if (i < mine) {
+                            if (!mbar_wait(bar(P_FULL + t), (uint32_t)(pc & 1), giveup)) { ok = false; break; }
+                            // the first product of an item overwrites O: the group must have taken the last item's O
+                            if (i == 0 && items > 0 && !mbar_wait(bar(O_FREE + t), (uint32_t)((items - 1) & 1), giveup)) { ok = false; break; }
+                            fence_after();
+                            // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
+                            const uint32_t va = base + OFF_V + st * KV_TILE_BYTES + (uint32_t)((i & 1) * (KB * 128));
+                            const uint32_t pa = s_tmem + (uint32_t)((i & 1) * KB);
+#pragma unroll
+                            for (int ks = 0; ks < KB / 8; ++ks)
+                                if (!KO(32)) mma_tf32_ts(od, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, (i > 0 || ks) ? 1u : 0u);
+                            commit(bar(PV_DONE + t));
+                            ++pc;
+                        }
+                        if ((i & 1) || i + 1 == it.maxstep) { commit(bar(V_EMPTY + st)); ++vc; }
+                    }
                     if (e < it.maxstep) {
                         const int st = kc % K_STAGES, hf = e & 1;
                         if (!hf && !mbar_wait(bar(K_FULL + st), (uint32_t)((kc / K_STAGES) & 1), giveup)) { ok = false; break; }
                         if (e < mine) {
-                            const int n = hf ? sn1 : sn0;
-                            // the group has taken the previous scores out of this half (also across items)
-                            if (n > 0 && !mbar_wait(bar(S_EMPTY + 2 * t + hf), (uint32_t)((n - 1) & 1), giveup)) { ok = false; break; }
-                            fence_after();
                             const uint32_t d = s_tmem + (uint32_t)(hf * KB);
                             const uint32_t kh = base + OFF_K + st * KV_TILE_BYTES + (uint32_t)(hf * (KB * 128));   // key rows 64 hf .. 64 hf + 63 of the block
 #pragma unroll
@@ -261,29 +282,12 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                                          smem_desc_kmajor(kh + half * (KBLK * 128) + off), idesc_s, ks ? 1u : 0u);
                             }
                             commit(bar(S_FULL + 2 * t + hf));
-                            if (hf) ++sn1; else ++sn0;
                         }
                         if (hf || e + 1 == it.maxstep) { commit(bar(K_EMPTY + st)); ++kc; }   // this tile's products that read the K block have been issued
                         if (e + 1 == it.maxstep) commit(bar(Q_EMPTY));                       // ... and all that read this item's Q tile
                     }
-                    const int i = e - 2;
-                    if (i >= 0) {
-                        const int st = vc % V_STAGES;
-                        if (!(i & 1) && !mbar_wait(bar(V_FULL + st), (uint32_t)((vc / V_STAGES) & 1), giveup)) { ok = false; break; }
-                        if (i < mine) {
-                            if (!mbar_wait(bar(P_FULL + t), (uint32_t)(pc & 1), giveup)) { ok = false; break; }
-                            fence_after();
-                            // P is read from tensor memory, where the softmax threads left it: 8 columns per K step
-                            const uint32_t va = base + OFF_V + st * KV_TILE_BYTES + (uint32_t)((i & 1) * (KB * 128));
-#pragma unroll
-                            for (int ks = 0; ks < KB / 8; ++ks)
-                                if (!KO(32)) mma_tf32_ts(pvd, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, ks ? 1u : 0u);
-                            commit(bar(PV_FULL + t));
-                            ++pc;
-                        }
-                        if ((i & 1) || i + 1 == it.maxstep) { commit(bar(V_EMPTY + st)); ++vc; }
-                    }
                 }
+                if (mine > 0) ++items;
             }
         }
     } else {
@@ -292,10 +296,10 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         const int rr = quad * 32 + lane;                // row inside the tile = TMEM lane
         KO_DECL();
         const uint32_t s_addr = tmem_base + (uint32_t)(t * TILE_COLS) + ((uint32_t)(quad * 32) << 16);
-        const uint32_t p_addr = s_addr + COL_P, pv_addr = s_addr + COL_PV;
+        const uint32_t o_addr = s_addr + COL_O;
         bool ok = true;
-        int sc[2] = {0, 0};                             // score halves taken so far, P tiles handed over so far (all items)
-        int pn = 0;
+        int sc[2] = {0, 0};                             // score halves taken so far (all items)
+        int pn = 0;                                     // P tiles handed over so far = P V products to expect (all items)
 #ifdef BMB_FLASH_TRACE
         const bool tracer = (warp == 0 && lane == 0);
         long long fw_s = 0, fw_pv = 0;
@@ -306,25 +310,19 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             const int b = it.bh / NH, h = it.bh % NH;
             const int tile_q0 = it.q0 + t * QT;
             const int qi = tile_q0 + rr;
-            float o[HS];
-#pragma unroll
-            for (int d = 0; d < HS; ++d) o[d] = 0.0f;
-            float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
+            // m is the maximum the exponentials are taken against; it follows the running maximum of the raw scores
+            // (the scale is positive, so the order is the same) only in jumps of more than 2^8, and O and l are
+            // rescaled only then: the output accumulates in tensor memory, and most steps never touch it.
+            float m = -INFINITY, l = 0.0f;
             for (int j = 0; j < nb; ++j) {
                 const int hf = j & 1;
-                // every step has its own half of the S buffer: wait for its product, take it, hand the half back
                 { FW_BEGIN(); if (!mbar_wait(bar(S_FULL + 2 * t + hf), (uint32_t)(sc[hf] & 1), giveup)) { ok = false; break; } FW_END(fw_s); }
                 FTR_IF(tracer && j == 0 && r < 5, 2 + 4 * r);
                 ++sc[hf];
                 fence_after();
                 float s[KB];
                 tmem_ld64(s_addr + (uint32_t)(hf * KB), s);
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(S_EMPTY + 2 * t + hf));       // this half may be overwritten
 
-                // m is the running maximum of the raw scores (the scale is positive, so the order is
-                // the same); the scale rides in the exponent's multiply-add.
                 const int k0 = j * KB;
                 if (k0 + KB - 1 > tile_q0) {                // the block touches the diagonal (warp-uniform)
 #pragma unroll
@@ -339,9 +337,27 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                         mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
                     }
                 }
-                const float m_new = fmax3(m, fmax3(mx0, mx1, s[KB - 2]), s[KB - 1]);   // finite: key 0 is visible to every row
-                const float mb = m_new * scale_log2e;
-                const float alpha = fast_exp2(fmaf(m, scale_log2e, -mb));
+                const float m_run = fmax3(m, fmax3(mx0, mx1, s[KB - 2]), s[KB - 1]);   // finite: key 0 is visible to every row
+                if (j == 0) {
+                    m = m_run;
+                } else {
+                    const bool grow = (m_run - m) * scale_log2e > RESCALE_LOG2;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        // O must be whole (the previous block's product retired) while it is rescaled; the next
+                        // product is not issued before this thread hands over P below.
+                        { FW_BEGIN(); if (!mbar_wait(bar(PV_DONE + t), (uint32_t)((pn - 1) & 1), giveup)) { ok = false; break; } FW_END(fw_pv); }
+                        fence_after();
+                        const float alpha = grow ? fast_exp2((m - m_run) * scale_log2e) : 1.0f;
+                        float o[HS];
+                        tmem_ld64(o_addr, o);
+#pragma unroll
+                        for (int d = 0; d < HS; ++d) o[d] *= alpha;
+                        tmem_st64(o_addr, o);
+                        l *= alpha;
+                        if (grow) m = m_run;
+                    }
+                }
+                const float mb = m * scale_log2e;
                 float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
                 for (int i = 0; i < KB; i += 2) {
@@ -353,50 +369,26 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     s[i] = round_tf32_for_mma(p0);
                     s[i + 1] = round_tf32_for_mma(p1);
                 }
-                l = l * alpha + (sum0 + sum1);
-                m = m_new;
-
-                if (j > 0) {
-                    // P V of the previous block is complete: the P buffer is free and PV readable.
-                    { FW_BEGIN(); if (!mbar_wait(bar(PV_FULL + t), (uint32_t)((pn - 1) & 1), giveup)) { ok = false; break; } FW_END(fw_pv); }
-                    fence_after();
-                }
-                // P row -> this thread's lane of tensor memory, the A operand of P V
-                if (!KO(8)) tmem_st64(p_addr, s);
-                // The previous block's P V must be out of TMEM before the next product may overwrite it;
-                // its fold into the output registers then runs while the tensor core works on this block.
-                if (j > 0 && !KO(2)) {
-                    float v0[32], v1[32];
-                    tmem_ld32_nowait(pv_addr, v0);
-                    tmem_ld32_nowait(pv_addr + 32, v1);
-                    tmem_wait_ld();
-                    fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(P_FULL + t));
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) { o[i] = fmaf(o[i], alpha_prev, v0[i]); o[32 + i] = fmaf(o[32 + i], alpha_prev, v1[i]); }
-                } else {
-                    fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(P_FULL + t));
-                }
+                l += sum0 + sum1;
+                // P row -> over the scores it came from, in this thread's lane of tensor memory: the A operand of P V
+                if (!KO(8)) tmem_st64(s_addr + (uint32_t)(hf * KB), s);
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(P_FULL + t));
                 ++pn;
-                alpha_prev = alpha;
             }
             FTR_IF(tracer && r < 5, 3 + 4 * r);
-            if (ok && !mbar_wait(bar(PV_FULL + t), (uint32_t)((pn - 1) & 1), giveup)) ok = false;
+            // The last two products may both be in flight (the scores this thread waited for last were issued before
+            // them): wait for them in order, a parity wait must never be two phases behind.
+            if (ok && nb > 1 && !mbar_wait(bar(PV_DONE + t), (uint32_t)((pn - 2) & 1), giveup)) ok = false;
+            if (ok && !mbar_wait(bar(PV_DONE + t), (uint32_t)((pn - 1) & 1), giveup)) ok = false;
             if (!group_all(t, ok)) { ok = false; break; }
             fence_after();
-            {
-                float v[32];
-                tmem_ld32(pv_addr, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha_prev, v[i]);
-                tmem_ld32(pv_addr + 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], alpha_prev, v[i]);
-            }
-            fence_before();                              // the next item's first P V may overwrite the accumulator
+            float o[HS];
+            tmem_ld64(o_addr, o);
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O_FREE + t));     // the next item's first product may overwrite O
             {
                 // The tile leaves through shared memory, 32 columns at a time: a thread writes its row's 128 bytes with
                 // the 16-byte pieces permuted as the store's 128-byte swizzle expects (which also spreads the warp's
