@@ -141,11 +141,14 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(gen + OFF_BAR);
-    // S_FULL: one per query tile and per 64-key half of the S buffer (index 2 * tile + half); P_FULL: the group has
-    // written P over the half it took the scores from; PV_DONE: a P V product has retired (O is readable, the half
-    // may be overwritten); O_FREE: the group has taken the finished item's O out of tensor memory
+    // One barrier per query tile and per 64-key half of the S buffer (index 2 * tile + half) for each of: S_FULL (the
+    // scores are in the half), P_FULL (the group has written P over them), PV_DONE (the P V product that read the half
+    // has retired).  Per half, because a parity wait tells the last phase from the one before only: the group may
+    // be two steps ahead of the P V issue (both halves' scores are there before the first P V), and a thread that has
+    // not waited for a while may be two products behind -- on one barrier for both halves either would alias.
+    // O_FREE: the group has taken the finished item's O out of tensor memory
     enum { Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = K_FULL + K_STAGES, V_FULL = K_EMPTY + K_STAGES, V_EMPTY = V_FULL + V_STAGES,
-           S_FULL = V_EMPTY + V_STAGES, P_FULL = S_FULL + 2 * NQ, PV_DONE = P_FULL + NQ, O_FREE = PV_DONE + NQ, NBARS = O_FREE + NQ };
+           S_FULL = V_EMPTY + V_STAGES, P_FULL = S_FULL + 2 * NQ, PV_DONE = P_FULL + 2 * NQ, O_FREE = PV_DONE + 2 * NQ, NBARS = O_FREE + NQ };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     volatile int *giveup = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -162,7 +165,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         for (int s = 0; s < V_STAGES; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), NQ); }
         for (int t = 0; t < NQ; ++t) {
             for (int hf = 0; hf < 2; ++hf) mbar_init(bar(S_FULL + 2 * t + hf), 1);
-            mbar_init(bar(P_FULL + t), 4); mbar_init(bar(PV_DONE + t), 1); mbar_init(bar(O_FREE + t), 4);
+            mbar_init(bar(O_FREE + t), 4);
+            for (int hf = 0; hf < 2; ++hf) { mbar_init(bar(P_FULL + 2 * t + hf), 4); mbar_init(bar(PV_DONE + 2 * t + hf), 1); }
         }
         *giveup = 0;
         mbar_init_fence();
@@ -238,7 +242,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             const uint32_t od = s_tmem + COL_O;
             bool ok = true;
             KO_DECL();
-            int kc = 0, vc = 0, pc = 0;                   // key blocks, value blocks, P tiles consumed so far (all items)
+            int kc = 0, vc = 0;                           // key blocks, value blocks consumed so far (all items)
+            int pc[2] = {0, 0};                           // P tiles consumed so far from each half (all items)
             int items = 0;                                // items in which this tile had rows (all so far)
             for (int r = 0; ok && fwd_item(r, T, BH, nqblk, it); ++r) {
                 const int mine = t ? it.nstep[1] : it.nstep[0];
@@ -253,7 +258,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                         const int st = vc % V_STAGES;
                         if (!(i & 1) && !mbar_wait(bar(V_FULL + st), (uint32_t)((vc / V_STAGES) & 1), giveup)) { ok = false; break; }
                         if (i < mine) {
-                            if (!mbar_wait(bar(P_FULL + t), (uint32_t)(pc & 1), giveup)) { ok = false; break; }
+                            if (!mbar_wait(bar(P_FULL + 2 * t + (i & 1)), (uint32_t)(pc[i & 1] & 1), giveup)) { ok = false; break; }
                             // the first product of an item overwrites O: the group must have taken the last item's O
                             if (i == 0 && items > 0 && !mbar_wait(bar(O_FREE + t), (uint32_t)((items - 1) & 1), giveup)) { ok = false; break; }
                             fence_after();
@@ -263,8 +268,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
 #pragma unroll
                             for (int ks = 0; ks < KB / 8; ++ks)
                                 if (!KO(32)) mma_tf32_ts(od, pa + (uint32_t)(ks * 8), smem_desc_mnmajor32(va + ks * 1024, KBLK * 128), idesc_pv, (i > 0 || ks) ? 1u : 0u);
-                            commit(bar(PV_DONE + t));
-                            ++pc;
+                            commit(bar(PV_DONE + 2 * t + (i & 1)));
+                            ++pc[i & 1];
                         }
                         if ((i & 1) || i + 1 == it.maxstep) { commit(bar(V_EMPTY + st)); ++vc; }
                     }
@@ -299,7 +304,7 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
         const uint32_t o_addr = s_addr + COL_O;
         bool ok = true;
         int sc[2] = {0, 0};                             // score halves taken so far (all items)
-        int pn = 0;                                     // P tiles handed over so far = P V products to expect (all items)
+        int pn[2] = {0, 0};                             // P tiles handed over so far from each half = P V products to expect (all items)
 #ifdef BMB_FLASH_TRACE
         const bool tracer = (warp == 0 && lane == 0);
         long long fw_s = 0, fw_pv = 0;
@@ -345,7 +350,8 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                     if (__any_sync(0xffffffffu, grow)) {
                         // O must be whole (the previous block's product retired) while it is rescaled; the next
                         // product is not issued before this thread hands over P below.
-                        { FW_BEGIN(); if (!mbar_wait(bar(PV_DONE + t), (uint32_t)((pn - 1) & 1), giveup)) { ok = false; break; } FW_END(fw_pv); }
+                        // (the product before it on that half has retired: the scores this step waited for were issued after it)
+                        { FW_BEGIN(); if (!mbar_wait(bar(PV_DONE + 2 * t + (hf ^ 1)), (uint32_t)((pn[hf ^ 1] - 1) & 1), giveup)) { ok = false; break; } FW_END(fw_pv); }
                         fence_after();
                         const float alpha = grow ? fast_exp2((m - m_run) * scale_log2e) : 1.0f;
                         float o[HS];
@@ -374,14 +380,14 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                 if (!KO(8)) tmem_st64(s_addr + (uint32_t)(hf * KB), s);
                 fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(P_FULL + t));
-                ++pn;
+                if (lane == 0) mbar_arrive(bar(P_FULL + 2 * t + hf));
+                ++pn[hf];
             }
             FTR_IF(tracer && r < 5, 3 + 4 * r);
             // The last two products may both be in flight (the scores this thread waited for last were issued before
-            // them): wait for them in order, a parity wait must never be two phases behind.
-            if (ok && nb > 1 && !mbar_wait(bar(PV_DONE + t), (uint32_t)((pn - 2) & 1), giveup)) ok = false;
-            if (ok && !mbar_wait(bar(PV_DONE + t), (uint32_t)((pn - 1) & 1), giveup)) ok = false;
+            // them); the ones before have retired.
+            if (ok && nb > 1 && !mbar_wait(bar(PV_DONE + 2 * t + (nb & 1)), (uint32_t)((pn[nb & 1] - 1) & 1), giveup)) ok = false;
+            if (ok && !mbar_wait(bar(PV_DONE + 2 * t + ((nb - 1) & 1)), (uint32_t)((pn[(nb - 1) & 1] - 1) & 1), giveup)) ok = false;
             if (!group_all(t, ok)) { ok = false; break; }
             fence_after();
             float o[HS];
@@ -495,7 +501,9 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
     const float scale_log2e = (1.0f / sqrtf((float)HS)) * 1.4426950408889634f;
     const int nqblk = (T + NQ * QT - 1) / (NQ * QT);
     const long long items = (long long)B * NH * nqblk;
-    const int grid = (int)(items < sm_count() ? items : sm_count());       // persistent: one CTA per SM
+    int grid = (int)(items < sm_count() ? items : sm_count());             // persistent: one CTA per SM
+    // BMB_FLASH_FWD_CTAS=n caps the grid, so that small problems also exercise CTAs that walk several work items (tests)
+    if (const char *e = getenv("BMB_FLASH_FWD_CTAS")) { const int cap = atoi(e); if (cap >= 1 && cap < grid) grid = cap; }
     flash_fwd_tc_k<<<grid, FWD_THREADS, FWD_SMEM, st>>>(mapQK, mapV, mapO, lse, T, NH, B * NH, nqblk, scale_log2e,
                                                         emit_rounded() ? 1 : 0, status_dev);
     count_launch();

@@ -222,6 +222,29 @@ def test_tensorcore_flash_forward_vs_oracle(bmb, orc, cuda, B, T, C, NH):
     assert e_out < 2e-3 and e_lse < 1e-3, (e_out, e_lse)
 
 
+@pytest.mark.parametrize("B,T,C,NH,ctas", [(1, 640, 64, 1, 1), (1, 1024, 64, 1, 1), (1, 640, 192, 3, 2), (1, 896, 64, 1, 1),
+                                           (2, 1000, 192, 3, 4), (3, 300, 128, 2, 3)])
+def test_tensorcore_flash_forward_walks_several_items_per_cta(bmb, orc, cuda, monkeypatch, B, T, C, NH, ctas):
+    """The forward kernel is persistent: a CTA walks several (head, 256-query) work items, and its warps carry ring
+    positions and barrier phases from one item to the next.  At test sizes every CTA gets one item, so the grid is
+    capped (BMB_FLASH_FWD_CTAS) to make a few CTAs walk all of them -- including items whose second query tile is
+    empty (T = 640, 896, 300), long items followed by short ones, and odd step counts.  Same bars as the one-item
+    test; a wrong phase shows as a bounded wait that runs out (BMB_E_TIMEOUT) or as non-finite output."""
+    from helpers import normal
+    monkeypatch.setenv("BMB_FLASH_FWD_CTAS", str(ctas))
+    qkv = normal(B * T * 3 * C, 4321)
+    wout, wlse = np.empty(B * T * C, np.float32), np.empty(B * NH * T, np.float32)
+    orc.orc_attention_forward(_np(wout), _np(wlse), None, _np(qkv), B, T, C, NH)
+    dq = dev(cuda, qkv)
+    out = cuda.full((B * T * C,), float("nan"), device="cuda")
+    lse = cuda.full((B * NH * T,), float("nan"), device="cuda")
+    bmb.call("bmb_flash_attention_forward_cfg", 2, out, lse, dq, B, T, C, NH)
+    got_out, got_lse = host(cuda, out), host(cuda, lse)
+    assert np.all(np.isfinite(got_out)) and np.all(np.isfinite(got_lse))
+    e_out, e_lse = normwise(got_out, wout), normwise(got_lse, wlse)
+    assert e_out < 2e-3 and e_lse < 1e-3, (e_out, e_lse)
+
+
 @pytest.mark.parametrize("B,T,C,NH", ATT_SHAPES)
 def test_tensorcore_flash_backward_vs_oracle(bmb, orc, cuda, B, T, C, NH):
     """Backward config 2 (tcgen05 dQ and dK/dV kernels) against the fp32 oracle:
