@@ -45,6 +45,27 @@ cudaStream_t cur_stream();
 bool emit_rounded();
 void set_emit_rounded(bool on);
 
+// ---- deferred column sums --------------------------------------------------
+// The parameter-gradient sums of the backward kernels are two-stage: a kernel leaves G partial rows, a small
+// launch adds them up in a fixed order.  While a collector is installed for the calling thread, those kernels take
+// their partial rows from the collector's arena (instead of the shared per-device scratch, which the next call
+// would overwrite) and only note the final sum as a job; one batched launch at the end of the backward pass then
+// does all of them -- the same sums in the same order, a few dozen launches fewer.
+struct ColumnAddJob {
+    float *dst, *dst2, *dst3;     // as launch_column_add: columns [ncols_first, ..) go to dst2, from 2 * ncols_first on to dst3
+    const float *partial;
+    int ncols_first, G, ncols;
+};
+struct ColumnAddCollector {
+    float *arena = nullptr;       // device memory for the partial rows of one backward pass
+    size_t cap = 0, used = 0;     // floats
+    ColumnAddJob *jobs = nullptr; // host array, filled while `record` is set (the job list is the same every pass)
+    int max_jobs = 0, njobs = 0, max_cols = 0;
+    bool record = false;
+};
+void set_column_add_collector(ColumnAddCollector *c);      // nullptr: sums are finished by their own launches again
+int launch_column_add_jobs(const ColumnAddJob *jobs_dev, int njobs, int max_cols, cudaStream_t st);
+
 // ---- data-parallel exchange: a list of ranges of a flat float buffer ------
 // (offsets and lengths in floats, each a multiple of 4)
 constexpr int DP_MAX_RANGES = 16;

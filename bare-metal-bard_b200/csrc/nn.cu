@@ -295,12 +295,11 @@ __global__ void layernorm_bwd_block_k(float *__restrict__ dinp, float *__restric
 // covers 32 columns, its 32 warps each sum every 32nd row of `partial`, and the 32
 // sub-sums are added in warp order.  If dst2 != nullptr the columns
 // [ncols_first, ncols) go to dst2; if dst3 != nullptr those from 2 * ncols_first on go to dst3.
-__global__ void __launch_bounds__(1024)
-column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
-             const float *__restrict__ partial, int G, int ncols, float *__restrict__ dst3 = nullptr) {
-    __shared__ float red[32][33];
+__device__ __forceinline__ void column_add_body(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
+                                                const float *__restrict__ partial, int G, int ncols, float *__restrict__ dst3,
+                                                int block_x, float (*red)[33]) {
     const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cx;
+    const int c = block_x * 32 + cx;
     // 32 warps share the G rows; four loads are in flight per thread before the first add
     float s = 0.0f;
     if (c < ncols) {
@@ -322,6 +321,19 @@ column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
         else if (dst2 && c >= ncols_first) dst2[c - ncols_first] += t;
         else dst[c] += t;
     }
+}
+__global__ void __launch_bounds__(1024)
+column_add_k(float *__restrict__ dst, float *__restrict__ dst2, int ncols_first,
+             const float *__restrict__ partial, int G, int ncols, float *__restrict__ dst3 = nullptr) {
+    __shared__ float red[32][33];
+    column_add_body(dst, dst2, ncols_first, partial, G, ncols, dst3, (int)blockIdx.x, red);
+}
+// The same sum for a list of jobs (blockIdx.y), each over its own partial rows.
+__global__ void __launch_bounds__(1024) column_add_jobs_k(const ColumnAddJob *__restrict__ jobs) {
+    __shared__ float red[32][33];
+    const ColumnAddJob j = jobs[blockIdx.y];
+    if ((int)blockIdx.x * 32 >= j.ncols) return;          // (uniform per block)
+    column_add_body(j.dst, j.dst2, j.ncols_first, j.partial, j.G, j.ncols, j.dst3, (int)blockIdx.x, red);
 }
 
 // --------------------------------------------------------------------- gelu
@@ -728,6 +740,37 @@ bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
 
+static thread_local ColumnAddCollector *g_collector = nullptr;
+void set_column_add_collector(ColumnAddCollector *c) { g_collector = c; }
+int launch_column_add_jobs(const ColumnAddJob *jobs_dev, int njobs, int max_cols, cudaStream_t st) {
+    if (njobs <= 0) return BMB_OK;
+    column_add_jobs_k<<<dim3(ceil_div(max_cols, 32), njobs), 1024, 0, st>>>(jobs_dev);
+    count_launch();
+    BMB_LAUNCH_CHECK();
+    return BMB_OK;
+}
+namespace {
+// Partial rows for a two-stage sum: from the installed collector's arena, else from the per-device scratch.
+// *deferred says which; a full arena or job list falls back to the scratch (and an immediate sum) for that call.
+float *partial_rows(size_t floats, bool *deferred) {
+    ColumnAddCollector *cc = g_collector;
+    *deferred = false;
+    if (cc && cc->njobs < cc->max_jobs) {
+        const size_t need = (floats + 3) & ~(size_t)3;
+        if (cc->used + need <= cc->cap) {
+            float *p = cc->arena + cc->used;
+            cc->used += need;
+            *deferred = true;
+            return p;
+        }
+    }
+    return (float *)device_scratch(SCR_REDUCE, floats * sizeof(float));
+}
+// Finish a two-stage sum now, or note it for the batched launch.
+int finish_column_sum(bool deferred, float *dst, float *dst2, int ncols_first, const float *partial, int G, int ncols,
+                      cudaStream_t st, float *dst3 = nullptr);
+}  // namespace
+
 // Shared with other translation units of the library.
 int launch_column_add(float *dst, float *dst2, int ncols_first, const float *partial, int G,
                       int ncols, cudaStream_t st, float *dst3 = nullptr) {
@@ -736,6 +779,18 @@ int launch_column_add(float *dst, float *dst2, int ncols_first, const float *par
     BMB_LAUNCH_CHECK();
     return BMB_OK;
 }
+
+namespace {
+int finish_column_sum(bool deferred, float *dst, float *dst2, int ncols_first, const float *partial, int G, int ncols,
+                      cudaStream_t st, float *dst3) {
+    if (!deferred) return launch_column_add(dst, dst2, ncols_first, partial, G, ncols, st, dst3);
+    ColumnAddCollector *cc = g_collector;
+    if (cc->record) cc->jobs[cc->njobs] = ColumnAddJob{dst, dst2, dst3, partial, ncols_first, G, ncols};
+    cc->njobs++;
+    if (ncols > cc->max_cols) cc->max_cols = ncols;
+    return BMB_OK;
+}
+}  // namespace
 
 // Layernorm backward with the scratch supplied by the caller: `partial` holds
 // at least layernorm_bwd_blocks(N) * 2 * C floats.
@@ -749,7 +804,7 @@ int layernorm_bwd_blocks(int N) {
 int layernorm_backward_with_scratch(float *dinp, float *dweight, float *dbias, const float *dout,
                                     const float *inp, const float *weight, const float *mean,
                                     const float *rstd, int N, int C, float *partial, int G,
-                                    cudaStream_t st, float *dcolsum = nullptr) {
+                                    cudaStream_t st, float *dcolsum = nullptr, bool deferred = false) {
     const int rnd = emit_rounded() ? 1 : 0;
     // registers follow the row length: V4 float4 per lane cover C <= 128 * V4
 #define BMB_LN_BWD(V4_)                                                                                                   \
@@ -764,7 +819,7 @@ int layernorm_backward_with_scratch(float *dinp, float *dweight, float *dbias, c
 #undef BMB_LN_BWD
     count_launch();
     BMB_LAUNCH_CHECK();
-    return launch_column_add(dweight, dbias, C, partial, G, (dcolsum ? 3 : 2) * C, st, dcolsum);
+    return finish_column_sum(deferred, dweight, dbias, C, partial, G, (dcolsum ? 3 : 2) * C, st, dcolsum);
 }
 
 }  // namespace bmb
@@ -860,9 +915,10 @@ int bmb_layernorm_backward_colsum(float *dinp, float *dweight, float *dbias, flo
         return dcolsum ? bmb_bias_backward(dcolsum, dinp, N, C) : BMB_OK;
     }
     const int G = layernorm_bwd_blocks(N);
-    float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)G * 3 * C * sizeof(float));
+    bool deferred = false;
+    float *partial = partial_rows((size_t)G * 3 * C, &deferred);
     if (!partial) return BMB_E_CUDA;
-    return layernorm_backward_with_scratch(dinp, dweight, dbias, dout, inp, weight, mean, rstd, N, C, partial, G, st, dcolsum);
+    return layernorm_backward_with_scratch(dinp, dweight, dbias, dout, inp, weight, mean, rstd, N, C, partial, G, st, dcolsum, deferred);
 }
 
 int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias, const float *dout,
@@ -874,10 +930,11 @@ int bmb_layernorm_backward(float *dinp, float *dweight, float *dbias, const floa
                       aligned16(dout) && aligned16(weight);
     if (fast) {
         const int G = layernorm_bwd_blocks(N);
-        float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)G * 2 * C * sizeof(float));
+        bool deferred = false;
+        float *partial = partial_rows((size_t)G * 2 * C, &deferred);
         if (!partial) return BMB_E_CUDA;
         return layernorm_backward_with_scratch(dinp, dweight, dbias, dout, inp, weight, mean, rstd, N,
-                                               C, partial, G, st);
+                                               C, partial, G, st, nullptr, deferred);
     }
     const int parts = 32;
     float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)parts * 2 * C * sizeof(float));
@@ -968,12 +1025,13 @@ int bmb_gelu_backward_colsum(float *dinp, float *dcolsum, const float *inp, cons
     int gy = (4 * sm_count()) / strips;
     if (gy < 1) gy = 1;
     if (gy > N) gy = N;
-    float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)gy * C * sizeof(float));
+    bool deferred = false;
+    float *partial = partial_rows((size_t)gy * C, &deferred);
     if (!partial) return BMB_E_CUDA;
     gelu_bwd_colsum_k<<<dim3(strips, gy), 256, 0, st>>>(partial, dinp, inp, dout, N, C, emit_rounded() ? 1 : 0);
     count_launch();
     BMB_LAUNCH_CHECK();
-    return launch_column_add(dcolsum, nullptr, C, partial, gy, C, st);
+    return finish_column_sum(deferred, dcolsum, nullptr, C, partial, gy, C, st);
 }
 int bmb_residual_forward(float *out, const float *a, const float *b, int n) {
     if (n % 4) return fail(BMB_E_ARG, "residual_forward: n=%d must be a multiple of 4", n);
@@ -1005,12 +1063,13 @@ int bmb_bias_backward(float *dbias, const float *dout, int N, int C) {
         int gy = (2 * sm_count()) / strips;
         if (gy < 1) gy = 1;
         if (gy > N) gy = N;
-        float *partial = (float *)device_scratch(SCR_REDUCE, (size_t)gy * C * sizeof(float));
+        bool deferred = false;
+        float *partial = partial_rows((size_t)gy * C, &deferred);
         if (!partial) return BMB_E_CUDA;
         bias_bwd_partial_k<<<dim3(strips, gy), 256, 0, st>>>(partial, dout, N, C);
         count_launch();
         BMB_LAUNCH_CHECK();
-        return launch_column_add(dbias, nullptr, C, partial, gy, C, st);
+        return finish_column_sum(deferred, dbias, nullptr, C, partial, gy, C, st);
     }
     bias_bwd_scalar_k<<<C, 256, 0, st>>>(dbias, dout, N, C);
     count_launch();

@@ -110,6 +110,16 @@ struct bmb_trainer {
     // default: measured at the 124M shapes the product gets 37 us slower (its epilogue is no longer hidden behind
     // the next tile's main loop) for the 35 us pass it saves.
     bool fuse_gelu = false;
+    // Deferred column sums (single-piece steps): the backward kernels' partial rows go to this arena and one batched
+    // launch at the end of backward finishes all the parameter-gradient sums (BMB_TRAINER_DEFER_COLSUMS=0: each
+    // sum by a launch of its own, right after its kernel).
+    bool defer_colsums = true;
+    ColumnAddCollector col;
+    std::vector<ColumnAddJob> col_jobs_host;
+    ColumnAddJob *col_jobs_dev = nullptr;
+    bool col_jobs_uploaded = false, col_active = false;
+    int col_njobs = 0, col_max_cols = 0;
+    bool unit_span_whole = false;         // the units being run cover the whole backward pass (set by run_units)
     // profiling
     bool prof = false;
     std::vector<cudaEvent_t> ev;
@@ -316,9 +326,26 @@ int dx_dw(bmb_trainer *t, const Dims &d, int xflags, int Mx, int Nx, int Kx, con
     return BMB_OK;
 }
 
+// Whether `st` is being captured into a graph.
+bool stream_capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) { cudaGetLastError(); return false; }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
 int bwd_head(bmb_trainer *t, const Dims &d) {
     const int N = d.N, C = d.C, L = d.L, Vp = d.Vp;
     float *G = d.G;
+    // Column sums are deferred to one launch at the end of backward when the whole step is one piece (nothing
+    // reads a gradient before the embedding's backward is done).  The job list is recorded during the first such
+    // pass, which is never a captured one, and uploaded then.
+    t->col_active = t->defer_colsums && t->col.arena && t->pieces.size() <= 1 && t->unit_span_whole &&
+                    (t->col_jobs_uploaded || !stream_capturing(t->st));
+    if (t->col_active) {
+        t->col.used = 0; t->col.njobs = 0; t->col.max_cols = 0;
+        t->col.record = !t->col_jobs_uploaded;
+        set_column_add_collector(&t->col);
+    }
     BMB_CUDA(cudaMemsetAsync(G, 0, t->num_params * sizeof(float), t->st));
     BMB_TRY(dx(t, d, d.wflag, N, C, Vp, t->dlogits, P_WTE, 0, t->dlnf));
     BMB_TRY(mm(t, d.gflag, 1, 0, Vp, C, N, t->dlogits, t->lnf, 1.0f, G + t->poff[P_WTE]));
@@ -371,7 +398,19 @@ int bwd_layer(bmb_trainer *t, const Dims &d, int l) {
 }
 
 int bwd_embed(bmb_trainer *t, const Dims &d) {
-    return bmb_encoder_backward(d.G + t->poff[P_WTE], d.G + t->poff[P_WPE], t->dres, t->d_tokens, d.B, d.T, d.C);
+    BMB_TRY(bmb_encoder_backward(d.G + t->poff[P_WTE], d.G + t->poff[P_WPE], t->dres, t->d_tokens, d.B, d.T, d.C));
+    if (!t->col_active) return BMB_OK;
+    set_column_add_collector(nullptr);
+    t->col_active = false;
+    if (!t->col_jobs_uploaded) {
+        BMB_CUDA(cudaMemcpyAsync(t->col_jobs_dev, t->col_jobs_host.data(), (size_t)t->col.njobs * sizeof(ColumnAddJob),
+                                 cudaMemcpyHostToDevice, t->st));
+        BMB_CUDA(cudaStreamSynchronize(t->st));          // (once per trainer: the host list may not change under the copy)
+        t->col_jobs_uploaded = true;
+        t->col_njobs = t->col.njobs;
+        t->col_max_cols = t->col.max_cols;
+    }
+    return launch_column_add_jobs(t->col_jobs_dev, t->col_njobs, t->col_max_cols, t->st);
 }
 
 // The units of a pass, in execution order: 0 embedding; 1 .. L the layers; L+1 the head with the loss;
@@ -381,15 +420,18 @@ int run_units(bmb_trainer *t, int u0, int u1, bool with_loss = true) {
     const Dims d = dims_of(t);
     const int L = d.L;
     set_emit_rounded(d.fz);
-    for (int u = u0; u < u1; ++u) {
-        if (u == 0) BMB_TRY(fwd_embed(t, d));
-        else if (u <= L) BMB_TRY(fwd_layer(t, d, u - 1));
-        else if (u == L + 1) BMB_TRY(fwd_head(t, d, with_loss));
-        else if (u == L + 2) BMB_TRY(bwd_head(t, d));
-        else if (u <= 2 * L + 2) BMB_TRY(bwd_layer(t, d, 2 * L + 2 - u));
-        else BMB_TRY(bwd_embed(t, d));
+    t->unit_span_whole = (u0 <= L + 2 && u1 == num_units(t));      // head backward .. embedding backward in this call
+    int rc = BMB_OK;
+    for (int u = u0; u < u1 && rc == BMB_OK; ++u) {
+        if (u == 0) rc = fwd_embed(t, d);
+        else if (u <= L) rc = fwd_layer(t, d, u - 1);
+        else if (u == L + 1) rc = fwd_head(t, d, with_loss);
+        else if (u == L + 2) rc = bwd_head(t, d);
+        else if (u <= 2 * L + 2) rc = bwd_layer(t, d, 2 * L + 2 - u);
+        else rc = bwd_embed(t, d);
     }
-    return BMB_OK;
+    if (t->col_active) { set_column_add_collector(nullptr); t->col_active = false; }    // (only after a failure part-way)
+    return rc;
 }
 int forward(bmb_trainer *t, bool with_loss = true) { return run_units(t, 0, t->c.n_layer + 2, with_loss); }
 int backward(bmb_trainer *t) { return run_units(t, t->c.n_layer + 2, num_units(t)); }
@@ -593,6 +635,7 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     if (const char *e = getenv("BMB_TRAINER_OVERLAP")) { const int v = atoi(e); t->overlap = v < 0 ? 0 : (v > 2 ? 2 : v); }
     if (const char *e = getenv("BMB_TRAINER_FUSE_GELU")) t->fuse_gelu = atoi(e) != 0;
     if (const char *e = getenv("BMB_TRAINER_TIMELINE")) t->tl_step = atoi(e);
+    if (const char *e = getenv("BMB_TRAINER_DEFER_COLSUMS")) t->defer_colsums = atoi(e) != 0;
     {
         // The exchange stream outranks the main stream: its small kernels (barrier collectives, piece-wise reduce
         // and update) must get the SMs that free up between two of the main stream's GPU-filling kernels, or they
@@ -659,6 +702,17 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     BMB_CUDA(cudaMalloc(&t->bacts, t->num_bacts * sizeof(float)));
     layout_bwd(t->bacts);
 
+    if (t->defer_colsums) {
+        // partial rows of one backward pass: per layer two layernorm backwards (3C columns), the GELU backward (4C) and
+        // the qkv bias (3C), each at most 4 rows per SM; the final layernorm; a job each (+ a few spare)
+        const size_t rows = 4 * (size_t)sm_count();
+        t->col.cap = ((size_t)L * (2 * 3 * C + 4 * C + 3 * C) + 3 * C) * rows + 64 * (4 * L + 8);
+        t->col.max_jobs = 4 * (int)L + 8;
+        BMB_CUDA(cudaMalloc(&t->col.arena, t->col.cap * sizeof(float)));
+        BMB_CUDA(cudaMalloc(&t->col_jobs_dev, t->col.max_jobs * sizeof(ColumnAddJob)));
+        t->col_jobs_host.resize(t->col.max_jobs);
+        t->col.jobs = t->col_jobs_host.data();
+    }
     BMB_CUDA(cudaMalloc(&t->d_tokens, BT * sizeof(int)));
     BMB_CUDA(cudaMalloc(&t->d_targets, BT * sizeof(int)));
     BMB_CUDA(cudaMemset(t->d_tokens, 0, BT * sizeof(int)));
@@ -718,6 +772,8 @@ int bmb_trainer_destroy(bmb_trainer *t) {
     cudaFree(t->acts); cudaFree(t->bacts); cudaFree(t->d_tokens); cudaFree(t->d_targets);
     cudaFree(t->d_loss); cudaFree(t->d_sumsq); cudaFree(t->d_token);
     if (t->gen_probs) cudaFree(t->gen_probs);
+    if (t->col.arena) cudaFree(t->col.arena);
+    if (t->col_jobs_dev) cudaFree(t->col_jobs_dev);
     dp_fused_destroy(t->dp);
     if (t->ev_fork) cudaEventDestroy(t->ev_fork);
     if (t->ev_join) cudaEventDestroy(t->ev_join);
