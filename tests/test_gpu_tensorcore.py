@@ -424,3 +424,29 @@ def test_two_streams_take_turns_on_the_staging_scratch(bmb, cuda):
     for i in range(2):
         for it in range(8):
             assert np.array_equal(host(cuda, outs[i][it]), alone[i]), (i, it)
+
+
+def test_deferred_column_sums_equal_a_launch_per_sum(bmb, cuda, monkeypatch):
+    """The trainer defers the final stage of the two-stage parameter-gradient sums (layernorm gains and biases,
+    projection biases) to one batched launch at the end of backward.  The batched kernel adds the same partial rows
+    in the same order, so in fp32 arithmetic (no tile of a product shared between CTAs) every gradient except the
+    token embedding's (atomic adds at colliding tokens) must come out bit for bit as with a launch per sum."""
+    cfg = dict(TINY, n_layer=3)
+    rng = np.random.default_rng(5)
+    toks = rng.integers(0, cfg["vocab_size"], (cfg["B"], cfg["T"]), dtype=np.int32)
+    tgts = rng.integers(0, cfg["vocab_size"], (cfg["B"], cfg["T"]), dtype=np.int32)
+    grads = []
+    for mode in ("1", "0"):
+        monkeypatch.setenv("BMB_TRAINER_DEFER_COLSUMS", mode)
+        tr = bmb.Trainer(seed=7, use_flash=1, math=bmb.MATH_FP32, fused=0, **cfg)
+        tr.upload(toks, tgts)
+        for _ in range(2):                       # the second pass replays what the first recorded
+            tr.forward_backward()
+        g = np.empty(tr.num_params, np.float32)
+        tr.get_grads(g)
+        tr.close()
+        grads.append(g)
+    wte = cfg["padded_vocab"] * cfg["n_embd"]
+    assert np.all(np.isfinite(grads[0])) and np.abs(grads[0][wte:]).max() > 0
+    assert np.array_equal(grads[0][wte:], grads[1][wte:])
+    assert normwise(grads[0][:wte], grads[1][:wte]) < 1e-6
