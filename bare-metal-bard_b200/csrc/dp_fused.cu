@@ -139,12 +139,22 @@ dp_adamw_broadcast_ranges_k(PeerBufs pb, int nranks, int rank, const float *__re
 // shadow[e] = params[e] rounded to TF32 over the whole of every listed range (local: each rank rounds what arrived).
 __global__ void __launch_bounds__(256)
 dp_round_ranges_k(DpRangeList rl, float *__restrict__ shadow, const float *__restrict__ params) {
+    constexpr int U = 4;                                    // loads in flight per thread
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (int q = 0; q < rl.n; ++q) {
         const size_t n4 = rl.len[q] >> 2;
-        for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-            const size_t e = rl.off[q] + i * 4;
-            const float4 p = ld4(params + e);
-            st4(shadow + e, make_float4(round_tf32(p.x), round_tf32(p.y), round_tf32(p.z), round_tf32(p.w)));
+        for (size_t i0 = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * U) {
+            float4 p[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t i = i0 + (size_t)u * stride;
+                if (i < n4) p[u] = ld4(params + rl.off[q] + i * 4);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t i = i0 + (size_t)u * stride;
+                if (i < n4) st4(shadow + rl.off[q] + i * 4, make_float4(round_tf32(p[u].x), round_tf32(p[u].y), round_tf32(p[u].z), round_tf32(p[u].w)));
+            }
         }
     }
 }
