@@ -994,8 +994,13 @@ void choose_schedule(int M, int N, int kblocks, int ctas, bool allow_split, int 
         double cost = whole;
         int dp = (int)tiles;
         if (allow_split && rem && kblocks >= 8) {
-            const double shared = ((double)full * (kblocks + epi) + (double)((rem * kblocks + ctas - 1) / ctas) + (mh == 2 ? 24.0 : 10.0)) * unit;
-            if (shared < whole) { cost = shared; dp = (int)(tiles - rem); }
+            const double run = (double)((rem * kblocks + ctas - 1) / ctas);          // K slices of a CTA's shared run
+            const double shared = ((double)full * (kblocks + epi) + run + (mh == 2 ? 24.0 : 10.0)) * unit;
+            // With a short K a shared run that is a sizeable part of a CTA's work costs more than the model says
+            // (measured at 8192 x 768 x 768 on 74 CTAs: 45.3 us shared against 37.5 us with a third, partly filled
+            // wave; the preparing launch and the parts' reductions do not shrink with K): keep such tiles whole.
+            const bool short_k_big_run = kblocks <= 32 && run > 0.10 * ((double)full * (kblocks + epi) + run);
+            if (shared < whole && !short_k_big_run) { cost = shared; dp = (int)(tiles - rem); }
         }
         if (best < 0.0 || cost < best) { best = cost; *bn_out = w; *mh_out = mh; *dp_tiles_out = dp; }
     }
