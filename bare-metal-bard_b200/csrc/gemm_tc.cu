@@ -1095,9 +1095,11 @@ int plan_gemm(Plan *p, bool bf16, int flags, int batch, int M, int N, int K, int
     // that fills the last round of items to 99 % (else the best up to 40), at least 16 K slices per item.
     static const bool no_chunks = getenv("BMB_GEMM_NO_KCHUNKS") != nullptr;
     const double operand_bytes = ((double)M + (double)N) * (double)K * (bf16 ? 2.0 : 4.0);
-    // (lowering the 96 MB bar to 40 or 8 MB, which takes in the smaller weight-gradient products, changed nothing
-    //  measurable in the training step)
-    if (!no_chunks && p->sk_tiles == p->tiles && p->dp_tiles == 0 && p->grid == ctas && p->g_sk == ctas && operand_bytes > 96.0e6) {
+    // The bar is twice the 126 MB L2.  Weight-gradient products whose operands are about one L2 (2304 x 768 x 8192 on
+    // half the SMs: 101 MB, 54 tiles) ran slower in this order (101 us against 79 us with end-to-end runs: three
+    // partial-tile additions per CTA instead of one or two, for operands that mostly stay in L2 anyway).
+    const double min_bytes = 252.0e6;
+    if (!no_chunks && p->sk_tiles == p->tiles && p->dp_tiles == 0 && p->grid == ctas && p->g_sk == ctas && operand_bytes > min_bytes) {
         int best = 0;
         double best_eff = 0.0;
         for (int s = 4; s <= 40 && p->kblocks / s >= 16; ++s) {
