@@ -128,10 +128,6 @@ __device__ __forceinline__ bool group_all(int t, bool ok) {
                  : "=r"(r) : "r"(1 + t), "r"((uint32_t)ok) : "memory");
     return r != 0;
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
-}
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant__ CUtensorMap mapV,

@@ -49,6 +49,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// A warp's 32 rows x 32 columns leave through 4 KB of shared memory and one tile store: a thread writes its row's 128
+// bytes with the 16-byte pieces permuted as the store's 128-byte swizzle expects (which also spreads the warp's rows
+// over the banks).  Written straight to global memory, a row per thread costs a transaction per row and instruction.
+// `stage` is 1024-byte aligned; rows at and beyond T are clipped by the tensor map.  The caller commits and waits.
+__device__ __forceinline__ void stage_rows32(uint32_t stage, int lane, const float (&v)[32], float mul, int rnd) {
+    const uint32_t row_addr = stage + (uint32_t)(lane * 128);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const float4 w = out4(v[4 * c] * mul, v[4 * c + 1] * mul, v[4 * c + 2] * mul, v[4 * c + 3] * mul, rnd);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"r"(row_addr + (uint32_t)((c ^ (lane & 7)) << 4)), "f"(w.x), "f"(w.y), "f"(w.z), "f"(w.w) : "memory");
+    }
+}
+
 #ifdef BMB_FLASH_TRACE
 __device__ long long g_trace_bwd[32];
 // phase times are summed in registers and written once, so a timer costs one clock read
@@ -85,7 +99,7 @@ constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DQ = 384;
 // refilled as soon as its own consumer is done, by two loading threads so that neither ring waits
 // for the other.
 __device__ __forceinline__ void
-flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, const CUtensorMap &mapDO_k, float *__restrict__ dqkv,
+flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, const CUtensorMap &mapDO_k, const CUtensorMap &mapD,
                   const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
                   int round_out, int *__restrict__ status, int ypos, int ny) {
     using namespace dq;
@@ -338,11 +352,15 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
             fence_after();
             float v[32];
             tmem_ld32(lane_addr + COL_DQ + (uint32_t)(colhalf * 32), v);
-            if (qi < T) {
-                float *dst = dqkv + ((size_t)b * T + qi) * 3 * C + h * HS + colhalf * 32;
-#pragma unroll
-                for (int d = 0; d < 32; d += 4)
-                    *reinterpret_cast<float4 *>(dst + d) = out4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale, round_out);
+            // Q and dO are no longer read (every product that does has retired): their space stages the output
+            const uint32_t stage = base + OFF_Q + (uint32_t)(warp * 4096);
+            stage_rows32(stage, lane, v, scale, round_out);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(&mapD, stage, h * HS + colhalf * 32, q0 + quad * 32, b);
+                tma_store_commit();
+                tma_store_wait_all();                    // landed before the CTA may exit
             }
         }
     }
@@ -389,7 +407,7 @@ constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DV = 384, COL_DK = 448;
 // a thread of their own.
 __device__ __forceinline__ void
 flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64, const CUtensorMap &mapDO_k64, const CUtensorMap &mapDO_n64,
-                   float *__restrict__ dqkv, const float *__restrict__ lse, const float *__restrict__ dsum,
+                   const CUtensorMap &mapD, const float *__restrict__ lse, const float *__restrict__ dsum,
                    int T, int NH, float scale, int round_out, int *__restrict__ status, int ypos) {
     using namespace dkv;
     extern __shared__ uint8_t smem_raw[];
@@ -428,17 +446,19 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
     float *stat_l = reinterpret_cast<float *>(gen + OFF_STAT), *stat_d = stat_l + STAT_MAX;
     const int nstat = nb * QB;
     const bool stats_in_smem = nstat <= STAT_MAX;
-    if (stats_in_smem) {
-        for (int i = threadIdx.x; i < nstat; i += blockDim.x) {
-            const int q = ib0 * QB + i;
-            stat_l[i] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
-            stat_d[i] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
-        }
-    }
     fence_before();
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (stats_in_smem && warp < 8) {
+        // by the 256 arithmetic threads alone, after the block-wide barrier: the loading threads need not wait for it
+        for (int i = threadIdx.x; i < nstat; i += 256) {
+            const int q = ib0 * QB + i;
+            stat_l[i] = (q < T) ? __ldg(lse + (size_t)bh * T + q) * LOG2E : 0.0f;
+            stat_d[i] = (q < T) ? __ldg(dsum + (size_t)bh * T + q) : 0.0f;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
 
     if (warp == 8) {
         // --------------------------- loads of K, V and the K-major Q / dO blocks
@@ -677,20 +697,25 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
 #endif
         if (ok && nb > 0 && mbar_wait(bar(ACC_DONE), 0, giveup)) {
             fence_after();
+            // K and V are no longer read (every product that does has retired): their space stages dV and dK
+            const uint32_t stage_v = base + OFF_K + (uint32_t)(warp * 4096), stage_k = base + OFF_V + (uint32_t)(warp * 4096);
             float v[32];
             tmem_ld32(lane_addr + COL_DV + (uint32_t)(colhalf * 32), v);
-            if (kj < T) {
-                float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + 2 * C + h * HS + colhalf * 32;
-#pragma unroll
-                for (int d = 0; d < 32; d += 4)
-                    *reinterpret_cast<float4 *>(dst + d) = out4(v[d], v[d + 1], v[d + 2], v[d + 3], round_out);
+            stage_rows32(stage_v, lane, v, 1.0f, round_out);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(&mapD, stage_v, 2 * C + h * HS + colhalf * 32, j0 + quad * 32, b);
+                tma_store_commit();
             }
             tmem_ld32(lane_addr + COL_DK + (uint32_t)(colhalf * 32), v);
-            if (kj < T) {
-                float *dst = dqkv + ((size_t)b * T + kj) * 3 * C + C + h * HS + colhalf * 32;
-#pragma unroll
-                for (int d = 0; d < 32; d += 4)
-                    *reinterpret_cast<float4 *>(dst + d) = out4(v[d] * scale, v[d + 1] * scale, v[d + 2] * scale, v[d + 3] * scale, round_out);
+            stage_rows32(stage_k, lane, v, scale, round_out);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(&mapD, stage_k, C + h * HS + colhalf * 32, j0 + quad * 32, b);
+                tma_store_commit();
+                tma_store_wait_all();                    // both landed before the CTA may exit
             }
         }
     }
@@ -716,11 +741,11 @@ static_assert(dq::THREADS == dkv::THREADS && dq::SMEM == dkv::SMEM, "the two bod
 __global__ void __launch_bounds__(dkv::THREADS, 1)
 flash_bwd_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
                const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
-               float *__restrict__ dqkv, const float *__restrict__ lse, const float *__restrict__ dsum,
+               const __grid_constant__ CUtensorMap mapD, const float *__restrict__ lse, const float *__restrict__ dsum,
                int T, int NH, float scale, int round_out, int *__restrict__ status) {
     const int ypos = (int)blockIdx.y >> 1, ny = (int)gridDim.y >> 1;
-    if (blockIdx.y & 1) flash_bwd_dq_body(mapQKV_k64, mapQKV_n64, mapDO_k64, dqkv, lse, dsum, T, NH, scale, round_out, status, ypos, ny);
-    else flash_bwd_dkv_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapDO_n64, dqkv, lse, dsum, T, NH, scale, round_out, status, ypos);
+    if (blockIdx.y & 1) flash_bwd_dq_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapD, lse, dsum, T, NH, scale, round_out, status, ypos, ny);
+    else flash_bwd_dkv_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapDO_n64, mapD, lse, dsum, T, NH, scale, round_out, status, ypos);
 }
 
 __global__ void round_copy2_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
@@ -763,7 +788,8 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
         q = sq; g = sg;
     }
     const long long rows = (long long)B * T;
-    CUtensorMap qk64, qn64, gk64, gn64;
+    CUtensorMap qk64, qn64, gk64, gn64, dmap;
+    BMB_TRY(make_map_rows3d(&dmap, dqkv, 3LL * C, T, B, 32));
     BMB_TRY(make_map_2d(&qk64, q, 4, rows, 3LL * C, 3LL * C * 4, 64, false));
     BMB_TRY(make_map_2d(&qn64, q, 4, rows, 3LL * C, 3LL * C * 4, 64, true));
     BMB_TRY(make_map_2d(&gk64, g, 4, rows, C, (long long)C * 4, 64, false));
@@ -781,7 +807,7 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
     // the most work first, so the long CTAs start early and the short ones fill the tail.
     static_assert(dkv::KT == dq::QT, "one grid row pair per 128 positions");
     dim3 grid(B * NH, 2 * ((T + dkv::KT - 1) / dkv::KT));
-    flash_bwd_tc_k<<<grid, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dqkv, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
+    flash_bwd_tc_k<<<grid, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dmap, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
     count_launch();
     BMB_LAUNCH_CHECK();
     if (!rounded) {
