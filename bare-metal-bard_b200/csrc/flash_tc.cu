@@ -420,7 +420,6 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             }
             FTR_IF(tracer && r < 5, 4 + 4 * r);
         }
-        if (rr == 0) tma_store_wait_all();              // this thread's stores have landed before the CTA may exit
 #ifdef BMB_FLASH_TRACE
         if (tracer) { g_flash_trace[blockIdx.x % 160][22] = (unsigned long long)fw_s; g_flash_trace[blockIdx.x % 160][23] = (unsigned long long)fw_pv; }
 #endif

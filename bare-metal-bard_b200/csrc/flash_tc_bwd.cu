@@ -83,7 +83,7 @@ constexpr int OFF_BAR = OFF_KN + 2 * 16384;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 384;
 enum { Q_FULL = 0, KS_FULL = 1, KS_EMPTY = 3, VK_FULL = 5, VK_EMPTY = 7, KN_FULL = 9, KN_EMPTY = 11, S_FULL = 13, DP_FULL = 15,
-       DS_FULL = 16, DQ_DONE = 18, S_EMPTY = 19, NBARS = 21 };
+       DS_FULL = 16, DQ_DONE = 18, S_EMPTY = 19, DO_FULL = 21, NBARS = 22 };
 // TMEM columns: S [2] at 0 / 128, dP / dS at 256 (two granules of 64), dQ at 384
 constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DQ = 384;
 }  // namespace dq
@@ -121,6 +121,7 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
+        mbar_init(bar(DO_FULL), 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(KS_FULL + s), 1); mbar_init(bar(KS_EMPTY + s), 1);
             mbar_init(bar(VK_FULL + s), 1); mbar_init(bar(VK_EMPTY + s), 1);
@@ -141,12 +142,11 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
     if (warp == 8) {
         // ------------------------------------- loads of Q, dO and the K-major K / V blocks
         if (lane == 0) {
-            mbar_arrive_expect_tx(bar(Q_FULL), 65536);
+            // in the order of first use: Q and the first K block (the scores), then dO and the first V block (dP)
+            mbar_arrive_expect_tx(bar(Q_FULL), 32768);
             for (int half = 0; half < 2; ++half)
-                for (int rr = 0; rr < 2; ++rr) {
+                for (int rr = 0; rr < 2; ++rr)
                     tma_load_2d(base + OFF_Q + half * 16384 + rr * 8192, &mapQKV_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(Q_FULL));
-                    tma_load_2d(base + OFF_DO + half * 16384 + rr * 8192, &mapDO_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(Q_FULL));
-                }
             bool ok = true;
             int armed_k[2] = {-1, -1}, armed_v[2] = {-1, -1};
             for (int j = 0; j < nb; ++j) {
@@ -159,6 +159,12 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
                     for (int rr = 0; rr < 2; ++rr)
                         tma_load_2d(base + OFF_KS + st * 32768 + half * 16384 + rr * 8192, &mapQKV_k, C + h * HS + half * 32,
                                     row0 + j * KB + rr * 64, bar(KS_FULL + st));
+                if (j == 0) {
+                    mbar_arrive_expect_tx(bar(DO_FULL), 32768);
+                    for (int half = 0; half < 2; ++half)
+                        for (int rr = 0; rr < 2; ++rr)
+                            tma_load_2d(base + OFF_DO + half * 16384 + rr * 8192, &mapDO_k, h * HS + half * 32, row0 + q0 + rr * 64, bar(DO_FULL));
+                }
                 if (!mbar_wait(bar(VK_EMPTY + st), ph ^ 1, giveup)) { ok = false; break; }
                 mbar_arrive_expect_tx(bar(VK_FULL + st), 32768);
                 armed_v[st] = (int)ph;
@@ -169,6 +175,7 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
             }
             if (!ok) {
                 mbar_drain(bar(Q_FULL), 0);
+                if (armed_k[0] >= 0) mbar_drain(bar(DO_FULL), 0);    // armed right after the first K block
                 for (int s = 0; s < 2; ++s) {
                     if (armed_k[s] >= 0) mbar_drain(bar(KS_FULL + s), (uint32_t)armed_k[s]);
                     if (armed_v[s] >= 0) mbar_drain(bar(VK_FULL + s), (uint32_t)armed_v[s]);
@@ -235,7 +242,7 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
             long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long tlast = clock64();
 #endif
-            bool ok = mbar_wait(bar(Q_FULL), 0, giveup);
+            bool ok = mbar_wait(bar(DO_FULL), 0, giveup);
             if (ok) ok = mbar_wait(bar(VK_FULL + 0), 0, giveup);
             if (ok) {
                 fence_after();
@@ -360,7 +367,7 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
             if (lane == 0) {
                 tma_store_3d(&mapD, stage, h * HS + colhalf * 32, q0 + quad * 32, b);
                 tma_store_commit();
-                tma_store_wait_all();                    // landed before the CTA may exit
+                tma_store_wait_read();                   // shared memory has been read before the CTA may exit
             }
         }
     }
@@ -391,7 +398,7 @@ constexpr int OFF_STAT = OFF_BAR + 256;                 // lse * log2(e), then D
 constexpr int SMEM = OFF_STAT + 2 * STAT_MAX * 4 + 1024;
 constexpr int THREADS = 384;
 enum { KV_FULL = 0, QK_FULL = 1, QK_EMPTY = 2, DOK_FULL = 3, DOK_EMPTY = 4, N_FULL = 5, N_EMPTY = 7, S_FULL = 9, DP_FULL = 11,
-       PD_FULL = 12, ACC_DONE = 14, NBARS = 15 };
+       PD_FULL = 12, ACC_DONE = 14, V_FULL = 15, NBARS = 16 };
 // TMEM columns: S^T / P^T [2] at 0 / 128, dP^T / dS^T at 256, dV at 384, dK at 448
 constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DV = 384, COL_DK = 448;
 }  // namespace dkv
@@ -429,6 +436,7 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
 
     if (threadIdx.x == 0) {
         mbar_init(bar(KV_FULL), 1);
+        mbar_init(bar(V_FULL), 1);
         mbar_init(bar(QK_FULL), 1); mbar_init(bar(QK_EMPTY), 1);
         mbar_init(bar(DOK_FULL), 1); mbar_init(bar(DOK_EMPTY), 1);
         for (int s = 0; s < 2; ++s) {
@@ -463,12 +471,12 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
     if (warp == 8) {
         // --------------------------- loads of K, V and the K-major Q / dO blocks
         if (lane == 0) {
-            mbar_arrive_expect_tx(bar(KV_FULL), 65536);
+            // in the order of first use: K and the first Q block (the scores), then V and the first dO block (dP)
+            mbar_arrive_expect_tx(bar(KV_FULL), 32768);
             for (int half = 0; half < 2; ++half)
-                for (int rr = 0; rr < 2; ++rr) {
+                for (int rr = 0; rr < 2; ++rr)
                     tma_load_2d(base + OFF_K + half * 16384 + rr * 8192, &mapQKV_k64, C + h * HS + half * 32, row0 + j0 + rr * 64, bar(KV_FULL));
-                    tma_load_2d(base + OFF_V + half * 16384 + rr * 8192, &mapQKV_k64, 2 * C + h * HS + half * 32, row0 + j0 + rr * 64, bar(KV_FULL));
-                }
+            bool v_armed = false;
             bool ok = true;
             int armed_q = -1, armed_g = -1;
             for (int i = 0; i < nb; ++i) {
@@ -480,6 +488,13 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
                 for (int half = 0; half < 2; ++half)
                     for (int rr = 0; rr < 2; ++rr)
                         tma_load_2d(base + OFF_QK + half * 16384 + rr * 8192, &mapQKV_k64, h * HS + half * 32, qrow + rr * 64, bar(QK_FULL));
+                if (i == 0) {
+                    mbar_arrive_expect_tx(bar(V_FULL), 32768);
+                    v_armed = true;
+                    for (int half = 0; half < 2; ++half)
+                        for (int rr = 0; rr < 2; ++rr)
+                            tma_load_2d(base + OFF_V + half * 16384 + rr * 8192, &mapQKV_k64, 2 * C + h * HS + half * 32, row0 + j0 + rr * 64, bar(V_FULL));
+                }
                 if (!mbar_wait(bar(DOK_EMPTY), ph ^ 1, giveup)) { ok = false; break; }
                 mbar_arrive_expect_tx(bar(DOK_FULL), 32768);
                 armed_g = (int)ph;
@@ -489,6 +504,7 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
             }
             if (!ok) {
                 mbar_drain(bar(KV_FULL), 0);
+                if (v_armed) mbar_drain(bar(V_FULL), 0);
                 if (armed_q >= 0) mbar_drain(bar(QK_FULL), (uint32_t)armed_q);
                 if (armed_g >= 0) mbar_drain(bar(DOK_FULL), (uint32_t)armed_g);
             }
@@ -542,7 +558,7 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
             long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             long long tlast = clock64();
 #endif
-            bool ok = mbar_wait(bar(KV_FULL), 0, giveup);
+            bool ok = first ? mbar_wait(bar(KV_FULL), 0, giveup) : (nb <= 0 || mbar_wait(bar(V_FULL), 0, giveup));
             if (ok && nb > 0) ok = mbar_wait(bar(IN_FULL), 0, giveup);
             if (ok && nb > 0) {
                 fence_after();
@@ -715,7 +731,7 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
             if (lane == 0) {
                 tma_store_3d(&mapD, stage_k, C + h * HS + colhalf * 32, j0 + quad * 32, b);
                 tma_store_commit();
-                tma_store_wait_all();                    // both landed before the CTA may exit
+                tma_store_wait_read();                   // shared memory has been read before the CTA may exit
             }
         }
     }
