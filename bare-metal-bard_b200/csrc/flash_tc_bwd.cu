@@ -119,7 +119,11 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
     const int nb = min(T - 1, q0 + QT - 1) / KB + 1;       // key blocks up to the diagonal
     const int row0 = b * T;
 
-    if (threadIdx.x == 0) {
+    // The loading thread sets up the barriers itself and goes straight on to its first copies; the other warps meet it
+    // at a barrier it only arrives at, so the first operands are on their way while tensor memory is still being claimed.
+    if (threadIdx.x == 256) {
+        prefetch_tensormap(&mapQKV_k);
+        prefetch_tensormap(&mapDO_k);
         mbar_init(bar(Q_FULL), 1);
         mbar_init(bar(DO_FULL), 1);
         for (int s = 0; s < 2; ++s) {
@@ -133,11 +137,16 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
         *giveup = 0;
         mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
-    fence_before();
-    __syncthreads();
-    fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    if (warp == 8) {
+        __syncwarp();
+        asm volatile("bar.arrive 2, 384;" ::: "memory");
+    } else {
+        if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
+        fence_before();
+        asm volatile("bar.sync 2, 384;" ::: "memory");
+        fence_after();
+    }
+    const uint32_t tmem_base = (warp == 8) ? 0u : *tmem_slot;      // the loading warp has no use for it
 
     if (warp == 8) {
         // ------------------------------------- loads of Q, dO and the K-major K / V blocks
@@ -434,7 +443,10 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
     const int nb = (T + QB - 1) / QB - ib0;                // query blocks to walk
     const int row0 = b * T;
 
-    if (threadIdx.x == 0) {
+    // As in the dQ body: the loading thread sets up the barriers and starts copying at once.
+    if (threadIdx.x == 256) {
+        prefetch_tensormap(&mapQKV_k64);
+        prefetch_tensormap(&mapDO_k64);
         mbar_init(bar(KV_FULL), 1);
         mbar_init(bar(V_FULL), 1);
         mbar_init(bar(QK_FULL), 1); mbar_init(bar(QK_EMPTY), 1);
@@ -448,16 +460,21 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
         *giveup = 0;
         mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
     // Every thread needs the lse and D of every query the CTA walks: park them in shared memory once
     // (zero beyond the end of the sequence), lse already in log2 units.
     float *stat_l = reinterpret_cast<float *>(gen + OFF_STAT), *stat_d = stat_l + STAT_MAX;
     const int nstat = nb * QB;
     const bool stats_in_smem = nstat <= STAT_MAX;
-    fence_before();
-    __syncthreads();
-    fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    if (warp == 8) {
+        __syncwarp();
+        asm volatile("bar.arrive 2, 384;" ::: "memory");
+    } else {
+        if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
+        fence_before();
+        asm volatile("bar.sync 2, 384;" ::: "memory");
+        fence_after();
+    }
+    const uint32_t tmem_base = (warp == 8) ? 0u : *tmem_slot;
     if (stats_in_smem && warp < 8) {
         // by the 256 arithmetic threads alone, after the block-wide barrier: the loading threads need not wait for it
         for (int i = threadIdx.x; i < nstat; i += 256) {
@@ -754,6 +771,7 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
 // launches each would end in a partly filled wave of its own (768 CTAs on 148 SMs at B8 H12 T1024);
 // together they end in one, and the short CTAs of either fill the gaps left by the long ones of both.
 static_assert(dq::THREADS == dkv::THREADS && dq::SMEM == dkv::SMEM, "the two bodies share one launch configuration");
+static_assert(dq::THREADS == 384, "the set-up barrier of both bodies counts 384 threads");
 __global__ void __launch_bounds__(dkv::THREADS, 1)
 flash_bwd_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
                const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
