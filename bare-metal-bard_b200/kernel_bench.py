@@ -5,6 +5,7 @@
     python bare-metal-bard_b200/kernel_bench.py registry --csv runs/a.csv [-s 1024,2048]   (the registry sweep as CSV)
     python bare-metal-bard_b200/kernel_bench.py timeline:tf32:nt:8192x3072x768:rounded     (per-CTA timeline, timer build)
     python bare-metal-bard_b200/kernel_bench.py flash_timeline                             (attention forward: work-item stamps and knock-out timings, timer build)
+    python bare-metal-bard_b200/kernel_bench.py flash_scan                                 (tensor-core attention at B*T = 8192 for T = 128 .. 4096: fixed cost per CTA against cost per block)
 
 `registry --csv` appends one row per (registry entry, size) in the columns the reference harness writes
 (src/bench.cu:238-245, 293-299): kernel_id,kernel,size,gflops_best,gflops_median,cublas_gflops_best,
@@ -143,6 +144,31 @@ def bench_flash(bmb, small):
     emit(kernel="flash_bwd", config=lib.bmb_flash_bwd_config_name(tc_bwd).decode() + ", operands pre-rounded", B=B, NH=NH, T=T, hs=hs,
          best_ms=round(best, 4), median_ms=round(med, 4), tflops_2p5x_best=round(2.5 * useful / best / 1e9, 2),
          tflops_3p5x_best=round(3.5 * useful / best / 1e9, 2), gbs_best=round(bbytes / best / 1e6, 1))
+
+
+def bench_flash_scan(bmb, small):
+    """Tensor-core attention, operands pre-rounded, at a constant B*T: the number of CTAs (work items) stays the same
+    while the 128 x 128 blocks they walk grow with T, so a straight line through the times separates the fixed cost per
+    CTA (intercept) from the cost per block (slope)."""
+    lib = bmb.lib()
+    NH, hs = 12, 64
+    C = NH * hs
+    tc_fwd, tc_bwd = lib.bmb_flash_num_configs() - 1, lib.bmb_flash_num_bwd_configs() - 1
+    tokens = 2048 if small else 8192
+    for T in (128, 256, 512, 1024, 2048, 4096):
+        if T > tokens:
+            continue
+        B = tokens // T
+        qkv, dout = torch.randn(B * T * 3 * C, device="cuda"), torch.randn(B * T * C, device="cuda")
+        out, lse = torch.zeros(B * T * C, device="cuda"), torch.zeros(B * NH * T, device="cuda")
+        dqkv, dsum = torch.zeros(B * T * 3 * C, device="cuda"), torch.zeros(B * NH * T, device="cuda")
+        bmb.call("bmb_round_tf32", qkv, qkv, qkv.numel(), None)
+        bmb.call("bmb_round_tf32", dout, dout, dout.numel(), None)
+        f, _ = timed(lambda: bmb.call("bmb_flash_attention_forward_ex", tc_fwd, bmb.FLASH_OPERANDS_ROUNDED, out, lse, qkv, B, T, C, NH))
+        g, _ = timed(lambda: bmb.call("bmb_flash_attention_backward_ex", tc_bwd, bmb.FLASH_OPERANDS_ROUNDED, dqkv, dsum, dout, qkv, out, lse, B, T, C, NH))
+        nb = T // 128
+        emit(kernel="flash_scan", B=B, NH=NH, T=T, hs=hs, fwd_us=round(f * 1e3, 1), bwd_us=round(g * 1e3, 1),
+             bwd_ctas=2 * B * NH * nb, blocks_128x128=B * NH * nb * (nb + 1) // 2)
 
 
 def bench_nn(bmb, small):
@@ -419,7 +445,9 @@ def main():
         bench_timeline(bmb, w)
     if "flash_timeline" in which:
         bench_flash_timeline(bmb, small)
-    which = [x for x in which if not x.startswith(("one:", "timeline:")) and x != "flash_timeline"]
+    if "flash_scan" in which:
+        bench_flash_scan(bmb, small)
+    which = [x for x in which if not x.startswith(("one:", "timeline:")) and x not in ("flash_timeline", "flash_scan")]
     for w in which:
         {"gemm": bench_gemm, "bgemm": bench_bgemm, "flash": bench_flash, "nn": bench_nn}[w](bmb, small)
 
