@@ -55,7 +55,7 @@ constexpr float RESCALE_LOG2 = 8.0f;               // O and the row sum are resc
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + NQ * Q_TILE_BYTES;
 constexpr int OFF_V = OFF_K + K_STAGES * KV_TILE_BYTES;
-constexpr int O_STAGE_BYTES = QT * 128;             // 16 KB per tile: 128 rows x 32 columns of the output, swizzled for the TMA store
+constexpr int O_STAGE_BYTES = QT * 128;             // 16 KB per tile: 4 KB per warp, its 32 rows x 32 columns of the output, swizzled for the tile store
 constexpr int OFF_O = OFF_V + V_STAGES * KV_TILE_BYTES;
 constexpr int OFF_BAR = OFF_O + NQ * O_STAGE_BYTES;
 constexpr int FWD_SMEM = OFF_BAR + 256 + 1024;
@@ -121,7 +121,6 @@ __device__ __forceinline__ bool fwd_item(int round, int T, int BH, int nqblk, Fw
 
 // Named barriers of one softmax group (128 threads): plain, and one that also tells every thread whether all of
 // them are still on course -- a thread whose bounded wait ran out must not leave the others at a barrier.
-__device__ __forceinline__ void group_sync(int t) { asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory"); }
 __device__ __forceinline__ bool group_all(int t, bool ok) {
     uint32_t r;
     asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %2, 0;\n\tbar.red.and.pred p, %1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -392,11 +391,13 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(O_FREE + t));     // the next item's first product may overwrite O
             {
-                // The tile leaves through shared memory, 32 columns at a time: a thread writes its row's 128 bytes with
-                // the 16-byte pieces permuted as the store's 128-byte swizzle expects (which also spreads the warp's
-                // rows over the banks); rows at and beyond T are clipped by the tensor map.
+                // The tile leaves through shared memory, 32 columns at a time, each warp on its own with its 32 rows (4 KB of
+                // the tile's staging buffer, one tile store): a thread writes its row's 128 bytes with the 16-byte pieces
+                // permuted as the store's 128-byte swizzle expects (which also spreads the warp's rows over the banks);
+                // rows at and beyond T are clipped by the tensor map.
                 const float inv = 1.0f / l;
-                const uint32_t stage = base + OFF_O + (uint32_t)(t * O_STAGE_BYTES), row_addr = stage + (uint32_t)(rr * 128);
+                const uint32_t stage = base + OFF_O + (uint32_t)(t * O_STAGE_BYTES) + (uint32_t)((rr >> 5) * 4096);
+                const uint32_t row_addr = stage + (uint32_t)(lane * 128);
 #pragma unroll
                 for (int p = 0; p < 2; ++p) {
 #pragma unroll
@@ -405,16 +406,16 @@ flash_fwd_tc_k(const __grid_constant__ CUtensorMap mapQK, const __grid_constant_
                         float4 w = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
                         if (round_out) w = make_float4(round_tf32(w.x), round_tf32(w.y), round_tf32(w.z), round_tf32(w.w));
                         asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
-                                     ::"r"(row_addr + (uint32_t)(((c ^ (rr & 7)) << 4))), "f"(w.x), "f"(w.y), "f"(w.z), "f"(w.w) : "memory");
+                                     ::"r"(row_addr + (uint32_t)(((c ^ (lane & 7)) << 4))), "f"(w.x), "f"(w.y), "f"(w.z), "f"(w.w) : "memory");
                     }
                     fence_proxy_async();
-                    group_sync(t);
-                    if (rr == 0) {
-                        tma_store_3d(&mapO, stage, h * HS + p * 32, tile_q0, b);
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&mapO, stage, h * HS + p * 32, tile_q0 + (rr >> 5) * 32, b);
                         tma_store_commit();
                         tma_store_wait_read();           // the staging buffer may be overwritten
                     }
-                    group_sync(t);
+                    __syncwarp();
                 }
                 if (qi < T) lse[(size_t)it.bh * T + qi] = (m * scale_log2e + log2f(l)) * 0.6931471805599453f;
             }
@@ -484,7 +485,7 @@ int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int
     CUtensorMap mapQK, mapV, mapO;
     BMB_TRY(make_map_2d(&mapQK, src, 4, (long long)B * T, 3LL * C, 3LL * C * 4, 64, false));
     BMB_TRY(make_map_2d(&mapV, src, 4, (long long)B * T, 3LL * C, 3LL * C * 4, 64, true));
-    BMB_TRY(make_map_rows3d(&mapO, out, C, T, B, QT));
+    BMB_TRY(make_map_rows3d(&mapO, out, C, T, B, 32));
     {
         std::lock_guard<std::mutex> lk(g_mu);
         const int d = current_device();
