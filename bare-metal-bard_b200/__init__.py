@@ -22,6 +22,7 @@ GEMM_TILE_M128, GEMM_TILE_M256 = 16, 32
 GEMM_PAIR, GEMM_NO_PAIR = 64, 128
 GEMM_HALF_SMS = 256
 GEMM_AUX_ROUNDED = 512
+GEMM_AUX_FAST = 1024
 FLASH_OPERANDS_ROUNDED = 1
 E_UNSUPPORTED = 3
 E_TIMEOUT = 4

@@ -430,7 +430,8 @@ gemm_tc_k(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                             if (round_c) x = make_float2(round_tf32(x.x), round_tf32(x.y));
                             if (m < M) *reinterpret_cast<float2 *>(C + (size_t)m * N + n) = x;
                             if (AUX && m < M) {                      // second output: GELU of the first
-                                float2 g = make_float2(gelu_tanh(x.x), gelu_tanh(x.y));
+                                float2 g = (AUX == 2) ? make_float2(gelu_tanh_fast(x.x), gelu_tanh_fast(x.y))
+                                                      : make_float2(gelu_tanh(x.x), gelu_tanh(x.y));
                                 if (round_aux) g = make_float2(round_tf32(g.x), round_tf32(g.y));
                                 *reinterpret_cast<float2 *>(aux + (size_t)m * N + n) = g;
                             }
@@ -1244,9 +1245,14 @@ int gemm_tc(int math, int flags, int transA, int transB, int batch, int M, int N
     }
 #define BMB_TC_ARGS grid, st, mapA, mapB, mapC, c_mode, batch, M, N, kblocks, kper, amn, bmn, alpha, beta, C, vec_ok, dp_tiles, g_sk, bias, round_c, status_dev, aux, round_aux
     if (aux) {
-        // the second output is compiled into three instances only (the plain kernels stay as lean as they were:
-        // the activation's code in every epilogue cost all products 13 %)
-        if (bn == 256) BMB_TRY((launch_tc<0, 256, 1, 1>(BMB_TC_ARGS)));
+        // the second output is compiled into instances of its own (the plain kernels stay as lean as they were:
+        // the activation's code in every epilogue cost all products 13 %), three with the accurate tanh and three
+        // with the approximate one (BMB_GEMM_AUX_FAST)
+        if (flags & BMB_GEMM_AUX_FAST) {
+            if (bn == 256) BMB_TRY((launch_tc<0, 256, 1, 2>(BMB_TC_ARGS)));
+            else if (bn == 192) BMB_TRY((launch_tc<0, 192, 1, 2>(BMB_TC_ARGS)));
+            else BMB_TRY((launch_tc<0, 128, 1, 2>(BMB_TC_ARGS)));
+        } else if (bn == 256) BMB_TRY((launch_tc<0, 256, 1, 1>(BMB_TC_ARGS)));
         else if (bn == 192) BMB_TRY((launch_tc<0, 192, 1, 1>(BMB_TC_ARGS)));
         else BMB_TRY((launch_tc<0, 128, 1, 1>(BMB_TC_ARGS)));
     } else if (bf16) {

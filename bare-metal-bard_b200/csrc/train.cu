@@ -109,7 +109,7 @@ struct bmb_trainer {
     // BMB_TRAINER_FUSE_GELU=1 (fused TF32 mode): the MLP's activation in the epilogue of the product before it.  Off by
     // default: measured at the 124M shapes the product gets 37 us slower (its epilogue is no longer hidden behind
     // the next tile's main loop) for the 35 us pass it saves.
-    bool fuse_gelu = false;
+    int fuse_gelu = 0;           // 0: GELU is a kernel of its own; 1: it rides in the fc product's epilogue; 2: with the approximate tanh
     // Deferred column sums (single-piece steps): the backward kernels' partial rows go to this arena and one batched
     // launch at the end of backward finishes all the parameter-gradient sums (BMB_TRAINER_DEFER_COLSUMS=0: each
     // sum by a launch of its own, right after its kernel).
@@ -270,7 +270,7 @@ int fwd_layer(bmb_trainer *t, const Dims &d, int l) {
                                            P + t->poff[P_LN2W] + (size_t)l * C, P + t->poff[P_LN2B] + (size_t)l * C, N, C));
     if (fz) {
         // bias and GELU ride in the product's epilogue: fch and fch_gelu leave the accumulator together
-        BMB_TRY(mm(t, wflag, 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch,
+        BMB_TRY(mm(t, wflag | (t->fuse_gelu == 2 ? BMB_GEMM_AUX_FAST : 0), 0, 1, N, 4 * C, C, ln2, W + t->poff[P_FCW] + (size_t)l * 4 * C * C, 0.0f, fch,
                    P + t->poff[P_FCB] + (size_t)l * 4 * C, nullptr, t->fuse_gelu ? fchg : nullptr));
         if (!t->fuse_gelu) BMB_TRY(bmb_gelu_forward(fchg, fch, (int)d.BT4C));
     } else {
@@ -633,7 +633,7 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     BMB_CUDA(cudaEventCreateWithFlags(&t->ev_join, cudaEventDisableTiming));
     if (const char *e = getenv("BMB_TRAINER_SIDE_BY_SIDE")) t->side_by_side = atoi(e) != 0;
     if (const char *e = getenv("BMB_TRAINER_OVERLAP")) { const int v = atoi(e); t->overlap = v < 0 ? 0 : (v > 2 ? 2 : v); }
-    if (const char *e = getenv("BMB_TRAINER_FUSE_GELU")) t->fuse_gelu = atoi(e) != 0;
+    if (const char *e = getenv("BMB_TRAINER_FUSE_GELU")) t->fuse_gelu = atoi(e);
     if (const char *e = getenv("BMB_TRAINER_TIMELINE")) t->tl_step = atoi(e);
     if (const char *e = getenv("BMB_TRAINER_DEFER_COLSUMS")) t->defer_colsums = atoi(e) != 0;
     {

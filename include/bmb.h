@@ -122,8 +122,11 @@ int bmb_gemm_ex(int math, int flags, int transA, int transB, int M, int N,
  * C_gelu = GELU(C), bit-identical to bmb_gelu_forward on C.  On the tensor-core paths both leave the
  * accumulator in the product's epilogue when C and C_gelu are 16-byte aligned and N % 4 == 0 (no tile is then
  * split along K); otherwise, and for BMB_MATH_FP32, the activation is a pass of its own.
- * BMB_GEMM_AUX_ROUNDED: C_gelu is stored rounded to TF32 (it feeds another tensor-core product). */
+ * BMB_GEMM_AUX_ROUNDED: C_gelu is stored rounded to TF32 (it feeds another tensor-core product).
+ * BMB_GEMM_AUX_FAST: where the activation rides in the epilogue, its tanh is the hardware's approximate one (absolute
+ * error about 2^-11, of the order of the TF32 rounding of C_gelu; no longer bit-identical to bmb_gelu_forward). */
 #define BMB_GEMM_AUX_ROUNDED 512
+#define BMB_GEMM_AUX_FAST 1024
 int bmb_gemm_bias_gelu(int math, int flags, int M, int N, int K, const float *A, const float *W, const float *bias,
                        float *C, float *C_gelu, void *stream);
 int bmb_batched_gemm(int transA, int transB, int batch, int M, int N, int K,

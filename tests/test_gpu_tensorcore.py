@@ -400,6 +400,27 @@ def test_gemm_bias_gelu_equals_the_three_calls(bmb, orc, cuda, M, N, K, pad, wit
     assert normwise(gf, want) <= 5e-4                            # TF32 rounding of the activation
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 384, 128), (1024, 3072, 768), (300, 256, 96)])
+def test_gemm_bias_gelu_with_the_approximate_tanh(bmb, orc, cuda, M, N, K):
+    """BMB_GEMM_AUX_FAST: the activation in the epilogue takes the hardware's approximate tanh.  C is unchanged (equal to
+    the accurate variant's bit for bit); C_gelu, unrounded, stays within 1e-3 of max|GELU| of the oracle's activation of
+    that C element by element (the approximation's absolute error is about 5e-4 of |x|/2), and within 5e-4 normwise."""
+    A, W, bias = rounded(orc, uniform(M * K, 31), "tf32"), rounded(orc, uniform(N * K, 32), "tf32"), uniform(N, 33)
+    dA, dW, db = dev(cuda, A), dev(cuda, W), dev(cuda, bias)
+    flags = bmb.GEMM_A_ROUNDED | bmb.GEMM_B_ROUNDED
+    c_a, g_a = cuda.full((M * N,), float("nan"), device="cuda"), cuda.full((M * N,), float("nan"), device="cuda")
+    c_f, g_f = cuda.full((M * N,), float("nan"), device="cuda"), cuda.full((M * N,), float("nan"), device="cuda")
+    bmb.call("bmb_gemm_bias_gelu", bmb.MATH_TF32, flags, M, N, K, dA, dW, db, c_a, g_a, None)
+    bmb.call("bmb_gemm_bias_gelu", bmb.MATH_TF32, flags | bmb.GEMM_AUX_FAST, M, N, K, dA, dW, db, c_f, g_f, None)
+    cf, gf = host(cuda, c_f), host(cuda, g_f)
+    assert np.array_equal(cf, host(cuda, c_a)) and np.all(np.isfinite(gf))
+    want = np.empty_like(cf)
+    orc.orc_gelu_forward(_np(want), _np(cf), cf.size)
+    assert float(np.max(np.abs(gf - want))) <= 1e-3 * float(np.max(np.abs(want)))
+    assert normwise(gf, want) <= 5e-4
+    assert normwise(host(cuda, g_a), want) <= 1e-6               # the accurate variant, for contrast
+
+
 def test_two_streams_take_turns_on_the_staging_scratch(bmb, cuda):
     """Tensor-core products whose operands are not flagged as rounded first round them into one per-device staging
     block.  Two streams of one device issuing such products at the same time must take turns on it (the library
