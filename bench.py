@@ -535,8 +535,8 @@ def run_bmb(args):
                 tr.attach_peers(rank, world, None)
                 args.nccl_dp = True
 
-    PROF_STEPS = 2
-    nsteps = args.warmup + 2 * args.steps + PROF_STEPS
+    PROF_WARM, PROF_STEPS = 1, 3
+    nsteps = args.warmup + 2 * args.steps + PROF_WARM + PROF_STEPS
     pinned = []
     for s in range(nsteps):
         x, y = dist_mod.synthetic_batch(s, B_PER_GPU * world, T, GPT124M["vocab_size"])
@@ -620,9 +620,13 @@ def run_bmb(args):
 
     # ---- GEMM breakdown: a few more steps launched one kernel at a time with an event pair around
     # every GEMM (not part of either timed region)
+    # (the first such step is not counted: the step leaves its CUDA graph for kernel-by-kernel launches there)
     tr.profile(True)
-    for i in range(PROF_STEPS):
+    for i in range(PROF_WARM):
         one_step(args.warmup + 2 * args.steps + i)
+    tr.profile(True)                                     # restarts the counters
+    for i in range(PROF_STEPS):
+        one_step(args.warmup + 2 * args.steps + PROF_WARM + i)
     prof = tr.profile_read()
     tr.profile(False)
     prof["steps"] = PROF_STEPS
