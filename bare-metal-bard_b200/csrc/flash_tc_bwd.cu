@@ -1,7 +1,8 @@
 // Fused causal attention backward on the tensor cores (head size 64), split
 // as in the reference (src/flash.cu:434-470): dQ reduces over keys, dK and dV
 // reduce over queries, so each keeps its accumulators on chip -- here in tensor
-// memory -- and writes its part of dqkv with plain stores.  The reference
+// memory -- and writes its part of dqkv once, through shared memory and tile
+// stores (no atomics).  The reference
 // launches the two as separate kernels; here they are two kinds of CTA in one
 // grid (flash_bwd_tc_k at the end of this file).
 // P is rebuilt from the saved lse, P = exp(S - lse), and
