@@ -131,6 +131,13 @@ def test_tensorcore_gemm_schedule_covers_every_slice_once(bmb):
                 st = lib.bmb_gemm_schedule_check(bmb.MATH_TF32, flags, 1, M, N, K, units, C.byref(bm), C.byref(bn), C.byref(dp), C.byref(grid))
                 assert st == 0, (M, N, K, units, flags, lib.bmb_last_error())
                 assert (bm.value, bn.value) == (256, 256) and 1 <= grid.value <= units
+    # a short K whose shared run would be a sizeable part of a CTA's work keeps its tiles whole (dX of the attention
+    # projection on half of the SMs: 192 tiles on 74 CTAs end in a partly filled wave instead); a long K is shared
+    bm, bn, dp = C.c_int(), C.c_int(), C.c_int()
+    assert lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 1, 8192, 768, 768, 74, C.byref(bm), C.byref(bn), C.byref(dp), None) == 0
+    assert dp.value == -(-8192 // bm.value) * -(-768 // bn.value)
+    assert lib.bmb_gemm_schedule_check(bmb.MATH_TF32, 0, 1, 2304, 768, 8192, 74, C.byref(bm), C.byref(bn), C.byref(dp), None) == 0
+    assert dp.value == 0
     for (M, N, K) in shapes[:10]:
         for flags, want in ((bmb.GEMM_TILE_M128 | bmb.GEMM_NO_PAIR, 128), (bmb.GEMM_TILE_M256 | bmb.GEMM_NO_PAIR, 256)):
             bm = C.c_int()
