@@ -616,7 +616,7 @@ def run_bmb(args):
     dist_mod.barrier()
     ms_e2e = dist_mod.max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
     step_clocks = clocks.window(t_mark, time.time()) if clocks else None
-    note("end-to-end region timed")
+    note("end-to-end region timed: %.2f ms/step by events, %.2f by the host clock" % (e0.elapsed_time(e1) / args.steps, wall_ms / args.steps))
 
     # ---- GEMM breakdown: a few more steps launched one kernel at a time with an event pair around
     # every GEMM (not part of either timed region)
