@@ -24,7 +24,7 @@ bool flash_tc_supported(int T, int C, int NH, const float *qkv, const float *out
 int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, bool qkv_rounded,
                      cudaStream_t st);
 int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
-                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st);
+                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st, float *dbias_qkv = nullptr);
 namespace {
 
 #define LD4(p) (*reinterpret_cast<const float4 *>(p))

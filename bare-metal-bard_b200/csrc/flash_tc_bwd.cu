@@ -32,6 +32,8 @@
 
 namespace bmb {
 int launch_flash_dsum(float *dsum, const float *dout, const float *out, int B, int T, int NH, int HS, cudaStream_t st);
+float *column_partial_rows(size_t floats, bool *deferred);
+int column_sum_finish(bool deferred, float *dst, const float *partial, int G, int ncols, cudaStream_t st);
 
 namespace {
 
@@ -74,6 +76,20 @@ __device__ long long g_trace_bwd[32];
 #define TRB_FLUSH(first, n)
 #endif
 
+// Column sums of the 32 x 32 block a warp has just staged (rows below `nvalid` only), one column per lane, written as
+// one row of partial sums: the bias gradient of the projection that produced q, k, v is the column sum of dqkv, and
+// the tile is at hand here.  The reads follow the staging layout's permutation, so a warp's 32 lanes hit 32 banks.
+__device__ __forceinline__ void stage_colsum32(uint32_t stage, int lane, int nvalid, float *__restrict__ dst) {
+    float s = 0.0f;
+    const uint32_t piece = (uint32_t)(lane >> 2), within = (uint32_t)((lane & 3) * 4);
+    for (int r = 0; r < nvalid; ++r) {
+        float x;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(stage + (uint32_t)(r * 128) + ((piece ^ (uint32_t)(r & 7)) << 4) + within));
+        s += x;
+    }
+    dst[lane] = s;
+}
+
 // ============================================================== dQ kernel
 namespace dq {
 constexpr int QT = 128, KB = 128, G = 64;               // keys per block (one S / dP product) and per granule (one dQ product)
@@ -102,7 +118,7 @@ constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DQ = 384;
 __device__ __forceinline__ void
 flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, const CUtensorMap &mapDO_k, const CUtensorMap &mapD,
                   const float *__restrict__ lse, const float *__restrict__ dsum, int T, int NH, float scale,
-                  int round_out, int *__restrict__ status, int ypos, int ny) {
+                  int round_out, int *__restrict__ status, int ypos, int ny, float *__restrict__ colpart) {
     using namespace dq;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -377,8 +393,11 @@ flash_bwd_dq_body(const CUtensorMap &mapQKV_k, const CUtensorMap &mapQKV_n, cons
             if (lane == 0) {
                 tma_store_3d(&mapD, stage, h * HS + colhalf * 32, q0 + quad * 32, b);
                 tma_store_commit();
-                tma_store_wait_read();                   // shared memory has been read before the CTA may exit
             }
+            if (colpart)       // partial row ((b, query block), quad): columns of q
+                stage_colsum32(stage, lane, max(0, min(32, T - (q0 + quad * 32))),
+                               colpart + ((size_t)(b * ny + q0 / QT) * 4 + quad) * (3 * C) + h * HS + colhalf * 32);
+            if (lane == 0) tma_store_wait_read();        // shared memory has been read before the CTA may exit
         }
     }
 
@@ -425,7 +444,8 @@ constexpr uint32_t COL_S = 0, COL_DP = 256, COL_DV = 384, COL_DK = 448;
 __device__ __forceinline__ void
 flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64, const CUtensorMap &mapDO_k64, const CUtensorMap &mapDO_n64,
                    const CUtensorMap &mapD, const float *__restrict__ lse, const float *__restrict__ dsum,
-                   int T, int NH, float scale, int round_out, int *__restrict__ status, int ypos) {
+                   int T, int NH, float scale, int round_out, int *__restrict__ status, int ypos, int ny,
+                   float *__restrict__ colpart) {
     using namespace dkv;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -742,6 +762,10 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
                 tma_store_3d(&mapD, stage_v, 2 * C + h * HS + colhalf * 32, j0 + quad * 32, b);
                 tma_store_commit();
             }
+            // partial row ((b, key block), quad): columns of v, then of k
+            const int nvalid = max(0, min(32, T - (j0 + quad * 32)));
+            float *part = colpart ? colpart + ((size_t)(b * ny + ypos) * 4 + quad) * (3 * C) + h * HS + colhalf * 32 : nullptr;
+            if (part) stage_colsum32(stage_v, lane, nvalid, part + 2 * C);
             tmem_ld32(lane_addr + COL_DK + (uint32_t)(colhalf * 32), v);
             stage_rows32(stage_k, lane, v, scale, round_out);
             fence_proxy_async();
@@ -749,8 +773,9 @@ flash_bwd_dkv_body(const CUtensorMap &mapQKV_k64, const CUtensorMap &mapQKV_n64,
             if (lane == 0) {
                 tma_store_3d(&mapD, stage_k, C + h * HS + colhalf * 32, j0 + quad * 32, b);
                 tma_store_commit();
-                tma_store_wait_read();                   // shared memory has been read before the CTA may exit
             }
+            if (part) stage_colsum32(stage_k, lane, nvalid, part + C);
+            if (lane == 0) tma_store_wait_read();        // shared memory has been read before the CTA may exit
         }
     }
 
@@ -777,10 +802,10 @@ __global__ void __launch_bounds__(dkv::THREADS, 1)
 flash_bwd_tc_k(const __grid_constant__ CUtensorMap mapQKV_k64, const __grid_constant__ CUtensorMap mapQKV_n64,
                const __grid_constant__ CUtensorMap mapDO_k64, const __grid_constant__ CUtensorMap mapDO_n64,
                const __grid_constant__ CUtensorMap mapD, const float *__restrict__ lse, const float *__restrict__ dsum,
-               int T, int NH, float scale, int round_out, int *__restrict__ status) {
+               int T, int NH, float scale, int round_out, int *__restrict__ status, float *__restrict__ colpart) {
     const int ypos = (int)blockIdx.y >> 1, ny = (int)gridDim.y >> 1;
-    if (blockIdx.y & 1) flash_bwd_dq_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapD, lse, dsum, T, NH, scale, round_out, status, ypos, ny);
-    else flash_bwd_dkv_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapDO_n64, mapD, lse, dsum, T, NH, scale, round_out, status, ypos);
+    if (blockIdx.y & 1) flash_bwd_dq_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapD, lse, dsum, T, NH, scale, round_out, status, ypos, ny, colpart);
+    else flash_bwd_dkv_body(mapQKV_k64, mapQKV_n64, mapDO_k64, mapDO_n64, mapD, lse, dsum, T, NH, scale, round_out, status, ypos, ny, colpart);
 }
 
 __global__ void round_copy2_k(float *__restrict__ dst, const float *__restrict__ src, long long n4) {
@@ -798,8 +823,10 @@ std::mutex g_mu;
 
 // dqkv is overwritten.  `rounded`: qkv and dout already hold TF32-representable
 // values; otherwise rounded copies are made in per-device scratch first.
+// dbias_qkv (optional, 3C floats): += the column sums of dqkv (src/nn.cu bias_backward on dqkv: the bias gradient of
+// the qkv projection), from partial sums the CTAs leave beside their tiles instead of another sweep over dqkv.
 int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
-                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st) {
+                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st, float *dbias_qkv) {
     int *status_dev = nullptr;
     volatile int *status_host = nullptr;
     BMB_TRY(tc::status_word(&status_dev, &status_host));
@@ -841,10 +868,22 @@ int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *
     // x = (batch, head), y = position: the dispatch order runs through all heads at the position with
     // the most work first, so the long CTAs start early and the short ones fill the tail.
     static_assert(dkv::KT == dq::QT, "one grid row pair per 128 positions");
-    dim3 grid(B * NH, 2 * ((T + dkv::KT - 1) / dkv::KT));
-    flash_bwd_tc_k<<<grid, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dmap, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev);
+    const int nblk = (T + dkv::KT - 1) / dkv::KT;
+    dim3 grid(B * NH, 2 * nblk);
+    // a row of partial column sums per (batch, block of 128 positions, quarter of the block): each (row, column) is
+    // written by exactly one warp of one CTA
+    const int part_rows = B * nblk * 4;
+    bool deferred = false;
+    float *colpart = nullptr;
+    if (dbias_qkv) {
+        colpart = column_partial_rows((size_t)part_rows * 3 * C, &deferred);
+        if (!colpart) return BMB_E_CUDA;
+    }
+    flash_bwd_tc_k<<<grid, dkv::THREADS, dkv::SMEM, st>>>(qk64, qn64, gk64, gn64, dmap, lse, dsum, T, NH, scale, emit_rounded() ? 1 : 0, status_dev,
+                                                           colpart);
     count_launch();
     BMB_LAUNCH_CHECK();
+    if (dbias_qkv) BMB_TRY(column_sum_finish(deferred, dbias_qkv, colpart, part_rows, 3 * C, st));
     if (!rounded) {
         BMB_TRY(scratch_release(SCR_GEMM_A, st));
         BMB_TRY(scratch_release(SCR_GEMM_B, st));

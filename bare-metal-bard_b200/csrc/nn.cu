@@ -792,6 +792,14 @@ int finish_column_sum(bool deferred, float *dst, float *dst2, int ncols_first, c
 }
 }  // namespace
 
+// Column sums whose partial rows another kernel's epilogue leaves (the attention backward, for the qkv bias): where
+// those rows go (the deferred-sum arena while a collector is installed, else per-device scratch) and how the sum into
+// dst (+=) is finished (noted for the batched launch, or launched now).
+float *column_partial_rows(size_t floats, bool *deferred) { return partial_rows(floats, deferred); }
+int column_sum_finish(bool deferred, float *dst, const float *partial, int G, int ncols, cudaStream_t st) {
+    return finish_column_sum(deferred, dst, nullptr, ncols, partial, G, ncols, st);
+}
+
 // Layernorm backward with the scratch supplied by the caller: `partial` holds
 // at least layernorm_bwd_blocks(N) * 2 * C floats.
 int layernorm_bwd_blocks(int N) {

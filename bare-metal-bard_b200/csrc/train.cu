@@ -20,7 +20,7 @@ bool flash_tc_supported(int T, int C, int NH, const float *qkv, const float *out
 int flash_forward_tc(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, bool qkv_rounded,
                      cudaStream_t st);
 int flash_backward_tc(float *dqkv, float *dsum, const float *dout, const float *qkv, const float *out,
-                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st);
+                      const float *lse, int B, int T, int C, int NH, bool rounded, cudaStream_t st, float *dbias_qkv = nullptr);
 namespace tc {
 int status_word(int **dev_ptr, volatile int **host_ptr);
 }
@@ -109,6 +109,7 @@ struct bmb_trainer {
     // BMB_TRAINER_FUSE_GELU=1 (fused TF32 mode): the MLP's activation in the epilogue of the product before it.  Off by
     // default: measured at the 124M shapes the product gets 37 us slower (its epilogue is no longer hidden behind
     // the next tile's main loop) for the 35 us pass it saves.
+    bool qkv_bias_in_attention = true;   // BMB_TRAINER_QKV_BIAS_IN_ATTENTION=0: a sweep over dqkv of its own again
     int fuse_gelu = 0;           // 0: GELU is a kernel of its own; 1: it rides in the fc product's epilogue; 2: with the approximate tanh
     // Deferred column sums (single-piece steps): the backward kernels' partial rows go to this arena and one batched
     // launch at the end of backward finishes all the parameter-gradient sums (BMB_TRAINER_DEFER_COLSUMS=0: each
@@ -382,8 +383,11 @@ int bwd_layer(bmb_trainer *t, const Dims &d, int l) {
                                           P + t->poff[P_LN2W] + lC, t->ln2_mean + l * BT, t->ln2_rstd + l * BT, N, C));
     BMB_TRY(dx_dw(t, d, wflag | (fz ? BMB_GEMM_C_ROUNDED : 0), N, C, C, t->dres, P_APW, (size_t)l * C * C, t->datty,
                   C, C, atty, G + t->poff[P_APW] + (size_t)l * C * C));
+    // the tensor-core attention backward leaves the qkv bias gradient (column sums of dqkv) from its own epilogue
+    const bool bias_in_attention = c.use_flash && fz && attn_cfg(c) == 2 && t->qkv_bias_in_attention;
     if (c.use_flash && fz && attn_cfg(c) == 2)
-        BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * d.lse_sz, B, T, C, NH, true, t->st));
+        BMB_TRY(flash_backward_tc(t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * d.lse_sz, B, T, C, NH, true, t->st,
+                                  bias_in_attention ? G + t->poff[P_QKVB] + 3 * lC : nullptr));
     else if (c.use_flash)
         BMB_TRY(bmb_flash_attention_backward_cfg(attn_cfg(c), t->dqkv, t->dsum, t->datty, qkv, atty, t->lse + l * d.lse_sz, B, T, C, NH));
     else
@@ -391,7 +395,7 @@ int bwd_layer(bmb_trainer *t, const Dims &d, int l) {
                                        t->att + l * d.att_sz, B, T, C, NH));
     BMB_TRY(dx_dw(t, d, wflag, N, C, 3 * C, t->dqkv, P_QKVW, (size_t)l * 3 * C * C, t->dln1,
                   3 * C, C, ln1, G + t->poff[P_QKVW] + (size_t)l * 3 * C * C));
-    BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
+    if (!bias_in_attention) BMB_TRY(bmb_bias_backward(G + t->poff[P_QKVB] + 3 * lC, t->dqkv, N, 3 * C));
     return bmb_layernorm_backward_colsum(t->dres, G + t->poff[P_LN1W] + lC, G + t->poff[P_LN1B] + lC,
                                          l > 0 ? G + t->poff[P_FPB] + lC - C : nullptr, t->dln1, residual,
                                          P + t->poff[P_LN1W] + lC, t->ln1_mean + l * BT, t->ln1_rstd + l * BT, N, C);
@@ -634,6 +638,7 @@ int trainer_build(bmb_trainer *t, const bmb_train_config &c, unsigned seed) {
     if (const char *e = getenv("BMB_TRAINER_SIDE_BY_SIDE")) t->side_by_side = atoi(e) != 0;
     if (const char *e = getenv("BMB_TRAINER_OVERLAP")) { const int v = atoi(e); t->overlap = v < 0 ? 0 : (v > 2 ? 2 : v); }
     if (const char *e = getenv("BMB_TRAINER_FUSE_GELU")) t->fuse_gelu = atoi(e);
+    if (const char *e = getenv("BMB_TRAINER_QKV_BIAS_IN_ATTENTION")) t->qkv_bias_in_attention = atoi(e) != 0;
     if (const char *e = getenv("BMB_TRAINER_TIMELINE")) t->tl_step = atoi(e);
     if (const char *e = getenv("BMB_TRAINER_DEFER_COLSUMS")) t->defer_colsums = atoi(e) != 0;
     {

@@ -471,3 +471,33 @@ def test_deferred_column_sums_equal_a_launch_per_sum(bmb, cuda, monkeypatch):
     assert np.all(np.isfinite(grads[0])) and np.abs(grads[0][wte:]).max() > 0
     assert np.array_equal(grads[0][wte:], grads[1][wte:])
     assert normwise(grads[0][:wte], grads[1][:wte]) < 1e-6
+
+
+def test_qkv_bias_gradient_from_the_attention_backward(bmb, cuda, monkeypatch):
+    """In the fused TF32 step the tensor-core attention backward leaves the qkv bias gradient (the column sums of dqkv)
+    as partial sums from its own epilogue, instead of another sweep over dqkv.  Against that sweep
+    (BMB_TRAINER_QKV_BIAS_IN_ATTENTION=0) on a ragged shape -- T = 200: a second block of 72 rows, quarters of 32, 32,
+    8 and 0 valid rows, and three sequences, so that the rows past the end of a sequence inside a tile hold the next
+    sequence's values and must be left out -- the bias gradient agrees to summation order, and so does the rest."""
+    cfg = dict(max_seq_len=200, vocab_size=300, padded_vocab=384, n_layer=2, n_head=2, n_embd=128, B=3, T=200)
+    rng = np.random.default_rng(9)
+    toks = rng.integers(0, cfg["vocab_size"], (cfg["B"], cfg["T"]), dtype=np.int32)
+    tgts = rng.integers(0, cfg["vocab_size"], (cfg["B"], cfg["T"]), dtype=np.int32)
+    grads = []
+    for mode in ("1", "0"):
+        monkeypatch.setenv("BMB_TRAINER_QKV_BIAS_IN_ATTENTION", mode)
+        tr = bmb.Trainer(seed=7, use_flash=1, math=bmb.MATH_TF32, fused=1, **cfg)
+        tr.upload(toks, tgts)
+        for _ in range(2):                       # the second pass replays the recorded job list / the captured graph
+            tr.forward_backward()
+        g = np.empty(tr.num_params, np.float32)
+        tr.get_grads(g)
+        tr.close()
+        grads.append(g)
+    L, C, Vp, maxT = cfg["n_layer"], cfg["n_embd"], cfg["padded_vocab"], cfg["max_seq_len"]
+    off = Vp * C + maxT * C + 2 * L * C + L * 3 * C * C          # wte, wpe, ln1 gain and bias, qkv weight (src/gpt.cu:32-51)
+    qb = [g[off:off + L * 3 * C] for g in grads]
+    assert np.all(np.isfinite(grads[0])) and np.abs(qb[0]).max() > 0
+    assert normwise(qb[0], qb[1]) < 1e-5, normwise(qb[0], qb[1])
+    assert normwise(grads[0], grads[1]) < 1e-5
+
