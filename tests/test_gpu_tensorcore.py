@@ -484,8 +484,10 @@ def test_qkv_bias_gradient_from_the_attention_backward(bmb, cuda, monkeypatch):
     toks = rng.integers(0, cfg["vocab_size"], (cfg["B"], cfg["T"]), dtype=np.int32)
     tgts = rng.integers(0, cfg["vocab_size"], (cfg["B"], cfg["T"]), dtype=np.int32)
     grads = []
-    for mode in ("1", "0"):
+    # from the epilogue with the sums deferred to the batched launch; from the epilogue with a launch per sum; the sweep
+    for mode, defer in (("1", "1"), ("0", "1"), ("1", "0")):
         monkeypatch.setenv("BMB_TRAINER_QKV_BIAS_IN_ATTENTION", mode)
+        monkeypatch.setenv("BMB_TRAINER_DEFER_COLSUMS", defer)
         tr = bmb.Trainer(seed=7, use_flash=1, math=bmb.MATH_TF32, fused=1, **cfg)
         tr.upload(toks, tgts)
         for _ in range(2):                       # the second pass replays the recorded job list / the captured graph
@@ -498,6 +500,7 @@ def test_qkv_bias_gradient_from_the_attention_backward(bmb, cuda, monkeypatch):
     off = Vp * C + maxT * C + 2 * L * C + L * 3 * C * C          # wte, wpe, ln1 gain and bias, qkv weight (src/gpt.cu:32-51)
     qb = [g[off:off + L * 3 * C] for g in grads]
     assert np.all(np.isfinite(grads[0])) and np.abs(qb[0]).max() > 0
-    assert normwise(qb[0], qb[1]) < 1e-5, normwise(qb[0], qb[1])
-    assert normwise(grads[0], grads[1]) < 1e-5
+    for other in (1, 2):
+        assert normwise(qb[0], qb[other]) < 1e-5, (other, normwise(qb[0], qb[other]))
+        assert normwise(grads[0], grads[other]) < 1e-5
 
